@@ -1,0 +1,531 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a.
+//
+//   C[M,N] (+)= alpha * A[M,K] * B[N,K]^T        fp32 accumulation in TMEM
+//
+// * operands are staged by TMA (128-byte swizzle) into a multi-stage smem ring,
+// * one elected thread issues tcgen05.mma (UMMA 128 x BN x 16, cta_group::1),
+// * accumulators live in TMEM and are double buffered (2 x BN columns), so the
+//   epilogue of tile i overlaps the main loop of tile i+1,
+// * four epilogue warps drain TMEM with tcgen05.ld and run one of several
+//   fused epilogues (bf16 / fp32 store, fp32 atomic accumulate for split-K and
+//   gradient accumulation, streaming log-sum-exp for the tied LM head, and the
+//   softmax-gradient tile for its backward).
+//
+// Either operand may be K-major (row = M or N index, K contiguous) or MN-major
+// (row = K index, M or N contiguous); the three layouts that a linear layer
+// needs (y = x W^T, dx = dy W, dW = dy^T x) map to (K,K), (K,MN), (MN,MN).
+//
+// Grouped variants (MoE experts): `tile_group` assigns each 128-row M tile to
+// an expert whose weight block is selected by a row offset in B; with
+// `k_group_offsets` each expert owns a K range (dW of grouped experts).
+//
+// The reference framework runs every linear layer through a library GEMM
+// (src/model/qwen3_5_text.cc:86-89, src/distributed/parallel_ops.cc:32-35).
+#include "ptx.cuh"
+#include "gemm_tcgen05.h"
+
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+#include <cstring>
+#include <cstdio>
+
+namespace cvb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;  // warp0 TMA, warp1 MMA, warps 2-5 epilogue
+
+template <int BN>
+struct TileCfg {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct WorkItem {
+  int mb, nb, kb0, kb1, group;
+  bool valid;
+};
+
+__device__ __forceinline__ WorkItem decode_item(const GemmParams& p, int item) {
+  WorkItem w;
+  w.group = 0;
+  w.valid = true;
+  int t;
+  if (p.k_group_offsets != nullptr) {
+    const int per = p.m_tiles * p.n_tiles;
+    w.group = item / per;
+    t = item - w.group * per;
+    w.kb0 = p.k_group_offsets[w.group] / BK;
+    w.kb1 = p.k_group_offsets[w.group + 1] / BK;
+    if (w.kb1 <= w.kb0) w.valid = false;
+  } else {
+    const int ks = item % p.split_k;
+    t = item / p.split_k;
+    w.kb0 = ks * p.kb_per_split;
+    w.kb1 = min(p.kblocks, w.kb0 + p.kb_per_split);
+  }
+  const int per_group = p.group_m * p.n_tiles;
+  const int g = t / per_group;
+  const int r = t - g * per_group;
+  const int m_first = g * p.group_m;
+  const int gsize = min(p.group_m, p.m_tiles - m_first);
+  w.mb = m_first + r % gsize;
+  w.nb = r / gsize;
+  if (p.tile_group != nullptr) {
+    w.group = p.tile_group[w.mb];
+    if (w.group < 0) w.valid = false;
+  }
+  return w;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const GemmParams p) {
+  using Cfg = TileCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full_bar = bars;                       // [STAGES]
+  uint64_t* empty_bar = bars + Cfg::STAGES;        // [STAGES]
+  uint64_t* tfull_bar = bars + 2 * Cfg::STAGES;    // [2]
+  uint64_t* tempty_bar = bars + 2 * Cfg::STAGES + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_items = p.total_items;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t armed = 0;         // stages with a copy that may still be in flight
+      uint32_t armed_parity = 0;  // parity of that copy's phase
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+        const WorkItem w = decode_item(p, item);
+        if (!w.valid) continue;
+        const int m0 = w.mb * BM;
+        const int n0 = w.nb * BN;
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
+            if (!*abort_flag) atomicCAS(p.status, 0, ERR_WAIT_EMPTY);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
+          uint8_t* sb = sa + Cfg::A_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(sa + j * (64 * BK * 2), &tmA, &full_bar[stage], m0 + 64 * j, k0);
+          }
+          if (!B_MN) {
+            tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0 + w.group * p.b_group_rows);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * (64 * BK * 2), &tmB, &full_bar[stage], n0 + 64 * j,
+                          k0 + w.group * p.b_group_rows);
+          }
+          armed |= (1u << stage);
+          armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+          if (++stage == Cfg::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok || *abort_flag) {
+        // leave no copy in flight: wait (bounded) for every armed stage to land
+        for (int s = 0; s < Cfg::STAGES; ++s) {
+          if (armed & (1u << s)) {
+            int dummy = 0;
+            mbar_wait_bounded(&full_bar[s], (armed_parity >> s) & 1, &dummy);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(BM, BN, /*bf16*/ 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      // K-major: 8-row groups are 1024 B apart; one UMMA_K step = 32 B along the row.
+      // MN-major: 64-element MN groups are (64*BK*2) B apart (LBO), 8-row K groups 1024 B (SBO);
+      //           one UMMA_K step = 16 K rows = 2048 B.
+      constexpr uint32_t A_LBO = A_MN ? 64 * BK * 2 : 16;
+      constexpr uint32_t B_LBO = B_MN ? 64 * BK * 2 : 16;
+      constexpr uint32_t A_KSTEP = A_MN ? 2048 : 32;
+      constexpr uint32_t B_KSTEP = B_MN ? 2048 : 32;
+      int stage = 0;
+      uint32_t phase = 0;
+      int local_tile = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+        const WorkItem w = decode_item(p, item);
+        if (!w.valid) continue;
+        const int acc = local_tile & 1;
+        const uint32_t acc_phase = (local_tile >> 1) & 1;
+        if (!mbar_wait_bounded(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) {
+          if (!*abort_flag) atomicCAS(p.status, 0, ERR_WAIT_TMEM_EMPTY);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
+            if (!*abort_flag) atomicCAS(p.status, 0, ERR_WAIT_FULL);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint32_t sb = sa + Cfg::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t ad = umma_smem_desc(sa + k * A_KSTEP, A_LBO, 1024);
+            const uint64_t bd = umma_smem_desc(sb + k * B_KSTEP, B_LBO, 1024);
+            umma_bf16(tmem_d, ad, bd, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // frees this smem stage when the MMAs retire
+          if (++stage == Cfg::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&tfull_bar[acc]);  // accumulator complete
+        ++local_tile;
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int q = warp & 3;  // TMEM lane quadrant this warp may access
+    int local_tile = 0;
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+      const WorkItem w = decode_item(p, item);
+      if (!w.valid) continue;
+      const int acc = local_tile & 1;
+      const uint32_t acc_phase = (local_tile >> 1) & 1;
+      bool ok = mbar_wait_bounded(&tfull_bar[acc], acc_phase, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) {
+          if (!*abort_flag) atomicCAS(p.status, 0, ERR_WAIT_TMEM_FULL);
+          *abort_flag = 1;
+        }
+        break;
+      }
+      tc_fence_after();
+      const int row = w.mb * BM + q * 32 + lane;
+      const int n0 = w.nb * BN;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      const long long c_off = static_cast<long long>(w.group) * p.c_group_stride;
+
+      // per-row state of the streaming-softmax epilogues
+      float run_max = -INFINITY, run_sum = 0.f;
+      long long tgt = -1;
+      float row_lse = 0.f, row_g = 0.f;
+      if (p.epi == EPI_LSE_PARTIAL && row_ok) tgt = p.targets[row];
+      if (p.epi == EPI_SOFTMAX_GRAD && row_ok) {
+        tgt = p.targets[row];
+        row_lse = p.lse[row];
+        row_g = p.gscale[row];
+      }
+
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32(taddr + c, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c;
+        if (!row_ok || col0 >= p.N) continue;
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+        if (p.epi == EPI_STORE_BF16) {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+          for (int g8 = 0; g8 < 4; ++g8) {
+            if (col0 + g8 * 8 < p.N) {
+              uint4 o;
+              o.x = pack_bf16x2(v[g8 * 8 + 0], v[g8 * 8 + 1]);
+              o.y = pack_bf16x2(v[g8 * 8 + 2], v[g8 * 8 + 3]);
+              o.z = pack_bf16x2(v[g8 * 8 + 4], v[g8 * 8 + 5]);
+              o.w = pack_bf16x2(v[g8 * 8 + 6], v[g8 * 8 + 7]);
+              *reinterpret_cast<uint4*>(dst + g8 * 8) = o;
+            }
+          }
+        } else if (p.epi == EPI_STORE_F32) {
+          float* dst = reinterpret_cast<float*>(p.C) + c_off + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+          for (int g4 = 0; g4 < 8; ++g4) {
+            if (col0 + g4 * 4 < p.N)
+              *reinterpret_cast<float4*>(dst + g4 * 4) =
+                  make_float4(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2], v[g4 * 4 + 3]);
+          }
+        } else if (p.epi == EPI_ATOMIC_F32) {
+          float* dst = reinterpret_cast<float*>(p.C) + c_off + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+          for (int g4 = 0; g4 < 8; ++g4) {
+            if (col0 + g4 * 4 < p.N)
+              red_add_v4_f32(dst + g4 * 4, v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2], v[g4 * 4 + 3]);
+          }
+        } else if (p.epi == EPI_LSE_PARTIAL) {
+          // streaming max / sum-exp over this tile's columns; pick the target logit
+          float cmax = -INFINITY;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (col0 + i < p.N) cmax = fmaxf(cmax, v[i]);
+          const float nmax = fmaxf(run_max, cmax);
+          float s = 0.f;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (col0 + i < p.N) s += __expf(v[i] - nmax);
+          run_sum = run_sum * __expf(run_max - nmax) + s;
+          run_max = nmax;
+          if (tgt >= col0 && tgt < col0 + 32) {
+            float tv = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i == tgt) tv = v[i];
+            p.tgt_logit[row] = tv;
+          }
+        } else {  // EPI_SOFTMAX_GRAD: d = g * (onehot - exp(logit - lse)) as bf16
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float pr = __expf(v[i] - row_lse);
+            v[i] = row_g * (((col0 + i) == tgt ? 1.f : 0.f) - pr);
+          }
+#pragma unroll
+          for (int g8 = 0; g8 < 4; ++g8) {
+            if (col0 + g8 * 8 < p.N) {
+              uint4 o;
+              o.x = pack_bf16x2(v[g8 * 8 + 0], v[g8 * 8 + 1]);
+              o.y = pack_bf16x2(v[g8 * 8 + 2], v[g8 * 8 + 3]);
+              o.z = pack_bf16x2(v[g8 * 8 + 4], v[g8 * 8 + 5]);
+              o.w = pack_bf16x2(v[g8 * 8 + 6], v[g8 * 8 + 7]);
+              *reinterpret_cast<uint4*>(dst + g8 * 8) = o;
+            }
+          }
+        }
+      }
+      if (p.epi == EPI_LSE_PARTIAL && row_ok) {
+        p.part_max[static_cast<long long>(w.nb) * p.M + row] = run_max;
+        p.part_sum[static_cast<long long>(w.nb) * p.M + row] = run_sum;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      ++local_tile;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// 2-D bf16 tensor map with 128-byte swizzle. `inner` is the contiguous extent.
+int make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
+                       uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+static int g_num_sms = 0;
+static int num_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
+                  cudaStream_t stream) {
+  using Cfg = TileCfg<BN>;
+  static bool attr_set = false;
+  auto kern = gemm_kernel<BN, A_MN, B_MN>;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  kern<<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace cvb
+
+using namespace cvb;
+
+extern "C" int cvb_gemm_bf16(const CvbGemmArgs* a, void* stream_v) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0) return 0;
+  if (!a->status) return -2;
+  // TMA needs 16-byte aligned bases and row strides
+  if ((reinterpret_cast<uintptr_t>(a->A) & 15) || (reinterpret_cast<uintptr_t>(a->B) & 15) ||
+      ((a->lda * 2) & 15) || ((a->ldb * 2) & 15))
+    return -3;
+  const int bn = a->block_n == 128 ? 128 : 256;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = a->M;
+  p.N = a->N;
+  p.K = a->K;
+  p.C = a->C;
+  p.ldc = a->ldc;
+  p.alpha = a->alpha;
+  p.epi = a->epi;
+  p.m_tiles = (a->M + BM - 1) / BM;
+  p.n_tiles = (a->N + bn - 1) / bn;
+  p.kblocks = (a->K + BK - 1) / BK;
+  p.tile_group = a->tile_group;
+  p.b_group_rows = a->b_group_rows;
+  p.k_group_offsets = a->k_group_offsets;
+  p.c_group_stride = a->c_group_stride;
+  p.targets = a->targets;
+  p.part_max = a->part_max;
+  p.part_sum = a->part_sum;
+  p.tgt_logit = a->tgt_logit;
+  p.lse = a->lse;
+  p.gscale = a->gscale;
+  p.status = a->status;
+  const int sms = num_sms();
+  int split = a->split_k;
+  const int mn_tiles = p.m_tiles * p.n_tiles;
+  if (a->k_group_offsets) {
+    split = 1;
+    p.total_items = mn_tiles * a->num_groups;
+  } else {
+    if (split <= 0) {  // auto: only atomically accumulating epilogues may split K
+      split = 1;
+      if (a->epi == EPI_ATOMIC_F32 && mn_tiles < sms) {
+        split = (2 * sms + mn_tiles - 1) / mn_tiles;
+        const int max_split = p.kblocks / 4 > 0 ? p.kblocks / 4 : 1;
+        if (split > max_split) split = max_split;
+      }
+    }
+    if (split > 1 && a->epi != EPI_ATOMIC_F32) return -4;
+    if (split > p.kblocks) split = p.kblocks;
+    p.kb_per_split = (p.kblocks + split - 1) / split;
+    split = (p.kblocks + p.kb_per_split - 1) / p.kb_per_split;
+    p.total_items = mn_tiles * split;
+  }
+  p.split_k = split;
+  if (!a->k_group_offsets) p.kb_per_split = (p.kblocks + split - 1) / split;
+  // rasterisation: walk group_m M-tiles per N-tile so that the CTAs running at
+  // the same time share B tiles (weights) and a band of A tiles in L2
+  p.group_m = a->group_m > 0 ? a->group_m : 16;
+  if (p.group_m > p.m_tiles) p.group_m = p.m_tiles;
+
+  CUtensorMap ta, tb;
+  int rc;
+  // A: K-major [rows = a_rows, K] or MN-major [rows = K, M]
+  if (!a->a_mn)
+    rc = make_tensor_map_2d(&ta, a->A, 2, a->K, a->M, a->lda * 2, BK, BM);
+  else
+    rc = make_tensor_map_2d(&ta, a->A, 2, a->M, a->K, a->lda * 2, 64, BK);
+  if (rc) return -10 - (rc > 0 ? 0 : 1);
+  const uint64_t b_rows = a->b_total_rows > 0 ? a->b_total_rows : (a->b_mn ? a->K : a->N);
+  if (!a->b_mn)
+    rc = make_tensor_map_2d(&tb, a->B, 2, a->K, b_rows, a->ldb * 2, BK, bn);
+  else
+    rc = make_tensor_map_2d(&tb, a->B, 2, a->N, b_rows, a->ldb * 2, 64, BK);
+  if (rc) return -12;
+
+  int grid = p.total_items < sms ? p.total_items : sms;
+  if (a->max_ctas > 0 && grid > a->max_ctas) grid = a->max_ctas;
+  if (grid <= 0) return 0;
+
+#define CVB_LAUNCH(BN_)                                                            \
+  do {                                                                             \
+    if (!a->a_mn && !a->b_mn) return launch<BN_, false, false>(ta, tb, p, grid, stream); \
+    if (!a->a_mn && a->b_mn) return launch<BN_, false, true>(ta, tb, p, grid, stream);   \
+    if (a->a_mn && a->b_mn) return launch<BN_, true, true>(ta, tb, p, grid, stream);     \
+    return launch<BN_, true, false>(ta, tb, p, grid, stream);                      \
+  } while (0)
+  if (bn == 256) CVB_LAUNCH(256);
+  CVB_LAUNCH(128);
+#undef CVB_LAUNCH
+}

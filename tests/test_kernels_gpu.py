@@ -1,0 +1,266 @@
+"""sm_100a kernels against plain PyTorch fp32 references of the same ops."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _rel_err(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    from cverl_b200 import _native as nv
+    if torch.cuda.is_available():
+        nv.check_status()
+
+
+# ------------------------------- norms --------------------------------------
+@pytest.mark.parametrize("D", [64, 128, 256, 1024, 2048, 3584])
+def test_add_rmsnorm(D):
+    from cverl_b200.ops import add_rmsnorm
+    from cverl_b200.ops.norm import rmsnorm_ref
+    torch.manual_seed(4)
+    T = 333
+    x = torch.randn(T, D, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(T, D, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    w = (0.1 * torch.randn(D, device=_dev())).to(torch.bfloat16).requires_grad_(True)
+    y, h = add_rmsnorm(x, r, w, 1e-6, 1.0)
+    dy, dh = torch.randn_like(y), torch.randn_like(h)
+    torch.autograd.backward([y, h], [dy, dh])
+    xr = x.detach().float().requires_grad_(True)
+    rr = r.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    hr = (xr + rr)
+    yr = rmsnorm_ref(hr, wr, 1e-6, 1.0)
+    torch.autograd.backward([yr, hr], [dy.float(), dh.float()])
+    assert _rel_err(h, hr) < 5e-3
+    assert _rel_err(y, yr) < 8e-3
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    assert _rel_err(r.grad, rr.grad) < 1e-2
+    assert _rel_err(w.grad, wr.grad) < 2e-2
+
+
+def test_rmsnorm_no_residual_and_main_grad():
+    from cverl_b200.ops import rmsnorm
+    from cverl_b200.ops.norm import rmsnorm_ref
+    torch.manual_seed(5)
+    x = torch.randn(100, 1024, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    w = torch.randn(1024, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    w.main_grad = torch.zeros(1024, device=_dev())
+    y = rmsnorm(x, w, 1e-6, 0.0)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    rmsnorm_ref(xr, wr, 1e-6, 0.0).backward(dy.float())
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    assert _rel_err(w.main_grad, wr.grad) < 1e-3
+
+
+def test_gated_rmsnorm():
+    from cverl_b200.ops import gated_rmsnorm
+    from cverl_b200.ops.norm import rmsnorm_ref
+    torch.manual_seed(6)
+    x = torch.randn(200, 16, 128, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    z = torch.randn(200, 16, 128, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    w = torch.randn(128, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    y = gated_rmsnorm(x, z, w, 1e-6)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, zr, wr = (t.detach().float().requires_grad_(True) for t in (x, z, w))
+    yr = rmsnorm_ref(xr, wr, 1e-6, 0.0, gate=zr)
+    yr.backward(dy.float())
+    assert _rel_err(y, yr) < 8e-3
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    assert _rel_err(z.grad, zr.grad) < 1e-2
+    assert _rel_err(w.grad, wr.grad) < 2e-2
+
+
+@pytest.mark.parametrize("D,rot,use_norm", [(256, 64, True), (128, 128, True), (128, 32, False)])
+def test_headnorm_rope(D, rot, use_norm):
+    from cverl_b200.ops import headnorm_rope, rope_tables
+    from cverl_b200.ops.norm import headnorm_rope_ref
+    torch.manual_seed(7)
+    T, Hh, S = 300, 4, 100
+    big = torch.randn(T, Hh, 2 * D, device=_dev(), dtype=torch.bfloat16)
+    x = big[..., :D].detach().requires_grad_(True)  # strided view, as the q half of a q|gate projection
+    w = (0.1 * torch.randn(D, device=_dev())).to(torch.bfloat16).requires_grad_(True)
+    cos, sin = rope_tables(S, rot, 1e7, _dev())
+    pos = (torch.arange(T, device=_dev()) % S).to(torch.int32)
+    y = headnorm_rope(x, w, cos, sin, pos, rot, 1e-6, 1.0, use_norm)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    yr = headnorm_rope_ref(xr, wr, cos, sin, pos.long(), rot, 1e-6, 1.0, use_norm)
+    yr.backward(dy.float())
+    assert _rel_err(y, yr) < 8e-3
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    if use_norm:
+        assert _rel_err(w.grad, wr.grad) < 2e-2
+
+
+# ---------------------------- activations -----------------------------------
+def test_swiglu():
+    from cverl_b200.ops import swiglu
+    from cverl_b200.ops.activation import swiglu_ref
+    torch.manual_seed(8)
+    gu = torch.randn(500, 2 * 3584, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    y = swiglu(gu)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    gr = gu.detach().float().requires_grad_(True)
+    yr = swiglu_ref(gr)
+    yr.backward(dy.float())
+    assert _rel_err(y, yr) < 6e-3
+    assert _rel_err(gu.grad, gr.grad) < 8e-3
+
+
+def test_siggate_strided_gate():
+    from cverl_b200.ops import siggate
+    torch.manual_seed(9)
+    T, Hh, D = 257, 8, 256
+    qg = torch.randn(T, Hh, 2 * D, device=_dev(), dtype=torch.bfloat16)
+    g = qg[..., D:].detach().requires_grad_(True)
+    a = torch.randn(T, Hh, D, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    y = siggate(a, g)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    ar, gr = a.detach().float().requires_grad_(True), g.detach().float().requires_grad_(True)
+    yr = ar * torch.sigmoid(gr)
+    yr.backward(dy.float())
+    assert _rel_err(y, yr) < 6e-3
+    assert _rel_err(a.grad, ar.grad) < 8e-3
+    assert _rel_err(g.grad, gr.grad) < 8e-3
+
+
+@pytest.mark.parametrize("S", [5, 64, 200])
+def test_conv1d_silu(S):
+    from cverl_b200.ops import conv1d_silu
+    from cverl_b200.ops.activation import conv1d_silu_ref
+    torch.manual_seed(10)
+    B, Cc = 3, 256
+    x = torch.randn(B, S, Cc, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    w = (0.5 * torch.randn(Cc, 4, device=_dev())).to(torch.bfloat16).requires_grad_(True)
+    y = conv1d_silu(x, w)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yr = conv1d_silu_ref(xr, wr)
+    yr.backward(dy.float())
+    assert _rel_err(y, yr) < 8e-3
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    assert _rel_err(w.grad, wr.grad) < 2e-2
+
+
+def test_embedding_fwd_bwd():
+    from cverl_b200.ops import embedding
+    torch.manual_seed(11)
+    V, H = 1000, 256
+    table = torch.randn(V, H, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    table.main_grad = torch.zeros(V, H, device=_dev())
+    ids = torch.randint(0, V, (4, 77), device=_dev())
+    out = embedding(ids, table)
+    assert torch.equal(out, table.detach()[ids])
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    ref = torch.zeros(V, H, device=_dev()).index_add_(0, ids.reshape(-1), dout.reshape(-1, H).float())
+    assert _rel_err(table.main_grad, ref) < 1e-5
+    # vocab-parallel shard: ids outside the shard give zero rows
+    half = embedding(ids, table.detach()[500:], vocab_lo=500)
+    assert torch.equal(half[ids < 500], torch.zeros_like(half[ids < 500]))
+
+
+# ------------------------------- RL math ------------------------------------
+def _rl_data(rows=64, cols=512, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    lp = -2 + 0.5 * torch.randn(rows, cols, generator=g)
+    old = lp + 0.05 * torch.randn(rows, cols, generator=g)
+    ref = lp + 0.1 * torch.randn(rows, cols, generator=g)
+    adv = torch.randn(rows, cols, generator=g)
+    lens = torch.randint(32, cols + 1, (rows,), generator=g)
+    mask = (torch.arange(cols)[None, :] < lens[:, None]).float()
+    return [t.to(_dev()) for t in (lp, old, ref, adv, mask)]
+
+
+def test_rl_masked_and_kl_kernels():
+    from cverl_b200.ops import rl
+    lp, old, ref, adv, mask = _rl_data()
+    assert abs(rl.fused_masked_mean(lp, mask).item() - rl.masked_mean(lp, mask).item()) < 1e-5
+    torch.testing.assert_close(rl.fused_masked_whiten(lp, mask), rl.masked_whiten(lp, mask), rtol=1e-4, atol=1e-5)
+    for kind in ("k1", "abs", "k2", "k3"):
+        torch.testing.assert_close(rl.fused_kl_penalty(lp, ref, kind), rl.kl_penalty(lp, ref, kind), rtol=1e-5,
+                                   atol=1e-6)
+
+
+def test_rl_gae_grpo_kernels():
+    from cverl_b200.ops import rl
+    lp, old, ref, adv, mask = _rl_data(rows=64, cols=128, seed=1)
+    rew = torch.zeros_like(lp)
+    rew[:, 5] = torch.bernoulli(torch.full((64,), 0.5, device=_dev()))
+    val = torch.randn_like(lp)
+    a, r = rl.fused_gae(rew, val, mask, 1.0, 0.95)
+    at, rt = rl.gae_advantage_return(rew, val, mask, 1.0, 0.95)
+    torch.testing.assert_close(a, at, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(r, rt, rtol=1e-5, atol=1e-5)
+    gid = torch.arange(64, device=_dev()) // 8
+    ga, _ = rl.fused_grpo_advantage(rew, mask, gid)
+    gt, _ = rl.grpo_outcome_advantage(rew, mask, gid)
+    torch.testing.assert_close(ga, gt, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("agg", [0, 1, 2])
+def test_rl_ppo_loss_kernel(agg):
+    from cverl_b200.ops import rl
+    lp, old, ref, adv, mask = _rl_data(seed=2 + agg)
+    metrics, grad = rl.fused_ppo_loss(old, lp, adv, mask, ref, agg=agg, kl_coef=0.01, kl_penalty_kind="k3")
+    x = lp.clone().requires_grad_(True)
+    res = rl.ppo_clipped_loss(old, x, adv, mask, agg=agg)
+    kl = rl.masked_mean(rl.kl_penalty(x, ref, "k3"), mask)
+    (res.pg_loss + 0.01 * kl).backward()
+    want = torch.stack([res.pg_loss, res.pg_clipfrac, res.ppo_kl, res.pg_clipfrac_lower, kl]).detach()
+    torch.testing.assert_close(metrics[:5], want, rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(grad, x.grad, rtol=1e-4, atol=1e-8)
+
+
+# ------------------------------- optimizer ----------------------------------
+@pytest.mark.parametrize("master", [True, False])
+def test_flat_adamw_kernel(master):
+    from cverl_b200.ops import optim
+    torch.manual_seed(13)
+    n = 100003
+    p0 = torch.randn(n, device=_dev())
+    g = torch.randn(n, device=_dev())
+    model = p0.to(torch.bfloat16)
+    mast = p0.clone() if master else None
+    m, v = torch.zeros(n, device=_dev()), torch.zeros(n, device=_dev())
+    ref_p = (p0.clone() if master else model.float())
+    rm, rv = torch.zeros(n), torch.zeros(n)
+    rp = ref_p.cpu()
+    sq = optim.sumsq(g)
+    assert abs(sq.item() - g.pow(2).sum().item()) / g.pow(2).sum().item() < 1e-5
+    clip = optim.clip_scale(sq, 1.0)
+    assert abs(clip[0].item() - 1.0 / (sq.sqrt().item() + 1e-6)) < 1e-6
+    for step in (1, 2, 3):
+        gg = g.clone()
+        optim.flat_adamw_step(gg, mast, model, m, v, clip=clip, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8,
+                              weight_decay=0.01, step=step, zero_grad=True)
+        assert gg.abs().max().item() == 0.0
+        gc = (g * clip[0]).cpu()
+        rm.mul_(0.9).add_(gc, alpha=0.1)
+        rv.mul_(0.95).addcmul_(gc, gc, value=0.05)
+        rp = rp * (1 - 1e-2 * 0.01)
+        rp = rp - (1e-2 / (1 - 0.9 ** step)) * rm / ((rv / (1 - 0.95 ** step)).sqrt() + 1e-8)
+        if not master:
+            rp = rp.to(torch.bfloat16).float()
+    if master:
+        torch.testing.assert_close(mast.cpu(), rp, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(model.float().cpu(), rp.to(torch.bfloat16).float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(m.cpu(), rm, rtol=1e-5, atol=1e-7)
