@@ -406,7 +406,15 @@ int make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint6
   CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr,
+            "[cverl_b200] cuTensorMapEncodeTiled failed (%d): base=%p elem=%d dims={%llu,%llu} stride=%llu box={%u,%u}\n",
+            static_cast<int>(r), base, elem_bytes, static_cast<unsigned long long>(inner),
+            static_cast<unsigned long long>(outer), static_cast<unsigned long long>(row_stride_bytes), box_inner,
+            box_outer);
+    return static_cast<int>(r);
+  }
+  return 0;
 }
 
 static int g_num_sms = 0;

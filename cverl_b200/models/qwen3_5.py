@@ -1,0 +1,351 @@
+"""Qwen3.5 hybrid (Gated-DeltaNet + full attention) and Qwen3-MoE text model.
+
+Activations are packed ``[B*S, H]`` (B equal-length sequences); every block is
+a chain of the fused ops in ``cverl_b200.ops``:
+
+    (delta, resid) -> add+RMSNorm -> mixer -> add+RMSNorm -> MLP/MoE -> ...
+
+* full attention: one GEMM for q|gate|k|v, per-head RMSNorm + partial RoPE in
+  one kernel, causal GQA attention, sigmoid output gate, o_proj
+  (reference: src/model/qwen3_5_text.cc:1036-1082);
+* linear attention: one GEMM for qkv|z|b|a, causal conv1d+SiLU, l2norm, gated
+  delta rule scan, gated RMSNorm, out_proj (:1228-1272);
+* SwiGLU MLP from one gate|up GEMM (:791-793), or the Qwen3-MoE router + experts
+  (:761-790, :796-993);
+* tied (or untied) LM head evaluated as fused log-probabilities (:1590-1630).
+
+Tensor parallelism is Megatron column/row sharding with the mathematically
+correct backward (the activation gradient entering a column-parallel GEMM is
+all-reduced); the reference skips that all-reduce and averages replicated
+parameters instead (tools/model/qwen3_5_pp_tp_ppo_trainer.cc:545-558), a
+deviation made on purpose.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from .. import ops
+from ..ops import attention as attn_ops
+from ..ops import gdn as gdn_ops
+from ..parallel.autograd_collectives import copy_to_tp, reduce_from_tp
+from ..parallel.context import SINGLE, ParallelContext
+from .config import Qwen35TextConfig
+from .params import FlatParams, ParamSpec, model_param_specs, shard_tensor, unshard_tensor
+
+
+def _packed_moe_names(layer: int) -> Tuple[str, str]:
+    return (f"__packed_moe.layers.{layer}.gate_up.weight", f"__packed_moe.layers.{layer}.down.weight")
+
+
+class Qwen35Model(torch.nn.Module):
+    """One pipeline stage (by default the whole model) of the text model."""
+
+    def __init__(self, cfg: Qwen35TextConfig, *, dtype=torch.bfloat16, device="cpu",
+                 ctx: ParallelContext = SINGLE, layer_begin: int = 0, layer_end: Optional[int] = None,
+                 first_stage: bool = True, last_stage: bool = True, pad_multiple: int = 1,
+                 with_main_grad: bool = True):
+        super().__init__()
+        self.cfg = cfg
+        self.ctx = ctx
+        self.dtype = dtype
+        self.layer_begin = layer_begin
+        self.layer_end = cfg.num_hidden_layers if layer_end is None else layer_end
+        self.first_stage, self.last_stage = first_stage, last_stage
+        tp = ctx.tp_size
+        if tp > 1:
+            if tp > cfg.num_key_value_heads:
+                raise ValueError("tensor-parallel size must not exceed num_key_value_heads")
+            if cfg.num_attention_heads % tp or cfg.num_key_value_heads % tp:
+                raise ValueError("attention heads must divide by the tensor-parallel size")
+        if cfg.is_qwen3_moe and cfg.num_experts % ctx.ep_size:
+            raise ValueError("num_experts must divide by the expert-parallel size")
+        self.specs: List[ParamSpec] = model_param_specs(cfg, self.layer_begin, self.layer_end, first_stage,
+                                                        last_stage)
+        self.spec_by_name: Dict[str, ParamSpec] = {s.name: s for s in self.specs}
+        entries = self._flat_entries()
+        self.flat = FlatParams(entries, dtype=dtype, device=device, pad_multiple=pad_multiple,
+                               with_main_grad=with_main_grad)
+        for name, p in self.flat.params.items():
+            self.register_parameter(name.replace(".", "/"), p)
+        self._build_fused_views()
+        self._rope_cache: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
+
+    # ------------------------------------------------------------------ layout
+    def _flat_entries(self) -> List[Tuple[str, Tuple[int, ...]]]:
+        cfg, tp, ep = self.cfg, self.ctx.tp_size, self.ctx.ep_size
+        entries: List[Tuple[str, Tuple[int, ...]]] = []
+        packed_done = set()
+        for s in self.specs:
+            if s.expert >= 0:
+                layer = int(s.name[len(cfg.layer_root):].split(".")[0])
+                if layer in packed_done:
+                    continue
+                packed_done.add(layer)
+                e_local = cfg.num_experts // ep
+                i_local = cfg.moe_intermediate_size // tp
+                gu, dn = _packed_moe_names(layer)
+                entries.append((gu, (e_local, 2 * i_local, cfg.hidden_size)))
+                entries.append((dn, (e_local, cfg.hidden_size, i_local)))
+            else:
+                entries.append((s.name, s.local_shape(tp)))
+        return entries
+
+    def _build_fused_views(self) -> None:
+        cfg, tp = self.cfg, self.ctx.tp_size
+        self.fused: Dict[str, torch.nn.Parameter] = {}
+        H = cfg.hidden_size
+        for i in range(self.layer_begin, self.layer_end):
+            p = f"{cfg.layer_root}{i}."
+            if cfg.layer_types[i] == "full_attention":
+                sa = p + "self_attn."
+                names = [sa + "q_proj.weight", sa + "k_proj.weight", sa + "v_proj.weight"]
+                rows = sum(self.flat.params[n].shape[0] for n in names)
+                self.fused[f"{i}.qkv"] = self.flat.fused_view(names, (rows, H))
+            else:
+                la = p + "linear_attn."
+                names = [la + "in_proj_qkv.weight", la + "in_proj_z.weight", la + "in_proj_b.weight",
+                         la + "in_proj_a.weight"]
+                rows = sum(self.flat.params[n].shape[0] for n in names)
+                self.fused[f"{i}.lin_in"] = self.flat.fused_view(names, (rows, H))
+            if not cfg.is_qwen3_moe:
+                mp = p + "mlp."
+                names = [mp + "gate_proj.weight", mp + "up_proj.weight"]
+                rows = sum(self.flat.params[n].shape[0] for n in names)
+                self.fused[f"{i}.gate_up"] = self.flat.fused_view(names, (rows, H))
+
+    def param(self, name: str) -> torch.nn.Parameter:
+        return self.flat.params[name]
+
+    # ------------------------------------------------------------------ weights IO
+    @torch.no_grad()
+    def init_weights(self, seed: int = 1234, std: float = 0.02) -> None:
+        """Random initialisation (normal, std 0.02; norm weights 0 for ``1+w`` norms, 1 otherwise).
+
+        The same full tensor is generated on every tensor-parallel rank and then
+        sharded, so a TP run starts from the weights a dense run would.
+        """
+        cfg = self.cfg
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        for s in self.specs:
+            if s.name.endswith("A_log"):
+                full = torch.log(torch.empty(s.full_shape).uniform_(1.0, 8.0, generator=gen))
+            elif s.name.endswith("dt_bias"):
+                full = torch.empty(s.full_shape).uniform_(-1.0, 1.0, generator=gen)
+            elif s.name.endswith("norm.weight") or s.name.endswith("layernorm.weight"):
+                gated = s.name.endswith("linear_attn.norm.weight")
+                base = 1.0 if (cfg.is_qwen3_moe or gated) else 0.0
+                full = torch.full(s.full_shape, base)
+            elif s.name.endswith("conv1d.weight"):
+                full = torch.empty(s.full_shape).uniform_(-0.5, 0.5, generator=gen)
+            else:
+                full = torch.empty(s.full_shape).normal_(0.0, std, generator=gen)
+            self.load_full_tensor(s.name, full)
+
+    @torch.no_grad()
+    def load_full_tensor(self, name: str, full: torch.Tensor) -> None:
+        """Shard a full Hugging Face tensor for this rank and copy it into the flat buffer."""
+        spec = self.spec_by_name[name]
+        cfg, ctx = self.cfg, self.ctx
+        local = shard_tensor(spec, full, ctx.tp_rank, ctx.tp_size)
+        if spec.expert >= 0:
+            e_local = cfg.num_experts // ctx.ep_size
+            lo = ctx.ep_rank * e_local
+            if not (lo <= spec.expert < lo + e_local):
+                return
+            layer = int(name[len(cfg.layer_root):].split(".")[0])
+            gu, dn = _packed_moe_names(layer)
+            e = spec.expert - lo
+            i_local = cfg.moe_intermediate_size // ctx.tp_size
+            if name.endswith("gate_proj.weight"):
+                self.flat.params[gu].data[e, :i_local].copy_(local)
+            elif name.endswith("up_proj.weight"):
+                self.flat.params[gu].data[e, i_local:].copy_(local)
+            else:
+                self.flat.params[dn].data[e].copy_(local)
+            return
+        self.flat.params[name].data.copy_(local.reshape(self.flat.params[name].shape))
+
+    @torch.no_grad()
+    def local_hf_tensors(self):
+        """``(name, local shard)`` in Hugging Face naming (per-expert tensors unpacked)."""
+        cfg, ctx = self.cfg, self.ctx
+        for s in self.specs:
+            if s.expert >= 0:
+                e_local = cfg.num_experts // ctx.ep_size
+                lo = ctx.ep_rank * e_local
+                if not (lo <= s.expert < lo + e_local):
+                    continue
+                layer = int(s.name[len(cfg.layer_root):].split(".")[0])
+                gu, dn = _packed_moe_names(layer)
+                e = s.expert - lo
+                i_local = cfg.moe_intermediate_size // ctx.tp_size
+                if s.name.endswith("gate_proj.weight"):
+                    yield s.name, self.flat.params[gu].data[e, :i_local]
+                elif s.name.endswith("up_proj.weight"):
+                    yield s.name, self.flat.params[gu].data[e, i_local:]
+                else:
+                    yield s.name, self.flat.params[dn].data[e]
+            else:
+                yield s.name, self.flat.params[s.name].data
+
+    def trainable_parameters(self) -> List[torch.nn.Parameter]:
+        return list(self.flat.params.values())
+
+    # ------------------------------------------------------------------ helpers
+    def _rope(self, seq_len: int, device, offset: int = 0):
+        key = (seq_len, offset, str(device))
+        hit = self._rope_cache.get(key)
+        if hit is None:
+            hit = ops.rope_tables(seq_len, self.cfg.rotary_dim, self.cfg.rope_theta, device, offset)
+            self._rope_cache[key] = hit
+        return hit
+
+    def _positions(self, batch: int, seq: int, device) -> torch.Tensor:
+        return torch.arange(seq, device=device, dtype=torch.int32).repeat(batch)
+
+    # ------------------------------------------------------------------ mixers
+    def full_attention(self, x: torch.Tensor, i: int, batch: int, seq: int) -> torch.Tensor:
+        cfg, ctx = self.cfg, self.ctx
+        p = f"{cfg.layer_root}{i}.self_attn."
+        d = cfg.head_dim
+        h = cfg.num_attention_heads // ctx.tp_size
+        kvh = cfg.num_key_value_heads // ctx.tp_size
+        T = x.shape[0]
+        x = copy_to_tp(x, ctx.tp_group)
+        qkv = ops.linear(x, self.fused[f"{i}.qkv"])
+        qmul = 1 if cfg.is_qwen3_moe else 2
+        q_all, k, v = qkv.split([h * d * qmul, kvh * d, kvh * d], dim=-1)
+        if cfg.is_qwen3_moe:
+            q, gate = q_all.view(T, h, d), None
+        else:
+            q, gate = q_all.view(T, h, 2 * d).split([d, d], dim=-1)
+        k = k.view(T, kvh, d)
+        v = v.view(T, kvh, d)
+        cos, sin = self._rope(seq, x.device)
+        pos = self._positions(batch, seq, x.device)
+        off = cfg.norm_weight_offset
+        q = ops.headnorm_rope(q, self.param(p + "q_norm.weight"), cos, sin, pos, cfg.rotary_dim, cfg.rms_norm_eps, off)
+        k = ops.headnorm_rope(k, self.param(p + "k_norm.weight"), cos, sin, pos, cfg.rotary_dim, cfg.rms_norm_eps, off)
+        o = attn_ops.causal_attention(q, k, v, batch, seq, 1.0 / math.sqrt(d))
+        if gate is not None:
+            o = ops.siggate(o, gate)
+        out = ops.linear(o.reshape(T, h * d), self.param(p + "o_proj.weight"))
+        return reduce_from_tp(out, ctx.tp_group)
+
+    def linear_attention(self, x: torch.Tensor, i: int, batch: int, seq: int,
+                         initial_state: Optional[torch.Tensor] = None, return_state: bool = False):
+        cfg, ctx = self.cfg, self.ctx
+        p = f"{cfg.layer_root}{i}.linear_attn."
+        tp = ctx.tp_size
+        kh, vh = cfg.linear_num_key_heads // tp, cfg.linear_num_value_heads // tp
+        kd, vd = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        key_dim, value_dim = kh * kd, vh * vd
+        conv_dim = 2 * key_dim + value_dim
+        T = x.shape[0]
+        x = copy_to_tp(x, ctx.tp_group)
+        proj = ops.linear(x, self.fused[f"{i}.lin_in"])
+        mixed, z, b, a = proj.split([conv_dim, value_dim, vh, vh], dim=-1)
+        conv_w = self.param(p + "conv1d.weight").view(conv_dim, cfg.linear_conv_kernel_dim)
+        mixed = ops.conv1d_silu(mixed.view(batch, seq, conv_dim), conv_w)
+        q, k, v = mixed.split([key_dim, key_dim, value_dim], dim=-1)
+        q = q.reshape(batch, seq, kh, kd)
+        k = k.reshape(batch, seq, kh, kd)
+        v = v.reshape(batch, seq, vh, vd)
+        beta = torch.sigmoid(b.float()).view(batch, seq, vh)
+        g = (-torch.exp(self.param(p + "A_log").float()) *
+             F.softplus(a.float() + self.param(p + "dt_bias").float())).view(batch, seq, vh)
+        if vh // kh > 1:
+            q = q.repeat_interleave(vh // kh, dim=2)
+            k = k.repeat_interleave(vh // kh, dim=2)
+        qf = gdn_ops.l2norm(q.float()).transpose(1, 2) * (1.0 / math.sqrt(kd))
+        kf = gdn_ops.l2norm(k.float()).transpose(1, 2)
+        core, state = gdn_ops.gated_delta_rule(qf, kf, v.transpose(1, 2), beta.transpose(1, 2), g.transpose(1, 2),
+                                               initial_state)
+        core = core.transpose(1, 2).to(x.dtype).reshape(T, vh, vd)
+        y = ops.gated_rmsnorm(core, z.reshape(T, vh, vd), self.param(p + "norm.weight"), cfg.rms_norm_eps)
+        out = ops.linear(y.reshape(T, value_dim), self.param(p + "out_proj.weight"))
+        out = reduce_from_tp(out, ctx.tp_group)
+        return (out, state) if return_state else out
+
+    def mlp(self, x: torch.Tensor, i: int) -> torch.Tensor:
+        cfg, ctx = self.cfg, self.ctx
+        if cfg.is_qwen3_moe:
+            from .moe import moe_mlp
+            return moe_mlp(self, x, i)
+        p = f"{cfg.layer_root}{i}.mlp."
+        x = copy_to_tp(x, ctx.tp_group)
+        gu = ops.linear(x, self.fused[f"{i}.gate_up"])
+        act = ops.swiglu(gu)
+        out = ops.linear(act, self.param(p + "down_proj.weight"))
+        return reduce_from_tp(out, ctx.tp_group)
+
+    # ------------------------------------------------------------------ forward
+    def embed(self, input_ids: torch.Tensor) -> torch.Tensor:
+        """[B, S] ids -> packed [B*S, H] embeddings (vocab-parallel over TP)."""
+        cfg, ctx = self.cfg, self.ctx
+        table = self.param(cfg.embed_name)
+        lo = ctx.tp_rank * table.shape[0] if ctx.tp_size > 1 else 0
+        e = ops.embedding(input_ids.reshape(-1), table, lo)
+        return reduce_from_tp(e, ctx.tp_group)
+
+    def forward_layers(self, x: torch.Tensor, batch: int, seq: int, final_norm: bool = True) -> torch.Tensor:
+        """Run this stage's layers on the packed residual stream ``x`` ``[B*S, H]``."""
+        cfg = self.cfg
+        eps, off = cfg.rms_norm_eps, cfg.norm_weight_offset
+        delta, resid = x, None
+        for i in range(self.layer_begin, self.layer_end):
+            p = f"{cfg.layer_root}{i}."
+            n1, resid = ops.add_rmsnorm(delta, resid, self.param(p + "input_layernorm.weight"), eps, off)
+            if cfg.layer_types[i] == "full_attention":
+                a = self.full_attention(n1, i, batch, seq)
+            else:
+                a = self.linear_attention(n1, i, batch, seq)
+            n2, resid = ops.add_rmsnorm(a, resid, self.param(p + "post_attention_layernorm.weight"), eps, off)
+            delta = self.mlp(n2, i)
+        if self.last_stage and final_norm:
+            out, _ = ops.add_rmsnorm(delta, resid, self.param(cfg.final_norm_name), eps, off)
+            return out
+        return delta if resid is None else delta + resid
+
+    def forward_hidden(self, input_ids: torch.Tensor) -> torch.Tensor:
+        """[B, S] ids -> final-normed hidden states ``[B, S, H]`` (single-stage model)."""
+        batch, seq = input_ids.shape
+        x = self.embed(input_ids)
+        return self.forward_layers(x, batch, seq).view(batch, seq, -1)
+
+    def lm_head_weight(self) -> torch.nn.Parameter:
+        return self.param(self.cfg.lm_head_name)
+
+    def token_logprobs(self, hidden: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """Log-probability of ``targets`` under the LM head at each row of ``hidden`` (fp32)."""
+        ctx = self.ctx
+        w = self.lm_head_weight()
+        lo = ctx.tp_rank * w.shape[0] if ctx.tp_size > 1 else 0
+        h2 = hidden.reshape(-1, hidden.shape[-1])
+        h2 = copy_to_tp(h2, ctx.tp_group)
+        lp = ops.lmhead_logprob(h2, w, targets.reshape(-1), lo, ctx.tp_group if ctx.tp_size > 1 else None)
+        return lp.view(targets.shape)
+
+    def response_logprobs(self, input_ids: torch.Tensor, prompt_len: int) -> torch.Tensor:
+        """Log-probs of the response tokens ``input_ids[:, P:]`` given their prefixes: [B, R] fp32."""
+        hidden = self.forward_hidden(input_ids)
+        R = input_ids.shape[1] - prompt_len
+        h = hidden[:, prompt_len - 1: prompt_len - 1 + R]
+        return self.token_logprobs(h, input_ids[:, prompt_len:])
+
+    def forward_logits(self, input_ids: torch.Tensor) -> torch.Tensor:
+        """Full fp32 logits ``[B, S, V]`` (debug / rollout sampling; the trainer never builds them)."""
+        hidden = self.forward_hidden(input_ids)
+        w = self.lm_head_weight()
+        logits = hidden.float() @ w.float().t()
+        if self.ctx.tp_size > 1:
+            from ..parallel.autograd_collectives import all_gather_rows
+            logits = all_gather_rows(logits.permute(2, 0, 1).contiguous(), self.ctx.tp_group).permute(1, 2, 0)
+        return logits
+
+    def forward(self, input_ids: torch.Tensor) -> torch.Tensor:
+        return self.forward_logits(input_ids)

@@ -1,0 +1,34 @@
+"""Process-group handles of one rank for every parallel axis the model code sees."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Optional
+
+
+@dataclass
+class ParallelContext:
+    """Groups are ``torch.distributed`` process groups (``None`` = axis of size 1)."""
+
+    tp_group: Optional[Any] = None
+    tp_rank: int = 0
+    tp_size: int = 1
+    ep_group: Optional[Any] = None
+    ep_rank: int = 0
+    ep_size: int = 1
+    cp_group: Optional[Any] = None
+    cp_rank: int = 0
+    cp_size: int = 1
+    dp_group: Optional[Any] = None
+    dp_rank: int = 0
+    dp_size: int = 1
+    pp_rank: int = 0
+    pp_size: int = 1
+    # fused NVLink kernels (symmetric-memory paths) instead of NCCL for TP / ZeRO
+    fused_comm: bool = False
+
+    @property
+    def single(self) -> bool:
+        return self.tp_size == 1 and self.ep_size == 1 and self.cp_size == 1
+
+
+SINGLE = ParallelContext()
