@@ -74,6 +74,8 @@ _CUDA_PROTOS = {
     "cvb_flat_adamw": "ppppppp l fffff f l i p",
     "cvb_lse_combine": "ppppppp l i p",
     "cvb_lse_merge_ranks": "ppppp l i p",
+    "cvb_gdn_scan_fwd": "pppppppp l i p p",
+    "cvb_gdn_scan_bwd": "pppppppppp l i p p",
 }
 
 

@@ -8,6 +8,7 @@
 // Reference behaviour: src/model/qwen3_5_text.cc:791-793 (SwiGLU), :1077-1079
 // (output gate), :1241-1243 (conv1d + SiLU), :692 (embedding).
 #include "ptx.cuh"
+#include <initializer_list>
 
 namespace cvb {
 
@@ -338,19 +339,25 @@ cast_f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict
 }  // namespace cvb
 
 using namespace cvb;
+// every vector access in this file is 16 bytes wide: refuse misaligned tensors on the host
+static inline bool cvb_misaligned(std::initializer_list<const void*> ptrs) {
+  for (const void* q : ptrs)
+    if (q != nullptr && (reinterpret_cast<uintptr_t>(q) & 15)) return true;
+  return false;
+}
 #define BF(p) static_cast<const __nv_bfloat16*>(p)
 #define BFM(p) static_cast<__nv_bfloat16*>(p)
 #define ST(s) static_cast<cudaStream_t>(s)
 
 extern "C" int cvb_swiglu_fwd(const void* gu, void* y, long long rows, int I, long long gu_stride, void* stream) {
-  if (I % 8 || gu_stride % 8) return -1;
+  if (I % 8 || gu_stride % 8 || cvb_misaligned({gu, y})) return -1;
   if (rows <= 0) return 0;
   swiglu_fwd_kernel<<<ew_grid(rows * (I / 8)), EW_THREADS, 0, ST(stream)>>>(BF(gu), BFM(y), rows, I, gu_stride);
   return static_cast<int>(cudaGetLastError());
 }
 extern "C" int cvb_swiglu_bwd(const void* dy, const void* gu, void* dgu, long long rows, int I,
                               long long gu_stride, void* stream) {
-  if (I % 8 || gu_stride % 8) return -1;
+  if (I % 8 || gu_stride % 8 || cvb_misaligned({dy, gu, dgu})) return -1;
   if (rows <= 0) return 0;
   swiglu_bwd_kernel<<<ew_grid(rows * (I / 8)), EW_THREADS, 0, ST(stream)>>>(BF(dy), BF(gu), BFM(dgu), rows, I,
                                                                           gu_stride);
@@ -358,7 +365,8 @@ extern "C" int cvb_swiglu_bwd(const void* dy, const void* gu, void* dgu, long lo
 }
 extern "C" int cvb_siggate_fwd(const void* a, const void* g, void* y, long long rows, int C, long long a_stride,
                                long long g_stride, int g_block, int g_block_stride, void* stream) {
-  if (C % 8 || a_stride % 8 || g_stride % 8 || g_block % 8 || g_block_stride % 8) return -1;
+  if (C % 8 || a_stride % 8 || g_stride % 8 || g_block % 8 || g_block_stride % 8 || cvb_misaligned({a, g, y}))
+    return -1;
   if (rows <= 0) return 0;
   siggate_fwd_kernel<<<ew_grid(rows * (C / 8)), EW_THREADS, 0, ST(stream)>>>(BF(a), BF(g), BFM(y), rows, C,
                                                                            a_stride, g_stride, g_block,
@@ -369,7 +377,7 @@ extern "C" int cvb_siggate_bwd(const void* dy, const void* a, const void* g, voi
                                int C, long long a_stride, long long g_stride, int g_block, int g_block_stride,
                                long long da_stride, long long dg_stride, int dg_block_stride, void* stream) {
   if (C % 8 || a_stride % 8 || g_stride % 8 || g_block % 8 || g_block_stride % 8 || da_stride % 8 ||
-      dg_stride % 8 || dg_block_stride % 8)
+      dg_stride % 8 || dg_block_stride % 8 || cvb_misaligned({dy, a, g, da, dg}))
     return -1;
   if (rows <= 0) return 0;
   siggate_bwd_kernel<<<ew_grid(rows * (C / 8)), EW_THREADS, 0, ST(stream)>>>(
@@ -379,7 +387,7 @@ extern "C" int cvb_siggate_bwd(const void* dy, const void* a, const void* g, voi
 }
 extern "C" int cvb_conv1d_silu_fwd(const void* x, const void* w, void* y, long long B, int S, int C, int KW,
                                    long long x_stride, void* stream) {
-  if (C % 8 || x_stride % 8) return -1;
+  if (C % 8 || x_stride % 8 || cvb_misaligned({x, y})) return -1;
   if (B <= 0) return 0;
   const int grid = ew_grid(B * S * (C / 8));
   if (KW == 4)
@@ -394,7 +402,7 @@ extern "C" int cvb_conv1d_silu_fwd(const void* x, const void* w, void* y, long l
 }
 extern "C" int cvb_conv1d_silu_bwd(const void* dy, const void* x, const void* w, void* dx, float* dw, long long B,
                                    int S, int C, int KW, long long x_stride, long long dx_stride, void* stream) {
-  if (C % 8 || x_stride % 8 || dx_stride % 8) return -1;
+  if (C % 8 || x_stride % 8 || dx_stride % 8 || cvb_misaligned({dy, x, dx})) return -1;
   if (B <= 0) return 0;
   // enough segments to fill the machine, long enough to amortise the atomics
   int seg_len = 64;
@@ -415,7 +423,7 @@ extern "C" int cvb_conv1d_silu_bwd(const void* dy, const void* x, const void* w,
 }
 extern "C" int cvb_embedding_fwd(const long long* ids, const void* table, void* out, long long tokens, int H,
                                  long long vocab_lo, long long vocab_hi, void* stream) {
-  if (H % 8) return -1;
+  if (H % 8 || cvb_misaligned({table, out})) return -1;
   if (tokens <= 0) return 0;
   embedding_fwd_kernel<<<ew_grid(tokens * (H / 8)), EW_THREADS, 0, ST(stream)>>>(ids, BF(table), BFM(out), tokens,
                                                                                H, vocab_lo, vocab_hi);
@@ -423,7 +431,7 @@ extern "C" int cvb_embedding_fwd(const long long* ids, const void* table, void* 
 }
 extern "C" int cvb_embedding_bwd(const long long* ids, const void* dout, float* dtable, long long tokens, int H,
                                  long long vocab_lo, long long vocab_hi, void* stream) {
-  if (H % 8) return -1;
+  if (H % 8 || cvb_misaligned({dout, dtable})) return -1;
   if (tokens <= 0) return 0;
   embedding_bwd_kernel<<<ew_grid(tokens * (H / 8)), EW_THREADS, 0, ST(stream)>>>(ids, BF(dout), dtable, tokens, H,
                                                                                vocab_lo, vocab_hi);

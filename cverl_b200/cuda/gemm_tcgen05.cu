@@ -451,6 +451,11 @@ extern "C" int cvb_gemm_bf16(const CvbGemmArgs* a, void* stream_v) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   if (a->M <= 0 || a->N <= 0 || a->K <= 0) return 0;
   if (!a->status) return -2;
+  // vector stores / reductions in the epilogue need 16-byte aligned output rows
+  if (a->C != nullptr) {
+    const int64_t c_elem = (a->epi == EPI_STORE_BF16 || a->epi == EPI_SOFTMAX_GRAD) ? 2 : 4;
+    if ((reinterpret_cast<uintptr_t>(a->C) & 15) || ((a->ldc * c_elem) & 15)) return -5;
+  }
   // TMA needs 16-byte aligned bases and row strides
   if ((reinterpret_cast<uintptr_t>(a->A) & 15) || (reinterpret_cast<uintptr_t>(a->B) & 15) ||
       ((a->lda * 2) & 15) || ((a->ldb * 2) & 15))

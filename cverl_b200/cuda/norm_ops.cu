@@ -13,6 +13,7 @@
 // Reference behaviour: src/model/qwen3_5_text.cc:698-711 (RMSNorm, gated
 // RMSNorm, fp32 compute), :724-757 and :1057-1066 (partial RoPE).
 #include "ptx.cuh"
+#include <initializer_list>
 
 namespace cvb {
 
@@ -391,12 +392,19 @@ static int norm_grid(long long rows, int rows_per_warp) {
 }  // namespace cvb
 
 using namespace cvb;
+// every vector access in this file is 16 bytes wide: refuse misaligned tensors on the host
+static inline bool cvb_misaligned(std::initializer_list<const void*> ptrs) {
+  for (const void* q : ptrs)
+    if (q != nullptr && (reinterpret_cast<uintptr_t>(q) & 15)) return true;
+  return false;
+}
 
 extern "C" int cvb_rmsnorm_fwd(const void* x, const void* resid_in, const void* w, const void* gate, void* y,
                                void* resid_out, float* rstd, long long rows, int D, long long x_stride,
                                long long gate_stride, float eps, float w_offset, void* stream) {
   const int nvec = norm_nvec(D);
   if (nvec < 0) return -1;
+  if (cvb_misaligned({x, resid_in, w, gate, y, resid_out}) || x_stride % 8 || gate_stride % 8) return -2;
   if (rows <= 0) return 0;
   const int lanes = D / 8 < 32 ? D / 8 : 32;
 #define CVB_FWD(NV)                                                                                          \
@@ -422,6 +430,8 @@ extern "C" int cvb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
                                void* stream) {
   const int nvec = norm_nvec(D);
   if (nvec < 0) return -1;
+  if (cvb_misaligned({dy, x, w, gate, dres, dx, dgate}) || x_stride % 8 || gate_stride % 8 || dx_stride % 8)
+    return -2;
   if (rows <= 0) return 0;
   const int lanes = D / 8 < 32 ? D / 8 : 32;
   int grid = norm_grid(rows, 32 / lanes);
@@ -449,6 +459,7 @@ extern "C" int cvb_headnorm_rope_fwd(const void* x, const void* w, const int* po
                                      const float* sin_tab, int seq_len, float eps, float w_offset,
                                      int use_norm, void* stream) {
   if (!(D == 64 || D == 128 || D == 256) || rot % 16 != 0 || rot > D) return -1;
+  if (cvb_misaligned({x, w, y}) || x_tok_stride % 8 || x_head_stride % 8) return -2;
   if (tokens <= 0) return 0;
   headnorm_rope_fwd_kernel<<<norm_grid(tokens * heads, 32 / (D / 8)), NORM_THREADS, 0,
                              static_cast<cudaStream_t>(stream)>>>(
@@ -464,6 +475,7 @@ extern "C" int cvb_headnorm_rope_bwd(const void* dy, const void* x, const void* 
                                      const float* cos_tab, const float* sin_tab, int seq_len,
                                      float w_offset, int use_norm, void* stream) {
   if (!(D == 64 || D == 128 || D == 256) || rot % 16 != 0 || rot > D) return -1;
+  if (cvb_misaligned({dy, x, w, dx}) || x_tok_stride % 8 || x_head_stride % 8) return -2;
   if (tokens <= 0) return 0;
   int grid = norm_grid(tokens * heads, 32 / (D / 8));
   if (grid > 148 * 2) grid = 148 * 2;

@@ -261,11 +261,9 @@ class Qwen35Model(torch.nn.Module):
         if vh // kh > 1:
             q = q.repeat_interleave(vh // kh, dim=2)
             k = k.repeat_interleave(vh // kh, dim=2)
-        qf = gdn_ops.l2norm(q.float()).transpose(1, 2) * (1.0 / math.sqrt(kd))
-        kf = gdn_ops.l2norm(k.float()).transpose(1, 2)
-        core, state = gdn_ops.gated_delta_rule(qf, kf, v.transpose(1, 2), beta.transpose(1, 2), g.transpose(1, 2),
-                                               initial_state)
-        core = core.transpose(1, 2).to(x.dtype).reshape(T, vh, vd)
+        # l2norm of q/k and the 1/sqrt(dk) scale on q are applied inside the fused op
+        core, state = gdn_ops.gated_delta_rule_fused(q, k, v, beta, g, initial_state, scale=1.0 / math.sqrt(kd))
+        core = core.to(x.dtype).reshape(T, vh, vd)
         y = ops.gated_rmsnorm(core, z.reshape(T, vh, vd), self.param(p + "norm.weight"), cfg.rms_norm_eps)
         out = ops.linear(y.reshape(T, value_dim), self.param(p + "out_proj.weight"))
         out = reduce_from_tp(out, ctx.tp_group)

@@ -96,3 +96,186 @@ def gated_delta_rule(q, k, v, beta, g, initial_state=None, *, chunk: int = 64, b
         if gdn_native.supported(q, v):
             return gdn_native.gated_delta_rule(q, k, v, beta, g, initial_state)
     return gdn_chunked(q, k, v, beta, g, initial_state, chunk)
+
+
+# ----------------------------------------------------------------------------
+# Chunked form with a hand-derived backward.  The chunk-local algebra is batched
+# over every chunk at once; only the two state scans walk the chunks in order,
+# and on CUDA those run as tcgen05 kernels with the state held in TMEM
+# (cuda/gdn_scan.cu).  Layout inside: [B, H, n_chunks, C, d].
+# ----------------------------------------------------------------------------
+def _chunk_local(q, k, v, beta, g, scale: float, eps: float = 1e-6):
+    """Chunk-local quantities.  q,k [B,H,n,C,dk], v [B,H,n,C,dv], beta,g [B,H,n,C] (fp32)."""
+    C = q.shape[-2]
+    rq = torch.rsqrt((q * q).sum(-1, keepdim=True) + eps)
+    rk = torch.rsqrt((k * k).sum(-1, keepdim=True) + eps)
+    qn = q * rq * scale
+    kn = k * rk
+    c = g.cumsum(-1)
+    tri_incl = torch.ones(C, C, dtype=torch.bool, device=q.device).tril(0)
+    tri_strict = torch.ones(C, C, dtype=torch.bool, device=q.device).tril(-1)
+    decay = torch.exp((c.unsqueeze(-1) - c.unsqueeze(-2)).masked_fill(~tri_incl, 0.0))
+    G = kn @ kn.transpose(-1, -2)
+    A = (beta.unsqueeze(-1) * decay * G).masked_fill(~tri_strict, 0.0)
+    eye = torch.eye(C, device=q.device, dtype=q.dtype)
+    T = torch.linalg.solve_triangular(eye + A, eye.expand_as(A), upper=False)
+    ec = torch.exp(c).unsqueeze(-1)
+    Kb = beta.unsqueeze(-1) * ec * kn
+    Vb = beta.unsqueeze(-1) * v
+    W = T @ Kb
+    U = T @ Vb
+    P = ((qn @ kn.transpose(-1, -2)) * decay).masked_fill(~tri_incl, 0.0)
+    gam = c[..., -1]
+    Kdec = torch.exp(gam.unsqueeze(-1) - c).unsqueeze(-1) * kn
+    Qd = ec * qn
+    return dict(rq=rq, rk=rk, qn=qn, kn=kn, c=c, decay=decay, G=G, A=A, T=T, Kb=Kb, Vb=Vb, W=W, U=U, P=P,
+                egam=torch.exp(gam), Kdec=Kdec, Qd=Qd, tri_incl=tri_incl, tri_strict=tri_strict)
+
+
+def scan_fwd_ref(W, U, Kdec, egam, S0):
+    """Vn_i = U_i - W_i S_i ; S_{i+1} = egam_i S_i + Kdec_i^T Vn_i.  Returns (Vn, S_chunks, S_final)."""
+    n = W.shape[2]
+    S = S0
+    Vn, Ss = [], []
+    for i in range(n):
+        Ss.append(S)
+        vn = U[:, :, i] - W[:, :, i] @ S
+        Vn.append(vn)
+        S = S * egam[:, :, i, None, None] + Kdec[:, :, i].transpose(-1, -2) @ vn
+    return torch.stack(Vn, 2), torch.stack(Ss, 2), S
+
+
+def scan_bwd_ref(dVloc, Kdec, Qd, W, dO, egam, dSf):
+    """dVn_i = dVloc_i + Kdec_i dS ; dS <- egam_i dS + Qd_i^T dO_i - W_i^T dVn_i (i descending).
+    Returns (dVn, dS_next per chunk, dS0)."""
+    n = W.shape[2]
+    dS = dSf
+    dVn, dSn = [None] * n, [None] * n
+    for i in range(n - 1, -1, -1):
+        dSn[i] = dS
+        dv = dVloc[:, :, i] + Kdec[:, :, i] @ dS
+        dVn[i] = dv
+        dS = dS * egam[:, :, i, None, None] + Qd[:, :, i].transpose(-1, -2) @ dO[:, :, i] \
+            - W[:, :, i].transpose(-1, -2) @ dv
+    return torch.stack(dVn, 2), torch.stack(dSn, 2), dS
+
+
+def _scan_fwd(W, U, Kdec, egam, S0):
+    if W.is_cuda:
+        from . import gdn_native
+        if gdn_native.scan_supported(W, U):
+            return gdn_native.scan_fwd(W, U, Kdec, egam, S0)
+    return scan_fwd_ref(W, U, Kdec, egam, S0)
+
+
+def _scan_bwd(dVloc, Kdec, Qd, W, dO, egam, dSf):
+    if W.is_cuda:
+        from . import gdn_native
+        if gdn_native.scan_supported(W, dO):
+            return gdn_native.scan_bwd(dVloc, Kdec, Qd, W, dO, egam, dSf)
+    return scan_bwd_ref(dVloc, Kdec, Qd, W, dO, egam, dSf)
+
+
+class _GdnChunked(torch.autograd.Function):
+    """q,k [B,T,H,dk] (raw, un-normalised), v [B,T,H,dv], beta,g [B,T,H] fp32, S0 [B,H,dk,dv] or None.
+    Returns (o [B,T,H,dv] in v's dtype, S_final fp32)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, beta, g, S0, scale, chunk):
+        B, T, H, dk = q.shape
+        dv = v.shape[-1]
+        pad = (-T) % chunk
+        n = (T + pad) // chunk
+
+        def blk(x, last):
+            x = x.float().transpose(1, 2)  # [B,H,T,*]
+            if pad:
+                x = F.pad(x, (0, 0, 0, pad)) if last else F.pad(x, (0, pad))
+            return x.reshape(B, H, n, chunk, -1) if last else x.reshape(B, H, n, chunk)
+
+        qb, kb, vb = blk(q, True), blk(k, True), blk(v, True)
+        bb, gb = blk(beta, False), blk(g, False)
+        loc = _chunk_local(qb, kb, vb, bb, gb, scale)
+        S0f = S0.float() if S0 is not None else qb.new_zeros(B, H, dk, dv)
+        Vn, Ss, Sf = _scan_fwd(loc["W"], loc["U"], loc["Kdec"], loc["egam"], S0f)
+        O = loc["Qd"] @ Ss + loc["P"] @ Vn
+        o = O.reshape(B, H, n * chunk, dv)[:, :, :T].transpose(1, 2).to(v.dtype)
+        ctx.save_for_backward(q, k, v, beta, g, Vn, Ss)
+        ctx.cfg = (scale, chunk, pad, n, S0 is not None)
+        return o, Sf
+
+    @staticmethod
+    def backward(ctx, do, dSf):
+        q, k, v, beta, g, Vn, Ss = ctx.saved_tensors
+        scale, chunk, pad, n, has_s0 = ctx.cfg
+        B, T, H, dk = q.shape
+        dv = v.shape[-1]
+
+        def blk(x, last):
+            x = x.float().transpose(1, 2)
+            if pad:
+                x = F.pad(x, (0, 0, 0, pad)) if last else F.pad(x, (0, pad))
+            return x.reshape(B, H, n, chunk, -1) if last else x.reshape(B, H, n, chunk)
+
+        qb, kb, vb = blk(q, True), blk(k, True), blk(v, True)
+        bb, gb = blk(beta, False), blk(g, False)
+        L = _chunk_local(qb, kb, vb, bb, gb, scale)
+        dO = blk(do, True)
+        dSf = dSf.float() if dSf is not None else Ss.new_zeros(B, H, dk, dv)
+        Vn, Ss = Vn.float(), Ss.float()
+        kn, qn, c, decay, Tm = L["kn"], L["qn"], L["c"], L["decay"], L["T"]
+        dVloc = L["P"].transpose(-1, -2) @ dO
+        dVn, dSn, dS0 = _scan_bwd(dVloc, L["Kdec"], L["Qd"], L["W"], dO, L["egam"], dSf)
+        dVn, dSn = dVn.float(), dSn.float()
+        # ---- chunk-local gradients -------------------------------------------------
+        dW = -(dVn @ Ss.transpose(-1, -2))
+        dU = dVn
+        dP = (dO @ Vn.transpose(-1, -2)).masked_fill(~L["tri_incl"], 0.0)
+        dQd = dO @ Ss.transpose(-1, -2)
+        ec = torch.exp(c).unsqueeze(-1)
+        dPd = dP * decay
+        dqn = ec * dQd + dPd @ kn
+        dkn = dPd.transpose(-1, -2) @ qn
+        dKdec = Vn @ dSn.transpose(-1, -2)
+        edec = torch.exp(c[..., -1:].clone() - c).unsqueeze(-1)
+        dkn = dkn + edec * dKdec
+        dc = (dQd * L["Qd"]).sum(-1)
+        MP = dP * L["P"]
+        dc = dc + MP.sum(-1) - MP.sum(-2)
+        s_t = (dKdec * L["Kdec"]).sum(-1)
+        dc = dc - s_t
+        dgam = s_t.sum(-1) + L["egam"] * (Ss * dSn).sum((-1, -2))
+        dT = dW @ L["Kb"].transpose(-1, -2) + dU @ L["Vb"].transpose(-1, -2)
+        dKb = Tm.transpose(-1, -2) @ dW
+        dVb = Tm.transpose(-1, -2) @ dU
+        dvb = bb.unsqueeze(-1) * dVb
+        dbeta = (dVb * vb).sum(-1) + (dKb * ec * kn).sum(-1)
+        dkn = dkn + bb.unsqueeze(-1) * ec * dKb
+        dc = dc + (dKb * L["Kb"]).sum(-1)
+        dA = -(Tm.transpose(-1, -2) @ dT @ Tm.transpose(-1, -2)).masked_fill(~L["tri_strict"], 0.0)
+        MA = dA * L["A"]
+        dbeta = dbeta + (dA * decay * L["G"]).sum(-1)
+        dc = dc + MA.sum(-1) - MA.sum(-2)
+        dG = dA * bb.unsqueeze(-1) * decay
+        dkn = dkn + dG @ kn + dG.transpose(-1, -2) @ kn
+        dc[..., -1] = dc[..., -1] + dgam
+        dg = dc.flip(-1).cumsum(-1).flip(-1)
+        # ---- l2norm backward -------------------------------------------------------
+        khat = kn
+        dk_raw = L["rk"] * (dkn - khat * (dkn * khat).sum(-1, keepdim=True))
+        qhat = qn / scale
+        dqh = dqn * scale
+        dq_raw = L["rq"] * (dqh - qhat * (dqh * qhat).sum(-1, keepdim=True))
+
+        def unblk(x, last, like):
+            x = x.reshape(B, H, n * chunk, -1)[:, :, :T] if last else x.reshape(B, H, n * chunk)[:, :, :T]
+            return x.transpose(1, 2).to(like.dtype)
+
+        return (unblk(dq_raw, True, q), unblk(dk_raw, True, k), unblk(dvb, True, v), unblk(dbeta, False, beta),
+                unblk(dg, False, g), (dS0 if has_s0 else None), None, None)
+
+
+def gated_delta_rule_fused(q, k, v, beta, g, initial_state=None, *, scale: float, chunk: int = 64):
+    """Gated delta rule on raw (un-normalised) q, k ``[B,T,H,d]``; l2norm and the ``scale`` on q are
+    applied inside.  Returns ``(o [B,T,H,dv], final_state [B,H,dk,dv] fp32)``."""
+    return _GdnChunked.apply(q, k, v, beta, g, initial_state, scale, chunk)

@@ -43,12 +43,30 @@ def _lib_mm(a: torch.Tensor, b: torch.Tensor, alpha: float) -> torch.Tensor:
 
 
 def _row_major_2d(t: torch.Tensor) -> torch.Tensor:
-    """2-D view with unit inner stride and a 16-byte aligned row stride."""
+    """2-D view with unit inner stride, 16-byte aligned base and row stride (what TMA needs)."""
     if t.dim() != 2:
         t = t.reshape(-1, t.shape[-1])
-    if t.stride(1) != 1 or (t.stride(0) * t.element_size()) % 16 != 0 or t.data_ptr() % 16 != 0:
+    per16 = 16 // t.element_size()
+    if t.stride(1) == 1 and t.stride(0) % per16 == 0 and t.data_ptr() % 16 == 0:
+        return t
+    cols = t.shape[1]
+    if cols % per16 == 0:
         t = t.contiguous()
-    return t
+        if t.data_ptr() % 16 == 0:
+            return t
+        return t.clone()
+    # odd width: copy into a buffer whose rows are padded to 16 bytes and hand back the narrow view
+    buf = torch.zeros((t.shape[0], (cols + per16 - 1) // per16 * per16), dtype=t.dtype, device=t.device)
+    buf[:, :cols].copy_(t)
+    return buf[:, :cols]
+
+
+def _alloc_out(M: int, N: int, dtype, device) -> torch.Tensor:
+    """[M, N] output whose row stride is a multiple of 16 bytes (vector stores in the epilogue)."""
+    per16 = 16 // torch.empty((), dtype=dtype).element_size()
+    Np = (N + per16 - 1) // per16 * per16
+    buf = torch.empty((M, Np), dtype=dtype, device=device)
+    return buf if Np == N else buf[:, :N]
 
 
 def gemm_raw(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, M: int, N: int, K: int, *, a_mn: bool,
@@ -102,7 +120,7 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *
     a, b = _row_major_2d(a), _row_major_2d(b)
     dt = out_dtype or torch.bfloat16
     if out is None:
-        out = torch.empty((M, N), dtype=dt, device=a.device)
+        out = _alloc_out(M, N, dt, a.device)
     epi = nv.EPI_STORE_BF16 if out.dtype == torch.bfloat16 else nv.EPI_STORE_F32
     gemm_raw(a, b, out, M, N, K, a_mn=False, b_mn=False, epi=epi, alpha=alpha, block_n=_pick_block_n(M, N))
     return out
@@ -122,7 +140,7 @@ def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *
     a, b = _row_major_2d(a), _row_major_2d(b)
     dt = out_dtype or torch.bfloat16
     if out is None:
-        out = torch.empty((M, N), dtype=dt, device=a.device)
+        out = _alloc_out(M, N, dt, a.device)
     epi = nv.EPI_STORE_BF16 if out.dtype == torch.bfloat16 else nv.EPI_STORE_F32
     gemm_raw(a, b, out, M, N, K, a_mn=False, b_mn=True, epi=epi, alpha=alpha, block_n=_pick_block_n(M, N))
     return out

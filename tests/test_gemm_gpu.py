@@ -102,3 +102,65 @@ def test_lmhead_logprob(M, V, K):
     assert _rel_err(emb.grad, er.grad) < 1.5e-2
 
 
+
+
+# --------------------------- Gated-DeltaNet scans ---------------------------
+def _gdn_scan_inputs(B=2, H=3, n=5, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    mk = lambda *s, sc=1.0: (sc * torch.randn(*s, generator=g)).to(torch.bfloat16).float().to(_dev())
+    W = mk(B, H, n, 64, 128, sc=0.1)
+    U = mk(B, H, n, 64, 128)
+    Kd = mk(B, H, n, 64, 128, sc=0.1)
+    Qd = mk(B, H, n, 64, 128, sc=0.1)
+    egam = torch.exp(-torch.rand(B, H, n, generator=g)).to(_dev())
+    S0 = (0.1 * torch.randn(B, H, 128, 128, generator=g)).to(_dev())
+    return W, U, Kd, Qd, egam, S0
+
+
+def test_gdn_scan_fwd_kernel():
+    from cverl_b200.ops import gdn, gdn_native
+    W, U, Kd, Qd, egam, S0 = _gdn_scan_inputs()
+    Vn, Ss, Sf = gdn_native.scan_fwd(W, U, Kd, egam, S0)
+    Vr, Sr, Sfr = gdn.scan_fwd_ref(W, U, Kd, egam, S0)
+    assert _rel_err(Vn, Vr) < 1e-2
+    assert _rel_err(Ss, Sr) < 1e-2
+    assert _rel_err(Sf, Sfr) < 1e-2
+    Vn0, _, _ = gdn_native.scan_fwd(W, U, Kd, egam, None)
+    Vr0, _, _ = gdn.scan_fwd_ref(W, U, Kd, egam, torch.zeros_like(S0))
+    assert _rel_err(Vn0, Vr0) < 1e-2
+
+
+def test_gdn_scan_bwd_kernel():
+    from cverl_b200.ops import gdn, gdn_native
+    W, U, Kd, Qd, egam, S0 = _gdn_scan_inputs(seed=1)
+    dVl, dO = U, (0.5 * U.flip(2)).to(torch.bfloat16).float()
+    dVn, dSn, dS0 = gdn_native.scan_bwd(dVl, Kd, Qd, W, dO, egam, S0)
+    rV, rS, r0 = gdn.scan_bwd_ref(dVl, Kd, Qd, W, dO, egam, S0)
+    assert _rel_err(dVn, rV) < 1e-2
+    assert _rel_err(dSn, rS) < 1e-2
+    assert _rel_err(dS0, r0) < 1e-2
+
+
+def test_gdn_fused_matches_recurrence_on_gpu():
+    from cverl_b200.ops import gdn
+    torch.manual_seed(5)
+    B, T, H = 2, 200, 2
+    q = torch.randn(B, T, H, 128, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(B, T, H, 128, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(B, T, H, 128, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    beta = torch.sigmoid(torch.randn(B, T, H, device=_dev())).requires_grad_(True)
+    g = (-0.5 * torch.rand(B, T, H, device=_dev())).requires_grad_(True)
+    scale = 128 ** -0.5
+    o, Sf = gdn.gated_delta_rule_fused(q, k, v, beta, g, None, scale=scale)
+    do = torch.randn_like(o)
+    o.backward(do)
+    ins = [t.detach().float().cpu().requires_grad_(True) for t in (q, k, v, beta, g)]
+    qq, kk, vv, bb, gg = ins
+    o_r, S_r = gdn.gdn_recurrent_ref((gdn.l2norm(qq) * scale).transpose(1, 2), gdn.l2norm(kk).transpose(1, 2),
+                                     vv.transpose(1, 2), bb.transpose(1, 2), gg.transpose(1, 2))
+    o_r = o_r.transpose(1, 2)
+    o_r.backward(do.float().cpu())
+    assert _rel_err(o.cpu(), o_r) < 2e-2
+    assert _rel_err(Sf.cpu(), S_r) < 2e-2
+    for a, b in zip((q, k, v, beta, g), ins):
+        assert _rel_err(a.grad.cpu(), b.grad) < 4e-2
