@@ -192,6 +192,36 @@ class Qwen35Model(torch.nn.Module):
             else:
                 yield s.name, self.flat.params[s.name].data
 
+    def tp_partial_grad_names(self) -> List[str]:
+        """Replicated parameters that act on head-sharded activations: each tensor-parallel rank
+        holds only its heads' share of their gradient, so the shares must be summed over TP."""
+        cfg = self.cfg
+        names = []
+        for i in range(self.layer_begin, self.layer_end):
+            p = f"{cfg.layer_root}{i}."
+            if cfg.layer_types[i] == "full_attention":
+                names += [p + "self_attn.q_norm.weight", p + "self_attn.k_norm.weight"]
+            else:
+                names.append(p + "linear_attn.norm.weight")
+        return names
+
+    @torch.no_grad()
+    def sync_replicated_grads(self) -> None:
+        """Sum the partial gradients of ``tp_partial_grad_names`` over the tensor-parallel group
+        (one all-reduce of their concatenation)."""
+        if self.ctx.tp_size == 1:
+            return
+        import torch.distributed as dist
+        grads = [self.flat.params[n].main_grad for n in self.tp_partial_grad_names()]
+        if not grads:
+            return
+        flat = torch.cat([g.reshape(-1) for g in grads])
+        dist.all_reduce(flat, group=self.ctx.tp_group)
+        off = 0
+        for g in grads:
+            g.copy_(flat[off:off + g.numel()].view_as(g))
+            off += g.numel()
+
     def trainable_parameters(self) -> List[torch.nn.Parameter]:
         return list(self.flat.params.values())
 

@@ -198,7 +198,7 @@ class _GdnChunked(torch.autograd.Function):
         loc = _chunk_local(qb, kb, vb, bb, gb, scale)
         S0f = S0.float() if S0 is not None else qb.new_zeros(B, H, dk, dv)
         Vn, Ss, Sf = _scan_fwd(loc["W"], loc["U"], loc["Kdec"], loc["egam"], S0f)
-        O = loc["Qd"] @ Ss + loc["P"] @ Vn
+        O = loc["Qd"] @ Ss.float() + loc["P"] @ Vn.float()
         o = O.reshape(B, H, n * chunk, dv)[:, :, :T].transpose(1, 2).to(v.dtype)
         ctx.save_for_backward(q, k, v, beta, g, Vn, Ss)
         ctx.cfg = (scale, chunk, pad, n, S0 is not None)

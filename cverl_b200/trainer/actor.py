@@ -88,6 +88,8 @@ class ActorEngine:
             scale = torch.tensor([1.0 / num_micro] * 5 + [1.0], device=total.device)
             total += metrics.to(total.device) * scale
         self.fold_autograd_grads()
+        if hasattr(self.model, "sync_replicated_grads"):
+            self.model.sync_replicated_grads()
         self.optimizer.step()
         return torch.cat([total, self.optimizer.last_metrics.to(total.device)])
 

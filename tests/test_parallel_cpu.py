@@ -1,0 +1,211 @@
+"""Tensor parallelism and ZeRO sharding on CPU ranks (gloo) and with scripted fake collectives."""
+import pytest
+import torch
+
+from cverl_b200.models.config import Qwen35TextConfig
+from cverl_b200.models.params import model_param_specs, shard_tensor, unshard_tensor
+from cverl_b200.models.qwen3_5 import Qwen35Model
+from cverl_b200.optim import AdamWOptions, FlatAdamW, Fp32MasterAdamW
+from cverl_b200.parallel.collectives import Collectives, ReduceOp, SingleProcessCollectives
+from cverl_b200.parallel.zero import (FlatZeroOptimizer, flat_sharded_adamw_step, flatten_parameter_shard,
+                                      greedy_parameter_owners)
+from dist_utils import run_ranks
+
+
+def _fold(model):
+    for p in list(model.flat.params.values()) + list(model.fused.values()):
+        if p.grad is not None:
+            p.main_grad.add_(p.grad.float())
+            p.grad = None
+
+
+def _tp_worker(rank, world, moe):
+    from cverl_b200.parallel.mesh import build_context
+    torch.manual_seed(0)
+    cfg = Qwen35TextConfig.tiny(moe=moe, layers=4)
+    ctx = build_context(world, rank, tp=2, dp=1)
+    tp_model = Qwen35Model(cfg, dtype=torch.float32, ctx=ctx)
+    tp_model.init_weights(seed=11)
+    dense = Qwen35Model(cfg, dtype=torch.float32)
+    dense.init_weights(seed=11)
+    ids = torch.randint(0, cfg.vocab_size, (2, 20), generator=torch.Generator().manual_seed(3))
+    w = torch.randn(2, 12, generator=torch.Generator().manual_seed(4))
+    lp_tp = tp_model.response_logprobs(ids, 8)
+    lp_d = dense.response_logprobs(ids, 8)
+    torch.testing.assert_close(lp_tp, lp_d, rtol=1e-4, atol=1e-4)
+    (lp_tp * w).sum().backward()
+    (lp_d * w).sum().backward()
+    _fold(tp_model)
+    _fold(dense)
+    tp_model.sync_replicated_grads()
+    # every local gradient equals the matching shard of the dense gradient (correct TP backward)
+    for spec in dense.specs:
+        if spec.expert >= 0:
+            continue
+        full = dense.flat.params[spec.name].main_grad
+        local = shard_tensor(spec, full, ctx.tp_rank, 2).reshape(tp_model.flat.params[spec.name].shape)
+        torch.testing.assert_close(tp_model.flat.params[spec.name].main_grad, local, rtol=2e-3, atol=2e-5,
+                                   msg=lambda m: f"{spec.name}: {m}")
+
+
+def test_tp2_matches_dense_forward_and_backward():
+    run_ranks(_tp_worker, 2, False)
+
+
+def test_shard_unshard_roundtrip():
+    cfg = Qwen35TextConfig.tiny(layers=4)
+    for spec in model_param_specs(cfg):
+        full = torch.randn(spec.full_shape)
+        shards = [shard_tensor(spec, full, r, 2) for r in range(2)]
+        assert tuple(shards[0].shape) == spec.local_shape(2)
+        torch.testing.assert_close(unshard_tensor(spec, shards), full)
+
+
+def _zero_worker(rank, world):
+    import torch.distributed as dist
+    from cverl_b200.parallel.mesh import build_context
+    cfg = Qwen35TextConfig.tiny(layers=2)
+    ctx = build_context(world, rank, tp=1, dp=2)
+    model = Qwen35Model(cfg, dtype=torch.float32, ctx=ctx, pad_multiple=2 * 8)
+    model.init_weights(seed=5)
+    ref = Qwen35Model(cfg, dtype=torch.float32, pad_multiple=2 * 8)
+    ref.init_weights(seed=5)
+    opts = AdamWOptions(lr=1e-2, beta2=0.95, use_master_weights=True)
+    opt = FlatZeroOptimizer(model.flat, opts, dp_group=ctx.dp_group, dp_rank=rank, dp_size=2, norm_group=None,
+                            norm_world=2, max_grad_norm=0.5)
+    ropt = FlatZeroOptimizer(ref.flat, opts, max_grad_norm=0.5)
+    gen = torch.Generator().manual_seed(9)
+    for step in range(2):
+        grads = [torch.randn(model.flat.padded_numel, generator=gen) for _ in range(2)]
+        for g in grads:
+            g[model.flat.numel:] = 0
+        model.flat.main_grad.copy_(grads[rank])
+        ref.flat.main_grad.copy_((grads[0] + grads[1]) / 2)
+        opt.step()
+        ropt.step()
+        torch.testing.assert_close(model.flat.flat, ref.flat.flat, rtol=1e-5, atol=2e-5)
+        # the global norm is the norm of the averaged gradient: shards' squared norms add up
+        assert abs(opt.last_metrics[1].item() - ropt.last_metrics[1].item()) < 1e-3 * ropt.last_metrics[1].item()
+        assert model.flat.main_grad.abs().max().item() == 0.0
+
+
+def test_flat_zero_dp2_matches_single_rank():
+    run_ranks(_zero_worker, 2)
+
+
+class SliceCollectives(Collectives):
+    """Simulates one rank of a DP group: reduce_scatter sums scripted peer tensors and returns this
+    rank's slice, all_gather returns scripted shards.  Records every call."""
+
+    def __init__(self, rank, world, peer_flat_grads=None, gathered=None):
+        self._rank, self._world = rank, world
+        self.peer_flat_grads, self.gathered = peer_flat_grads, gathered
+        self.calls = []
+
+    def rank(self): return self._rank
+    def world_size(self): return self._world
+    def barrier(self, group=None): self.calls.append(("barrier",))
+    def broadcast(self, tensor, root, group=None): return tensor.clone()
+
+    def all_reduce(self, tensor, op=ReduceOp.SUM, group=None):
+        self.calls.append(("all_reduce", op, tensor.dtype))
+        return tensor * self._world if op == ReduceOp.SUM else tensor.clone()
+
+    def all_gather(self, tensor, group=None):
+        self.calls.append(("all_gather", tensor.dtype))
+        parts = list(self.gathered)
+        parts[self._rank] = tensor
+        return torch.cat(parts)
+
+    def reduce_scatter(self, tensor, op=ReduceOp.SUM, group=None):
+        self.calls.append(("reduce_scatter", op, tensor.dtype))
+        total = tensor.clone()
+        for r, g in enumerate(self.peer_flat_grads):
+            if r != self._rank:
+                total += g.to(tensor.dtype)
+        if op == ReduceOp.MEAN:
+            total /= self._world
+        n = total.numel() // self._world
+        return total[self._rank * n:(self._rank + 1) * n].clone()
+
+    def all_to_all(self, tensor, group=None): return tensor.clone()
+    def send(self, tensor, dst): raise RuntimeError
+    def recv_like(self, like, src): raise RuntimeError
+
+
+def test_flat_sharded_adamw_two_simulated_ranks_equals_dense():
+    torch.manual_seed(0)
+    shapes = [(5, 3), (7,), (4, 4)]
+    params0 = [torch.randn(s) for s in shapes]
+    grads = [[torch.randn(s) for s in shapes] for _ in range(2)]
+    opts = AdamWOptions(lr=1e-2, beta1=0.9, beta2=0.95, weight_decay=0.01, use_master_weights=True)
+    dense_p = [p.clone().requires_grad_(True) for p in params0]
+    dense = Fp32MasterAdamW(dense_p, opts)
+    for p, g0, g1 in zip(dense_p, grads[0], grads[1]):
+        p.grad = (g0 + g1) / 2
+    dense.step()
+    total = sum(p.numel() for p in params0)
+    padded = (total + 1) // 2 * 2
+
+    def flat_of(gs):
+        f = torch.zeros(padded)
+        f[:total] = torch.cat([g.reshape(-1) for g in gs])
+        return f
+    new_shards = []
+    for rank in range(2):
+        ps = [p.clone().requires_grad_(True) for p in params0]
+        for p, g in zip(ps, grads[rank]):
+            p.grad = g.clone()
+        shard = flatten_parameter_shard(ps, rank, 2, dtype=torch.float32)
+        assert (shard.original_numel, shard.padded_numel) == (total, padded)
+        comm = SliceCollectives(rank, 2, peer_flat_grads=[flat_of(grads[0]), flat_of(grads[1])],
+                                gathered=[torch.zeros(padded // 2)] * 2)
+        opt = FlatAdamW(shard.shard.clone(), opts)
+        res = flat_sharded_adamw_step(ps, shard, opt, comm, [0, 1], comm, [0, 1], max_grad_norm=0.0,
+                                      apply_parameters=False)
+        assert ("reduce_scatter", ReduceOp.MEAN, torch.float32) in comm.calls
+        assert all(p.grad is None for p in ps)
+        assert res.grad_clip_scale == 1.0
+        new_shards.append(shard.shard.clone())
+    flat_new = torch.cat(new_shards)[:total]
+    dense_flat = torch.cat([p.detach().reshape(-1) for p in dense_p])
+    torch.testing.assert_close(flat_new, dense_flat, rtol=1e-5, atol=2e-5)
+
+
+def test_dp1_skips_collectives_and_clipping():
+    torch.manual_seed(1)
+    ps = [torch.randn(6, 2).requires_grad_(True)]
+    ps[0].grad = torch.full((6, 2), 10.0)
+    shard = flatten_parameter_shard(ps, 0, 1)
+    comm = SingleProcessCollectives()
+    opt = FlatAdamW(shard.shard.clone(), AdamWOptions(lr=1e-3, use_master_weights=False))
+    res = flat_sharded_adamw_step(ps, shard, opt, comm, [0], comm, [0], max_grad_norm=1.0)
+    norm = (10.0 ** 2 * 12) ** 0.5
+    assert res.global_grad_norm == pytest.approx(norm, rel=1e-5)
+    assert res.grad_clip_scale == pytest.approx(1.0 / (norm + 1e-6), rel=1e-5)
+
+
+def test_greedy_owners_balance():
+    owners = greedy_parameter_owners([100, 90, 50, 40, 10, 5], 2)
+    load = [0, 0]
+    for n, o in zip([100, 90, 50, 40, 10, 5], owners):
+        load[o] += n
+    assert owners[0] != owners[1] and abs(load[0] - load[1]) <= 15
+
+
+def test_adamw_master_keeps_small_updates_and_load_state():
+    p = torch.ones(16, dtype=torch.bfloat16)
+    opts = AdamWOptions(lr=1e-5, weight_decay=0.0, use_master_weights=True)
+    opt = FlatAdamW(p, opts)
+    opt.step(torch.ones(16))
+    assert (opt.master < 1.0).all()          # fp32 master moved
+    assert (p == 1.0).all()                  # bf16 rounds the tiny update away
+    nomaster = FlatAdamW(torch.ones(16, dtype=torch.bfloat16), AdamWOptions(use_master_weights=False))
+    assert nomaster.master is None and nomaster.parameter_shard.dtype == torch.bfloat16
+    opt2 = FlatAdamW(torch.zeros(16), opts)
+    opt2.load_state(opt.master, opt.exp_avg, opt.exp_avg_sq, opt.step_count)
+    opt.step(torch.ones(16))
+    opt2.step(torch.ones(16))
+    torch.testing.assert_close(opt.master, opt2.master)
+    with pytest.raises(ValueError):
+        opt2.load_state(opt.master[:4], opt.exp_avg, opt.exp_avg_sq, 1)
