@@ -176,12 +176,35 @@ def _scan_bwd(dVloc, Kdec, Qd, W, dO, egam, dSf):
     return scan_bwd_ref(dVloc, Kdec, Qd, W, dO, egam, dSf)
 
 
+class _tf32_matmul:
+    """Chunk-local products are [64 x 64 x 128]-sized batched GEMMs on operands that were bf16 a
+    moment ago; on CUDA they run on the tensor cores in TF32 instead of the SIMT fp32 path."""
+
+    def __enter__(self):
+        self.prev = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = True
+
+    def __exit__(self, *exc):
+        torch.backends.cuda.matmul.allow_tf32 = self.prev
+        return False
+
+
 class _GdnChunked(torch.autograd.Function):
     """q,k [B,T,H,dk] (raw, un-normalised), v [B,T,H,dv], beta,g [B,T,H] fp32, S0 [B,H,dk,dv] or None.
     Returns (o [B,T,H,dv] in v's dtype, S_final fp32)."""
 
     @staticmethod
     def forward(ctx, q, k, v, beta, g, S0, scale, chunk):
+        with _tf32_matmul():
+            return _GdnChunked._forward(ctx, q, k, v, beta, g, S0, scale, chunk)
+
+    @staticmethod
+    def backward(ctx, do, dSf):
+        with _tf32_matmul():
+            return _GdnChunked._backward(ctx, do, dSf)
+
+    @staticmethod
+    def _forward(ctx, q, k, v, beta, g, S0, scale, chunk):
         B, T, H, dk = q.shape
         dv = v.shape[-1]
         pad = (-T) % chunk
@@ -205,7 +228,7 @@ class _GdnChunked(torch.autograd.Function):
         return o, Sf
 
     @staticmethod
-    def backward(ctx, do, dSf):
+    def _backward(ctx, do, dSf):
         q, k, v, beta, g, Vn, Ss = ctx.saved_tensors
         scale, chunk, pad, n, has_s0 = ctx.cfg
         B, T, H, dk = q.shape
