@@ -74,6 +74,13 @@ _CUDA_PROTOS = {
     "cvb_flat_adamw": "ppppppp l fffff f l i p",
     "cvb_lse_combine": "ppppppp l i p",
     "cvb_lse_merge_ranks": "ppppp l i p",
+    "cvb_ipc_get_handle": "ppp",
+    "cvb_ipc_open_handle": "pp",
+    "cvb_ipc_close_handle": "p",
+    "cvb_device_malloc": "pl",
+    "cvb_device_free": "p",
+    "cvb_device_memset": "pilp",
+    "cvb_can_access_peer": "ii",
     "cvb_gdn_scan_fwd": "pppppppp l i p p",
     "cvb_gdn_scan_bwd": "pppppppppp l i p p",
 }

@@ -238,7 +238,7 @@ class Qwen35Model(torch.nn.Module):
         return torch.arange(seq, device=device, dtype=torch.int32).repeat(batch)
 
     # ------------------------------------------------------------------ mixers
-    def full_attention(self, x: torch.Tensor, i: int, batch: int, seq: int) -> torch.Tensor:
+    def full_attention(self, x: torch.Tensor, i: int, batch: int, seq: int, cache: Optional[dict] = None) -> torch.Tensor:
         cfg, ctx = self.cfg, self.ctx
         p = f"{cfg.layer_root}{i}.self_attn."
         d = cfg.head_dim
@@ -260,6 +260,8 @@ class Qwen35Model(torch.nn.Module):
         off = cfg.norm_weight_offset
         q = ops.headnorm_rope(q, self.param(p + "q_norm.weight"), cos, sin, pos, cfg.rotary_dim, cfg.rms_norm_eps, off)
         k = ops.headnorm_rope(k, self.param(p + "k_norm.weight"), cos, sin, pos, cfg.rotary_dim, cfg.rms_norm_eps, off)
+        if cache is not None:  # prefill of a cached decode: keep the rotated keys and the values
+            cache["k"], cache["v"] = k.view(batch, seq, kvh, d), v.reshape(batch, seq, kvh, d)
         o = attn_ops.causal_attention(q, k, v, batch, seq, 1.0 / math.sqrt(d))
         if gate is not None:
             o = ops.siggate(o, gate)
@@ -267,7 +269,8 @@ class Qwen35Model(torch.nn.Module):
         return reduce_from_tp(out, ctx.tp_group)
 
     def linear_attention(self, x: torch.Tensor, i: int, batch: int, seq: int,
-                         initial_state: Optional[torch.Tensor] = None, return_state: bool = False):
+                         initial_state: Optional[torch.Tensor] = None, return_state: bool = False,
+                         cache: Optional[dict] = None):
         cfg, ctx = self.cfg, self.ctx
         p = f"{cfg.layer_root}{i}.linear_attn."
         tp = ctx.tp_size
@@ -280,6 +283,12 @@ class Qwen35Model(torch.nn.Module):
         proj = ops.linear(x, self.fused[f"{i}.lin_in"])
         mixed, z, b, a = proj.split([conv_dim, value_dim, vh, vh], dim=-1)
         conv_w = self.param(p + "conv1d.weight").view(conv_dim, cfg.linear_conv_kernel_dim)
+        if cache is not None:  # the last KW-1 pre-convolution rows seed the decode-time window
+            kw = cfg.linear_conv_kernel_dim
+            tail = mixed.reshape(batch, seq, conv_dim)[:, max(0, seq - (kw - 1)):]
+            if tail.shape[1] < kw - 1:
+                tail = F.pad(tail, (0, 0, kw - 1 - tail.shape[1], 0))
+            cache["conv"] = tail.clone()
         mixed = ops.conv1d_silu(mixed.view(batch, seq, conv_dim), conv_w)
         q, k, v = mixed.split([key_dim, key_dim, value_dim], dim=-1)
         q = q.reshape(batch, seq, kh, kd)
@@ -297,6 +306,8 @@ class Qwen35Model(torch.nn.Module):
         y = ops.gated_rmsnorm(core, z.reshape(T, vh, vd), self.param(p + "norm.weight"), cfg.rms_norm_eps)
         out = ops.linear(y.reshape(T, value_dim), self.param(p + "out_proj.weight"))
         out = reduce_from_tp(out, ctx.tp_group)
+        if cache is not None:
+            cache["state"] = state
         return (out, state) if return_state else out
 
     def mlp(self, x: torch.Tensor, i: int) -> torch.Tensor:
@@ -320,7 +331,8 @@ class Qwen35Model(torch.nn.Module):
         e = ops.embedding(input_ids.reshape(-1), table, lo)
         return reduce_from_tp(e, ctx.tp_group)
 
-    def forward_layers(self, x: torch.Tensor, batch: int, seq: int, final_norm: bool = True) -> torch.Tensor:
+    def forward_layers(self, x: torch.Tensor, batch: int, seq: int, final_norm: bool = True,
+                       caches: Optional[list] = None) -> torch.Tensor:
         """Run this stage's layers on the packed residual stream ``x`` ``[B*S, H]``."""
         cfg = self.cfg
         eps, off = cfg.rms_norm_eps, cfg.norm_weight_offset
@@ -328,10 +340,14 @@ class Qwen35Model(torch.nn.Module):
         for i in range(self.layer_begin, self.layer_end):
             p = f"{cfg.layer_root}{i}."
             n1, resid = ops.add_rmsnorm(delta, resid, self.param(p + "input_layernorm.weight"), eps, off)
+            cache = None
+            if caches is not None:
+                cache = {}
+                caches.append(cache)
             if cfg.layer_types[i] == "full_attention":
-                a = self.full_attention(n1, i, batch, seq)
+                a = self.full_attention(n1, i, batch, seq, cache=cache)
             else:
-                a = self.linear_attention(n1, i, batch, seq)
+                a = self.linear_attention(n1, i, batch, seq, cache=cache)
             n2, resid = ops.add_rmsnorm(a, resid, self.param(p + "post_attention_layernorm.weight"), eps, off)
             delta = self.mlp(n2, i)
         if self.last_stage and final_norm:

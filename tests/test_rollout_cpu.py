@@ -1,0 +1,267 @@
+"""Rollout layer on CPU: workers, cached decode, plugin loader, transports, batch builder, weight sync."""
+import multiprocessing as mp
+import os
+
+import pytest
+import torch
+
+from cverl_b200._build import LIB_DIR
+from cverl_b200.models.config import Qwen35TextConfig
+from cverl_b200.models.policy import (CausalLmPolicyOptions, Qwen3_5CausalLmPolicy, TinyCausalLmPolicy,
+                                      make_causal_lm_policy, response_log_probs)
+from cverl_b200.models.qwen3_5 import Qwen35Model
+from cverl_b200.parallel.collectives import Collectives, ReduceOp, SingleProcessCollectives
+from cverl_b200.parallel.weight_sync import (ParameterView, broadcast_parameters_from_root, recv_parameter_shards,
+                                             send_parameter_shards)
+from cverl_b200.rollout import (CachedQwenRolloutWorker, GenerationConfig, LoopbackRolloutTransport,
+                                PolicyRolloutWorker, RolloutRequest, RolloutSample, SharedMemoryRegion,
+                                SharedMemoryRolloutTransport, TokenBatch, build_gsm8k_rollout_batch,
+                                load_rollout_worker_plugin)
+from cverl_b200.rollout.gpu_batch_transport import (GpuBatchReceiver, GpuBatchSender, GpuRolloutBatch,
+                                                    TrainerIngressQueue)
+from cverl_b200.rollout.transport import (deserialize_request, deserialize_response, serialize_request,
+                                          serialize_response)
+from cverl_b200.text import ByteTokenizer
+from dist_utils import run_ranks
+
+
+def _batch(B=2, P=5, vocab=50):
+    ids = torch.randint(4, vocab, (B, P), generator=torch.Generator().manual_seed(0))
+    return TokenBatch(ids, torch.ones_like(ids), torch.full((B,), P))
+
+
+class DeterministicEosPolicy(TinyCausalLmPolicy):
+    """Always predicts eos after `eos_after` generated tokens; counts forwards."""
+
+    def __init__(self, eos=2, eos_after=3):
+        super().__init__(vocab_size=16, hidden_size=8)
+        self.eos, self.eos_after, self.calls = eos, eos_after, 0
+
+    def forward(self, prompt_ids, response_ids):
+        self.calls += 1
+        B, R = response_ids.shape
+        logits = torch.full((B, R, 16), -10.0)
+        tok = self.eos if R > self.eos_after else 5
+        logits[:, :, tok] = 10.0
+        return logits
+
+
+def test_policy_worker_greedy_eos_interval():
+    pol = DeterministicEosPolicy()
+    w = PolicyRolloutWorker(pol)
+    out = w.generate(_batch(), GenerationConfig(max_new_tokens=32, temperature=0.0, eos_token_id=2,
+                                                eos_check_interval=4))
+    assert out.lengths.tolist() == [4, 4]
+    assert out.token_ids[0, :4].tolist() == [5, 5, 5, 2]
+    assert pol.calls == 4            # stopped at the first interval check after every row finished
+    pol2 = DeterministicEosPolicy()
+    PolicyRolloutWorker(pol2).generate(_batch(), GenerationConfig(max_new_tokens=12, temperature=0.0, eos_token_id=2,
+                                                                  eos_check_interval=0))
+    assert pol2.calls == 12          # no host check: runs to max_new_tokens
+
+
+def test_sampling_top_k_top_p():
+    from cverl_b200.rollout import sample_next_tokens
+    logits = torch.tensor([[0.0, 1.0, 5.0, 4.0]]).repeat(64, 1)
+    g = torch.Generator().manual_seed(1)
+    tok, lp = sample_next_tokens(logits, GenerationConfig(top_k=2), g)
+    assert set(tok.tolist()) <= {2, 3}
+    tok, _ = sample_next_tokens(logits, GenerationConfig(top_p=0.5), g)
+    assert set(tok.tolist()) == {2}
+    tok, lp = sample_next_tokens(logits, GenerationConfig(temperature=0.0), None)
+    assert tok.tolist() == [2] * 64 and torch.allclose(lp, torch.log_softmax(logits, -1)[:, 2])
+
+
+def test_cached_decode_equals_recompute_generation():
+    cfg = Qwen35TextConfig.tiny(layers=4, vocab=64)
+    pol = Qwen3_5CausalLmPolicy(cfg, torch.float32)
+    pol.model.init_weights(seed=3)
+    b = _batch(B=2, P=6, vocab=64)
+    gc = GenerationConfig(max_new_tokens=6, temperature=0.0)
+    slow = PolicyRolloutWorker(pol).generate(b, gc)
+    fast = CachedQwenRolloutWorker(pol.model).generate(b, gc)
+    assert torch.equal(slow.token_ids, fast.token_ids)
+    torch.testing.assert_close(slow.logprobs, fast.logprobs, rtol=1e-4, atol=1e-4)
+
+
+def test_tiny_policy_and_reference_clone():
+    pol = make_causal_lm_policy(CausalLmPolicyOptions(kind="tiny", vocab_size=32, hidden_size=16))
+    p, r = torch.randint(1, 32, (3, 4)), torch.randint(1, 32, (3, 5))
+    logits = pol(p, r)
+    assert logits.shape == (3, 5, 32)
+    # row t must not depend on response tokens >= t
+    r2 = r.clone()
+    r2[:, 3:] = 7
+    torch.testing.assert_close(pol(p, r2)[:, :4], logits[:, :4])
+    ref = pol.clone_as_reference()
+    assert all(not q.requires_grad for q in ref.parameters())
+    lp = response_log_probs(logits, r)
+    lp.sum().backward()
+    with torch.no_grad():
+        for q in pol.parameters():
+            q.add_(0.1)
+    assert not torch.allclose(ref(p, r), pol(p, r))
+
+
+def test_qwen_policy_hf_roundtrip(tmp_path):
+    from cverl_b200.models.hf_io import synthesize_model_dir
+    cfg = Qwen35TextConfig.tiny(layers=2, vocab=64)
+    d = synthesize_model_dir(cfg, tmp_path / "m", dtype=torch.float32)
+    pol = Qwen3_5CausalLmPolicy.from_model_dir(d)
+    p, r = torch.randint(1, 64, (2, 4)), torch.randint(1, 64, (2, 3))
+    torch.testing.assert_close(pol.response_log_probs(p, r), response_log_probs(pol(p, r), r), rtol=1e-4, atol=1e-5)
+    pol.save_hf_checkpoint(tmp_path / "out")
+    again = Qwen3_5CausalLmPolicy.from_model_dir(tmp_path / "out")
+    assert torch.equal(again.model.flat.flat, pol.model.flat.flat)
+    assert (tmp_path / "out" / "config.json").exists()
+
+
+def test_plugin_loader_fixture():
+    w = load_rollout_worker_plugin(str(LIB_DIR / "libplugin_worker_fixture.so"), '{"vocab": 50, "eos_after": 3}')
+    b = TokenBatch(torch.tensor([[0, 5, 7], [1, 2, 3]]), torch.ones(2, 3, dtype=torch.long), torch.tensor([3, 3]))
+    o = w.generate(b, GenerationConfig(max_new_tokens=6, eos_token_id=2))
+    assert o.token_ids[0].tolist() == [8, 9, 10, 2, 0, 0] and o.lengths.tolist() == [4, 4]
+    pv = w.actor_parameters()
+    assert pv[0].name == "fixture.weight" and pv[0].tensor.tolist() == [1, 2, 3, 4]
+    pv[0].tensor[0] = 9.0                                   # live view into the plugin's memory
+    assert w.actor_parameters()[0].tensor[0].item() == 9.0
+    with pytest.raises(RuntimeError):
+        load_rollout_worker_plugin(str(LIB_DIR / "libcverl.so"))
+    with pytest.raises(RuntimeError):
+        load_rollout_worker_plugin("/nonexistent/plugin.so")
+    with pytest.raises(RuntimeError):
+        load_rollout_worker_plugin(str(LIB_DIR / "libplugin_worker_fixture.so"), '{"fail": 1}')
+
+
+def test_loopback_and_serialization_roundtrip():
+    req = RolloutRequest(prompts=["a", "b"], prompt_token_ids=[[1, 2], [3]], n=2, max_tokens=4, temperature=0.5,
+                         stop=["x"], model="m", extra_params={"k": "v"}, request_id=7, seed=3)
+    assert deserialize_request(serialize_request(req)) == req
+    resp = LoopbackRolloutTransport().generate(req)
+    assert len(resp.sequences) == 4 and resp.sequences[2].prompt_index == 1
+    assert deserialize_response(serialize_response(resp)) == resp
+    again = LoopbackRolloutTransport().generate(req)
+    assert again.sequences[1].token_ids == resp.sequences[1].token_ids
+    with pytest.raises(ValueError):
+        deserialize_request(serialize_request(req)[:10])
+
+
+def _shm_child(name):
+    c = SharedMemoryRolloutTransport(name, 1 << 16, create=False, timeout_ms=5000)
+    r = c.generate(RolloutRequest(prompts=["hi", "yo"], n=2, max_tokens=4))
+    ok = len(r.sequences) == 4 and r.sequences[0].text.startswith("hi")
+    try:
+        c.generate(RolloutRequest(prompts=["boom"]))
+        ok = False
+    except RuntimeError:
+        pass
+    os._exit(0 if ok else 1)
+
+
+def test_shared_memory_transport_forked_server_and_timeout():
+    name = f"/cvb_t_{os.getpid()}"
+    srv = SharedMemoryRolloutTransport(name, 1 << 16, create=True, timeout_ms=5000)
+    p = mp.get_context("fork").Process(target=_shm_child, args=(name,))
+    p.start()
+
+    def handler(req):
+        if req.prompts == ["boom"]:
+            raise ValueError("handler failure")
+        return LoopbackRolloutTransport().generate(req)
+    assert srv.serve_one(handler) and srv.serve_one(handler)
+    assert srv.serve_one(handler, timeout_ms=100) is False       # nothing pending: timeout, no hang
+    p.join(10)
+    assert p.exitcode == 0
+    cli = SharedMemoryRolloutTransport(name, 1 << 16, create=False, timeout_ms=150)
+    with pytest.raises(TimeoutError):
+        cli.generate(RolloutRequest(prompts=["nobody listens"]))
+    cli.close()
+    srv.close()
+    with pytest.raises(OSError):
+        SharedMemoryRolloutTransport(name, 1 << 16, create=False)
+
+
+def test_shared_memory_region():
+    name = f"/cvb_r_{os.getpid()}"
+    with SharedMemoryRegion(name, 4096, create=True) as a:
+        a.buffer()[0] = 42
+        with SharedMemoryRegion(name) as b:
+            assert b.size >= 4096 and b.buffer()[0] == 42
+    with pytest.raises(OSError):
+        SharedMemoryRegion(name)
+
+
+def test_build_gsm8k_rollout_batch():
+    tok = ByteTokenizer()
+    prompts, answers = ["What is 2+2?", "What is 3+3?"], ["#### 4", "6"]
+    samples = [RolloutSample(0, "it is #### 4"), RolloutSample(0, "it is #### 5"), RolloutSample(1, "no idea")]
+    b = build_gsm8k_rollout_batch(tok, prompts, answers, samples, max_prompt_len=8, max_response_len=16)
+    assert b.prompt_ids.shape == (3, 8) and b.response_ids.shape == (3, 16)
+    assert tok.decode(b.prompt_ids[0].tolist()) == " is 2+2?"     # truncated keeping the tail
+    assert b.rewards.tolist() == [1.0, 0.0, 0.0]
+    n0 = int(b.response_mask[0].sum())
+    assert n0 == len("it is #### 4") and b.token_rewards[0, n0 - 1] == 1.0 and b.token_rewards[0].sum() == 1.0
+    assert b.group_ids.tolist() == [0, 0, 1]
+    short = build_gsm8k_rollout_batch(tok, ["hi"], ["1"], [RolloutSample(0, "#### 1")], 8, 16)
+    assert short.prompt_ids[0, :6].tolist() == [0] * 6            # left padded
+
+
+class CountingCollectives(SingleProcessCollectives):
+    def __init__(self, world=2, rank=1):
+        self._w, self._r, self.broadcasts, self.barriers, self.sent = world, rank, 0, 0, []
+    def world_size(self): return self._w
+    def rank(self): return self._r
+    def _check(self, group): pass
+    def broadcast(self, tensor, root, group=None):
+        self.broadcasts += 1
+        return torch.full_like(tensor, 3)
+    def barrier(self, group=None): self.barriers += 1
+    def send(self, tensor, dst): self.sent.append(tensor.clone())
+    def recv_like(self, like, src): return self.sent.pop(0)
+
+
+def test_weight_sync_buckets_barrier_and_p2p():
+    params = [ParameterView(f"p{i}", torch.zeros(1024, dtype=torch.float32)) for i in range(4)]
+    params.append(ParameterView("h", torch.zeros(8, dtype=torch.bfloat16)))
+    c = CountingCollectives()
+    st = broadcast_parameters_from_root(params, c, root=0, group=[0, 1], bucket_bytes=1 << 20)
+    assert (st.buckets, c.broadcasts, c.barriers) == (2, 2, 1)      # dtype change splits the bucket
+    assert all((p.tensor == 3).all() for p in params)
+    c2 = CountingCollectives()
+    st2 = broadcast_parameters_from_root(params, c2, 0, [0, 1], bucket_bytes=16, barrier=False)
+    assert st2.buckets == 5 and c2.barriers == 0
+    single = SingleProcessCollectives()
+    assert broadcast_parameters_from_root(params, single, 0, [0]).buckets == 0
+    with pytest.raises(ValueError):
+        broadcast_parameters_from_root(params, c, root=5, group=[0, 1])
+    src = [ParameterView("a", torch.arange(10.0)), ParameterView("b", torch.arange(6.0).view(2, 3))]
+    dst = [ParameterView("a", torch.zeros(10)), ParameterView("b", torch.zeros(2, 3))]
+    c3 = CountingCollectives()
+    send_parameter_shards(src, c3, dst=1, bucket_bytes=32)
+    recv_parameter_shards(dst, c3, src=0, bucket_bytes=32)
+    assert torch.equal(dst[0].tensor, src[0].tensor) and torch.equal(dst[1].tensor, src[1].tensor)
+
+
+def _gpu_batch_worker(rank, world, mode):
+    from cverl_b200.parallel.collectives import TorchDistCollectives
+    os.environ["CVERL_GPU_BATCH_NCCL_MODE"] = mode
+    comm = TorchDistCollectives()
+    if rank == 0:
+        b = GpuRolloutBatch(step=3, weight_version=9, prompt_len=4, response_len=6)
+        b.tensors["prompt_ids"] = torch.arange(8).view(2, 4)
+        b.tensors["response_ids"] = torch.arange(12).view(2, 6)
+        b.tensors["response_mask"] = torch.ones(2, 6)
+        b.tensors["rewards"] = torch.tensor([1.0, 0.0])
+        GpuBatchSender(comm, "cpu").send(b, 1)
+    else:
+        got = GpuBatchReceiver(comm, "cpu").recv(0)
+        assert (got.step, got.weight_version, got.prompt_len, got.response_len, got.batch) == (3, 9, 4, 6, 2)
+        assert list(got.tensors) == ["prompt_ids", "response_ids", "response_mask", "rewards"]
+        assert torch.equal(got.tensors["response_ids"], torch.arange(12).view(2, 6))
+        q = TrainerIngressQueue(1)
+        assert q.push(got) and not q.push(got) and q.pop() is got and q.pop() is None
+
+
+@pytest.mark.parametrize("mode", ["direct", "slab"])
+def test_gpu_batch_transport_over_gloo(mode):
+    run_ranks(_gpu_batch_worker, 2, mode)
