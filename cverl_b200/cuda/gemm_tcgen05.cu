@@ -398,6 +398,13 @@ int make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint6
                        uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;
+  // The driver call needs this thread to have a current context.  Autograd runs backward on
+  // its own threads, where the runtime binds the primary context only at its first call.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    cudaFree(nullptr);
+    context_bound = true;
+  }
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {row_stride_bytes};
   cuuint32_t box[2] = {box_inner, box_outer};

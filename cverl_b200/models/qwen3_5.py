@@ -73,6 +73,7 @@ class Qwen35Model(torch.nn.Module):
             self.register_parameter(name.replace(".", "/"), p)
         self._build_fused_views()
         self._rope_cache: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
+        self._cp_original_len: Optional[int] = None
 
     # ------------------------------------------------------------------ layout
     def _flat_entries(self) -> List[Tuple[str, Tuple[int, ...]]]:
@@ -255,14 +256,22 @@ class Qwen35Model(torch.nn.Module):
             q, gate = q_all.view(T, h, 2 * d).split([d, d], dim=-1)
         k = k.view(T, kvh, d)
         v = v.view(T, kvh, d)
-        cos, sin = self._rope(seq, x.device)
+        cp_off = ctx.cp_rank * seq if ctx.cp_size > 1 else 0     # this shard's first position
+        cos, sin = self._rope(seq, x.device, cp_off)
         pos = self._positions(batch, seq, x.device)
         off = cfg.norm_weight_offset
         q = ops.headnorm_rope(q, self.param(p + "q_norm.weight"), cos, sin, pos, cfg.rotary_dim, cfg.rms_norm_eps, off)
         k = ops.headnorm_rope(k, self.param(p + "k_norm.weight"), cos, sin, pos, cfg.rotary_dim, cfg.rms_norm_eps, off)
         if cache is not None:  # prefill of a cached decode: keep the rotated keys and the values
             cache["k"], cache["v"] = k.view(batch, seq, kvh, d), v.reshape(batch, seq, kvh, d)
-        o = attn_ops.causal_attention(q, k, v, batch, seq, 1.0 / math.sqrt(d))
+        if ctx.cp_size > 1:
+            from ..parallel.context_parallel import ring_attention
+            o = ring_attention(q.view(batch, seq, h, d).transpose(1, 2), k.view(batch, seq, kvh, d).transpose(1, 2),
+                               v.reshape(batch, seq, kvh, d).transpose(1, 2), ctx.cp_group, ctx.cp_rank, ctx.cp_size,
+                               self._cp_original_len or seq * ctx.cp_size, 1.0 / math.sqrt(d))
+            o = o.transpose(1, 2).reshape(T, h, d)
+        else:
+            o = attn_ops.causal_attention(q, k, v, batch, seq, 1.0 / math.sqrt(d))
         if gate is not None:
             o = ops.siggate(o, gate)
         out = ops.linear(o.reshape(T, h * d), self.param(p + "o_proj.weight"))
@@ -289,7 +298,15 @@ class Qwen35Model(torch.nn.Module):
             if tail.shape[1] < kw - 1:
                 tail = F.pad(tail, (0, 0, kw - 1 - tail.shape[1], 0))
             cache["conv"] = tail.clone()
-        mixed = ops.conv1d_silu(mixed.view(batch, seq, conv_dim), conv_w)
+        if ctx.cp_size > 1:
+            from ..parallel.context_parallel import conv_halo, recv_initial_state, send_final_state
+            halo = cfg.linear_conv_kernel_dim - 1
+            ext = conv_halo(mixed.reshape(batch, seq, conv_dim), ctx.cp_group, ctx.cp_rank, ctx.cp_size, halo)
+            mixed = ops.conv1d_silu(ext, conv_w)[:, halo:]
+            like = torch.zeros(batch, vh, kd, vd, dtype=torch.float32, device=x.device)
+            initial_state = recv_initial_state(proj, like, ctx.cp_group, ctx.cp_rank)
+        else:
+            mixed = ops.conv1d_silu(mixed.view(batch, seq, conv_dim), conv_w)
         q, k, v = mixed.split([key_dim, key_dim, value_dim], dim=-1)
         q = q.reshape(batch, seq, kh, kd)
         k = k.reshape(batch, seq, kh, kd)
@@ -303,6 +320,8 @@ class Qwen35Model(torch.nn.Module):
         # l2norm of q/k and the 1/sqrt(dk) scale on q are applied inside the fused op
         core, state = gdn_ops.gated_delta_rule_fused(q, k, v, beta, g, initial_state, scale=1.0 / math.sqrt(kd))
         core = core.to(x.dtype).reshape(T, vh, vd)
+        if ctx.cp_size > 1:  # hand the state on; the zero token ties the send into the backward pass
+            core = core + send_final_state(state, ctx.cp_group, ctx.cp_rank, ctx.cp_size).to(core.dtype)
         y = ops.gated_rmsnorm(core, z.reshape(T, vh, vd), self.param(p + "norm.weight"), cfg.rms_norm_eps)
         out = ops.linear(y.reshape(T, value_dim), self.param(p + "out_proj.weight"))
         out = reduce_from_tp(out, ctx.tp_group)
@@ -376,10 +395,33 @@ class Qwen35Model(torch.nn.Module):
 
     def response_logprobs(self, input_ids: torch.Tensor, prompt_len: int) -> torch.Tensor:
         """Log-probs of the response tokens ``input_ids[:, P:]`` given their prefixes: [B, R] fp32."""
+        if self.ctx.cp_size > 1:
+            return self._response_logprobs_cp(input_ids, prompt_len)
         hidden = self.forward_hidden(input_ids)
         R = input_ids.shape[1] - prompt_len
         h = hidden[:, prompt_len - 1: prompt_len - 1 + R]
         return self.token_logprobs(h, input_ids[:, prompt_len:])
+
+    def _response_logprobs_cp(self, input_ids: torch.Tensor, prompt_len: int) -> torch.Tensor:
+        """Context parallel: every rank runs its contiguous shard of the sequence, scores its own
+        positions against the next tokens, and the per-position log-probs are all-gathered (the
+        backward of the gather is a reduce-scatter, so each rank back-propagates only its shard)."""
+        from ..parallel.autograd_collectives import all_gather_rows
+        from ..parallel.context_parallel import padded_shard_len, shard_sequence
+        ctx = self.ctx
+        B, S = input_ids.shape
+        s_loc = padded_shard_len(S, ctx.cp_size)
+        self._cp_original_len = S
+        local_ids = shard_sequence(input_ids, ctx.cp_rank, ctx.cp_size, dim=1)
+        x = self.embed(local_ids)
+        hidden = self.forward_layers(x, B, s_loc).view(B, s_loc, -1)
+        # position p predicts token p+1; the final padded position predicts nothing (target 0, masked below)
+        nxt = torch.nn.functional.pad(input_ids[:, 1:], (0, s_loc * ctx.cp_size - (S - 1)))
+        targets = nxt[:, ctx.cp_rank * s_loc:(ctx.cp_rank + 1) * s_loc]
+        lp_local = self.token_logprobs(hidden, targets)                       # [B, s_loc]
+        lp_full = all_gather_rows(lp_local.t().contiguous(), ctx.cp_group).t()  # [B, cp*s_loc]
+        R = S - prompt_len
+        return lp_full[:, prompt_len - 1: prompt_len - 1 + R]
 
     def forward_logits(self, input_ids: torch.Tensor) -> torch.Tensor:
         """Full fp32 logits ``[B, S, V]`` (debug / rollout sampling; the trainer never builds them)."""

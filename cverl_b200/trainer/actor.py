@@ -61,6 +61,11 @@ class ActorEngine:
         if n % mb:
             raise ValueError("batch size must be a multiple of the micro-batch size")
         num_micro = n // mb
+        ctx = getattr(self.model, "ctx", None)
+        cp = ctx.cp_size if ctx is not None else 1
+        # under context parallelism every rank evaluates the same loss on the gathered log-probs and
+        # back-propagates only its shard: 1/cp here makes the CP-summed gradient the true one
+        grad_scale = 1.0 / (num_micro * cp)
         total = torch.zeros(len(METRIC_NAMES), dtype=torch.float32, device=ids.device)
         for m in range(num_micro):
             sl = slice(m * mb, (m + 1) * mb)
@@ -68,7 +73,7 @@ class ActorEngine:
             mask = batch["response_mask"][sl]
             if cfg.mode == "sft":
                 denom = mask.sum() + rl.EPS
-                dlogp = (-mask / denom) * (1.0 / num_micro)
+                dlogp = (-mask / denom) * grad_scale
                 nll = -(lp.detach() * mask).sum() / denom
                 metrics = torch.stack([nll, nll.new_zeros(()), nll.new_zeros(()), nll.new_zeros(()),
                                        nll.new_zeros(()), mask.sum()])
@@ -83,13 +88,16 @@ class ActorEngine:
                                                clip_ratio_low=cfg.clip_ratio_low,
                                                clip_ratio_high=cfg.clip_ratio_high, clip_ratio_c=cfg.clip_ratio_c,
                                                agg=cfg.loss_agg, kl_coef=cfg.kl_coef,
-                                               kl_penalty_kind=cfg.kl_penalty, loss_scale=1.0 / num_micro)
+                                               kl_penalty_kind=cfg.kl_penalty, loss_scale=grad_scale)
             lp.backward(dlogp.to(lp.dtype))
             scale = torch.tensor([1.0 / num_micro] * 5 + [1.0], device=total.device)
             total += metrics.to(total.device) * scale
         self.fold_autograd_grads()
         if hasattr(self.model, "sync_replicated_grads"):
             self.model.sync_replicated_grads()
+        if cp > 1:
+            import torch.distributed as dist
+            dist.all_reduce(self.model.flat.main_grad, group=ctx.cp_group)
         self.optimizer.step()
         return torch.cat([total, self.optimizer.last_metrics.to(total.device)])
 
