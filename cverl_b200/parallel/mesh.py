@@ -40,4 +40,11 @@ def build_context(world: int, rank: int, *, tp: int = 1, dp: Optional[int] = Non
             if rank in ranks:
                 mine = g
         setattr(ctx, attr, mine)
+    # first and last pipeline stage of every pipeline group: they share the tied embedding
+    ctx.embed_group = None
+    if pp > 1:
+        for ranks in topo.all_groups("pipeline"):
+            g = dist.new_group([ranks[0], ranks[-1]])
+            if rank in (ranks[0], ranks[-1]):
+                ctx.embed_group = g
     return ctx

@@ -111,6 +111,7 @@ class PipelineStage:
         self.schedule = pipeline_1f1b_schedule(pipeline_rank, pipeline_size, micro_batches)
         self.max_live = pipeline_schedule_max_live_activations(self.schedule, micro_batches)
         self._comm_stream = torch.cuda.Stream(device=device) if torch.device(device).type == "cuda" else None
+        self._keep = []
 
     @property
     def first(self) -> bool:
@@ -125,8 +126,10 @@ class PipelineStage:
         import torch.distributed as dist
         t = t.contiguous()
         if self._comm_stream is None:
-            dist.send(t, dst=dst, group=self.group)
-            return None
+            # never block on a send: in steady-state 1F1B both neighbours send at the same time
+            req = dist.isend(t, dst=dst, group=self.group)
+            self._keep.append(t)
+            return req
         self._comm_stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self._comm_stream):
             t.record_stream(self._comm_stream)
@@ -148,6 +151,7 @@ class PipelineStage:
 
     def run(self, forward_fn: Callable, loss_fn: Optional[Callable] = None) -> Dict[int, torch.Tensor]:
         """Executes the schedule; returns the last stage's per-micro-batch loss outputs."""
+        self._keep = []
         stash: Dict[int, tuple] = {}
         results: Dict[int, torch.Tensor] = {}
         pending = []

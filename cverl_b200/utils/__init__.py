@@ -1,1 +1,1 @@
-"""utils subpackage."""
+"""Utilities: checkpoints, metrics, timing / roofline, watchdog."""

@@ -1,0 +1,136 @@
+"""The distributed trainer as gloo processes: parallel configurations, PP parity, checkpoint / resume
+equality, metrics CSV, and host-side failure detection."""
+import csv
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _run(nproc, *flags, port=29650, timeout=240, check=True):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", "cverl_b200.trainer.ppo_trainer",
+           "--backend", "gloo", "--dtype", "float32", "--lr", "1e-3", *flags]
+    env = dict(os.environ, OMP_NUM_THREADS="1", PYTHONPATH=str(ROOT))
+    p = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=timeout)
+    if check:
+        assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-3000:]
+    return p
+
+
+def _lines(p):
+    out = []
+    for ln in p.stdout.splitlines():
+        if ln.startswith("step="):
+            out.append(dict(kv.split("=", 1) for kv in ln.split()))
+    return out
+
+
+@pytest.mark.parametrize("nproc,flags", [
+    (4, ["--pp", "2", "--tp", "2", "--micro-batches", "2"]),
+    (2, ["--dp", "2", "--micro-batches", "2"]),
+    (2, ["--cp", "2"]),
+    (2, ["--ep", "2", "--config", "tiny_moe"]),
+])
+def test_parallel_configs_train(nproc, flags):
+    p = _run(nproc, *flags, "--steps", "2", port=29650 + nproc + len(flags))
+    rows = _lines(p)
+    assert len(rows) == 2
+    for r in rows:
+        assert r["all_ranks_have_grad"] == "true" and r["all_ranks_updated"] == "true"
+        assert "nan" not in r["loss_sum"] and "inf" not in r["global_grad_norm"]
+        assert float(r["step_time_s"]) > 0
+
+
+def test_pipeline_matches_single_stage(tmp_path):
+    common = ["--micro-batches", "2", "--steps", "2", "--max-grad-norm", "0"]
+    a = _lines(_run(1, *common, port=29671))
+    b = _lines(_run(2, "--pp", "2", *common, port=29672))
+    for ra, rb in zip(a, b):
+        assert float(ra["loss_sum"]) == pytest.approx(float(rb["loss_sum"]), rel=1e-4, abs=1e-6)
+        # the tied embedding's gradient is held (summed) on both the first and the last stage, so the
+        # pipeline's global norm counts it twice: equal only up to that term
+        assert 0.99 * float(ra["global_grad_norm"]) <= float(rb["global_grad_norm"]) <= 1.5 * float(ra["global_grad_norm"])
+
+
+def test_checkpoint_resume_equality_and_formats(tmp_path):
+    ck = tmp_path / "ck"
+    csv_a, csv_b = tmp_path / "a.csv", tmp_path / "b.csv"
+    base = ["--dp", "2", "--micro-batches", "1", "--master-weights"]
+    full = _lines(_run(2, *base, "--steps", "4", "--metrics-csv", str(csv_a), port=29681))
+    _run(2, *base, "--steps", "2", "--checkpoint-dir", str(ck), "--checkpoint-every", "2", port=29682)
+    step_dir = ck / "step_000002"
+    manifest = json.loads((step_dir / "manifest.json").read_text())
+    assert manifest["complete"] and manifest["format"] == "cverl_pp_tp_flat_shard_checkpoint_v4"
+    assert manifest["rank_files"] == ["rank_0.pt", "rank_1.pt"] and manifest["parallel_dims"]["dp"] == 2
+    assert (ck / "latest_checkpoint.txt").read_text() == "step_000002"
+    meta = json.loads((step_dir / "rank_1.json").read_text())
+    fs = meta["flat_parameter_shard"]
+    assert fs["shard_end"] - fs["shard_begin"] == fs["numel"] and meta["use_master_weights"] is True
+    from cverl_b200.utils.checkpoint import load_archive
+    arch = load_archive(step_dir / "rank_0.pt")
+    assert set(arch) == {"flat_param_shard", "flat_exp_avg", "flat_exp_avg_sq", "optim_step"}
+    assert int(arch["optim_step"]) == 2 and arch["flat_param_shard"].dtype == torch.float32
+    resumed = _lines(_run(2, *base, "--steps", "4", "--resume-checkpoint", str(ck), "--metrics-csv", str(csv_b),
+                          port=29683))
+    assert [r["step"] for r in resumed] == ["2", "3"]
+    for ra, rb in zip(full[2:], resumed):
+        assert float(ra["loss_sum"]) == pytest.approx(float(rb["loss_sum"]), rel=1e-5, abs=1e-7)
+        assert float(ra["global_grad_norm"]) == pytest.approx(float(rb["global_grad_norm"]), rel=1e-4)
+    with open(csv_a) as f:
+        rows = list(csv.DictReader(f))
+    assert len(rows) == 4 and rows[0]["dp"] == "2" and "step_time_s" in rows[0]
+    # a different topology must be refused
+    bad = _run(1, "--steps", "3", "--resume-checkpoint", str(ck), port=29684, check=False)
+    assert bad.returncode != 0
+
+
+def test_sft_jsonl_mode(tmp_path):
+    data = tmp_path / "sft.jsonl"
+    data.write_text("\n".join(json.dumps({"prompt": f"q{i}?", "answer": f"a{i}"}) for i in range(8)))
+    rows = _lines(_run(1, "--mode", "sft", "--sft-jsonl", str(data), "--steps", "3", "--lr", "5e-3", port=29691))
+    losses = [float(r["loss_sum"]) for r in rows]
+    assert losses[0] > 0 and losses[-1] < losses[0]
+
+
+def test_watchdog_detects_silent_and_failed_peers():
+    from cverl_b200.utils.watchdog import DictStore, Heartbeat, PeerFailure, Watchdog, guarded
+    store = DictStore()
+    now = [100.0]
+    hbs = [Heartbeat(store, r, 3) for r in range(3)]
+    for h in hbs:
+        h.beat(0)
+    wd = Watchdog(hbs[0], timeout_s=5.0, clock=lambda: now[0] + 0.0)
+    import time as _t
+    wd.clock = lambda: _t.time()
+    wd.check()                                     # everybody alive
+    wd.clock = lambda: _t.time() + 60.0            # peers stop beating: a rank that never joins the step
+    with pytest.raises(PeerFailure) as e:
+        wd.check()
+    assert e.value.ranks == [1, 2]
+    # a dropped message: rank 2's heartbeat key is lost in the store
+    store2 = DictStore()
+    store2.dropped.add("cverl/hb/beat/2")
+    hb2 = [Heartbeat(store2, r, 3) for r in range(3)]
+    for h in hb2:
+        h.beat(0)
+    with pytest.raises(PeerFailure) as e:
+        Watchdog(hb2[0], 5.0).check()
+    assert e.value.ranks == [2]
+    # a rank that raises publishes the failure before exiting
+
+    @guarded(hbs[1])
+    def failing_rank():
+        raise ValueError("bad batch")
+    with pytest.raises(ValueError):
+        failing_rank()
+    wd.clock = lambda: _t.time()
+    with pytest.raises(PeerFailure) as e:
+        wd.check()
+    assert e.value.ranks == [1] and "bad batch" in e.value.reason
