@@ -81,6 +81,8 @@ _CUDA_PROTOS = {
     "cvb_device_free": "p",
     "cvb_device_memset": "pilp",
     "cvb_can_access_peer": "ii",
+    "cvb_gdn_chunk_prep": "ppp l pp l ii ff pppppppp p p",
+    "cvb_gdn_chunk_out": "ppppp l ii p p",
     "cvb_gdn_scan_fwd": "pppppppp l i p p",
     "cvb_gdn_scan_bwd": "pppppppppp l i p p",
 }

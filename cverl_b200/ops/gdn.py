@@ -207,6 +207,13 @@ class _GdnChunked(torch.autograd.Function):
     def _forward(ctx, q, k, v, beta, g, S0, scale, chunk):
         B, T, H, dk = q.shape
         dv = v.shape[-1]
+        if q.is_cuda and chunk == 64:
+            from . import gdn_native
+            if gdn_native.chunk_supported(q, k, v):
+                o, Sf, Vn, SsT = gdn_native.chunk_forward(q, k, v, beta, g, S0, scale)
+                ctx.save_for_backward(q, k, v, beta, g, Vn, SsT.transpose(-1, -2))
+                ctx.cfg = (scale, chunk, 0, T // chunk, S0 is not None)
+                return o, Sf
         pad = (-T) % chunk
         n = (T + pad) // chunk
 

@@ -57,6 +57,71 @@ def scan_bwd(dVloc, Kdec, Qd, W, dO, egam, dSf):
     return dVn, dSnT.transpose(-1, -2), dS0
 
 
+def chunk_supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
+    """The chunk kernels read q/k/v in place: bf16 [B,T,H,128] views with unit inner stride, head stride
+    128, one common token stride and batch stride T * token stride; T a multiple of 64."""
+    if os.environ.get("CVERL_B200_GDN", "native") != "native" or os.environ.get("CVERL_B200_GDN_CHUNK", "1") != "1":
+        return False
+    if not (q.is_cuda and q.dtype == k.dtype == v.dtype == torch.bfloat16):
+        return False
+    B, T, H, D = q.shape
+    if D != 128 or v.shape[-1] != 128 or T % 64 != 0 or k.shape != q.shape or v.shape != q.shape:
+        return False
+    ts = q.stride(1)
+    for t in (q, k, v):
+        if t.stride(3) != 1 or t.stride(2) != 128 or t.stride(1) != ts or (B > 1 and t.stride(0) != T * ts):
+            return False
+        if t.data_ptr() % 16 or ts % 8:
+            return False
+    return True
+
+
+def chunk_prep(q, k, v, beta, g, scale: float, eps: float = 1e-6, want_aux: bool = False):
+    """Runs the chunk-local prep kernel. Returns dict(W, U, Kd, Qd [BH,n,64,128] bf16, P [BH,n,64,64] bf16,
+    egam [BH,n] fp32 and, when ``want_aux``, Tm [BH,n,64,64] and aux [BH,n,3,64] fp32)."""
+    B, T, H, _ = q.shape
+    n = T // 64
+    dev = q.device
+    mk = lambda *s, dt=torch.bfloat16: torch.empty(s, dtype=dt, device=dev)
+    out = dict(W=mk(B, H, n, 64, 128), U=mk(B, H, n, 64, 128), Kd=mk(B, H, n, 64, 128), Qd=mk(B, H, n, 64, 128),
+               P=mk(B, H, n, 64, 64), egam=mk(B, H, n, dt=torch.float32))
+    Tm = mk(B, H, n, 64, 64, dt=torch.float32) if want_aux else None
+    aux = mk(B, H, n, 3, 64, dt=torch.float32) if want_aux else None
+    bf, gf = beta.float().contiguous(), g.float().contiguous()
+    rc = nv.cuda().cvb_gdn_chunk_prep(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(1), bf.data_ptr(),
+                                      gf.data_ptr(), B, T, H, scale, eps, out["W"].data_ptr(), out["U"].data_ptr(),
+                                      out["Kd"].data_ptr(), out["Qd"].data_ptr(), out["P"].data_ptr(),
+                                      out["egam"].data_ptr(), nv.ptr(Tm), nv.ptr(aux),
+                                      nv.status_word(dev).data_ptr(), nv.stream())
+    nv.check(rc, "cvb_gdn_chunk_prep")
+    count_launch()
+    out["Tm"], out["aux"] = Tm, aux
+    return out
+
+
+def chunk_forward(q, k, v, beta, g, S0, scale: float):
+    """Full chunked forward on the three kernels. Returns (o [B,T,H,128] bf16, Sf fp32, Vn, SsT)."""
+    B, T, H, _ = q.shape
+    n = T // 64
+    dev = q.device
+    pre = chunk_prep(q, k, v, beta, g, scale)
+    s0 = S0.float().contiguous() if S0 is not None else None
+    Vn = torch.empty((B, H, n, 64, 128), dtype=torch.bfloat16, device=dev)
+    SsT = torch.empty((B, H, n, 128, 128), dtype=torch.bfloat16, device=dev)
+    Sf = torch.empty((B, H, 128, 128), dtype=torch.float32, device=dev)
+    lib = nv.cuda()
+    rc = lib.cvb_gdn_scan_fwd(pre["W"].data_ptr(), pre["U"].data_ptr(), pre["Kd"].data_ptr(), pre["egam"].data_ptr(),
+                              nv.ptr(s0), Sf.data_ptr(), Vn.data_ptr(), SsT.data_ptr(), B * H, n,
+                              nv.status_word(dev).data_ptr(), nv.stream())
+    nv.check(rc, "cvb_gdn_scan_fwd")
+    o = torch.empty((B, T, H, 128), dtype=torch.bfloat16, device=dev)
+    rc = lib.cvb_gdn_chunk_out(SsT.data_ptr(), pre["Qd"].data_ptr(), Vn.data_ptr(), pre["P"].data_ptr(), o.data_ptr(),
+                               B, T, H, nv.status_word(dev).data_ptr(), nv.stream())
+    nv.check(rc, "cvb_gdn_chunk_out")
+    count_launch(2)
+    return o, Sf, Vn, SsT
+
+
 def supported(q: torch.Tensor, v: torch.Tensor) -> bool:
     return False
 

@@ -212,3 +212,31 @@ def test_moe_model_gpu_matches_cpu():
     lc = cm.response_logprobs(ids, 16)
     assert (lg.cpu() - lc).abs().mean().item() < 0.03
     lg.sum().backward()
+
+
+def test_gdn_chunk_kernels_strided_inputs():
+    """Chunk prep / scan / output kernels on q, k, v read in place from one [B, T, 3*H*128] buffer."""
+    from cverl_b200.ops import gdn, gdn_native
+    torch.manual_seed(6)
+    B, T, H = 2, 256, 3
+    mixed = torch.randn(B, T, 3 * H * 128, device=_dev(), dtype=torch.bfloat16)
+    q, k, v = (m.reshape(B, T, H, 128) for m in mixed.split(H * 128, dim=-1))
+    assert gdn_native.chunk_supported(q, k, v)
+    beta = torch.sigmoid(torch.randn(B, T, H, device=_dev()))
+    g = -0.5 * torch.rand(B, T, H, device=_dev())
+    S0 = 0.1 * torch.randn(B, H, 128, 128, device=_dev())
+    scale = 128 ** -0.5
+    o, Sf, Vn, SsT = gdn_native.chunk_forward(q, k, v, beta, g, S0, scale)
+    qq, kk, vv = (t.float().cpu() for t in (q, k, v))
+    o_r, S_r = gdn.gdn_recurrent_ref((gdn.l2norm(qq) * scale).transpose(1, 2), gdn.l2norm(kk).transpose(1, 2),
+                                     vv.transpose(1, 2), beta.cpu().transpose(1, 2), g.cpu().transpose(1, 2), S0.cpu())
+    assert _rel_err(o.cpu(), o_r.transpose(1, 2)) < 2e-2
+    assert _rel_err(Sf.cpu(), S_r) < 2e-2
+    # the prep kernel against the PyTorch chunk-local algebra
+    pre = gdn_native.chunk_prep(q, k, v, beta, g, scale, want_aux=True)
+    blk = lambda x: x.float().transpose(1, 2).reshape(B, H, T // 64, 64, -1)
+    L = gdn._chunk_local(blk(q), blk(k), blk(v), beta.transpose(1, 2).reshape(B, H, T // 64, 64),
+                         g.transpose(1, 2).reshape(B, H, T // 64, 64), scale)
+    for name, ref in (("W", L["W"]), ("U", L["U"]), ("Kd", L["Kdec"]), ("Qd", L["Qd"]), ("P", L["P"]), ("Tm", L["T"])):
+        assert _rel_err(pre[name], ref) < 2e-2, name
+    assert _rel_err(pre["egam"], L["egam"]) < 1e-4
