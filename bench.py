@@ -99,7 +99,7 @@ class ClockSampler(threading.Thread):
 
 def reference_arm(args):
     """The reference is a CMake/LibTorch C++ project without Python packaging; the offline pip install
-    fails, so the reference arm reports itself unavailable (details in DESIGN.md)."""
+    fails, so the reference arm reports itself unavailable."""
     print(json.dumps({"impl": "reference",
                       "unavailable": "reference is a CMake C++ project with no setup.py/pyproject; offline pip "
                                      "install fails and its CMake needs pcre2.h, which this image lacks"}))

@@ -85,6 +85,10 @@ _CUDA_PROTOS = {
     "cvb_gdn_chunk_out": "ppppp l ii p p",
     "cvb_gdn_scan_fwd": "pppppppp l i p p",
     "cvb_gdn_scan_bwd": "pppppppppp l i p p",
+    "cvb_symm_barrier": "p iii p p",
+    "cvb_reduce_scatter_sumsq": "p ii ll f pp p",
+    "cvb_flat_adamw_allgather": "ppppp p ii ll fffff l p",
+    "cvb_broadcast_store": "pp i l p",
 }
 
 

@@ -176,7 +176,7 @@ class FlatParams:
     """
 
     def __init__(self, entries: Sequence[Tuple[str, Tuple[int, ...]]], dtype=torch.bfloat16, device="cpu",
-                 pad_multiple: int = 1, with_main_grad: bool = True, entry_align: int = 8):
+                 pad_multiple: int = 1, with_main_grad: bool = True, entry_align: int = 8, allocator=None):
         # Entries start on a 16-byte boundary (8 bf16 elements) so that vector loads and TMA can
         # address every tensor in place.  Every tensor of the shipped model shapes has a multiple
         # of 8 elements, for which this is exactly the gap-free concatenation of the reference.
@@ -191,8 +191,11 @@ class FlatParams:
             off += _align(n, entry_align) if entry_align > 1 else n
         self.numel = off
         self.padded_numel = _align(max(off, 1), pad_multiple)
-        self.flat = torch.zeros(self.padded_numel, dtype=dtype, device=device)
-        self.main_grad = torch.zeros(self.padded_numel, dtype=torch.float32, device=device) if with_main_grad else None
+        # ``allocator(numel, dtype) -> zeroed 1-D tensor`` places the buffers elsewhere, e.g. in
+        # peer-mapped memory for the symmetric-memory ZeRO path (parameters first, then gradients)
+        alloc = allocator or (lambda n, dt: torch.zeros(n, dtype=dt, device=device))
+        self.flat = alloc(self.padded_numel, dtype)
+        self.main_grad = alloc(self.padded_numel, torch.float32) if with_main_grad else None
         self.params: Dict[str, torch.nn.Parameter] = {}
         for name, shape in self.entries:
             self.params[name] = self._make_param(name, *self.offsets[name], shape)

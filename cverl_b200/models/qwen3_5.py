@@ -47,7 +47,7 @@ class Qwen35Model(torch.nn.Module):
     def __init__(self, cfg: Qwen35TextConfig, *, dtype=torch.bfloat16, device="cpu",
                  ctx: ParallelContext = SINGLE, layer_begin: int = 0, layer_end: Optional[int] = None,
                  first_stage: bool = True, last_stage: bool = True, pad_multiple: int = 1,
-                 with_main_grad: bool = True):
+                 with_main_grad: bool = True, flat_allocator=None):
         super().__init__()
         self.cfg = cfg
         self.ctx = ctx
@@ -68,7 +68,7 @@ class Qwen35Model(torch.nn.Module):
         self.spec_by_name: Dict[str, ParamSpec] = {s.name: s for s in self.specs}
         entries = self._flat_entries()
         self.flat = FlatParams(entries, dtype=dtype, device=device, pad_multiple=pad_multiple,
-                               with_main_grad=with_main_grad)
+                               with_main_grad=with_main_grad, allocator=flat_allocator)
         for name, p in self.flat.params.items():
             self.register_parameter(name.replace(".", "/"), p)
         self._build_fused_views()

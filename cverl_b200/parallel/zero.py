@@ -245,10 +245,11 @@ class FlatZeroOptimizer:
     def step(self) -> None:
         import torch.distributed as dist
         fp = self.fp
+        if self.dp_size > 1 and self.fused_comm is not None:
+            self._fused_step()
+            return
         if self.dp_size > 1:
-            if self.fused_comm is not None:
-                gshard = self.fused_comm.reduce_scatter_mean(fp.main_grad, self.grad_shard)
-            elif self.comm_dtype is not None and self.comm_dtype != torch.float32:
+            if self.comm_dtype is not None and self.comm_dtype != torch.float32:
                 src = fp.main_grad.to(self.comm_dtype)
                 out = torch.empty(self.shard_numel, dtype=self.comm_dtype, device=src.device)
                 dist.reduce_scatter_tensor(out, src, op=dist.ReduceOp.SUM, group=self.dp_group)
@@ -281,6 +282,23 @@ class FlatZeroOptimizer:
                 parts = [torch.empty_like(shard) for _ in range(self.dp_size)]
                 dist.all_gather(parts, shard.clone(), group=self.dp_group)
                 fp.flat.copy_(torch.cat(parts))
+
+    def _fused_step(self) -> None:
+        """Symmetric-memory step: the reduce-scatter pulls peers' gradients and produces the squared
+        norm in the same pass; the AdamW kernel's stores are the parameter all-gather.  The only
+        library collective left is the 1-float norm all-reduce."""
+        import torch.distributed as dist
+        fc = self.fused_comm
+        if fc.param_flat is not self.fp.flat or fc.grad_flat is not self.fp.main_grad:
+            raise RuntimeError("fused ZeRO path needs FlatParams allocated by FusedZeroComm.allocator")
+        local_sq = fc.reduce_scatter_mean_sumsq(self.grad_shard, self.begin).clone()
+        global_sq = local_sq
+        if self.norm_world > 1:
+            global_sq = local_sq.clone()
+            dist.all_reduce(global_sq, group=self.norm_group)
+        clip = optim_ops.clip_scale(global_sq, self.max_grad_norm)
+        fc.adamw_allgather(self.adam, self.grad_shard, clip if self.max_grad_norm > 0 else None, self.begin)
+        self.last_metrics = torch.cat([local_sq.reshape(1), global_sq.reshape(1), clip[:1]])
 
     def _gloo_reduce_scatter(self) -> None:
         import torch.distributed as dist

@@ -1,4 +1,4 @@
-"""Spawns gloo ranks on 127.0.0.1 for multi-process CPU tests."""
+"""Spawns ranks on 127.0.0.1: gloo for multi-process CPU tests, nccl (one GPU per rank) for GPU tests."""
 import os
 import socket
 import traceback
@@ -13,12 +13,16 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _entry(rank, world, port, fn, args, errq):
+def _entry(rank, world, port, fn, args, errq, backend):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     import torch.distributed as dist
     torch.set_num_threads(1)
     try:
-        dist.init_process_group("gloo", rank=rank, world_size=world)
+        if backend == "nccl":
+            torch.cuda.set_device(rank)
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        else:
+            dist.init_process_group("gloo", rank=rank, world_size=world)
         fn(rank, world, *args)
         dist.barrier()
         dist.destroy_process_group()
@@ -27,11 +31,11 @@ def _entry(rank, world, port, fn, args, errq):
         raise
 
 
-def run_ranks(fn, world: int, *args, timeout: float = 240.0):
+def run_ranks(fn, world: int, *args, timeout: float = 240.0, backend: str = "gloo"):
     ctx = mp.get_context("spawn")
     errq = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, errq)) for r in range(world)]
+    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, errq, backend)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:

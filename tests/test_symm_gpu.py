@@ -1,0 +1,141 @@
+"""Symmetric-memory kernels: one-GPU emulation (all "ranks" are buffers of one device; these kernels
+never wait on one another), the bounded barrier wait, and the real 2-GPU paths over NVLink."""
+import ctypes as C
+
+import pytest
+import torch
+
+from tests.dist_utils import run_ranks
+
+pytestmark = pytest.mark.gpu
+
+
+def _ptrs(tensors):
+    return (C.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+
+
+def test_reduce_scatter_sumsq_emulated():
+    from cverl_b200 import _native as nv
+    world, n_full = 4, 4 * 50_000
+    g = torch.Generator(device="cuda").manual_seed(0)
+    grads = [torch.randn(n_full, device="cuda", generator=g) for _ in range(world)]
+    shard = n_full // world
+    for rank in range(world):
+        out = torch.empty(shard, device="cuda")
+        sq = torch.zeros(1, device="cuda")
+        nv.check(nv.cuda().cvb_reduce_scatter_sumsq(_ptrs(grads), world, rank, rank * shard, shard, 1.0 / world,
+                                                    out.data_ptr(), sq.data_ptr(), nv.stream()), "rs")
+        ref = torch.stack([x[rank * shard:(rank + 1) * shard] for x in grads]).double().mean(0)
+        torch.testing.assert_close(out.double(), ref, rtol=1e-6, atol=1e-6)
+        assert abs(sq.item() - ref.pow(2).sum().item()) < 1e-4 * ref.pow(2).sum().item()
+
+
+@pytest.mark.parametrize("master", [True, False])
+def test_adamw_allgather_emulated(master):
+    from cverl_b200 import _native as nv
+    from cverl_b200.ops import optim as optim_ops
+    world, shard = 2, 40_000
+    g = torch.Generator(device="cuda").manual_seed(1)
+    full0 = torch.randn(world * shard, device="cuda", generator=g).bfloat16()
+    bufs = [full0.clone() for _ in range(world)]
+    ref_full = full0.clone()
+    clip = torch.tensor([0.5], device="cuda")
+    for rank in range(world):
+        sl = slice(rank * shard, (rank + 1) * shard)
+        grad = torch.randn(shard, device="cuda", generator=g)
+        m, v = torch.rand(shard, device="cuda", generator=g), torch.rand(shard, device="cuda", generator=g)
+        mst = full0[sl].float() if master else None
+        m2, v2 = m.clone(), v.clone()
+        mst2 = mst.clone() if master else None
+        optim_ops.flat_adamw_step(grad.clone(), mst2, ref_full[sl], m2, v2, clip=clip, grad_scale=1.0, lr=1e-2,
+                                  beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.01, step=3, zero_grad=False)
+        nv.check(nv.cuda().cvb_flat_adamw_allgather(grad.data_ptr(), nv.ptr(mst), m.data_ptr(), v.data_ptr(),
+                                                    clip.data_ptr(), _ptrs(bufs), world, rank, rank * shard, shard,
+                                                    1e-2, 0.9, 0.95, 1e-8, 0.01, 3, nv.stream()), "adam")
+        torch.testing.assert_close(m, m2)
+        torch.testing.assert_close(v, v2)
+        if master:
+            torch.testing.assert_close(mst, mst2)
+    for b in bufs:
+        torch.testing.assert_close(b.float(), ref_full.float(), rtol=8e-3, atol=1e-6)
+
+
+def test_broadcast_store_emulated():
+    from cverl_b200 import _native as nv
+    src = torch.randn(1 << 20, device="cuda").bfloat16()
+    dst = [torch.zeros_like(src) for _ in range(3)]
+    nv.check(nv.cuda().cvb_broadcast_store(src.data_ptr(), _ptrs(dst), 3, src.numel() * 2, nv.stream()), "bcast")
+    for d in dst:
+        assert torch.equal(d, src)
+
+
+def test_barrier_wait_runs_out_to_status():
+    """A flag that nothing sets: the wait gives up within its clock budget, the kernel returns and the
+    host reads the status word; the context stays usable."""
+    from cverl_b200 import _native as nv
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    other = torch.zeros(8, dtype=torch.int32, device="cuda")     # stands for a silent peer's flag array
+    st = nv.status_word()
+    st.zero_()
+    nv.check(nv.cuda().cvb_symm_barrier(_ptrs([flags, other]), 0, 2, 1, st.data_ptr(), nv.stream()), "barrier")
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="status 5"):
+        nv.check_status()
+    assert int(other[0].item()) == 1 and int(flags[0].item()) == 1 and int(flags[1].item()) == 0
+    assert int(st.item()) == 0                                     # cleared by the host read
+    x = torch.ones(4, device="cuda") * 2                           # context still works
+    assert float(x.sum().item()) == 8.0
+
+
+def _fused_zero_rank(rank, world):
+    import torch.distributed as dist
+    from cverl_b200 import _native as nv
+    from cverl_b200.models.params import FlatParams
+    from cverl_b200.optim.adamw import AdamWOptions
+    from cverl_b200.parallel.symm import FusedZeroComm, P2pBroadcaster, SymmetricHeap
+    from cverl_b200.parallel.zero import FlatZeroOptimizer
+    dev = torch.device("cuda", rank)
+    heap = SymmetricHeap(None, dev)
+    fc = FusedZeroComm(heap)
+    entries = [("a", (1000, 64)), ("b", (64,)), ("c", (333, 8))]
+    fused = FlatParams(entries, device=dev, pad_multiple=world * 8, allocator=fc.allocator)
+    plain = FlatParams(entries, device=dev, pad_multiple=world * 8)
+    g = torch.Generator(device=dev).manual_seed(5)
+    init = torch.randn(fused.padded_numel, device=dev, generator=g).bfloat16()
+    fused.flat.copy_(init)
+    plain.flat.copy_(init)
+    for use_master in (True,):
+        opts = AdamWOptions(lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.01, use_master_weights=use_master)
+        kw = dict(dp_group=None, dp_rank=rank, dp_size=world, norm_group=None, norm_world=world, max_grad_norm=1.0)
+        of = FlatZeroOptimizer(fused, opts, fused_comm=fc, **kw)
+        op = FlatZeroOptimizer(plain, opts, **kw)
+        gr = torch.Generator(device=dev).manual_seed(100 + rank)
+        for _ in range(3):
+            grad = torch.randn(fused.padded_numel, device=dev, generator=gr)
+            fused.main_grad.copy_(grad)
+            plain.main_grad.copy_(grad)
+            of.step()
+            op.step()
+            torch.cuda.synchronize()
+            nv.check_status()
+            torch.testing.assert_close(fused.flat.float(), plain.flat.float(), rtol=8e-3, atol=1e-6)
+            torch.testing.assert_close(of.last_metrics, op.last_metrics, rtol=1e-4, atol=1e-6)
+            assert float(fused.main_grad.abs().sum()) == 0.0
+    # weight push: rank 0 -> rank 1
+    bc = P2pBroadcaster(heap, 1 << 20)
+    mine = bc.tensor(1 << 19, torch.bfloat16)
+    if rank == 0:
+        src = torch.arange(1 << 19, device=dev).bfloat16()
+        bc.push(src, [1])
+    bc.sync()
+    torch.cuda.synchronize()
+    nv.check_status()
+    if rank == 1:
+        assert torch.equal(mine, torch.arange(1 << 19, device=dev).bfloat16())
+    dist.barrier()
+    heap.close()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_zero_and_push_two_gpus():
+    run_ranks(_fused_zero_rank, 2, backend="nccl", timeout=300)
