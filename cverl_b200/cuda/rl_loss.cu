@@ -372,3 +372,68 @@ extern "C" int cvb_ppo_loss(const float* old_lp, const float* lp, const float* a
   ppo_finalize_kernel<<<1, 32, 0, ST(stream)>>>(ws, metrics_out);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------- GRPO advantage without allocation -------------------
+// Same three kernels as cvb_grpo_advantage; the 2*rows floats of per-row scratch (row scores,
+// then per-row scalars) come from a fixed array in this library's device image, so neither the
+// caller nor this function allocates.  See rl_no_alloc.h for who needs that and for the rules.
+#include <cstdio>
+#include <mutex>
+
+#include "rl_no_alloc.h"
+
+namespace cvb {
+// 2 * CVB_GRPO_STATIC_MAX_ROWS floats = 128 KB, one instance per device that loads this module.
+static __device__ __align__(256) float g_grpo_static_scratch[2 * CVB_GRPO_STATIC_MAX_ROWS];
+
+constexpr int kMaxDevices = 64;
+static float* g_grpo_scratch_addr[kMaxDevices] = {};  // per-device address of the array, looked up once
+static std::mutex g_grpo_scratch_mutex;
+
+// Device address of the scratch array on the CURRENT device.  The look-up runs once per device,
+// under that device's context (the symbol has a different address on every device).
+static int grpo_static_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    std::fprintf(stderr, "cvb_grpo_advantage_static: no usable current device (%s)\n", cudaGetErrorString(e));
+    return CVB_ERR_STATIC_SCRATCH_SETUP;
+  }
+  std::lock_guard<std::mutex> lock(g_grpo_scratch_mutex);
+  if (!g_grpo_scratch_addr[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_grpo_static_scratch);
+    if (e != cudaSuccess || !p) {
+      std::fprintf(stderr, "cvb_grpo_advantage_static: cudaGetSymbolAddress failed on device %d: %s\n", dev,
+                   cudaGetErrorString(e));
+      return CVB_ERR_STATIC_SCRATCH_SETUP;
+    }
+    g_grpo_scratch_addr[dev] = p;
+  }
+  *out = g_grpo_scratch_addr[dev];
+  return 0;
+}
+}  // namespace cvb
+
+extern "C" int cvb_grpo_advantage_static(const float* rewards, const float* mask, const long long* gid, float eps,
+                                         int norm_by_std, float* adv, float* ret, long long rows, int cols,
+                                         void* stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (rows > CVB_GRPO_STATIC_MAX_ROWS) {
+    std::fprintf(stderr,
+                 "cvb_grpo_advantage_static: %lld rows exceed the fixed scratch of %d rows; use cvb_grpo_advantage "
+                 "with a caller-owned scratch buffer\n",
+                 rows, CVB_GRPO_STATIC_MAX_ROWS);
+    return CVB_ERR_STATIC_SCRATCH_LIMIT;
+  }
+  float* scratch = nullptr;
+  if (const int rc = grpo_static_scratch(&scratch)) return rc;
+  // scratch[0, rows): row scores; scratch[rows, 2*rows): per-row scalars.  Both ranges are fully
+  // written by the first two kernels before the next one reads them: no zeroing between calls.
+  const int warps_grid = static_cast<int>((rows * 32 + RL_THREADS - 1) / RL_THREADS);
+  row_sum_kernel<<<warps_grid, RL_THREADS, 0, ST(stream)>>>(rewards, scratch, rows, cols);
+  grpo_scalar_kernel<<<warps_grid, RL_THREADS, 0, ST(stream)>>>(scratch, gid, scratch + rows, rows, eps, norm_by_std);
+  grpo_broadcast_kernel<<<rl_grid(rows * cols), RL_THREADS, 0, ST(stream)>>>(scratch + rows, mask, adv, ret, rows,
+                                                                            cols);
+  return static_cast<int>(cudaGetLastError());
+}
