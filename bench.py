@@ -40,6 +40,8 @@ def parse_args():
     ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("CVERL_BENCH_MICRO_BATCH", "16")))
     ap.add_argument("--tp", type=int, default=int(os.environ.get("CVERL_BENCH_TP", "0")))
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
+    ap.add_argument("--zero-comm", default=os.environ.get("CVERL_BENCH_ZERO", "symm"), choices=["symm", "nccl"],
+                    help="ZeRO communication: symm = own kernels over peer-mapped memory, nccl = library collectives")
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (result marked invalid)")
     return ap.parse_args()
 
@@ -139,12 +141,17 @@ def main():
     cfg = Qwen35TextConfig.qwen3_5_0_8b()
     if args.layers:
         cfg = Qwen35TextConfig(num_hidden_layers=args.layers)
-    model = Qwen35Model(cfg, dtype=torch.bfloat16, device=dev, ctx=ctx, pad_multiple=dp * 8)
+    fused_comm = None
+    if dp > 1 and args.zero_comm == "symm":
+        from cverl_b200.parallel.symm import FusedZeroComm, SymmetricHeap
+        fused_comm = FusedZeroComm(SymmetricHeap(ctx.dp_group, dev))
+    model = Qwen35Model(cfg, dtype=torch.bfloat16, device=dev, ctx=ctx, pad_multiple=dp * 8,
+                        flat_allocator=fused_comm.allocator if fused_comm else None)
     model.init_weights(seed=1234)
     opt = FlatZeroOptimizer(model.flat, AdamWOptions(lr=1e-6, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.01,
                                                      use_master_weights=False),
                             dp_group=ctx.dp_group, dp_rank=ctx.dp_rank, dp_size=dp,
-                            norm_group=None, norm_world=world, max_grad_norm=1.0)
+                            norm_group=None, norm_world=world, max_grad_norm=1.0, fused_comm=fused_comm)
     engine = ActorEngine(model, opt, ActorConfig(mode="ppo", micro_batch_size=args.micro_batch))
 
     # each DP rank sees its own sequences; TP peers of one DP rank see the same ones
@@ -207,6 +214,7 @@ def main():
                        "prompt_len": PROMPT_LEN, "response_len": RESPONSE_LEN,
                        "parallelism": f"dp{dp}xtp{tp}", "micro_batch_seqs": args.micro_batch,
                        "optimizer": "FlatAdamW ZeRO-1 reduce-scatter, clip 1.0",
+                       "zero_comm": args.zero_comm if dp > 1 else "none",
                        "l2": "per-step working set (activations + 1.5 GB weights + 3 GB fp32 grads) exceeds the "
                              "126 MB L2, no explicit flush"},
             "clocks": sampler.summary(),

@@ -73,6 +73,9 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--kl-penalty", default="k1")
     g.add_argument("--advantage-scale", type=float, default=1.0)
     g.add_argument("--max-grad-norm", type=float, default=1.0)
+    g.add_argument("--zero-comm", default="nccl", choices=["nccl", "symm"],
+                   help="ZeRO gradient reduce-scatter / parameter all-gather: library collectives, or this "
+                        "package's kernels over peer-mapped memory (CUDA, bf16 parameters, same node)")
     g.add_argument("--master-weights", action="store_true")
     g.add_argument("--dp-grad-comm-dtype", default="float32")
     g.add_argument("--seed", type=int, default=1234)
@@ -230,8 +233,15 @@ def run(argv=None) -> int:
                                   "layer_types": cfg.layer_types[:args.max_layers]})
     lb, le = topo.pipeline_layer_range(cfg.num_hidden_layers, info.pipeline_rank)
     first, last = info.pipeline_rank == 0, info.pipeline_rank == args.pp - 1
+    fused_comm = None
+    if args.zero_comm == "symm" and args.dp > 1:
+        if not use_cuda or dtype != torch.bfloat16:
+            raise SystemExit("--zero-comm symm needs CUDA and --dtype bfloat16")
+        from ..parallel.symm import FusedZeroComm, SymmetricHeap
+        fused_comm = FusedZeroComm(SymmetricHeap(ctx.dp_group, device))
     model = Qwen35Model(cfg, dtype=dtype, device=device, ctx=ctx, layer_begin=lb, layer_end=le, first_stage=first,
-                        last_stage=last, pad_multiple=args.dp * 8)
+                        last_stage=last, pad_multiple=args.dp * 8,
+                        flat_allocator=fused_comm.allocator if fused_comm else None)
     if loader is not None:
         load_model_weights(model, loader)
     else:
@@ -241,7 +251,8 @@ def run(argv=None) -> int:
                                                      weight_decay=args.weight_decay,
                                                      use_master_weights=args.master_weights),
                             dp_group=ctx.dp_group, dp_rank=ctx.dp_rank, dp_size=args.dp, norm_group=None,
-                            norm_world=world, max_grad_norm=args.max_grad_norm, comm_dtype=comm_dtype)
+                            norm_world=world, max_grad_norm=args.max_grad_norm, comm_dtype=comm_dtype,
+                            fused_comm=fused_comm)
     ecfg = ActorConfig(mode=args.mode, micro_batch_size=args.micro_batch_seqs, clip_ratio=args.clip_ratio,
                        clip_ratio_c=args.clip_ratio_c, kl_coef=args.kl_coef, kl_penalty=args.kl_penalty,
                        advantage_scale=args.advantage_scale)
