@@ -211,9 +211,11 @@ class _GdnChunked(torch.autograd.Function):
             from . import gdn_native
             if gdn_native.chunk_supported(q, k, v):
                 o, Sf, Vn, SsT = gdn_native.chunk_forward(q, k, v, beta, g, S0, scale)
-                ctx.save_for_backward(q, k, v, beta, g, Vn, SsT.transpose(-1, -2))
+                ctx.save_for_backward(q, k, v, beta, g, Vn, SsT.transpose(-1, -2), Sf)
                 ctx.cfg = (scale, chunk, 0, T // chunk, S0 is not None)
+                ctx.native = True
                 return o, Sf
+        ctx.native = False
         pad = (-T) % chunk
         n = (T + pad) // chunk
 
@@ -236,8 +238,16 @@ class _GdnChunked(torch.autograd.Function):
 
     @staticmethod
     def _backward(ctx, do, dSf):
-        q, k, v, beta, g, Vn, Ss = ctx.saved_tensors
         scale, chunk, pad, n, has_s0 = ctx.cfg
+        if ctx.native:
+            q, k, v, beta, g, Vn, Ss, Sf = ctx.saved_tensors
+            from . import gdn_native
+            if gdn_native.chunk_bwd_enabled():
+                dq, dk, dv, dbeta, dg, dS0 = gdn_native.chunk_backward(q, k, v, beta, g, scale, Vn,
+                                                                       Ss.transpose(-1, -2), Sf, do, dSf)
+                return (dq, dk, dv, dbeta.to(beta.dtype), dg.to(g.dtype), (dS0 if has_s0 else None), None, None)
+        else:
+            q, k, v, beta, g, Vn, Ss = ctx.saved_tensors
         B, T, H, dk = q.shape
         dv = v.shape[-1]
 

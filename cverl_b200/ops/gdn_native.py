@@ -76,6 +76,10 @@ def chunk_supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
     return True
 
 
+def chunk_bwd_enabled() -> bool:
+    return os.environ.get("CVERL_B200_GDN_CHUNK_BWD", "1") == "1"
+
+
 def chunk_prep(q, k, v, beta, g, scale: float, eps: float = 1e-6, want_aux: bool = False):
     """Runs the chunk-local prep kernel. Returns dict(W, U, Kd, Qd [BH,n,64,128] bf16, P [BH,n,64,64] bf16,
     egam [BH,n] fp32 and, when ``want_aux``, Tm [BH,n,64,64] and aux [BH,n,3,64] fp32)."""
@@ -122,9 +126,37 @@ def chunk_forward(q, k, v, beta, g, S0, scale: float):
     return o, Sf, Vn, SsT
 
 
-def supported(q: torch.Tensor, v: torch.Tensor) -> bool:
-    return False
-
-
-def gated_delta_rule(q, k, v, beta, g, initial_state=None):  # pragma: no cover
-    raise NotImplementedError
+def chunk_backward(q, k, v, beta, g, scale: float, Vn, SsT, Sf, do, dSf):
+    """Backward of ``chunk_forward`` on the kernels: prep (recomputed), P^T dO, the reverse state scan and the
+    chunk-local backward.  Returns (dq, dk, dv [B,T,H,128] bf16, dbeta, dg [B,T,H] fp32, dS0 fp32)."""
+    B, T, H, _ = q.shape
+    n = T // 64
+    dev = q.device
+    lib = nv.cuda()
+    st = nv.status_word(dev).data_ptr()
+    pre = chunk_prep(q, k, v, beta, g, scale, want_aux=True)
+    do = do.to(torch.bfloat16).contiguous()
+    dOb = do.view(B, n, 64, H, 128).permute(0, 3, 1, 2, 4).contiguous()          # [B,H,n,64,128]
+    dVloc = torch.matmul(pre["P"].transpose(-1, -2), dOb)
+    dsf = dSf.float().contiguous() if dSf is not None else None
+    dVn = torch.empty((B, H, n, 64, 128), dtype=torch.bfloat16, device=dev)
+    dSnT = torch.empty((B, H, n, 128, 128), dtype=torch.bfloat16, device=dev)
+    dS0 = torch.empty((B, H, 128, 128), dtype=torch.float32, device=dev)
+    rc = lib.cvb_gdn_scan_bwd(dVloc.data_ptr(), pre["Kd"].data_ptr(), pre["Qd"].data_ptr(), pre["W"].data_ptr(),
+                              dOb.data_ptr(), pre["egam"].data_ptr(), nv.ptr(dsf), dS0.data_ptr(), dVn.data_ptr(),
+                              dSnT.data_ptr(), B * H, n, st, nv.stream())
+    nv.check(rc, "cvb_gdn_scan_bwd")
+    dq, dk, dv = (torch.empty((B, T, H, 128), dtype=torch.bfloat16, device=dev) for _ in range(3))
+    dbeta = torch.empty((B, T, H), dtype=torch.float32, device=dev)
+    dg = torch.empty((B, T, H), dtype=torch.float32, device=dev)
+    dgam = torch.empty((B, H, n), dtype=torch.float32, device=dev)
+    bf = beta.float().contiguous()
+    SsT, Vn, Sf = SsT.contiguous(), Vn.contiguous(), Sf.float().contiguous()
+    rc = lib.cvb_gdn_chunk_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(1), do.data_ptr(), bf.data_ptr(),
+                               pre["Tm"].data_ptr(), pre["aux"].data_ptr(), Vn.data_ptr(), dVn.data_ptr(),
+                               SsT.data_ptr(), dSnT.data_ptr(), Sf.data_ptr(), dgam.data_ptr(), B, T, H, scale,
+                               dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dbeta.data_ptr(), dg.data_ptr(), st,
+                               nv.stream())
+    nv.check(rc, "cvb_gdn_chunk_bwd")
+    count_launch(4)
+    return dq, dk, dv, dbeta, dg, dS0
