@@ -34,10 +34,20 @@ FORMAT_RANK_LOCAL = "cverl_pp_tp_rank_local_checkpoint_v2"
 
 
 class _Holder(torch.nn.Module):
+    """Buffers named by ``tensors``; a dotted name ``a.b`` becomes buffer ``b`` of sub-module ``a``, which
+    is how a nested archive is laid out."""
+
     def __init__(self, tensors: Dict[str, torch.Tensor]):
         super().__init__()
+        nested: Dict[str, Dict[str, torch.Tensor]] = {}
         for k, v in tensors.items():
-            self.register_buffer(k, v.detach().cpu().contiguous())
+            if "." in k:
+                head, rest = k.split(".", 1)
+                nested.setdefault(head, {})[rest] = v
+            else:
+                self.register_buffer(k, v.detach().cpu().contiguous())
+        for head, sub in nested.items():
+            self.add_module(head, _Holder(sub))
 
 
 def save_archive(path, tensors: Dict[str, torch.Tensor]) -> None:
