@@ -39,6 +39,7 @@ class GemmArgs(C.Structure):
         ("k_group_offsets", c_void_p), ("num_groups", C.c_int32), ("c_group_stride", C.c_int64),
         ("targets", c_void_p), ("part_max", c_void_p), ("part_sum", c_void_p), ("tgt_logit", c_void_p),
         ("lse", c_void_p), ("gscale", c_void_p), ("status", c_void_p),
+        ("mirror", c_void_p * 7), ("n_mirror", C.c_int32),
     ]
 
 

@@ -144,36 +144,59 @@ siggate_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
 // ------------------- depthwise causal conv1d (k=KW) + SiLU -----------------
 // x: [B, S, C] channels-last (row stride x_stride), w: [C, KW] bf16.
 //   pre[b,s,c] = sum_j w[c,j] * x[b, s-(KW-1)+j, c];  y = silu(pre)
+// One thread owns 8 channels and walks `seg_len` consecutive positions with the previous KW-1 inputs in
+// registers: one 16-byte load and one 16-byte store per output vector, weights read once per segment.
 template <int KW>
 __global__ void __launch_bounds__(EW_THREADS)
 conv1d_silu_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-                       __nv_bfloat16* __restrict__ y, long long B, int S, int C, long long x_stride) {
+                       __nv_bfloat16* __restrict__ y, long long B, int S, int C, long long x_stride, int seg_len) {
   const int vec_per_row = C / 8;
-  const long long total = B * S * vec_per_row;
+  const int segs = (S + seg_len - 1) / seg_len;
+  const long long total = B * segs * vec_per_row;
   for (long long i = static_cast<long long>(blockIdx.x) * EW_THREADS + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * EW_THREADS) {
-    const long long row = i / vec_per_row;  // b*S + s
-    const int s = static_cast<int>(row % S);
     const int c = static_cast<int>(i % vec_per_row) * 8;
+    const long long bs = i / vec_per_row;
+    const long long b = bs / segs;
+    const int s_begin = static_cast<int>(bs % segs) * seg_len;
+    const int s_end = min(S, s_begin + seg_len);
     float wv[8][KW];
 #pragma unroll
     for (int j = 0; j < 8; ++j)
 #pragma unroll
       for (int t = 0; t < KW; ++t) wv[j][t] = __bfloat162float(w[(c + j) * KW + t]);
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    float win[KW][8];  // win[k] = x[s - (KW-1) + k]
 #pragma unroll
-    for (int t = 0; t < KW; ++t) {
-      const int sp = s - (KW - 1) + t;
+    for (int k = 0; k < KW - 1; ++k) {
+      const int sp = s_begin - (KW - 1) + k;
       if (sp >= 0) {
-        V8 xv = ld8(x + (row - (KW - 1) + t) * x_stride + c);
+        const V8 xv = ld8(x + (b * S + sp) * x_stride + c);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] += wv[j][t] * xv.v[j];
+        for (int j = 0; j < 8; ++j) win[k + 1][j] = xv.v[j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) win[k + 1][j] = 0.f;
       }
     }
-    V8 o;
+    const __nv_bfloat16* xp = x + (b * S + s_begin) * x_stride + c;
+    __nv_bfloat16* yp = y + (b * S + s_begin) * C + c;
+    for (int s = s_begin; s < s_end; ++s, xp += x_stride, yp += C) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o.v[j] = acc[j] * sigm(acc[j]);
-    st8(y + row * C + c, o);
+      for (int k = 0; k < KW - 1; ++k)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) win[k][j] = win[k + 1][j];
+      const V8 xv = ld8(xp);
+      V8 o;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        win[KW - 1][j] = xv.v[j];
+        float acc = 0.f;
+#pragma unroll
+        for (int t = 0; t < KW; ++t) acc += wv[j][t] * win[t][j];
+        o.v[j] = acc * sigm(acc);
+      }
+      st8(yp, o);
+    }
   }
 }
 
@@ -389,13 +412,15 @@ extern "C" int cvb_conv1d_silu_fwd(const void* x, const void* w, void* y, long l
                                    long long x_stride, void* stream) {
   if (C % 8 || x_stride % 8 || cvb_misaligned({x, y})) return -1;
   if (B <= 0) return 0;
-  const int grid = ew_grid(B * S * (C / 8));
+  const int seg_len = 32;
+  const int segs = (S + seg_len - 1) / seg_len;
+  const int grid = ew_grid(B * segs * (C / 8));
   if (KW == 4)
-    conv1d_silu_fwd_kernel<4><<<grid, EW_THREADS, 0, ST(stream)>>>(BF(x), BF(w), BFM(y), B, S, C, x_stride);
+    conv1d_silu_fwd_kernel<4><<<grid, EW_THREADS, 0, ST(stream)>>>(BF(x), BF(w), BFM(y), B, S, C, x_stride, seg_len);
   else if (KW == 3)
-    conv1d_silu_fwd_kernel<3><<<grid, EW_THREADS, 0, ST(stream)>>>(BF(x), BF(w), BFM(y), B, S, C, x_stride);
+    conv1d_silu_fwd_kernel<3><<<grid, EW_THREADS, 0, ST(stream)>>>(BF(x), BF(w), BFM(y), B, S, C, x_stride, seg_len);
   else if (KW == 2)
-    conv1d_silu_fwd_kernel<2><<<grid, EW_THREADS, 0, ST(stream)>>>(BF(x), BF(w), BFM(y), B, S, C, x_stride);
+    conv1d_silu_fwd_kernel<2><<<grid, EW_THREADS, 0, ST(stream)>>>(BF(x), BF(w), BFM(y), B, S, C, x_stride, seg_len);
   else
     return -1;
   return static_cast<int>(cudaGetLastError());

@@ -4,7 +4,7 @@
 // sequential passes over the chunks of a sequence (C = 64 tokens, dk = dv = 128):
 //
 //   forward   Vn_i = U_i - W_i S_i ;            S_{i+1} = e^{g_i} S_i + Kd_i^T Vn_i
-//   backward  dVn_i = dVl_i + Kd_i dS ;         dS <- e^{g_i} dS + Qd_i^T dO_i - W_i^T dVn_i
+//   backward  dVn_i = P_i^T dO_i + Kd_i dS ;    dS <- e^{g_i} dS + Qd_i^T dO_i - W_i^T dVn_i
 //
 // One CTA owns one (batch, head) sequence.  The fp32 state is kept TRANSPOSED
 // in tensor memory, S^T [dv = 128 lanes x dk = 128 columns], so that every
@@ -48,9 +48,14 @@ struct ScanSmem {
   static constexpr int T1 = T0 + 16384;          // tile 1 (Kd fwd / Qd bwd)
   static constexpr int T2 = T1 + 16384;          // tile 2 (U fwd / W bwd)
   static constexpr int A2 = T2 + 16384;          // Vn^T (fwd) or -dVn^T (bwd), K-major A, 16 KB
-  static constexpr int A3 = A2 + 16384;          // dO^T (bwd only)
-  static constexpr int BARS_FWD = A3;            // forward does not use A3
-  static constexpr int BARS_BWD = A3 + 16384;
+  static constexpr int BARS_FWD = A2 + 16384;
+  // backward: the -dVn^T operand reuses the Kd tile (dead after MMA 1), which keeps two CTAs per SM
+  static constexpr int B_KD = 32768;             // Kd, then -dVn^T
+  static constexpr int B_QD = B_KD + 16384;
+  static constexpr int B_W = B_QD + 16384;
+  static constexpr int B_DO = B_W + 16384;       // dO tile, read MN-major as dO^T
+  static constexpr int B_P = B_DO + 16384;       // P tile [64 x 64], 8 KB
+  static constexpr int BARS_BWD = B_P + 8192;
   static constexpr int BYTES_FWD = BARS_FWD + 128 + 1024;
   static constexpr int BYTES_BWD = BARS_BWD + 128 + 1024;
 };
@@ -62,8 +67,6 @@ struct ScanArgs {
   float* s_final;             // [BH, dk, dv] fp32
   __nv_bfloat16* out_v;       // Vn / dVn  [BH, n, C, dv]
   __nv_bfloat16* out_s;       // per-chunk state (transposed) [BH, n, dv, dk]
-  const __nv_bfloat16* dvloc; // bwd: [BH, n, C, dv]
-  const __nv_bfloat16* dout;  // bwd: dO [BH, n, C, dv]
   int* status;
 };
 
@@ -282,13 +285,14 @@ gdn_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 // ---------------------------------------------------------------------------
 // backward scan (chunks in descending order)
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(GTHREADS, 1)
+__global__ void __launch_bounds__(GTHREADS, 2)
 gdn_scan_bwd_kernel(const __grid_constant__ CUtensorMap tmKd, const __grid_constant__ CUtensorMap tmQd,
-                    const __grid_constant__ CUtensorMap tmW, const ScanArgs a) {
+                    const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmDO,
+                    const __grid_constant__ CUtensorMap tmP, const ScanArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ScanSmem::BARS_BWD);
-  uint64_t *bar_kd = bars, *bar_qd = bars + 1, *bar_w = bars + 2, *bar_m1 = bars + 3, *bar_m2 = bars + 4;
+  uint64_t *bar_a = bars, *bar_b = bars + 1, *bar_m1 = bars + 2, *bar_m2 = bars + 3;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int v = threadIdx.x;
@@ -297,10 +301,9 @@ gdn_scan_bwd_kernel(const __grid_constant__ CUtensorMap tmKd, const __grid_const
   const int n = a.n_chunks;
 
   if (v == 0) {
-    mbar_init(bar_kd, 1); mbar_init(bar_qd, 1); mbar_init(bar_w, 1); mbar_init(bar_m1, 1); mbar_init(bar_m2, 1);
+    mbar_init(bar_a, 1); mbar_init(bar_b, 1); mbar_init(bar_m1, 1); mbar_init(bar_m2, 1);
     *abort_flag = 0;
     mbar_fence_init();
-    tma_prefetch_desc(&tmKd); tma_prefetch_desc(&tmQd); tma_prefetch_desc(&tmW);
   }
   if (warp == 0) {
     __syncwarp();
@@ -314,19 +317,29 @@ gdn_scan_bwd_kernel(const __grid_constant__ CUtensorMap tmKd, const __grid_const
   const uint32_t t_d1 = tmem;
   const uint32_t t_state = tmem + 128;
   uint8_t* s_op = smem + ScanSmem::S_OP;
-  uint8_t* s_kd = smem + ScanSmem::T0;
-  uint8_t* s_qd = smem + ScanSmem::T1;
-  uint8_t* s_w = smem + ScanSmem::T2;
-  uint8_t* s_a2 = smem + ScanSmem::A2;
-  uint8_t* s_a3 = smem + ScanSmem::A3;
+  uint8_t* s_kd = smem + ScanSmem::B_KD;   // also -dVn^T
+  uint8_t* s_qd = smem + ScanSmem::B_QD;
+  uint8_t* s_w = smem + ScanSmem::B_W;
+  uint8_t* s_do = smem + ScanSmem::B_DO;
+  uint8_t* s_p = smem + ScanSmem::B_P;
   const long long row_base = bh * n * GC;
 
-  if (v == 0 && n > 0) {
-    const int r0 = static_cast<int>(row_base + (n - 1) * GC);
-    load_tile(s_kd, &tmKd, bar_kd, r0);
-    load_tile(s_qd, &tmQd, bar_qd, r0);
-    load_tile(s_w, &tmW, bar_w, r0);
-  }
+  // all five tiles of one chunk: {Kd, dO, P} complete bar_a, {Qd, W} complete bar_b
+  auto load_chunk = [&](int i) {
+    const int r0 = static_cast<int>(row_base + static_cast<long long>(i) * GC);
+    mbar_arrive_expect_tx(bar_a, 16384 + 16384 + 8192);
+    tma_load_2d(s_kd, &tmKd, bar_a, 0, r0);
+    tma_load_2d(s_kd + 8192, &tmKd, bar_a, 64, r0);
+    tma_load_2d(s_do, &tmDO, bar_a, 0, r0);
+    tma_load_2d(s_do + 8192, &tmDO, bar_a, 64, r0);
+    tma_load_2d(s_p, &tmP, bar_a, 0, r0);
+    mbar_arrive_expect_tx(bar_b, 32768);
+    tma_load_2d(s_qd, &tmQd, bar_b, 0, r0);
+    tma_load_2d(s_qd + 8192, &tmQd, bar_b, 64, r0);
+    tma_load_2d(s_w, &tmW, bar_b, 0, r0);
+    tma_load_2d(s_w + 8192, &tmW, bar_b, 64, r0);
+  };
+  if (v == 0 && n > 0) load_chunk(n - 1);
   // dS^T[v][k] = s_init[k][v]  (gradient of the final state, or zero)
 #pragma unroll 1
   for (int c0 = 0; c0 < GD; c0 += 32) {
@@ -348,11 +361,16 @@ gdn_scan_bwd_kernel(const __grid_constant__ CUtensorMap tmKd, const __grid_const
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    // 2. D1 = dS^T Kd^T
+    // 2. D1 = dS^T Kd^T + dO^T P   (= dVn^T; dO^T is the dO tile read MN-major, P^T dO never leaves the SM)
     if (v == 0) {
-      if (mbar_wait_bounded(bar_kd, phase, abort_flag)) {
+      if (mbar_wait_bounded(bar_a, phase, abort_flag)) {
         tc_fence_after();
         issue_mma_state_times_tile(t_d1, smem_u32(s_op), smem_u32(s_kd));
+        constexpr uint32_t idesc = umma_idesc(128, GC, 1, 1, 1);
+#pragma unroll
+        for (int k = 0; k < GC / 16; ++k)
+          umma_bf16(t_d1, umma_smem_desc(smem_u32(s_do) + k * 2048, 8192, 1024),
+                    umma_smem_desc(smem_u32(s_p) + k * 2048, 8192, 1024), idesc, 1u);
         umma_commit(bar_m1);
       } else {
         SCAN_FAIL(ERR_WAIT_FULL);
@@ -362,34 +380,25 @@ gdn_scan_bwd_kernel(const __grid_constant__ CUtensorMap tmKd, const __grid_const
     __syncthreads();
     if (*abort_flag) { ok = false; break; }
     tc_fence_after();
-    if (v == 0 && i > 0) load_tile(s_kd, &tmKd, bar_kd, static_cast<int>(row_base + (i - 1) * GC));
-    // 3. dVn^T = dVl^T + D1 ; A2 = -dVn^T ; A3 = dO^T
-    const long long tile_off = (bh * n + i) * GC * GD + v;
-    __nv_bfloat16* g_v = a.out_v + tile_off;
-    const __nv_bfloat16* g_l = a.dvloc + tile_off;
-    const __nv_bfloat16* g_o = a.dout + tile_off;
+    // 3. store dVn; A2 = -dVn^T over the (now dead) Kd tile
+    __nv_bfloat16* g_v = a.out_v + (bh * n + i) * GC * GD + v;
 #pragma unroll 1
     for (int c0 = 0; c0 < GC; c0 += 32) {
       uint32_t r[32];
       tmem_ld_32x32(t_d1 + c0, r);
       tmem_ld_wait();
-      uint32_t p2[16], p3[16];
+      uint32_t p2[16];
 #pragma unroll
       for (int j = 0; j < 32; j += 2) {
-        const float x0 = __bfloat162float(g_l[(c0 + j) * GD]) + __uint_as_float(r[j]);
-        const float x1 = __bfloat162float(g_l[(c0 + j + 1) * GD]) + __uint_as_float(r[j + 1]);
+        const float x0 = __uint_as_float(r[j]), x1 = __uint_as_float(r[j + 1]);
         g_v[(c0 + j) * GD] = __float2bfloat16_rn(x0);
         g_v[(c0 + j + 1) * GD] = __float2bfloat16_rn(x1);
         p2[j >> 1] = pack_bf16x2(-x0, -x1);
-        const __nv_bfloat162 o2 = __halves2bfloat162(g_o[(c0 + j) * GD], g_o[(c0 + j + 1) * GD]);
-        p3[j >> 1] = *reinterpret_cast<const uint32_t*>(&o2);
       }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint32_t off = sw128(v, (c0 >> 3) + j);
-        *reinterpret_cast<uint4*>(s_a2 + off) = make_uint4(p2[4 * j], p2[4 * j + 1], p2[4 * j + 2], p2[4 * j + 3]);
-        *reinterpret_cast<uint4*>(s_a3 + off) = make_uint4(p3[4 * j], p3[4 * j + 1], p3[4 * j + 2], p3[4 * j + 3]);
-      }
+      for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<uint4*>(s_kd + sw128(v, (c0 >> 3) + j)) =
+            make_uint4(p2[4 * j], p2[4 * j + 1], p2[4 * j + 2], p2[4 * j + 3]);
     }
     fence_proxy_async_smem();
     tc_fence_before();
@@ -397,10 +406,14 @@ gdn_scan_bwd_kernel(const __grid_constant__ CUtensorMap tmKd, const __grid_const
     tc_fence_after();
     // 4. dS^T += dO^T Qd - dVn^T W
     if (v == 0) {
-      if (mbar_wait_bounded(bar_qd, phase, abort_flag) && mbar_wait_bounded(bar_w, phase, abort_flag)) {
+      if (mbar_wait_bounded(bar_b, phase, abort_flag)) {
         tc_fence_after();
-        issue_mma_update(t_state, smem_u32(s_a3), smem_u32(s_qd));
-        issue_mma_update(t_state, smem_u32(s_a2), smem_u32(s_w));
+        constexpr uint32_t idesc = umma_idesc(128, GD, 1, 1, 1);
+#pragma unroll
+        for (int k = 0; k < GC / 16; ++k)
+          umma_bf16(t_state, umma_smem_desc(smem_u32(s_do) + k * 2048, 8192, 1024),
+                    umma_smem_desc(smem_u32(s_qd) + k * 2048, 8192, 1024), idesc, 1u);
+        issue_mma_update(t_state, smem_u32(s_kd), smem_u32(s_w));
         umma_commit(bar_m2);
       } else {
         SCAN_FAIL(ERR_WAIT_FULL);
@@ -410,18 +423,13 @@ gdn_scan_bwd_kernel(const __grid_constant__ CUtensorMap tmKd, const __grid_const
     __syncthreads();
     if (*abort_flag) { ok = false; break; }
     tc_fence_after();
-    if (v == 0 && i > 0) {
-      const int r0 = static_cast<int>(row_base + (i - 1) * GC);
-      load_tile(s_qd, &tmQd, bar_qd, r0);
-      load_tile(s_w, &tmW, bar_w, r0);
-    }
+    if (v == 0 && i > 0) load_chunk(i - 1);
     phase ^= 1;
   }
   if (!ok && v == 0) {  // leave no copy in flight
     int dummy = 0;
-    mbar_wait_bounded(bar_kd, phase, &dummy);
-    mbar_wait_bounded(bar_qd, phase, &dummy);
-    mbar_wait_bounded(bar_w, phase, &dummy);
+    mbar_wait_bounded(bar_a, phase, &dummy);
+    mbar_wait_bounded(bar_b, phase, &dummy);
   }
   if (ok) {
 #pragma unroll 1
@@ -474,20 +482,23 @@ extern "C" int cvb_gdn_scan_fwd(const void* W, const void* U, const void* Kd, co
   return static_cast<int>(cudaGetLastError());
 }
 
-// dVloc, dO, Kd, Qd, W: [BH, n, 64, 128] bf16.  ds_final (may be null) / ds_init_out: [BH, 128, 128] fp32.
-// out_dv: dVn.  out_ds: dS_{i+1} per chunk, transposed [BH, n, dv, dk] bf16.
-extern "C" int cvb_gdn_scan_bwd(const void* dVloc, const void* Kd, const void* Qd, const void* W, const void* dO,
+// P: [BH, n, 64, 64] bf16 (the chunk's decayed, masked Q K^T); dO, Kd, Qd, W: [BH, n, 64, 128] bf16.
+// ds_final (may be null) / ds_init_out: [BH, 128, 128] fp32.
+// out_dv: dVn = P^T dO + Kd dS.  out_ds: dS_{i+1} per chunk, transposed [BH, n, dv, dk] bf16.
+extern "C" int cvb_gdn_scan_bwd(const void* P, const void* Kd, const void* Qd, const void* W, const void* dO,
                                 const float* egam, const float* ds_final, float* ds_init_out, void* out_dv,
                                 void* out_ds, long long BH, int n_chunks, int* status, void* stream) {
   if (BH <= 0 || n_chunks <= 0) return 0;
   if (BH * n_chunks * GC > 0x7fffffffLL) return -2;
-  CUtensorMap mK, mQ, mW;
+  CUtensorMap mK, mQ, mW, mO, mP;
   const long long rows = BH * n_chunks * GC;
-  if (make_rows128_map(&mK, Kd, rows) || make_rows128_map(&mQ, Qd, rows) || make_rows128_map(&mW, W, rows)) return -10;
+  if (make_rows128_map(&mK, Kd, rows) || make_rows128_map(&mQ, Qd, rows) || make_rows128_map(&mW, W, rows) ||
+      make_rows128_map(&mO, dO, rows) ||
+      make_tensor_map_2d(&mP, P, 2, GC, static_cast<uint64_t>(rows), GC * 2, 64, 64))
+    return -10;
   ScanArgs a{};
   a.n_chunks = n_chunks; a.egam = egam; a.s_init = ds_final; a.s_final = ds_init_out;
   a.out_v = static_cast<__nv_bfloat16*>(out_dv); a.out_s = static_cast<__nv_bfloat16*>(out_ds);
-  a.dvloc = static_cast<const __nv_bfloat16*>(dVloc); a.dout = static_cast<const __nv_bfloat16*>(dO);
   a.status = status;
   static bool attr = false;
   if (!attr) {
@@ -497,6 +508,6 @@ extern "C" int cvb_gdn_scan_bwd(const void* dVloc, const void* Kd, const void* Q
     attr = true;
   }
   gdn_scan_bwd_kernel<<<static_cast<int>(BH), GTHREADS, ScanSmem::BYTES_BWD, static_cast<cudaStream_t>(stream)>>>(
-      mK, mQ, mW, a);
+      mK, mQ, mW, mO, mP, a);
   return static_cast<int>(cudaGetLastError());
 }

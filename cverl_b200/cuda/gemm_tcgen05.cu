@@ -296,6 +296,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               o.z = pack_bf16x2(v[g8 * 8 + 4], v[g8 * 8 + 5]);
               o.w = pack_bf16x2(v[g8 * 8 + 6], v[g8 * 8 + 7]);
               *reinterpret_cast<uint4*>(dst + g8 * 8) = o;
+#pragma unroll 1
+              for (int m = 0; m < p.n_mirror; ++m)
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.mirror[m]) + (dst - reinterpret_cast<__nv_bfloat16*>(p.C)) + g8 * 8) = o;
             }
           }
         } else if (p.epi == EPI_STORE_F32) {
@@ -491,6 +494,12 @@ extern "C" int cvb_gemm_bf16(const CvbGemmArgs* a, void* stream_v) {
   p.lse = a->lse;
   p.gscale = a->gscale;
   p.status = a->status;
+  if (a->n_mirror < 0 || a->n_mirror > 7 || (a->n_mirror > 0 && a->epi != EPI_STORE_BF16)) return -6;
+  p.n_mirror = a->n_mirror;
+  for (int m = 0; m < a->n_mirror; ++m) {
+    if (!a->mirror[m] || (reinterpret_cast<uintptr_t>(a->mirror[m]) & 15)) return -6;
+    p.mirror[m] = a->mirror[m];
+  }
   const int sms = num_sms();
   int split = a->split_k;
   const int mn_tiles = p.m_tiles * p.n_tiles;

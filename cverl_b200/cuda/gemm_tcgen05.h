@@ -47,6 +47,10 @@ typedef struct CvbGemmArgs {
   const float* lse;        // [M]
   const float* gscale;     // [M]
   int32_t* status;         // device status word (0 = OK), required
+  // EPI_STORE_BF16 only: the same tile is also stored at the same offsets into these buffers, e.g. peer
+  // GPUs' mapped copies of C (plain stores over NVLink from the epilogue warps, tile by tile)
+  void* mirror[7];
+  int32_t n_mirror;
 } CvbGemmArgs;
 
 // Launches on `stream` (a cudaStream_t).  Returns 0 or a negative/CUDA error.
@@ -77,6 +81,8 @@ struct GemmParams {
   const float* lse;
   const float* gscale;
   int* status;
+  void* mirror[7];
+  int n_mirror;
 };
 int make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
                        uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);

@@ -168,12 +168,12 @@ def _scan_fwd(W, U, Kdec, egam, S0):
     return scan_fwd_ref(W, U, Kdec, egam, S0)
 
 
-def _scan_bwd(dVloc, Kdec, Qd, W, dO, egam, dSf):
+def _scan_bwd(P, Kdec, Qd, W, dO, egam, dSf):
     if W.is_cuda:
         from . import gdn_native
         if gdn_native.scan_supported(W, dO):
-            return gdn_native.scan_bwd(dVloc, Kdec, Qd, W, dO, egam, dSf)
-    return scan_bwd_ref(dVloc, Kdec, Qd, W, dO, egam, dSf)
+            return gdn_native.scan_bwd(P, Kdec, Qd, W, dO, egam, dSf)
+    return scan_bwd_ref(P.transpose(-1, -2) @ dO, Kdec, Qd, W, dO, egam, dSf)
 
 
 class _tf32_matmul:
@@ -210,10 +210,16 @@ class _GdnChunked(torch.autograd.Function):
         if q.is_cuda and chunk == 64:
             from . import gdn_native
             if gdn_native.chunk_supported(q, k, v):
-                o, Sf, Vn, SsT = gdn_native.chunk_forward(q, k, v, beta, g, S0, scale)
-                ctx.save_for_backward(q, k, v, beta, g, Vn, SsT.transpose(-1, -2), Sf)
+                keep = gdn_native.chunk_bwd_enabled() and any(ctx.needs_input_grad[:6])
+                o, Sf, Vn, SsT, pre = gdn_native.chunk_forward(q, k, v, beta, g, S0, scale, keep_prep=keep)
                 ctx.cfg = (scale, chunk, 0, T // chunk, S0 is not None)
                 ctx.native = True
+                ctx.keep = keep
+                if keep:   # the backward kernels reuse the chunk-local operands instead of recomputing them
+                    ctx.save_for_backward(q, k, v, beta, g, Vn, SsT.transpose(-1, -2), Sf, pre["W"], pre["Kd"],
+                                          pre["Qd"], pre["P"], pre["egam"], pre["Tm"], pre["aux"])
+                else:
+                    ctx.save_for_backward(q, k, v, beta, g, Vn, SsT.transpose(-1, -2), Sf)
                 return o, Sf
         ctx.native = False
         pad = (-T) % chunk
@@ -239,13 +245,15 @@ class _GdnChunked(torch.autograd.Function):
     @staticmethod
     def _backward(ctx, do, dSf):
         scale, chunk, pad, n, has_s0 = ctx.cfg
+        if ctx.native and ctx.keep:
+            q, k, v, beta, g, Vn, Ss, Sf, W_, Kd_, Qd_, P_, eg_, Tm_, aux_ = ctx.saved_tensors
+            from . import gdn_native
+            pre = dict(W=W_, Kd=Kd_, Qd=Qd_, P=P_, egam=eg_, Tm=Tm_, aux=aux_)
+            dq, dk, dv, dbeta, dg, dS0 = gdn_native.chunk_backward(q, k, v, beta, scale, pre, Vn,
+                                                                   Ss.transpose(-1, -2), Sf, do, dSf)
+            return (dq, dk, dv, dbeta.to(beta.dtype), dg.to(g.dtype), (dS0 if has_s0 else None), None, None)
         if ctx.native:
             q, k, v, beta, g, Vn, Ss, Sf = ctx.saved_tensors
-            from . import gdn_native
-            if gdn_native.chunk_bwd_enabled():
-                dq, dk, dv, dbeta, dg, dS0 = gdn_native.chunk_backward(q, k, v, beta, g, scale, Vn,
-                                                                       Ss.transpose(-1, -2), Sf, do, dSf)
-                return (dq, dk, dv, dbeta.to(beta.dtype), dg.to(g.dtype), (dS0 if has_s0 else None), None, None)
         else:
             q, k, v, beta, g, Vn, Ss = ctx.saved_tensors
         B, T, H, dk = q.shape
@@ -264,8 +272,7 @@ class _GdnChunked(torch.autograd.Function):
         dSf = dSf.float() if dSf is not None else Ss.new_zeros(B, H, dk, dv)
         Vn, Ss = Vn.float(), Ss.float()
         kn, qn, c, decay, Tm = L["kn"], L["qn"], L["c"], L["decay"], L["T"]
-        dVloc = L["P"].transpose(-1, -2) @ dO
-        dVn, dSn, dS0 = _scan_bwd(dVloc, L["Kdec"], L["Qd"], L["W"], dO, L["egam"], dSf)
+        dVn, dSn, dS0 = _scan_bwd(L["P"], L["Kdec"], L["Qd"], L["W"], dO, L["egam"], dSf)
         dVn, dSn = dVn.float(), dSn.float()
         # ---- chunk-local gradients -------------------------------------------------
         dW = -(dVn @ Ss.transpose(-1, -2))

@@ -40,16 +40,17 @@ def scan_fwd(W, U, Kdec, egam, S0):
     return Vn, SsT.transpose(-1, -2), Sf
 
 
-def scan_bwd(dVloc, Kdec, Qd, W, dO, egam, dSf):
+def scan_bwd(P, Kdec, Qd, W, dO, egam, dSf):
+    """Reverse state scan; ``P^T dO`` is formed inside.  Returns (dVn, dS_next per chunk, dS0)."""
     B, H, n = W.shape[:3]
     dev = W.device
-    dVl, Kb, Qb, Wb, dOb = _bf(dVloc), _bf(Kdec), _bf(Qd), _bf(W), _bf(dO)
+    Pb, Kb, Qb, Wb, dOb = _bf(P), _bf(Kdec), _bf(Qd), _bf(W), _bf(dO)
     eg = egam.float().contiguous()
     dsf = dSf.float().contiguous() if dSf is not None else None
     dVn = torch.empty((B, H, n, 64, 128), dtype=torch.bfloat16, device=dev)
     dSnT = torch.empty((B, H, n, 128, 128), dtype=torch.bfloat16, device=dev)
     dS0 = torch.empty((B, H, 128, 128), dtype=torch.float32, device=dev)
-    rc = nv.cuda().cvb_gdn_scan_bwd(dVl.data_ptr(), Kb.data_ptr(), Qb.data_ptr(), Wb.data_ptr(), dOb.data_ptr(),
+    rc = nv.cuda().cvb_gdn_scan_bwd(Pb.data_ptr(), Kb.data_ptr(), Qb.data_ptr(), Wb.data_ptr(), dOb.data_ptr(),
                                     eg.data_ptr(), nv.ptr(dsf), dS0.data_ptr(), dVn.data_ptr(), dSnT.data_ptr(),
                                     B * H, n, nv.status_word(dev).data_ptr(), nv.stream())
     nv.check(rc, "cvb_gdn_scan_bwd")
@@ -103,12 +104,13 @@ def chunk_prep(q, k, v, beta, g, scale: float, eps: float = 1e-6, want_aux: bool
     return out
 
 
-def chunk_forward(q, k, v, beta, g, S0, scale: float):
-    """Full chunked forward on the three kernels. Returns (o [B,T,H,128] bf16, Sf fp32, Vn, SsT)."""
+def chunk_forward(q, k, v, beta, g, S0, scale: float, keep_prep: bool = False):
+    """Full chunked forward on the three kernels. Returns (o [B,T,H,128] bf16, Sf fp32, Vn, SsT, prep) where
+    ``prep`` is the prep kernel's output dict (with T and the per-token scalars when ``keep_prep``)."""
     B, T, H, _ = q.shape
     n = T // 64
     dev = q.device
-    pre = chunk_prep(q, k, v, beta, g, scale)
+    pre = chunk_prep(q, k, v, beta, g, scale, want_aux=keep_prep)
     s0 = S0.float().contiguous() if S0 is not None else None
     Vn = torch.empty((B, H, n, 64, 128), dtype=torch.bfloat16, device=dev)
     SsT = torch.empty((B, H, n, 128, 128), dtype=torch.bfloat16, device=dev)
@@ -123,26 +125,25 @@ def chunk_forward(q, k, v, beta, g, S0, scale: float):
                                B, T, H, nv.status_word(dev).data_ptr(), nv.stream())
     nv.check(rc, "cvb_gdn_chunk_out")
     count_launch(2)
-    return o, Sf, Vn, SsT
+    return o, Sf, Vn, SsT, pre
 
 
-def chunk_backward(q, k, v, beta, g, scale: float, Vn, SsT, Sf, do, dSf):
-    """Backward of ``chunk_forward`` on the kernels: prep (recomputed), P^T dO, the reverse state scan and the
-    chunk-local backward.  Returns (dq, dk, dv [B,T,H,128] bf16, dbeta, dg [B,T,H] fp32, dS0 fp32)."""
+def chunk_backward(q, k, v, beta, scale: float, pre, Vn, SsT, Sf, do, dSf):
+    """Backward of ``chunk_forward`` on two kernels: the reverse state scan and the chunk-local backward.
+    ``pre`` holds the forward's prep outputs (W, Kd, Qd, P, egam, Tm, aux).
+    Returns (dq, dk, dv [B,T,H,128] bf16, dbeta, dg [B,T,H] fp32, dS0 fp32)."""
     B, T, H, _ = q.shape
     n = T // 64
     dev = q.device
     lib = nv.cuda()
     st = nv.status_word(dev).data_ptr()
-    pre = chunk_prep(q, k, v, beta, g, scale, want_aux=True)
     do = do.to(torch.bfloat16).contiguous()
     dOb = do.view(B, n, 64, H, 128).permute(0, 3, 1, 2, 4).contiguous()          # [B,H,n,64,128]
-    dVloc = torch.matmul(pre["P"].transpose(-1, -2), dOb)
     dsf = dSf.float().contiguous() if dSf is not None else None
     dVn = torch.empty((B, H, n, 64, 128), dtype=torch.bfloat16, device=dev)
     dSnT = torch.empty((B, H, n, 128, 128), dtype=torch.bfloat16, device=dev)
     dS0 = torch.empty((B, H, 128, 128), dtype=torch.float32, device=dev)
-    rc = lib.cvb_gdn_scan_bwd(dVloc.data_ptr(), pre["Kd"].data_ptr(), pre["Qd"].data_ptr(), pre["W"].data_ptr(),
+    rc = lib.cvb_gdn_scan_bwd(pre["P"].data_ptr(), pre["Kd"].data_ptr(), pre["Qd"].data_ptr(), pre["W"].data_ptr(),
                               dOb.data_ptr(), pre["egam"].data_ptr(), nv.ptr(dsf), dS0.data_ptr(), dVn.data_ptr(),
                               dSnT.data_ptr(), B * H, n, st, nv.stream())
     nv.check(rc, "cvb_gdn_scan_bwd")
@@ -158,5 +159,5 @@ def chunk_backward(q, k, v, beta, g, scale: float, Vn, SsT, Sf, do, dSf):
                                dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dbeta.data_ptr(), dg.data_ptr(), st,
                                nv.stream())
     nv.check(rc, "cvb_gdn_chunk_bwd")
-    count_launch(4)
+    count_launch(3)
     return dq, dk, dv, dbeta, dg, dS0

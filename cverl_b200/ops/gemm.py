@@ -73,7 +73,7 @@ def gemm_raw(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, M: int, N: int
              b_mn: bool, epi: int, alpha: float = 1.0, split_k: int = 0, block_n: int = 0,
              tile_group=None, b_group_rows: int = 0, b_total_rows: int = 0, k_group_offsets=None,
              num_groups: int = 0, c_group_stride: int = 0, targets=None, part_max=None, part_sum=None,
-             tgt_logit=None, lse=None, gscale=None, max_ctas: int = 0) -> None:
+             tgt_logit=None, lse=None, gscale=None, max_ctas: int = 0, mirrors=()) -> None:
     """One launch of the tcgen05 GEMM. Operands are 2-D bf16 tensors with unit inner stride."""
     lib = nv.cuda()
     args = nv.GemmArgs()
@@ -91,6 +91,9 @@ def gemm_raw(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, M: int, N: int
     args.targets, args.part_max, args.part_sum = nv.ptr(targets), nv.ptr(part_max), nv.ptr(part_sum)
     args.tgt_logit, args.lse, args.gscale = nv.ptr(tgt_logit), nv.ptr(lse), nv.ptr(gscale)
     args.status = nv.status_word(a.device).data_ptr()
+    args.n_mirror = len(mirrors)
+    for i, m in enumerate(mirrors):   # raw addresses of peers' copies of ``out``
+        args.mirror[i] = m
     rc = lib.cvb_gemm_bf16(C.byref(args), nv.stream())
     nv.check(rc, "cvb_gemm_bf16")
     count_launch()

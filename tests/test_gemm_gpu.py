@@ -133,9 +133,10 @@ def test_gdn_scan_fwd_kernel():
 def test_gdn_scan_bwd_kernel():
     from cverl_b200.ops import gdn, gdn_native
     W, U, Kd, Qd, egam, S0 = _gdn_scan_inputs(seed=1)
-    dVl, dO = U, (0.5 * U.flip(2)).to(torch.bfloat16).float()
-    dVn, dSn, dS0 = gdn_native.scan_bwd(dVl, Kd, Qd, W, dO, egam, S0)
-    rV, rS, r0 = gdn.scan_bwd_ref(dVl, Kd, Qd, W, dO, egam, S0)
+    dO = (0.5 * U.flip(2)).to(torch.bfloat16).float()
+    P = (0.2 * torch.randn(*U.shape[:3], 64, 64, device=U.device)).tril().to(torch.bfloat16).float()
+    dVn, dSn, dS0 = gdn_native.scan_bwd(P, Kd, Qd, W, dO, egam, S0)
+    rV, rS, r0 = gdn.scan_bwd_ref(P.transpose(-1, -2) @ dO, Kd, Qd, W, dO, egam, S0)
     assert _rel_err(dVn, rV) < 1e-2
     assert _rel_err(dSn, rS) < 1e-2
     assert _rel_err(dS0, r0) < 1e-2
@@ -226,7 +227,7 @@ def test_gdn_chunk_kernels_strided_inputs():
     g = -0.5 * torch.rand(B, T, H, device=_dev())
     S0 = 0.1 * torch.randn(B, H, 128, 128, device=_dev())
     scale = 128 ** -0.5
-    o, Sf, Vn, SsT = gdn_native.chunk_forward(q, k, v, beta, g, S0, scale)
+    o, Sf, Vn, SsT, _ = gdn_native.chunk_forward(q, k, v, beta, g, S0, scale)
     qq, kk, vv = (t.float().cpu() for t in (q, k, v))
     o_r, S_r = gdn.gdn_recurrent_ref((gdn.l2norm(qq) * scale).transpose(1, 2), gdn.l2norm(kk).transpose(1, 2),
                                      vv.transpose(1, 2), beta.cpu().transpose(1, 2), g.cpu().transpose(1, 2), S0.cpu())
