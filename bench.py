@@ -40,6 +40,9 @@ def parse_args():
     ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("CVERL_BENCH_MICRO_BATCH", "16")))
     ap.add_argument("--tp", type=int, default=int(os.environ.get("CVERL_BENCH_TP", "0")))
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
+    ap.add_argument("--tp-comm", default=os.environ.get("CVERL_BENCH_TP_COMM", "symm"), choices=["symm", "nccl"],
+                    help="tensor-parallel all-reduces: symm = fused into the GEMM epilogue over peer-mapped "
+                         "memory, nccl = library collectives")
     ap.add_argument("--zero-comm", default=os.environ.get("CVERL_BENCH_ZERO", "symm"), choices=["symm", "nccl"],
                     help="ZeRO communication: symm = own kernels over peer-mapped memory, nccl = library collectives")
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (result marked invalid)")
@@ -141,6 +144,9 @@ def main():
     cfg = Qwen35TextConfig.qwen3_5_0_8b()
     if args.layers:
         cfg = Qwen35TextConfig(num_hidden_layers=args.layers)
+    if tp > 1 and args.tp_comm == "symm":
+        from cverl_b200.parallel.tp_symm import TpSymm
+        ctx.tp_symm = TpSymm(ctx.tp_group, dev, args.micro_batch * (PROMPT_LEN + RESPONSE_LEN), cfg.hidden_size)
     fused_comm = None
     if dp > 1 and args.zero_comm == "symm":
         from cverl_b200.parallel.symm import FusedZeroComm, SymmetricHeap
@@ -215,6 +221,7 @@ def main():
                        "parallelism": f"dp{dp}xtp{tp}", "micro_batch_seqs": args.micro_batch,
                        "optimizer": "FlatAdamW ZeRO-1 reduce-scatter, clip 1.0",
                        "zero_comm": args.zero_comm if dp > 1 else "none",
+                       "tp_comm": args.tp_comm if tp > 1 else "none",
                        "l2": "per-step working set (activations + 1.5 GB weights + 3 GB fp32 grads) exceeds the "
                              "126 MB L2, no explicit flush"},
             "clocks": sampler.summary(),

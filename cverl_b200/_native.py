@@ -91,6 +91,7 @@ _CUDA_PROTOS = {
     "cvb_reduce_scatter_sumsq": "p ii ll f pp p",
     "cvb_flat_adamw_allgather": "ppppp p ii ll fffff l p",
     "cvb_broadcast_store": "pp i l p",
+    "cvb_sum_parts": "p l i p l p",
 }
 
 

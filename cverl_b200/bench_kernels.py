@@ -1,0 +1,247 @@
+"""Per-kernel micro-benchmarks with roofline fractions.
+
+``python -m cverl_b200.bench_kernels --kernel gemm_nt [--m 8192 --n 8192 --k 8192] [--iters 10]``
+
+Each case times one hot kernel with CUDA events after warm-up, on operands larger than the 126 MB L2
+(or with an L2 flush between iterations for the small ones), and prints one JSON line with the
+achieved TFLOP/s or GB/s and its fraction of the measured peak (``MEASURED_PEAKS.json`` beside the
+package when present, else the stated fallback).  ``--small`` shrinks the case to a few hundred MB
+for profiler captures.  The same cases serve as the kernel rows of the performance tables.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import sys
+from pathlib import Path
+
+import torch
+
+FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def _peaks():
+    p = Path(__file__).resolve().parents[1] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+    return dict(FALLBACK, source="fallback")
+
+
+class _Flush:
+    def __init__(self, dev):
+        self.buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def __call__(self):
+        self.buf.fill_(1)
+
+
+def _time(fn, iters, flush=None):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / iters
+
+
+def _bf(*shape, dev, scale=1.0):
+    return (scale * torch.randn(*shape, device=dev)).to(torch.bfloat16)
+
+
+def case_gemm(a, dev, kind):
+    from . import ops
+    M, N, K = a.m, a.n, a.k
+    if kind == "gemm_nt":
+        x, w = _bf(M, K, dev=dev), _bf(N, K, dev=dev)
+        fn = lambda: ops.gemm_nt(x, w)
+    elif kind == "gemm_nn":
+        x, w = _bf(M, K, dev=dev), _bf(K, N, dev=dev)
+        fn = lambda: ops.gemm_nn(x, w)
+    else:
+        x, w = _bf(K, M, dev=dev), _bf(K, N, dev=dev)
+        acc = torch.zeros(M, N, device=dev)
+        fn = lambda: ops.gemm_tn_acc(x, w, acc)
+    return fn, 2.0 * M * N * K, None
+
+
+def case_lmhead(a, dev, backward):
+    from . import ops
+    T, H, V = a.m, a.k, a.n
+    h = _bf(T, H, dev=dev).requires_grad_(True)
+    w = _bf(V, H, dev=dev, scale=0.02).requires_grad_(True)
+    w.main_grad = torch.zeros(V, H, device=dev)
+    tgt = torch.randint(0, V, (T,), device=dev)
+    if not backward:
+        def fn():
+            with torch.no_grad():
+                ops.lmhead_logprob(h, w, tgt, 0, None)
+        return fn, 2.0 * T * V * H, None
+    g = torch.randn(T, device=dev)
+
+    def fn():
+        lp = ops.lmhead_logprob(h, w, tgt, 0, None)
+        lp.backward(g)
+        h.grad = None
+    return fn, 4 * 2.0 * T * V * H, None       # forward + recompute + dX + dW
+
+
+def _gdn_inputs(a, dev):
+    B, T, H = a.batch, a.seq, a.heads
+    mixed = _bf(B, T, 3 * H * 128, dev=dev)
+    q, k, v = (m.reshape(B, T, H, 128) for m in mixed.split(H * 128, dim=-1))
+    beta = torch.sigmoid(torch.randn(B, T, H, device=dev))
+    g = -0.3 * torch.rand(B, T, H, device=dev)
+    return q, k, v, beta, g
+
+
+def case_gdn(a, dev, which):
+    from .ops import gdn_native as gn
+    q, k, v, beta, g = _gdn_inputs(a, dev)
+    B, T, H = a.batch, a.seq, a.heads
+    scale = 128 ** -0.5
+    o, Sf, Vn, SsT, pre = gn.chunk_forward(q, k, v, beta, g, None, scale, keep_prep=True)
+    do = torch.randn_like(o)
+    tile = B * T * H * 128 * 2            # bytes of one [B,T,H,128] bf16 operand
+    state = B * H * (T // 64) * 128 * 128 * 2
+    if which == "gdn_prep":
+        return (lambda: gn.chunk_prep(q, k, v, beta, g, scale, want_aux=True)), None, 3 * tile + 4.5 * tile + 2 * tile
+    if which == "gdn_fwd":
+        return (lambda: gn.chunk_forward(q, k, v, beta, g, None, scale)), None, 3 * tile + 2 * (4.5 * tile) + 2 * state + 4 * tile
+    if which == "gdn_bwd":
+        return (lambda: gn.chunk_backward(q, k, v, beta, scale, pre, Vn, SsT, Sf, do, None)), None, \
+            (5 + 4 + 3 + 5) * tile + 3 * state
+    raise ValueError(which)
+
+
+def case_conv(a, dev, backward):
+    from . import ops
+    B, S, C = a.batch, a.seq, a.channels
+    x = _bf(B, S, C, dev=dev).requires_grad_(True)
+    w = _bf(C, 4, dev=dev, scale=0.3).requires_grad_(True)
+    w.main_grad = torch.zeros(C, 4, device=dev)
+    nbytes = B * S * C * 2
+    if not backward:
+        def fn():
+            with torch.no_grad():
+                ops.conv1d_silu(x, w)
+        return fn, None, 2 * nbytes
+    y = ops.conv1d_silu(x, w)
+    dy = torch.randn_like(y)
+
+    def fn():
+        y.backward(dy, retain_graph=True)
+        x.grad = None
+    return fn, None, 3 * nbytes
+
+
+def case_rmsnorm(a, dev, backward):
+    from . import ops
+    T, H = a.m, a.k
+    x, r = _bf(T, H, dev=dev).requires_grad_(True), _bf(T, H, dev=dev).requires_grad_(True)
+    w = _bf(H, dev=dev).requires_grad_(True)
+    w.main_grad = torch.zeros(H, device=dev)
+    nbytes = T * H * 2
+    if not backward:
+        def fn():
+            with torch.no_grad():
+                ops.add_rmsnorm(x, r, w, 1e-6, 1.0)
+        return fn, None, 4 * nbytes
+    y, s = ops.add_rmsnorm(x, r, w, 1e-6, 1.0)
+    dy = torch.randn_like(y)
+
+    def fn():
+        torch.autograd.backward([y, s], [dy, dy], retain_graph=True)
+        x.grad = r.grad = None
+    return fn, None, 4 * nbytes
+
+
+def case_adamw(a, dev):
+    from .ops import optim as oo
+    n = a.numel
+    g = torch.randn(n, device=dev)
+    p = torch.randn(n, device=dev).bfloat16()
+    m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    clip = torch.ones(1, device=dev)
+    fn = lambda: oo.flat_adamw_step(g, None, p, m, v, clip=clip, grad_scale=1.0, lr=1e-6, beta1=0.9, beta2=0.95,
+                                    eps=1e-8, weight_decay=0.01, step=3, zero_grad=True)
+    return fn, None, n * (4 + 4 + 2 + 2 + 8 + 8)
+
+
+def case_ppo(a, dev):
+    from .ops import rl
+    rows, cols = a.m, a.k
+    old, lp, adv = (torch.randn(rows, cols, device=dev) * 0.1 for _ in range(3))
+    mask = (torch.rand(rows, cols, device=dev) > 0.1).float()
+    fn = lambda: rl.fused_ppo_loss(old, lp, adv, mask, None, clip_ratio=0.2)
+    return fn, None, rows * cols * 4 * 5
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", required=True)
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--seq", type=int, default=1280)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--channels", type=int, default=6144)
+    ap.add_argument("--numel", type=int, default=1 << 28)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--small", action="store_true", help="a few hundred MB: for profiler captures")
+    a = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device"}))
+        return 1
+    if a.small:
+        a.m, a.n, a.k = min(a.m, 4096), min(a.n, 4096), min(a.k, 4096)
+        a.batch, a.numel = min(a.batch, 8), min(a.numel, 1 << 26)
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    k = a.kernel
+    if k in ("gemm_nt", "gemm_nn", "gemm_tn"):
+        fn, flops, nbytes = case_gemm(a, dev, k)
+    elif k in ("lmhead_fwd", "lmhead_bwd"):
+        fn, flops, nbytes = case_lmhead(a, dev, k.endswith("bwd"))
+    elif k in ("gdn_prep", "gdn_fwd", "gdn_bwd"):
+        fn, flops, nbytes = case_gdn(a, dev, k)
+    elif k in ("conv_fwd", "conv_bwd"):
+        fn, flops, nbytes = case_conv(a, dev, k.endswith("bwd"))
+    elif k in ("rmsnorm_fwd", "rmsnorm_bwd"):
+        fn, flops, nbytes = case_rmsnorm(a, dev, k.endswith("bwd"))
+    elif k == "adamw":
+        fn, flops, nbytes = case_adamw(a, dev)
+    elif k == "ppo_loss":
+        fn, flops, nbytes = case_ppo(a, dev)
+    else:
+        raise SystemExit(f"unknown kernel {k}")
+    flush = _Flush(dev) if (nbytes is not None and nbytes < (512 << 20)) or (flops is not None and a.small) else None
+    ms = _time(fn, a.iters, flush)
+    from . import _native as nv
+    nv.check_status(dev)
+    pk = _peaks()
+    out = {"kernel": k, "ms": ms, "l2": "flushed between iterations" if flush else "operands exceed L2",
+           "peaks": pk["source"]}
+    if flops is not None:
+        out["tflops"] = flops / ms / 1e9
+        out["frac_of_bf16_peak"] = out["tflops"] / pk["bf16_tflops"]
+    if nbytes is not None:
+        out["algorithmic_gbs"] = nbytes / ms / 1e6
+        out["frac_of_hbm_peak"] = out["algorithmic_gbs"] / pk["hbm_gbs"]
+    out["shape"] = {kk: getattr(a, kk) for kk in ("m", "n", "k", "batch", "seq", "heads", "channels", "numel")}
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -17,6 +17,17 @@ constexpr int EW_THREADS = 256;
 struct V8 {
   float v[8];
 };
+__device__ __forceinline__ V8 unpack8v(const uint4& u) {
+  V8 r;
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __bfloat1622float2(h[j]);
+    r.v[2 * j] = f.x;
+    r.v[2 * j + 1] = f.y;
+  }
+  return r;
+}
 __device__ __forceinline__ V8 ld8(const __nv_bfloat16* p) {
   uint4 u = *reinterpret_cast<const uint4*>(p);
   V8 r;
@@ -201,104 +212,114 @@ conv1d_silu_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
 }
 
 // backward: recomputes pre; dx[s'] = sum_t w[t] * dpre[s' + (KW-1) - t]; dw[c,t] += sum dpre[s]*x[s-(KW-1)+t]
-// One thread owns 8 channels and walks a segment of the sequence so that dw is
-// reduced in registers before the atomics.
+// One thread owns 4 channels and walks a segment of the sequence, so that dw is reduced in registers
+// before the atomics.  Rows are taken four at a time with all eight loads issued up front: each thread
+// keeps several memory requests in flight instead of one dependent load per row, and 4 channels per
+// thread keep the register count low enough for two resident blocks per SM.
+constexpr int CB = 4;  // channels per thread in the backward kernel
+__device__ __forceinline__ void unpack4(const uint2& u, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+  f[0] = a.x, f[1] = a.y, f[2] = b.x, f[3] = b.y;
+}
 template <int KW>
-__global__ void __launch_bounds__(EW_THREADS)
+__global__ void __launch_bounds__(EW_THREADS, 2)
 conv1d_silu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                        const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ dx,
                        float* __restrict__ dw, long long B, int S, int C, long long x_stride, int seg_len,
                        long long dx_stride) {
-  const int vec_per_row = C / 8;
+  const int vec_per_row = C / CB;
   const int segs = (S + seg_len - 1) / seg_len;
   const long long total = B * segs * vec_per_row;
   for (long long i = static_cast<long long>(blockIdx.x) * EW_THREADS + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * EW_THREADS) {
-    const int c = static_cast<int>(i % vec_per_row) * 8;
+    const int c = static_cast<int>(i % vec_per_row) * CB;
     const long long bs = i / vec_per_row;
     const long long b = bs / segs;
     const int s_begin = static_cast<int>(bs % segs) * seg_len;
     const int s_end = min(S, s_begin + seg_len);
-    float wv[8][KW];
+    float wv[CB][KW], dwa[CB][KW];
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int j = 0; j < CB; ++j)
 #pragma unroll
-      for (int t = 0; t < KW; ++t) wv[j][t] = __bfloat162float(w[(c + j) * KW + t]);
-    float dwa[8][KW];
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-#pragma unroll
-      for (int t = 0; t < KW; ++t) dwa[j][t] = 0.f;
-    // Walk output positions s in [s_begin, s_end + KW - 1): dpre[s] feeds dx[s-(KW-1)+t].
-    // dx for position p collects dpre[p .. p+KW-1]; keep a sliding window of dpre.
-    // window[k] = dpre[s - k], k = 0..KW-1 ; x window xw[k] = x[s - k]
-    float dpre_win[KW][8];
-    float x_win[KW][8];
+      for (int t = 0; t < KW; ++t) wv[j][t] = __bfloat162float(w[(c + j) * KW + t]), dwa[j][t] = 0.f;
+    // windows: dpre_win[k] = dpre[s - k], x_win[k] = x[s - k]
+    float dpre_win[KW][CB], x_win[KW][CB];
 #pragma unroll
     for (int k = 0; k < KW; ++k)
 #pragma unroll
-      for (int j = 0; j < 8; ++j) dpre_win[k][j] = 0.f, x_win[k][j] = 0.f;
-    // preload x history before s_begin
+      for (int j = 0; j < CB; ++j) dpre_win[k][j] = 0.f, x_win[k][j] = 0.f;
 #pragma unroll
-    for (int k = 1; k < KW; ++k) {
+    for (int k = 1; k < KW; ++k) {  // x history before s_begin (index k-1: shifted at the loop head)
       const int sp = s_begin - k;
-      if (sp >= 0) {
-        V8 xv = ld8(x + (b * S + sp) * x_stride + c);
+      if (sp >= 0) unpack4(*reinterpret_cast<const uint2*>(x + (b * S + sp) * x_stride + c), x_win[k - 1]);
+    }
+    const int s_last = s_end + (KW - 1);
+    for (int s0 = s_begin; s0 < s_last; s0 += 4) {
+      uint2 xr[4], dr[4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) x_win[k - 1][j] = xv.v[j];
+      for (int u = 0; u < 4; ++u) {
+        const int s = s0 + u;
+        xr[u] = make_uint2(0u, 0u);
+        dr[u] = xr[u];
+        if (s < s_last && s < S) {
+          xr[u] = *reinterpret_cast<const uint2*>(x + (b * S + s) * x_stride + c);
+          dr[u] = *reinterpret_cast<const uint2*>(dy + (b * S + s) * C + c);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int s = s0 + u;
+        if (s >= s_last) break;
+#pragma unroll
+        for (int k = KW - 1; k > 0; --k)
+#pragma unroll
+          for (int j = 0; j < CB; ++j) {
+            dpre_win[k][j] = dpre_win[k - 1][j];
+            x_win[k][j] = x_win[k - 1][j];
+          }
+        if (s < S) {
+          float d[CB];
+          unpack4(xr[u], x_win[0]);
+          unpack4(dr[u], d);
+#pragma unroll
+          for (int j = 0; j < CB; ++j) {
+            float pre = 0.f;
+#pragma unroll
+            for (int t = 0; t < KW; ++t) pre += wv[j][t] * x_win[KW - 1 - t][j];
+            const float sg = sigm(pre);
+            dpre_win[0][j] = d[j] * sg * (1.f + pre * (1.f - sg));
+          }
+          if (s < s_end) {
+#pragma unroll
+            for (int j = 0; j < CB; ++j)
+#pragma unroll
+              for (int t = 0; t < KW; ++t) dwa[j][t] += dpre_win[0][j] * x_win[KW - 1 - t][j];
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < CB; ++j) dpre_win[0][j] = 0.f, x_win[0][j] = 0.f;
+        }
+        // dx for position p = s - (KW-1): sum_t w[t] * dpre[p + (KW-1) - t] = sum_t w[t] * dpre_win[t]
+        const int p = s - (KW - 1);
+        if (p >= s_begin && p < s_end) {
+          float o[CB];
+#pragma unroll
+          for (int j = 0; j < CB; ++j) {
+            float acc = 0.f;
+#pragma unroll
+            for (int t = 0; t < KW; ++t) acc += wv[j][t] * dpre_win[t][j];
+            o[j] = acc;
+          }
+          *reinterpret_cast<uint2*>(dx + (b * S + p) * dx_stride + c) =
+              make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
+        }
       }
     }
-    // x_win here holds x[s-1-k] at index k (k = 0..KW-2) before the shift at the loop head
-    for (int s = s_begin; s < s_end + (KW - 1); ++s) {
-      // shift windows
 #pragma unroll
-      for (int k = KW - 1; k > 0; --k)
+    for (int j = 0; j < CB; ++j)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          dpre_win[k][j] = dpre_win[k - 1][j];
-          x_win[k][j] = x_win[k - 1][j];
-        }
-      if (s < S) {
-        V8 xv = ld8(x + (b * S + s) * x_stride + c);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) x_win[0][j] = xv.v[j];
-        V8 d = ld8(dy + (b * S + s) * C + c);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float pre = 0.f;
-#pragma unroll
-          for (int t = 0; t < KW; ++t) pre += wv[j][t] * x_win[KW - 1 - t][j];
-          const float sg = sigm(pre);
-          dpre_win[0][j] = d.v[j] * sg * (1.f + pre * (1.f - sg));
-        }
-        if (s < s_end) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-#pragma unroll
-            for (int t = 0; t < KW; ++t) dwa[j][t] += dpre_win[0][j] * x_win[KW - 1 - t][j];
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) dpre_win[0][j] = 0.f, x_win[0][j] = 0.f;
-      }
-      // dx for position p = s - (KW-1): sum_t w[t] * dpre[p + (KW-1) - t] = sum_t w[t] * dpre_win[t]
-      const int p = s - (KW - 1);
-      if (p >= s_begin && p < s_end) {
-        V8 o;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float a = 0.f;
-#pragma unroll
-          for (int t = 0; t < KW; ++t) a += wv[j][t] * dpre_win[t][j];
-          o.v[j] = a;
-        }
-        st8(dx + (b * S + p) * dx_stride + c, o);
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-#pragma unroll
-      for (int t = 0; t < KW; ++t) atomicAdd(&dw[(c + j) * KW + t], dwa[j][t]);
+      for (int t = 0; t < KW; ++t) atomicAdd(dw + (c + j) * KW + t, dwa[j][t]);
   }
 }
 
@@ -432,7 +453,7 @@ extern "C" int cvb_conv1d_silu_bwd(const void* dy, const void* x, const void* w,
   // enough segments to fill the machine, long enough to amortise the atomics
   int seg_len = 64;
   const int segs = (S + seg_len - 1) / seg_len;
-  const int grid = ew_grid(B * segs * (C / 8));
+  const int grid = ew_grid(B * segs * (C / CB));
   if (KW == 4)
     conv1d_silu_bwd_kernel<4><<<grid, EW_THREADS, 0, ST(stream)>>>(BF(dy), BF(x), BF(w), BFM(dx), dw, B, S, C,
                                                                   x_stride, seg_len, dx_stride);

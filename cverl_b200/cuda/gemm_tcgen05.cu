@@ -44,7 +44,11 @@ struct TileCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  // epilogue staging for mirrored stores: per epilogue warp 32 rows x 64 bf16, rows padded to 144 bytes
+  static constexpr int STG_ROW = 144;
+  static constexpr int STG_WARP = 32 * STG_ROW;
+  static constexpr int STG_OFF = STAGES * STAGE_BYTES + 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + 4 * STG_WARP;
 };
 
 struct WorkItem {
@@ -281,6 +285,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         tmem_ld_32x32(taddr + c, r);
         tmem_ld_wait();
         const int col0 = n0 + c;
+        if (p.n_mirror > 0) {
+          // Mirrored bf16 store (N % 64 == 0): two 32-column chunks of this warp's 32 rows are staged in
+          // shared memory, then written out as 128-byte row segments (8 lanes per row) to the local C and
+          // to every mirror: full-line stores keep the NVLink writes efficient.
+          if (col0 < p.N) {
+            uint8_t* stg = smem + Cfg::STG_OFF + q * Cfg::STG_WARP;
+            uint8_t* mine = stg + lane * Cfg::STG_ROW + (c & 32) * 2;
+#pragma unroll
+            for (int g8 = 0; g8 < 4; ++g8) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r[g8 * 8 + 0]) * p.alpha, __uint_as_float(r[g8 * 8 + 1]) * p.alpha);
+              o.y = pack_bf16x2(__uint_as_float(r[g8 * 8 + 2]) * p.alpha, __uint_as_float(r[g8 * 8 + 3]) * p.alpha);
+              o.z = pack_bf16x2(__uint_as_float(r[g8 * 8 + 4]) * p.alpha, __uint_as_float(r[g8 * 8 + 5]) * p.alpha);
+              o.w = pack_bf16x2(__uint_as_float(r[g8 * 8 + 6]) * p.alpha, __uint_as_float(r[g8 * 8 + 7]) * p.alpha);
+              *reinterpret_cast<uint4*>(mine + g8 * 16) = o;
+            }
+            if (c & 32) {
+              __syncwarp();
+              const int cbase = n0 + (c & ~63);
+#pragma unroll 1
+              for (int it = 0; it < 8; ++it) {
+                const int rr = it * 4 + (lane >> 3), ch = lane & 7;
+                const int grow = w.mb * BM + q * 32 + rr;
+                if (grow < p.M) {
+                  const uint4 o = *reinterpret_cast<const uint4*>(stg + rr * Cfg::STG_ROW + ch * 16);
+                  const long long off = c_off + static_cast<long long>(grow) * p.ldc + cbase + ch * 8;
+                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + off) = o;
+#pragma unroll 1
+                  for (int m = 0; m < p.n_mirror; ++m)
+                    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.mirror[m]) + off) = o;
+                }
+              }
+              __syncwarp();
+            }
+          }
+          continue;
+        }
         if (!row_ok || col0 >= p.N) continue;
         float v[32];
 #pragma unroll
@@ -296,9 +337,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               o.z = pack_bf16x2(v[g8 * 8 + 4], v[g8 * 8 + 5]);
               o.w = pack_bf16x2(v[g8 * 8 + 6], v[g8 * 8 + 7]);
               *reinterpret_cast<uint4*>(dst + g8 * 8) = o;
-#pragma unroll 1
-              for (int m = 0; m < p.n_mirror; ++m)
-                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.mirror[m]) + (dst - reinterpret_cast<__nv_bfloat16*>(p.C)) + g8 * 8) = o;
             }
           }
         } else if (p.epi == EPI_STORE_F32) {
@@ -494,7 +532,8 @@ extern "C" int cvb_gemm_bf16(const CvbGemmArgs* a, void* stream_v) {
   p.lse = a->lse;
   p.gscale = a->gscale;
   p.status = a->status;
-  if (a->n_mirror < 0 || a->n_mirror > 7 || (a->n_mirror > 0 && a->epi != EPI_STORE_BF16)) return -6;
+  if (a->n_mirror < 0 || a->n_mirror > 7 || (a->n_mirror > 0 && (a->epi != EPI_STORE_BF16 || a->N % 64 != 0)))
+    return -6;
   p.n_mirror = a->n_mirror;
   for (int m = 0; m < a->n_mirror; ++m) {
     if (!a->mirror[m] || (reinterpret_cast<uintptr_t>(a->mirror[m]) & 15)) return -6;

@@ -10,6 +10,8 @@
 //                           every peer's parameter buffer: the parameter all-gather rides on the
 //                           optimizer's own stores
 //  * broadcast_store        trainer -> rollout weight push: one read of the source, one store per peer
+//  * sum_parts              second half of the tensor-parallel all-reduce whose first half is the GEMM
+//                           epilogue's mirror stores into every peer (gemm_tcgen05.cu)
 //
 // The reference does these with ncclReduceScatter / ATen ops / ncclAllGather / ncclBroadcast
 // (src/distributed/optimizer_sharding.cc:463-733, src/distributed/weight_sync.cc:140-189).
@@ -151,6 +153,35 @@ broadcast_store_kernel(const uint4* __restrict__ src, PeerPtrs dst, int n_dst, l
   }
 }
 
+// out[i] = sum_r parts[r * slot_stride + i]   (bf16 in, fp32 sum, bf16 out; 8 elements per thread)
+// The addends are the per-rank partial products that the GEMM epilogues of a tensor-parallel group stored
+// into every member's copy of `parts` (mirror stores): summing the local copy completes the all-reduce.
+__global__ void __launch_bounds__(SY_THREADS)
+sum_parts_kernel(const __nv_bfloat16* __restrict__ parts, long long slot_stride, int world,
+                 __nv_bfloat16* __restrict__ out, long long nvec) {
+  for (long long i = static_cast<long long>(blockIdx.x) * SY_THREADS + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * SY_THREADS) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+    for (int r = 0; r < world; ++r) {
+      const uint4 u = *reinterpret_cast<const uint4*>(parts + r * slot_stride + i * 8);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + i * 8) = o;
+  }
+}
+
 static int sy_grid(long long nvec) {
   long long b = (nvec + SY_THREADS - 1) / SY_THREADS;
   if (b > 148 * 8) b = 148 * 8;
@@ -204,5 +235,16 @@ extern "C" int cvb_broadcast_store(const void* src, void* const* dst_ptrs, int n
   if (nbytes == 0) return 0;
   broadcast_store_kernel<<<sy_grid(nbytes / 16), SY_THREADS, 0, ST(stream)>>>(static_cast<const uint4*>(src), d, n_dst,
                                                                               nbytes / 16);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int cvb_sum_parts(const void* parts, long long slot_stride, int world, void* out, long long n,
+                             void* stream) {
+  if (world <= 0 || world > MAX_PEERS || n % 8 || slot_stride % 8 ||
+      ((reinterpret_cast<uintptr_t>(parts) | reinterpret_cast<uintptr_t>(out)) & 15))
+    return -1;
+  if (n == 0) return 0;
+  sum_parts_kernel<<<sy_grid(n / 8), SY_THREADS, 0, ST(stream)>>>(static_cast<const __nv_bfloat16*>(parts), slot_stride,
+                                                                  world, static_cast<__nv_bfloat16*>(out), n / 8);
   return static_cast<int>(cudaGetLastError());
 }

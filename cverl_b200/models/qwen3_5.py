@@ -238,6 +238,25 @@ class Qwen35Model(torch.nn.Module):
     def _positions(self, batch: int, seq: int, device) -> torch.Tensor:
         return torch.arange(seq, device=device, dtype=torch.int32).repeat(batch)
 
+    # ------------------------------------------------------------------ tensor-parallel linears
+    def _col_linear(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """Column-parallel linear on a replicated input: the input gradient is all-reduced over TP."""
+        ctx = self.ctx
+        if ctx.tp_size > 1 and ctx.tp_symm is not None:
+            from ..parallel import tp_symm
+            if tp_symm.usable(ctx.tp_symm, x, x.reshape(-1, x.shape[-1]).shape[0], x.shape[-1]):
+                return tp_symm.column_parallel_linear(x, w, ctx.tp_symm)
+        return ops.linear(copy_to_tp(x, ctx.tp_group), w)
+
+    def _row_linear(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """Row-parallel linear on a sharded input: the output is all-reduced over TP."""
+        ctx = self.ctx
+        if ctx.tp_size > 1 and ctx.tp_symm is not None:
+            from ..parallel import tp_symm
+            if tp_symm.usable(ctx.tp_symm, x, x.reshape(-1, x.shape[-1]).shape[0], w.shape[0]):
+                return tp_symm.row_parallel_linear(x, w, ctx.tp_symm)
+        return reduce_from_tp(ops.linear(x, w), ctx.tp_group)
+
     # ------------------------------------------------------------------ mixers
     def full_attention(self, x: torch.Tensor, i: int, batch: int, seq: int, cache: Optional[dict] = None) -> torch.Tensor:
         cfg, ctx = self.cfg, self.ctx
@@ -246,8 +265,7 @@ class Qwen35Model(torch.nn.Module):
         h = cfg.num_attention_heads // ctx.tp_size
         kvh = cfg.num_key_value_heads // ctx.tp_size
         T = x.shape[0]
-        x = copy_to_tp(x, ctx.tp_group)
-        qkv = ops.linear(x, self.fused[f"{i}.qkv"])
+        qkv = self._col_linear(x, self.fused[f"{i}.qkv"])
         qmul = 1 if cfg.is_qwen3_moe else 2
         q_all, k, v = qkv.split([h * d * qmul, kvh * d, kvh * d], dim=-1)
         if cfg.is_qwen3_moe:
@@ -274,8 +292,7 @@ class Qwen35Model(torch.nn.Module):
             o = attn_ops.causal_attention(q, k, v, batch, seq, 1.0 / math.sqrt(d))
         if gate is not None:
             o = ops.siggate(o, gate)
-        out = ops.linear(o.reshape(T, h * d), self.param(p + "o_proj.weight"))
-        return reduce_from_tp(out, ctx.tp_group)
+        return self._row_linear(o.reshape(T, h * d), self.param(p + "o_proj.weight"))
 
     def linear_attention(self, x: torch.Tensor, i: int, batch: int, seq: int,
                          initial_state: Optional[torch.Tensor] = None, return_state: bool = False,
@@ -288,8 +305,7 @@ class Qwen35Model(torch.nn.Module):
         key_dim, value_dim = kh * kd, vh * vd
         conv_dim = 2 * key_dim + value_dim
         T = x.shape[0]
-        x = copy_to_tp(x, ctx.tp_group)
-        proj = ops.linear(x, self.fused[f"{i}.lin_in"])
+        proj = self._col_linear(x, self.fused[f"{i}.lin_in"])
         mixed, z, b, a = proj.split([conv_dim, value_dim, vh, vh], dim=-1)
         conv_w = self.param(p + "conv1d.weight").view(conv_dim, cfg.linear_conv_kernel_dim)
         if cache is not None:  # the last KW-1 pre-convolution rows seed the decode-time window
@@ -323,8 +339,7 @@ class Qwen35Model(torch.nn.Module):
         if ctx.cp_size > 1:  # hand the state on; the zero token ties the send into the backward pass
             core = core + send_final_state(state, ctx.cp_group, ctx.cp_rank, ctx.cp_size).to(core.dtype)
         y = ops.gated_rmsnorm(core, z.reshape(T, vh, vd), self.param(p + "norm.weight"), cfg.rms_norm_eps)
-        out = ops.linear(y.reshape(T, value_dim), self.param(p + "out_proj.weight"))
-        out = reduce_from_tp(out, ctx.tp_group)
+        out = self._row_linear(y.reshape(T, value_dim), self.param(p + "out_proj.weight"))
         if cache is not None:
             cache["state"] = state
         return (out, state) if return_state else out
@@ -335,11 +350,9 @@ class Qwen35Model(torch.nn.Module):
             from .moe import moe_mlp
             return moe_mlp(self, x, i)
         p = f"{cfg.layer_root}{i}.mlp."
-        x = copy_to_tp(x, ctx.tp_group)
-        gu = ops.linear(x, self.fused[f"{i}.gate_up"])
+        gu = self._col_linear(x, self.fused[f"{i}.gate_up"])
         act = ops.swiglu(gu)
-        out = ops.linear(act, self.param(p + "down_proj.weight"))
-        return reduce_from_tp(out, ctx.tp_group)
+        return self._row_linear(act, self.param(p + "down_proj.weight"))
 
     # ------------------------------------------------------------------ forward
     def embed(self, input_ids: torch.Tensor) -> torch.Tensor:

@@ -25,6 +25,8 @@ class ParallelContext:
     pp_size: int = 1
     # fused NVLink kernels (symmetric-memory paths) instead of NCCL for TP / ZeRO
     fused_comm: bool = False
+    # ``parallel.tp_symm.TpSymm`` when tensor-parallel linears fuse their all-reduce into the GEMM
+    tp_symm: Optional[Any] = None
 
     @property
     def single(self) -> bool:

@@ -139,3 +139,41 @@ def _fused_zero_rank(rank, world):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_fused_zero_and_push_two_gpus():
     run_ranks(_fused_zero_rank, 2, backend="nccl", timeout=300)
+
+
+def _tp_symm_rank(rank, world):
+    import torch.distributed as dist
+    from cverl_b200 import _native as nv
+    from cverl_b200.ops import gemm as G
+    from cverl_b200.parallel import tp_symm
+    dev = torch.device("cuda", rank)
+    tps = tp_symm.TpSymm(None, dev, max_rows=640, max_cols=256)
+    g = torch.Generator(device=dev).manual_seed(11 + rank)
+    for it in range(5):                                   # more uses than buffers: exercises the alternation
+        rows = 640 if it % 2 == 0 else 300
+        x = torch.randn(rows, 384, device=dev, generator=g).bfloat16().requires_grad_(True)
+        w_row = (0.05 * torch.randn(256, 384, device=dev, generator=g)).bfloat16().requires_grad_(True)
+        y = tp_symm.row_parallel_linear(x, w_row, tps)
+        ref = (x.detach().float() @ w_row.detach().float().t())
+        dist.all_reduce(ref)
+        torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=2e-2)
+        # column parallel: replicated input, all-reduced input gradient
+        xr = torch.randn(rows, 256, device=dev, generator=torch.Generator(device=dev).manual_seed(77 + it))
+        xr = xr.bfloat16().requires_grad_(True)
+        w_col = (0.05 * torch.randn(384, 256, device=dev, generator=g)).bfloat16().requires_grad_(True)
+        yc = tp_symm.column_parallel_linear(xr, w_col, tps)
+        dy = torch.randn(yc.shape, device=dev, generator=g).bfloat16()
+        yc.backward(dy)
+        dref = dy.float() @ w_col.detach().float()
+        dist.all_reduce(dref)
+        torch.testing.assert_close(xr.grad.float(), dref, rtol=2e-2, atol=3e-2)
+        torch.testing.assert_close(w_col.grad.float(), dy.float().t() @ xr.detach().float(), rtol=2e-2, atol=5e-2)
+    torch.cuda.synchronize()
+    nv.check_status()
+    dist.barrier()
+    tps.heap.close()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp_fused_linear_two_gpus():
+    run_ranks(_tp_symm_rank, 2, backend="nccl", timeout=300)
