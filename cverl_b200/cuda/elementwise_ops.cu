@@ -189,24 +189,40 @@ conv1d_silu_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
         for (int j = 0; j < 8; ++j) win[k + 1][j] = 0.f;
       }
     }
-    const __nv_bfloat16* xp = x + (b * S + s_begin) * x_stride + c;
-    __nv_bfloat16* yp = y + (b * S + s_begin) * C + c;
-    for (int s = s_begin; s < s_end; ++s, xp += x_stride, yp += C) {
+    // software pipeline: four rows per group, the next group's loads in flight during the computation
+    uint4 xn[4];
+    auto fetch = [&](int s0) {
 #pragma unroll
-      for (int k = 0; k < KW - 1; ++k)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) win[k][j] = win[k + 1][j];
-      const V8 xv = ld8(xp);
-      V8 o;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        win[KW - 1][j] = xv.v[j];
-        float acc = 0.f;
-#pragma unroll
-        for (int t = 0; t < KW; ++t) acc += wv[j][t] * win[t][j];
-        o.v[j] = acc * sigm(acc);
+      for (int u = 0; u < 4; ++u) {
+        xn[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (s0 + u < s_end) xn[u] = *reinterpret_cast<const uint4*>(x + (b * S + s0 + u) * x_stride + c);
       }
-      st8(yp, o);
+    };
+    fetch(s_begin);
+    for (int s0 = s_begin; s0 < s_end; s0 += 4) {
+      uint4 xr[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) xr[u] = xn[u];
+      fetch(s0 + 4);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (s0 + u >= s_end) break;
+#pragma unroll
+        for (int k = 0; k < KW - 1; ++k)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) win[k][j] = win[k + 1][j];
+        const V8 xv = unpack8v(xr[u]);
+        V8 o;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          win[KW - 1][j] = xv.v[j];
+          float acc = 0.f;
+#pragma unroll
+          for (int t = 0; t < KW; ++t) acc += wv[j][t] * win[t][j];
+          o.v[j] = acc * sigm(acc);
+        }
+        st8(y + (b * S + s0 + u) * C + c, o);
+      }
     }
   }
 }
@@ -255,18 +271,26 @@ conv1d_silu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16
       if (sp >= 0) unpack4(*reinterpret_cast<const uint2*>(x + (b * S + sp) * x_stride + c), x_win[k - 1]);
     }
     const int s_last = s_end + (KW - 1);
-    for (int s0 = s_begin; s0 < s_last; s0 += 4) {
-      uint2 xr[4], dr[4];
+    // software pipeline: the loads of group g+1 are in flight while group g is computed
+    uint2 xn[4], dn[4];
+    auto fetch = [&](int s0) {
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int s = s0 + u;
-        xr[u] = make_uint2(0u, 0u);
-        dr[u] = xr[u];
+        xn[u] = make_uint2(0u, 0u);
+        dn[u] = xn[u];
         if (s < s_last && s < S) {
-          xr[u] = *reinterpret_cast<const uint2*>(x + (b * S + s) * x_stride + c);
-          dr[u] = *reinterpret_cast<const uint2*>(dy + (b * S + s) * C + c);
+          xn[u] = *reinterpret_cast<const uint2*>(x + (b * S + s) * x_stride + c);
+          dn[u] = *reinterpret_cast<const uint2*>(dy + (b * S + s) * C + c);
         }
       }
+    };
+    fetch(s_begin);
+    for (int s0 = s_begin; s0 < s_last; s0 += 4) {
+      uint2 xr[4], dr[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) xr[u] = xn[u], dr[u] = dn[u];
+      fetch(s0 + 4);
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int s = s0 + u;

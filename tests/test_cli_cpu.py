@@ -1,0 +1,61 @@
+"""Command-line tools on a synthesized tiny model directory and gloo ranks."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+@pytest.fixture(scope="module")
+def tiny_dir(tmp_path_factory):
+    from cverl_b200.models.config import Qwen35TextConfig
+    from cverl_b200.models.hf_io import synthesize_model_dir
+    d = tmp_path_factory.mktemp("tiny_model")
+    synthesize_model_dir(Qwen35TextConfig.tiny(), d, seed=3, dtype=torch.float32)
+    return d
+
+
+def test_weight_manifest_and_inspect(tiny_dir, capsys):
+    from cverl_b200.cli import inspect_hf_model, vllm_weight_manifest
+    assert vllm_weight_manifest.main(["--model-dir", str(tiny_dir), "--send-dtype", "bfloat16", "--no-packed"]) == 0
+    out = json.loads(capsys.readouterr().out)
+    info = out["update_info"]
+    assert out["backend"] == "vllm_native_rl_nccl" and info["packed"] is False and not info["is_checkpoint_format"]
+    assert len(info["names"]) == len(info["shapes"]) == len(info["dtype_names"]) > 10
+    assert set(info["dtype_names"]) == {"bfloat16"} and info["names"][0].endswith("embed_tokens.weight")
+    assert inspect_hf_model.main(["--model-dir", str(tiny_dir), "--check", "--tensors"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["check"]["ok"] and rep["num_tensors"] == len(rep["tensors"])
+
+
+def test_forward_dump_and_compare(tiny_dir, tmp_path, capsys):
+    from cverl_b200.cli import qwen3_5_forward
+    dump = tmp_path / "fwd.pt"
+    assert qwen3_5_forward.main(["--model-dir", str(tiny_dir), "--ids", "5,6,7,8,9", "--dump", str(dump)]) == 0
+    first = json.loads(capsys.readouterr().out)
+    assert first["shape"][:2] == [1, 5] and len(first["argmax"]) == 5
+    assert qwen3_5_forward.main(["--model-dir", str(tiny_dir), "--ids", "5,6,7,8,9", "--compare", str(dump)]) == 0
+    second = json.loads(capsys.readouterr().out)
+    assert second["compare"]["max_abs"] < 1e-5 and second["compare"]["argmax_equal"]
+
+
+def test_rollout_batch_source_to_receiver_gloo():
+    env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1", MASTER_ADDR="127.0.0.1", MASTER_PORT="29733",
+               WORLD_SIZE="2")
+    common = [sys.executable, "-m", "cverl_b200.cli.rollout_batch_source", "--backend", "gloo", "--steps", "2",
+              "--batch", "4", "--prompt-len", "6", "--response-len", "3"]
+    src = subprocess.Popen(common + ["--target-ranks", "1"], env=dict(env, RANK="0", LOCAL_RANK="0"), cwd=ROOT,
+                           stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    dst = subprocess.Popen(common + ["--receive-from", "0"], env=dict(env, RANK="1", LOCAL_RANK="0"), cwd=ROOT,
+                           stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    so, se = src.communicate(timeout=120)
+    do, de = dst.communicate(timeout=120)
+    assert src.returncode == 0, se[-2000:]
+    assert dst.returncode == 0, de[-2000:]
+    assert "rollout source step 2 sent batch=4" in so
+    assert "step 2 received batch=4 weight_version=2 reward_sum=2.0" in do
