@@ -59,3 +59,19 @@ def test_rollout_batch_source_to_receiver_gloo():
     assert dst.returncode == 0, de[-2000:]
     assert "rollout source step 2 sent batch=4" in so
     assert "step 2 received batch=4 weight_version=2 reward_sum=2.0" in do
+
+
+def test_golden_dump_and_replay_through_c_abi(tmp_path, capsys):
+    from cverl_b200.cli import golden
+    path = tmp_path / "golden.bin"
+    assert golden.main(["dump", str(path), "--seed", "7"]) == 0
+    assert path.read_bytes()[:8] == b"CVERLGD1"
+    assert golden.main(["compare", str(path)]) == 0
+    assert "golden replay: ok" in capsys.readouterr().out
+    # a corrupted expectation is reported
+    raw = bytearray(path.read_bytes())
+    import struct
+    raw[-4:] = struct.pack("<f", 1234.5)
+    bad = tmp_path / "bad.bin"
+    bad.write_bytes(bytes(raw))
+    assert golden.main(["compare", str(bad)]) == 1
