@@ -107,9 +107,15 @@ class Qwen3_5CausalLmPolicy(CausalLmPolicy):
         self._pad = pad_id
 
     @classmethod
-    def from_model_dir(cls, model_dir, param_dtype=torch.float32, device="cpu", pad_id: int = 0):
+    def from_model_dir(cls, model_dir, param_dtype=torch.float32, device="cpu", pad_id: int = 0,
+                       max_layers: int = -1):
         loader = HfModelLoader(model_dir).load_metadata()
-        pol = cls(loader.config(), param_dtype, device, str(model_dir), pad_id)
+        cfg = loader.config()
+        if 0 < max_layers < cfg.num_hidden_layers:   # a truncated stack for smoke runs
+            fields = {k: getattr(cfg, k) for k in cfg.__dataclass_fields__}
+            fields.update(num_hidden_layers=max_layers, layer_types=cfg.layer_types[:max_layers])
+            cfg = Qwen35TextConfig(**fields)
+        pol = cls(cfg, param_dtype, device, str(model_dir), pad_id)
         load_model_weights(pol.model, loader)
         return pol
 
@@ -164,5 +170,6 @@ def make_causal_lm_policy(options: CausalLmPolicyOptions) -> CausalLmPolicy:
     if options.kind in ("qwen3_5", "qwen"):
         if not options.model_dir:
             raise ValueError("qwen3_5 policy requires model_dir")
-        return Qwen3_5CausalLmPolicy.from_model_dir(options.model_dir, options.param_dtype, pad_id=options.pad_id)
+        return Qwen3_5CausalLmPolicy.from_model_dir(options.model_dir, options.param_dtype, pad_id=options.pad_id,
+                                                    max_layers=options.max_layers)
     raise ValueError(f"unknown policy kind {options.kind!r}")

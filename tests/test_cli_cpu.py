@@ -75,3 +75,20 @@ def test_golden_dump_and_replay_through_c_abi(tmp_path, capsys):
     bad = tmp_path / "bad.bin"
     bad.write_bytes(bytes(raw))
     assert golden.main(["compare", str(bad)]) == 1
+
+
+def test_vllm_bridge_policy_update_and_manifest(tiny_dir):
+    from cverl_b200.rollout.vllm_bridge import QwenPolicy
+    pol = QwenPolicy(str(tiny_dir), device="cpu", param_dtype="float32")
+    named = pol.named_parameters()
+    info = pol.update_info(packed=True, packed_buffer_size_bytes=1 << 20, packed_num_buffers=3)
+    assert [n for n, _ in named] == info["names"] and info["packed_num_buffers"] == 3
+    before = named[1][1].detach().clone()
+    prompts, answers = ["What is 2+2?", "What is 3+3?"], ["#### 4", "#### 6"]
+    responses = ["so #### 4", "hm #### 5", "it is #### 6", "no idea"]
+    m = pol.gsm8k_grpo_update(prompts, responses, answers, [0, 0, 1, 1], [0, 1, 0, 1], max_prompt_tokens=16,
+                              max_response_tokens=12, ppo_epochs=2, learning_rate=1e-3, kl_coef=0.01,
+                              reward_method="flexible", measure_param_delta=True)
+    assert m["total_seq"] == 4.0 and m["mean_reward"] == pytest.approx(0.5) and m["success_rate"] == pytest.approx(0.5)
+    assert m["param_delta"] > 0 and m["adv_abs_sum"] > 0
+    assert not torch.equal(named[1][1], before)          # the named tensors are live views of the weights
