@@ -92,3 +92,14 @@ def test_vllm_bridge_policy_update_and_manifest(tiny_dir):
     assert m["total_seq"] == 4.0 and m["mean_reward"] == pytest.approx(0.5) and m["success_rate"] == pytest.approx(0.5)
     assert m["param_delta"] > 0 and m["adv_abs_sum"] > 0
     assert not torch.equal(named[1][1], before)          # the named tensors are live views of the weights
+
+
+@pytest.mark.parametrize("mode,nproc", [("tp", 2), ("dp_tp", 4), ("pp_tp", 4)])
+def test_parallel_smokes_gloo(mode, nproc):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29750 + nproc + len(mode)), "-m", "cverl_b200.cli.parallel_smoke",
+           "--mode", mode, "--backend", "gloo"]
+    p = subprocess.run(cmd, cwd=ROOT, env=dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1"),
+                       capture_output=True, text=True, timeout=240)
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-3000:]
+    assert f"{mode} smoke passed" in p.stdout
