@@ -24,14 +24,9 @@ from ..parallel.autograd_collectives import all_to_all_rows, copy_to_tp, reduce_
 
 
 def router(x: torch.Tensor, gate_w: torch.Tensor, top_k: int, norm_topk_prob: bool) -> Tuple[torch.Tensor, torch.Tensor]:
-    """x [T, H] -> (expert ids [T, k] int64, routing weights [T, k] fp32)."""
-    logits = x.float() @ gate_w.float().t()
-    top_val, top_idx = logits.topk(top_k, dim=-1)
-    if norm_topk_prob:
-        w = torch.softmax(top_val, dim=-1)
-    else:
-        w = torch.softmax(logits, dim=-1).gather(-1, top_idx)
-    return top_idx, w
+    """x [T, H] -> (expert ids [T, k] int64, routing weights [T, k] fp32); fused kernel on CUDA."""
+    from ..ops.router import route
+    return route(x, gate_w, top_k, norm_topk_prob)
 
 
 def _expert_ffn_ref(x, gate_up_w, down_w):

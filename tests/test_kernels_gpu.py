@@ -264,3 +264,30 @@ def test_flat_adamw_kernel(master):
         torch.testing.assert_close(mast.cpu(), rp, rtol=1e-5, atol=1e-6)
     torch.testing.assert_close(model.float().cpu(), rp.to(torch.bfloat16).float(), rtol=1e-2, atol=1e-2)
     torch.testing.assert_close(m.cpu(), rm, rtol=1e-5, atol=1e-7)
+
+
+@pytest.mark.parametrize("norm_topk", [True, False])
+def test_router_topk_kernel(norm_topk):
+    from cverl_b200.ops import router
+    torch.manual_seed(4)
+    T, H, E, k = 1000, 256, 128, 8
+    x = torch.randn(T, H, device="cuda").bfloat16().requires_grad_(True)
+    gw = (0.2 * torch.randn(E, H, device="cuda")).bfloat16().requires_grad_(True)
+    idx, w = router.route(x, gw, k, norm_topk)
+    xr, gr = x.detach().float().requires_grad_(True), gw.detach().float().requires_grad_(True)
+    ridx, rw = router.route_ref(xr, gr, k, norm_topk)
+    # same experts (as sets; ties and bf16-vs-fp32 logits may reorder near-equal entries) on almost every token
+    same = (idx.sort(-1).values == ridx.sort(-1).values).all(-1)
+    assert same.float().mean() > 0.97
+    order, rorder = idx.argsort(-1), ridx.argsort(-1)
+    torch.testing.assert_close(w.gather(-1, order)[same], rw.gather(-1, rorder)[same], rtol=2e-2, atol=2e-3)
+    assert torch.allclose(w.sum(-1), torch.ones(T, device="cuda"), atol=1e-4) or not norm_topk
+    dw = torch.randn_like(w)
+    w.backward(dw)
+    # reference gradient with the kernel's own selection, so that differing tie-breaks do not matter
+    logits = xr @ gr.t()
+    sel = logits.gather(-1, idx)
+    rw2 = torch.softmax(sel, -1) if norm_topk else torch.softmax(logits, -1).gather(-1, idx)
+    rw2.backward(dw)
+    assert ((x.grad.float() - xr.grad).norm() / xr.grad.norm()).item() < 3e-2
+    assert ((gw.grad.float() - gr.grad).norm() / gr.grad.norm()).item() < 3e-2
