@@ -165,6 +165,28 @@ def case_rmsnorm(a, dev, backward):
     return fn, None, 4 * nbytes
 
 
+def case_attention(a, dev, backward):
+    """Causal GQA attention, Qwen3.5-0.8B shape by default (8 query heads, 2 kv heads, head dim 256)."""
+    from .ops import attention
+    B, S, Hq, Hkv, D = a.batch, a.seq, a.heads if a.heads != 16 else 8, 2, a.head_dim
+    q = _bf(B * S, Hq, D, dev=dev).requires_grad_(True)
+    k = _bf(B * S, Hkv, D, dev=dev).requires_grad_(True)
+    v = _bf(B * S, Hkv, D, dev=dev).requires_grad_(True)
+    flops = 4.0 * B * Hq * S * S * D / 2          # causal: half of the S x S score matrix
+    if not backward:
+        def fn():
+            with torch.no_grad():
+                attention.causal_attention(q, k, v, B, S)
+        return fn, flops, None
+    o = attention.causal_attention(q, k, v, B, S)
+    do = torch.randn_like(o)
+
+    def fn():
+        o.backward(do, retain_graph=True)
+        q.grad = k.grad = v.grad = None
+    return fn, 2.5 * flops, None
+
+
 def case_adamw(a, dev):
     from .ops import optim as oo
     n = a.numel
@@ -196,6 +218,7 @@ def main(argv=None) -> int:
     ap.add_argument("--seq", type=int, default=1280)
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--channels", type=int, default=6144)
+    ap.add_argument("--head-dim", type=int, default=256)
     ap.add_argument("--numel", type=int, default=1 << 28)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--small", action="store_true", help="a few hundred MB: for profiler captures")
@@ -219,6 +242,8 @@ def main(argv=None) -> int:
         fn, flops, nbytes = case_conv(a, dev, k.endswith("bwd"))
     elif k in ("rmsnorm_fwd", "rmsnorm_bwd"):
         fn, flops, nbytes = case_rmsnorm(a, dev, k.endswith("bwd"))
+    elif k in ("attn_fwd", "attn_bwd"):
+        fn, flops, nbytes = case_attention(a, dev, k.endswith("bwd"))
     elif k == "adamw":
         fn, flops, nbytes = case_adamw(a, dev)
     elif k == "ppo_loss":

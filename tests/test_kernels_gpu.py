@@ -291,3 +291,49 @@ def test_router_topk_kernel(norm_topk):
     rw2.backward(dw)
     assert ((x.grad.float() - xr.grad).norm() / xr.grad.norm()).item() < 3e-2
     assert ((gw.grad.float() - gr.grad).norm() / gr.grad.norm()).item() < 3e-2
+
+
+@pytest.mark.parametrize("D,Hq,Hkv", [(256, 4, 1), (128, 4, 2)])
+def test_attention_tcgen05_forward_backward(D, Hq, Hkv):
+    """tcgen05 attention kernels against the fp32 eager statement (GQA, causal), forward and backward."""
+    from cverl_b200.ops import attention, attention_native
+    torch.manual_seed(12)
+    B, S = 2, 384
+    q = torch.randn(B * S, Hq, D, device="cuda").bfloat16().requires_grad_(True)
+    k = torch.randn(B * S, Hkv, D, device="cuda").bfloat16().requires_grad_(True)
+    v = torch.randn(B * S, Hkv, D, device="cuda").bfloat16().requires_grad_(True)
+    assert attention_native.supported(q, k, v, S)
+    o = attention_native.causal_attention(q, k, v, B, S)
+    do = torch.randn_like(o)
+    o.backward(do)
+    from cverl_b200 import _native as nv
+    nv.check_status()
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    o_r = attention.causal_attention_ref(qr, kr, vr, B, S)
+    o_r.backward(do.float())
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
+    assert rel(o, o_r) < 1e-2
+    assert rel(q.grad, qr.grad) < 2e-2
+    assert rel(k.grad, kr.grad) < 2e-2
+    assert rel(v.grad, vr.grad) < 2e-2
+
+
+def test_attention_block_offsets_merge_to_full_attention():
+    """Two key ranges run as separate blocks (the second one causal with position offsets) merge, through their
+    LSEs, to the full causal attention: the contract ring attention relies on."""
+    from cverl_b200.ops import attention, attention_native
+    torch.manual_seed(13)
+    B, S, H, D = 1, 256, 2, 128
+    q = torch.randn(B, S, H, D, device="cuda").bfloat16()
+    k = torch.randn(B, S, H, D, device="cuda").bfloat16()
+    v = torch.randn(B, S, H, D, device="cuda").bfloat16()
+    scale = D ** -0.5
+    q2 = q[:, 128:].contiguous()                      # queries 128..255 against keys 0..127 (all visible) and 128..255
+    o1, l1 = attention_native.attention_block(q2, k[:, :128].contiguous(), v[:, :128].contiguous(), scale, False, 128, 0)
+    o2, l2 = attention_native.attention_block(q2, k[:, 128:].contiguous(), v[:, 128:].contiguous(), scale, True, 128, 128)
+    lse = torch.logaddexp(l1, l2)
+    w1, w2 = (l1 - lse).exp().transpose(1, 2).unsqueeze(-1), (l2 - lse).exp().transpose(1, 2).unsqueeze(-1)
+    merged = o1.float() * w1 + o2.float() * w2
+    full = attention.causal_attention_ref(q.reshape(S, H, D), k.reshape(S, H, D), v.reshape(S, H, D), B, S)
+    ref = full.view(B, S, H, D)[:, 128:].float()
+    assert ((merged - ref).norm() / ref.norm()).item() < 1e-2
