@@ -107,10 +107,86 @@ def _exchange(send: torch.Tensor, send_to: int, recv_from: int, group):
     return recv, dist.batch_isend_irecv(ops)
 
 
+def _native_hops(q, k, v, shard_len: int, original_len: int, cp: int) -> bool:
+    """True when every hop can run on the tcgen05 attention kernels: CUDA bf16, head dim 128 / 256, shards of
+    a multiple of 128 tokens and no padding inside the sequence."""
+    if not q.is_cuda:
+        return False
+    from ..ops import attention_native
+    return attention_native.supported(q, k, v, shard_len) and original_len == cp * shard_len and q.shape[2] == shard_len
+
+
+def _ring_forward_native(ctx, q, k, v, group, cp_rank, cp, shard_len, original_len, scale):
+    """Ring forward with one attention-kernel launch per visible hop: the hop of this rank's own block is
+    causal, earlier blocks are fully visible, later ones are skipped; (out, lse) pairs merge in fp32."""
+    from ..ops import attention_native as an
+    q4 = q.transpose(1, 2).contiguous()                        # [B, Tq, Hq, D]
+    kv = torch.cat([k.transpose(1, 2), v.transpose(1, 2)], dim=-1).contiguous()   # [B, Tk, Hkv, 2D], one payload
+    D = q.shape[-1]
+    out = lse = None
+    for owner, send_to, recv_from in ring_schedule(cp_rank, cp):
+        nxt, reqs = (None, [])
+        if cp > 1 and owner != (cp_rank + 1) % cp:              # not the last step: post the next hop first
+            nxt, reqs = _exchange(kv, send_to, recv_from, group)
+        if owner <= cp_rank:
+            o_h, l_h = an._fwd(q4, kv[..., :D].contiguous(), kv[..., D:].contiguous(), scale, owner == cp_rank,
+                               cp_rank * shard_len, owner * shard_len)
+            if out is None:
+                out, lse = o_h.float(), l_h
+            else:
+                new = torch.logaddexp(lse, l_h)
+                w0 = torch.exp(lse - new).transpose(1, 2).unsqueeze(-1)
+                w1 = torch.exp(l_h - new).transpose(1, 2).unsqueeze(-1)
+                out = out * w0 + o_h.float() * w1
+                lse = new
+        for r in reqs:
+            r.wait()
+        if nxt is not None:
+            kv = nxt
+    out = out.to(q.dtype)
+    ctx.save_for_backward(q4, k, v, out, lse)
+    ctx.cfg = (group, cp_rank, cp, shard_len, original_len, scale)
+    return out.transpose(1, 2)
+
+
+def _ring_backward_native(ctx, do):
+    """Ring backward: K | V travel with their fp32 gradient accumulators; each visible hop runs the attention
+    backward kernels against the FINAL (merged) output and log-sum-exp."""
+    from ..ops import attention_native as an
+    q4, k, v, out, lse = ctx.saved_tensors
+    group, cp_rank, cp, shard_len, original_len, scale = ctx.cfg
+    D = q4.shape[-1]
+    do4 = do.transpose(1, 2).contiguous()
+    dq = torch.zeros(q4.shape, dtype=torch.float32, device=q4.device)
+    k4, v4 = k.transpose(1, 2), v.transpose(1, 2)
+    pay = torch.cat([k4.float(), v4.float(), torch.zeros_like(k4, dtype=torch.float32),
+                     torch.zeros_like(v4, dtype=torch.float32)], dim=-1).contiguous()
+    for owner, send_to, recv_from in ring_schedule(cp_rank, cp):
+        if owner <= cp_rank:
+            kb = pay[..., :D].to(torch.bfloat16).contiguous()
+            vb = pay[..., D:2 * D].to(torch.bfloat16).contiguous()
+            dq_h, dk_h, dv_h = an._bwd(q4, kb, vb, out, lse, do4, scale, owner == cp_rank, cp_rank * shard_len,
+                                       owner * shard_len)
+            dq += dq_h.float()
+            pay[..., 2 * D:3 * D] += dk_h.float()
+            pay[..., 3 * D:] += dv_h.float()
+        if cp > 1:                                              # cp hops bring every block home
+            nxt, reqs = _exchange(pay, send_to, recv_from, group)
+            for r in reqs:
+                r.wait()
+            pay = nxt
+    dk = pay[..., 2 * D:3 * D].to(k.dtype).transpose(1, 2)
+    dv = pay[..., 3 * D:].to(v.dtype).transpose(1, 2)
+    return dq.to(q4.dtype).transpose(1, 2), dk, dv, None, None, None, None, None, None
+
+
 class _RingAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, group, cp_rank, cp, shard_len, original_len, scale):
         B, Hq, Tq, D = q.shape
+        ctx.native = _native_hops(q, k, v, shard_len, original_len, cp)
+        if ctx.native:
+            return _ring_forward_native(ctx, q, k, v, group, cp_rank, cp, shard_len, original_len, scale)
         q_begin = cp_rank * shard_len
         q_pos = torch.arange(q_begin, q_begin + Tq, device=q.device)
         m = torch.full((B, Hq, Tq), float("-inf"), device=q.device)
@@ -147,6 +223,8 @@ class _RingAttention(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, do):
+        if ctx.native:
+            return _ring_backward_native(ctx, do)
         q, k, v, out, lse = ctx.saved_tensors
         group, cp_rank, cp, shard_len, original_len, scale = ctx.cfg
         B, Hq, Tq, D = q.shape

@@ -177,3 +177,41 @@ def _tp_symm_rank(rank, world):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_tp_fused_linear_two_gpus():
     run_ranks(_tp_symm_rank, 2, backend="nccl", timeout=300)
+
+
+def _ring_native_rank(rank, world):
+    import torch.distributed as dist
+    from cverl_b200 import _native as nv
+    from cverl_b200.ops import attention
+    from cverl_b200.parallel.context_parallel import ring_attention
+    dev = torch.device("cuda", rank)
+    B, S, Hq, Hkv, D = 2, 256 * world, 4, 2, 128
+    L = S // world
+    g = torch.Generator(device=dev).manual_seed(21)           # same full tensors on every rank
+    qf = torch.randn(B, Hq, S, D, device=dev, generator=g).bfloat16()
+    kf = torch.randn(B, Hkv, S, D, device=dev, generator=g).bfloat16()
+    vf = torch.randn(B, Hkv, S, D, device=dev, generator=g).bfloat16()
+    wf = torch.randn(B, Hq, S, D, device=dev, generator=g).bfloat16()
+    sl = slice(rank * L, (rank + 1) * L)
+    q, k, v = (t[:, :, sl].contiguous().requires_grad_(True) for t in (qf, kf, vf))
+    out = ring_attention(q, k, v, dist.group.WORLD, rank, world, S)
+    (out.float() * wf[:, :, sl].float()).sum().backward()
+    torch.cuda.synchronize()
+    nv.check_status()
+    # oracle: full causal attention in fp32 on the whole sequence
+    qr, kr, vr = (t.float().requires_grad_(True) for t in (qf, kf, vf))
+    o_r = attention.causal_attention_ref(qr.transpose(1, 2).reshape(B * S, Hq, D), kr.transpose(1, 2).reshape(B * S, Hkv, D),
+                                         vr.transpose(1, 2).reshape(B * S, Hkv, D), B, S)
+    o_r = o_r.view(B, S, Hq, D).transpose(1, 2)
+    (o_r * wf.float()).sum().backward()
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
+    assert rel(out, o_r[:, :, sl]) < 1e-2
+    assert rel(q.grad, qr.grad[:, :, sl]) < 2e-2
+    assert rel(k.grad, kr.grad[:, :, sl]) < 2e-2
+    assert rel(v.grad, vr.grad[:, :, sl]) < 2e-2
+    dist.barrier()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_ring_attention_native_hops_two_gpus():
+    run_ranks(_ring_native_rank, 2, backend="nccl", timeout=300)
