@@ -248,3 +248,55 @@ extern "C" int cvb_sum_parts(const void* parts, long long slot_stride, int world
                                                                   world, static_cast<__nv_bfloat16*>(out), n / 8);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Row scatter / gather over peer memory: the expert-parallel dispatch and combine.
+// Row i of a local [n, row_bytes] matrix corresponds to row `peer_row[i]` of the symmetric matrix on group
+// member `peer_rank[i]` (negative rank = skip).  scatter pushes local rows to the peers, gather pulls them
+// back; one warp moves one row in 16-byte pieces, so a 4 KB activation row is eight coalesced requests.
+// A dispatch is scatter + flag barrier, a combine is flag barrier + gather; their backward passes are each
+// other.  The reference does four ncclSend/ncclRecv all-to-alls per MoE layer
+// (src/distributed/expert_parallel.cc:43-167).
+// ---------------------------------------------------------------------------------------------------
+namespace cvb {
+
+template <bool GATHER>
+__global__ void __launch_bounds__(SY_THREADS)
+p2p_rows_kernel(uint8_t* local, PeerPtrs peers, const int* __restrict__ peer_rank,
+                const long long* __restrict__ peer_row, long long n, int row_vec /* 16-byte vectors per row */) {
+  const long long row = (static_cast<long long>(blockIdx.x) * SY_THREADS + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= n) return;
+  const int pr = peer_rank[row];
+  if (pr < 0 || pr >= MAX_PEERS) return;
+  uint4* mine = reinterpret_cast<uint4*>(local) + row * row_vec;
+  uint4* theirs = reinterpret_cast<uint4*>(peers.p[pr]) + peer_row[row] * row_vec;
+  for (int c = lane; c < row_vec; c += 32) {
+    if (GATHER) mine[c] = theirs[c];
+    else theirs[c] = mine[c];
+  }
+}
+
+}  // namespace cvb
+
+extern "C" int cvb_p2p_scatter_rows(const void* local, void* const* peer_ptrs, int world, const int* peer_rank,
+                                    const long long* peer_row, long long n, long long row_bytes, void* stream) {
+  PeerPtrs pp;
+  if (!fill(&pp, peer_ptrs, world) || row_bytes % 16 || (reinterpret_cast<uintptr_t>(local) & 15)) return -1;
+  if (n <= 0) return 0;
+  const long long blocks = (n * 32 + SY_THREADS - 1) / SY_THREADS;
+  p2p_rows_kernel<false><<<static_cast<unsigned>(blocks), SY_THREADS, 0, ST(stream)>>>(
+      static_cast<uint8_t*>(const_cast<void*>(local)), pp, peer_rank, peer_row, n, static_cast<int>(row_bytes / 16));
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int cvb_p2p_gather_rows(void* local, void* const* peer_ptrs, int world, const int* peer_rank,
+                                   const long long* peer_row, long long n, long long row_bytes, void* stream) {
+  PeerPtrs pp;
+  if (!fill(&pp, peer_ptrs, world) || row_bytes % 16 || (reinterpret_cast<uintptr_t>(local) & 15)) return -1;
+  if (n <= 0) return 0;
+  const long long blocks = (n * 32 + SY_THREADS - 1) / SY_THREADS;
+  p2p_rows_kernel<true><<<static_cast<unsigned>(blocks), SY_THREADS, 0, ST(stream)>>>(
+      static_cast<uint8_t*>(local), pp, peer_rank, peer_row, n, static_cast<int>(row_bytes / 16));
+  return static_cast<int>(cudaGetLastError());
+}

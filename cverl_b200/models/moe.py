@@ -99,6 +99,14 @@ def moe_mlp(model, x: torch.Tensor, layer: int) -> torch.Tensor:
     flat_e = idx.reshape(-1)
     if ctx.ep_size == 1:
         y = _local_experts(rows, flat_e, gate_up, down, e_local)
+    elif ctx.ep_symm is not None and rows.is_cuda and rows.dtype == torch.bfloat16:
+        # dispatch / combine by our own kernels over NVLink peer memory: no host read of the split sizes
+        from ..parallel import ep_symm
+        eps = ctx.ep_symm
+        peer_rank, peer_row, recv_expert = eps.plan(flat_e // e_local, flat_e % e_local, e_local)
+        got_rows = ep_symm.dispatch(rows, peer_rank, peer_row, eps)
+        got_y = _local_experts(got_rows, recv_expert, gate_up, down, e_local)
+        y = ep_symm.combine(got_y, peer_rank, peer_row, eps)
     else:
         import torch.distributed as dist
         dst_rank = flat_e // e_local

@@ -27,6 +27,8 @@ class ParallelContext:
     fused_comm: bool = False
     # ``parallel.tp_symm.TpSymm`` when tensor-parallel linears fuse their all-reduce into the GEMM
     tp_symm: Optional[Any] = None
+    # ``parallel.ep_symm.EpSymm`` when expert-parallel dispatch / combine run over peer-mapped memory
+    ep_symm: Optional[Any] = None
 
     @property
     def single(self) -> bool:

@@ -1,0 +1,155 @@
+"""Expert-parallel dispatch / combine over peer-mapped memory, without a host read.
+
+Every (token, slot) row routed to an expert on another rank is stored straight into that rank's receive
+buffer over NVLink by ``cvb_p2p_scatter_rows`` (one warp per row); expert outputs are pulled back with
+``cvb_p2p_gather_rows``.  The destination row of every routed entry is computed on the device from a
+table of per-(source, destination) counts that the ranks push to each other first, so the layer never
+synchronises with the host (the all-to-all path reads the split sizes on the host).  The backward of a
+dispatch is a gather, the backward of a combine is a scatter.
+
+Buffers have a fixed capacity (``capacity_rows`` per rank); rows beyond the received count are marked with
+the expert id ``num_local_experts`` and skipped by the grouped GEMM.  Overflow sets a device flag that
+``check()`` turns into an exception.
+
+The reference exchanges rows with four NCCL all-to-alls per layer (src/distributed/expert_parallel.cc:43-167).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _native as nv
+from ..ops.gemm import count_launch
+from .symm import SymmBarrier, SymmetricHeap
+
+
+class EpSymm:
+    def __init__(self, group, device, capacity_rows: int, hidden: int):
+        self.heap = SymmetricHeap(group, device)
+        self.world, self.rank = self.heap.world, self.heap.index
+        self.device = torch.device(device)
+        self.cap, self.hidden = capacity_rows, hidden
+        row = hidden * 2
+        self.row_bytes = row
+        self.b_rows = self.heap.alloc(capacity_rows * row)      # dispatched activations (forward)
+        self.b_out = self.heap.alloc(capacity_rows * row)       # expert outputs to be pulled (forward)
+        self.b_gout = self.heap.alloc(capacity_rows * row)      # gradient of the expert outputs (backward)
+        self.b_grow = self.heap.alloc(capacity_rows * row)      # gradient of the dispatched rows (backward)
+        self.b_ids = self.heap.alloc(capacity_rows * 16)        # local expert id of each received row (int32 x4)
+        self.b_cnt = self.heap.alloc(self.world * 32)           # count table [src][8] int32
+        self.rows = self.b_rows.tensor(capacity_rows * hidden, torch.bfloat16).view(capacity_rows, hidden)
+        self.out = self.b_out.tensor(capacity_rows * hidden, torch.bfloat16).view(capacity_rows, hidden)
+        self.gout = self.b_gout.tensor(capacity_rows * hidden, torch.bfloat16).view(capacity_rows, hidden)
+        self.grow = self.b_grow.tensor(capacity_rows * hidden, torch.bfloat16).view(capacity_rows, hidden)
+        self.ids = self.b_ids.tensor(capacity_rows * 4, torch.int32).view(capacity_rows, 4)
+        self.cnt = self.b_cnt.tensor(self.world * 8, torch.int32).view(self.world, 8)
+        self.barrier = SymmBarrier(self.heap)
+        self.overflow = torch.zeros(1, dtype=torch.int32, device=self.device)
+        if self.world > 8:
+            raise ValueError("EpSymm supports up to 8 ranks per expert-parallel group")
+
+    # -- raw row movement ------------------------------------------------------------------------------
+    def _move(self, gather: bool, local: torch.Tensor, buf, peer_rank: torch.Tensor, peer_row: torch.Tensor,
+              row_bytes: int) -> None:
+        fn = nv.cuda().cvb_p2p_gather_rows if gather else nv.cuda().cvb_p2p_scatter_rows
+        nv.check(fn(local.data_ptr(), buf.ptr_array(), self.world, peer_rank.data_ptr(), peer_row.data_ptr(),
+                    peer_rank.numel(), row_bytes, nv.stream()), "cvb_p2p_rows")
+        count_launch()
+
+    def plan(self, dst_rank: torch.Tensor, local_expert: torch.Tensor, num_local: int):
+        """Exchanges counts and returns ``(peer_rank int32 [n], peer_row int64 [n], recv_expert int64 [cap])``:
+        where each routed entry lands, and the local expert of every row this rank receives (``num_local``
+        marks unused capacity)."""
+        n = dst_rank.numel()
+        dev = self.device
+        counts = torch.bincount(dst_rank, minlength=self.world)[:self.world].to(torch.int32)
+        mine = torch.zeros(8, dtype=torch.int32, device=dev)
+        mine[:self.world] = counts
+        self.barrier()                                           # previous users of the table are done
+        src = mine.unsqueeze(0).expand(self.world, 8).contiguous()
+        peers = torch.arange(self.world, dtype=torch.int32, device=dev)
+        slot = torch.full((self.world,), self.rank, dtype=torch.int64, device=dev)
+        self._move(False, src, self.b_cnt, peers, slot, 32)
+        self.barrier()
+        table = self.cnt[:, :self.world].to(torch.int64)         # [src, dst]
+        base = table[:self.rank].sum(0)                          # rows that lower ranks send to each destination
+        received = table[:, self.rank].sum()
+        self.overflow.copy_(torch.maximum(self.overflow, (table.sum(0).max() > self.cap).to(torch.int32).reshape(1)))
+        order = torch.argsort(dst_rank, stable=True)
+        starts = torch.zeros(self.world + 1, dtype=torch.int64, device=dev)
+        starts[1:] = counts.to(torch.int64).cumsum(0)
+        sorted_dst = dst_rank[order]
+        idx_in_seg = torch.arange(n, device=dev) - starts[sorted_dst]
+        peer_row = torch.empty(n, dtype=torch.int64, device=dev)
+        peer_row[order] = (base[sorted_dst] + idx_in_seg).clamp_(max=self.cap - 1)
+        peer_rank = dst_rank.to(torch.int32)
+        # expert ids travel as 16-byte rows
+        idrow = torch.zeros((n, 4), dtype=torch.int32, device=dev)
+        idrow[:, 0] = local_expert.to(torch.int32)
+        self._move(False, idrow, self.b_ids, peer_rank, peer_row, 16)
+        self.barrier()
+        recv_expert = torch.where(torch.arange(self.cap, device=dev) < received, self.ids[:, 0].to(torch.int64),
+                                  torch.full((self.cap,), num_local, dtype=torch.int64, device=dev))
+        return peer_rank, peer_row, recv_expert
+
+    def check(self) -> None:
+        if int(self.overflow.item()) != 0:
+            self.overflow.zero_()
+            raise RuntimeError("EpSymm: a rank received more rows than its buffer capacity")
+
+
+class _Dispatch(torch.autograd.Function):
+    """rows [n, H] -> this rank's receive buffer [cap, H] (a view of symmetric memory)."""
+
+    @staticmethod
+    def forward(ctx, rows, peer_rank, peer_row, eps: EpSymm):
+        ctx.eps, ctx.n = eps, rows.shape[0]
+        ctx.save_for_backward(peer_rank, peer_row)
+        eps.barrier()                                            # receivers finished with the previous contents
+        eps._move(False, rows.contiguous(), eps.b_rows, peer_rank, peer_row, eps.row_bytes)
+        eps.barrier()
+        return eps.rows.clone()
+
+    @staticmethod
+    def backward(ctx, g):
+        eps = ctx.eps
+        peer_rank, peer_row = ctx.saved_tensors
+        eps.barrier()
+        eps.grow.copy_(g)
+        eps.barrier()                                            # every rank's gradient rows are in place
+        out = torch.empty((ctx.n, eps.hidden), dtype=torch.bfloat16, device=g.device)
+        eps._move(True, out, eps.b_grow, peer_rank, peer_row, eps.row_bytes)
+        return out, None, None, None
+
+
+class _Combine(torch.autograd.Function):
+    """expert outputs [cap, H] on the expert ranks -> rows [n, H] back at their source."""
+
+    @staticmethod
+    def forward(ctx, y, peer_rank, peer_row, eps: EpSymm):
+        ctx.eps = eps
+        ctx.save_for_backward(peer_rank, peer_row)
+        eps.barrier()
+        eps.out.copy_(y)
+        eps.barrier()
+        out = torch.empty((peer_rank.numel(), eps.hidden), dtype=torch.bfloat16, device=y.device)
+        eps._move(True, out, eps.b_out, peer_rank, peer_row, eps.row_bytes)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        eps = ctx.eps
+        peer_rank, peer_row = ctx.saved_tensors
+        eps.barrier()
+        eps.gout.zero_()
+        eps.barrier()                                            # cleared everywhere before anyone writes
+        eps._move(False, g.contiguous(), eps.b_gout, peer_rank, peer_row, eps.row_bytes)
+        eps.barrier()
+        return eps.gout.clone(), None, None, None
+
+
+def dispatch(rows: torch.Tensor, peer_rank, peer_row, eps: EpSymm) -> torch.Tensor:
+    return _Dispatch.apply(rows, peer_rank, peer_row, eps)
+
+
+def combine(y: torch.Tensor, peer_rank, peer_row, eps: EpSymm) -> torch.Tensor:
+    return _Combine.apply(y, peer_rank, peer_row, eps)

@@ -103,3 +103,14 @@ def test_parallel_smokes_gloo(mode, nproc):
                        capture_output=True, text=True, timeout=240)
     assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-3000:]
     assert f"{mode} smoke passed" in p.stdout
+
+
+def test_static_trainer_rollout_split_gloo():
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr",
+           "127.0.0.1", "--master-port", "29771", "-m", "cverl_b200.cli.static_split", "--backend", "gloo",
+           "--trainers", "2", "--steps", "2"]
+    p = subprocess.run(cmd, cwd=ROOT, env=dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1"),
+                       capture_output=True, text=True, timeout=240)
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-3000:]
+    assert "weights_in_sync=True" in p.stdout and "trainer rank 0 step 2" in p.stdout
+    assert "rollout rank 2 step 2 sent 16 sequences weight_version=1" in p.stdout     # generated with pushed weights

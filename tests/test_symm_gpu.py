@@ -215,3 +215,44 @@ def _ring_native_rank(rank, world):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_ring_attention_native_hops_two_gpus():
     run_ranks(_ring_native_rank, 2, backend="nccl", timeout=300)
+
+
+def _ep_symm_rank(rank, world):
+    """MoE layer with expert parallelism: dispatch / combine over peer memory against the NCCL all-to-all path."""
+    import torch.distributed as dist
+    from cverl_b200 import _native as nv
+    from cverl_b200.models.config import Qwen35TextConfig
+    from cverl_b200.models.qwen3_5 import Qwen35Model
+    from cverl_b200.parallel.ep_symm import EpSymm
+    from cverl_b200.parallel.mesh import build_context
+    dev = torch.device("cuda", rank)
+    cfg = Qwen35TextConfig.tiny(moe=True, layers=2)
+    outs = []
+    for use_symm in (False, True):
+        ctx = build_context(world, rank, tp=1, dp=1, ep=world)
+        if use_symm:
+            ctx.ep_symm = EpSymm(ctx.ep_group, dev, capacity_rows=2 * 24 * cfg.num_experts_per_tok * world,
+                                 hidden=cfg.hidden_size)
+        model = Qwen35Model(cfg, dtype=torch.bfloat16, device=dev, ctx=ctx)
+        model.init_weights(seed=5)
+        ids = torch.randint(0, cfg.vocab_size, (2, 24), generator=torch.Generator().manual_seed(100 + rank)).to(dev)
+        lp = model.response_logprobs(ids, 8)
+        lp.sum().backward()
+        for p in list(model.flat.params.values()) + list(model.fused.values()):
+            if p.grad is not None:
+                p.main_grad.add_(p.grad.float())
+                p.grad = None
+        torch.cuda.synchronize()
+        nv.check_status()
+        if use_symm:
+            ctx.ep_symm.check()
+        outs.append((lp.detach().float().clone(), model.flat.main_grad.clone()))
+    (lp_a, g_a), (lp_b, g_b) = outs
+    torch.testing.assert_close(lp_b, lp_a, rtol=2e-2, atol=2e-2)
+    assert ((g_b - g_a).norm() / g_a.norm()).item() < 2e-2
+    dist.barrier()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_symm_matches_all_to_all_two_gpus():
+    run_ranks(_ep_symm_rank, 2, backend="nccl", timeout=300)
