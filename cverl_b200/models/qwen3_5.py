@@ -286,7 +286,8 @@ class Qwen35Model(torch.nn.Module):
             from ..parallel.context_parallel import ring_attention
             o = ring_attention(q.view(batch, seq, h, d).transpose(1, 2), k.view(batch, seq, kvh, d).transpose(1, 2),
                                v.reshape(batch, seq, kvh, d).transpose(1, 2), ctx.cp_group, ctx.cp_rank, ctx.cp_size,
-                               self._cp_original_len or seq * ctx.cp_size, 1.0 / math.sqrt(d))
+                               self._cp_original_len or seq * ctx.cp_size, 1.0 / math.sqrt(d),
+                               symm=ctx.cp_symm, key=i)
             o = o.transpose(1, 2).reshape(T, h, d)
         else:
             o = attn_ops.causal_attention(q, k, v, batch, seq, 1.0 / math.sqrt(d))

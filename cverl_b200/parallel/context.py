@@ -29,6 +29,8 @@ class ParallelContext:
     tp_symm: Optional[Any] = None
     # ``parallel.ep_symm.EpSymm`` when expert-parallel dispatch / combine run over peer-mapped memory
     ep_symm: Optional[Any] = None
+    # ``parallel.cp_symm.CpSymm`` when context-parallel attention pulls K / V from peers instead of a ring
+    cp_symm: Optional[Any] = None
 
     @property
     def single(self) -> bool:

@@ -182,9 +182,13 @@ def _ring_backward_native(ctx, do):
 
 class _RingAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, group, cp_rank, cp, shard_len, original_len, scale):
+    def forward(ctx, q, k, v, group, cp_rank, cp, shard_len, original_len, scale, symm=None, key=None):
         B, Hq, Tq, D = q.shape
         ctx.native = _native_hops(q, k, v, shard_len, original_len, cp)
+        ctx.pull = ctx.native and symm is not None and cp > 1
+        if ctx.pull:       # K / V stay where they are: every hop pulls its tiles from the owner over NVLink
+            from . import cp_symm
+            return cp_symm.ring_forward(ctx, q, k, v, symm, key, shard_len, scale)
         if ctx.native:
             return _ring_forward_native(ctx, q, k, v, group, cp_rank, cp, shard_len, original_len, scale)
         q_begin = cp_rank * shard_len
@@ -223,8 +227,11 @@ class _RingAttention(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, do):
+        if ctx.pull:
+            from . import cp_symm
+            return cp_symm.ring_backward(ctx, do) + (None,) * 8
         if ctx.native:
-            return _ring_backward_native(ctx, do)
+            return _ring_backward_native(ctx, do) + (None, None)
         q, k, v, out, lse = ctx.saved_tensors
         group, cp_rank, cp, shard_len, original_len, scale = ctx.cfg
         B, Hq, Tq, D = q.shape
@@ -265,17 +272,20 @@ class _RingAttention(torch.autograd.Function):
                 pay = nxt
         dk = pay[..., D + Dv:2 * D + Dv].to(k.dtype)
         dv = pay[..., 2 * D + Dv:].to(v.dtype)
-        return dq.to(q.dtype), dk, dv, None, None, None, None, None, None
+        return dq.to(q.dtype), dk, dv, None, None, None, None, None, None, None, None
 
 
-def ring_attention(q, k, v, group, cp_rank: int, cp: int, original_len: int, scale: Optional[float] = None):
+def ring_attention(q, k, v, group, cp_rank: int, cp: int, original_len: int, scale: Optional[float] = None,
+                   symm=None, key=None):
     """Causal GQA attention of this rank's query shard over the whole (sharded) sequence.
 
     ``q [B,Hq,Tq,D]``, ``k/v [B,Hkv,Tq,D]`` are this rank's contiguous shard; positions are
-    ``cp_rank*Tq + arange(Tq)``; keys at positions >= ``original_len`` are padding.
+    ``cp_rank*Tq + arange(Tq)``; keys at positions >= ``original_len`` are padding.  With ``symm`` (a
+    ``cp_symm.CpSymm``) and a per-layer ``key`` the hops pull K / V from the owners' peer-mapped buffers instead
+    of passing them around the ring.
     """
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-    return _RingAttention.apply(q, k, v, group, cp_rank, cp, q.shape[2], original_len, scale)
+    return _RingAttention.apply(q, k, v, group, cp_rank, cp, q.shape[2], original_len, scale, symm, key)
 
 
 # ---------------------------------------------------------------------------------------------

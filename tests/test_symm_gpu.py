@@ -179,7 +179,7 @@ def test_tp_fused_linear_two_gpus():
     run_ranks(_tp_symm_rank, 2, backend="nccl", timeout=300)
 
 
-def _ring_native_rank(rank, world):
+def _ring_native_rank(rank, world, pull=False):
     import torch.distributed as dist
     from cverl_b200 import _native as nv
     from cverl_b200.ops import attention
@@ -194,7 +194,11 @@ def _ring_native_rank(rank, world):
     wf = torch.randn(B, Hq, S, D, device=dev, generator=g).bfloat16()
     sl = slice(rank * L, (rank + 1) * L)
     q, k, v = (t[:, :, sl].contiguous().requires_grad_(True) for t in (qf, kf, vf))
-    out = ring_attention(q, k, v, dist.group.WORLD, rank, world, S)
+    symm = None
+    if pull:
+        from cverl_b200.parallel.cp_symm import CpSymm
+        symm = CpSymm(dist.group.WORLD, dev)
+    out = ring_attention(q, k, v, dist.group.WORLD, rank, world, S, symm=symm, key=0)
     (out.float() * wf[:, :, sl].float()).sum().backward()
     torch.cuda.synchronize()
     nv.check_status()
@@ -215,6 +219,13 @@ def _ring_native_rank(rank, world):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_ring_attention_native_hops_two_gpus():
     run_ranks(_ring_native_rank, 2, backend="nccl", timeout=300)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_ring_attention_peer_pull_two_gpus():
+    """Same oracle, but K / V are pulled from the owner's peer-mapped buffer by the attention kernels' TMA loads
+    and dK | dV come home through the staged pull-reduce."""
+    run_ranks(_ring_native_rank, 2, True, backend="nccl", timeout=300)
 
 
 def _ep_symm_rank(rank, world):
