@@ -76,6 +76,15 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--zero-comm", default="nccl", choices=["nccl", "symm"],
                    help="ZeRO gradient reduce-scatter / parameter all-gather: library collectives, or this "
                         "package's kernels over peer-mapped memory (CUDA, bf16 parameters, same node)")
+    g.add_argument("--tp-comm", default="nccl", choices=["nccl", "symm"],
+                   help="tensor-parallel all-reduces: NCCL, or fused into the GEMM epilogue over peer-mapped memory")
+    g.add_argument("--ep-comm", default="nccl", choices=["nccl", "symm"],
+                   help="expert-parallel dispatch / combine: NCCL all-to-all, or row scatter / gather kernels over "
+                        "peer-mapped memory (no host read)")
+    g.add_argument("--cp-comm", default="nccl", choices=["nccl", "symm"],
+                   help="context-parallel attention: ring send/recv, or K / V pulled from the owners by the kernels")
+    g.add_argument("--ep-capacity-factor", type=float, default=2.0,
+                   help="receive-buffer rows per rank for --ep-comm symm, as a multiple of the balanced load")
     g.add_argument("--master-weights", action="store_true")
     g.add_argument("--dp-grad-comm-dtype", default="float32")
     g.add_argument("--seed", type=int, default=1234)
@@ -239,6 +248,19 @@ def run(argv=None) -> int:
             raise SystemExit("--zero-comm symm needs CUDA and --dtype bfloat16")
         from ..parallel.symm import FusedZeroComm, SymmetricHeap
         fused_comm = FusedZeroComm(SymmetricHeap(ctx.dp_group, device))
+    symm_ok = use_cuda and dtype == torch.bfloat16
+    seq_local = (args.prompt_len + args.response_len) // max(args.cp, 1)
+    rows = args.micro_batch_seqs * seq_local
+    if args.tp_comm == "symm" and args.tp > 1 and symm_ok:
+        from ..parallel.tp_symm import TpSymm
+        ctx.tp_symm = TpSymm(ctx.tp_group, device, rows, cfg.hidden_size)
+    if args.ep_comm == "symm" and args.ep > 1 and symm_ok and cfg.is_qwen3_moe:
+        from ..parallel.ep_symm import EpSymm
+        cap = int(rows * cfg.num_experts_per_tok * args.ep_capacity_factor) + 128
+        ctx.ep_symm = EpSymm(ctx.ep_group, device, cap, cfg.hidden_size)
+    if args.cp_comm == "symm" and args.cp > 1 and symm_ok:
+        from ..parallel.cp_symm import CpSymm
+        ctx.cp_symm = CpSymm(ctx.cp_group, device)
     model = Qwen35Model(cfg, dtype=dtype, device=device, ctx=ctx, layer_begin=lb, layer_end=le, first_stage=first,
                         last_stage=last, pad_multiple=args.dp * 8,
                         flat_allocator=fused_comm.allocator if fused_comm else None)
