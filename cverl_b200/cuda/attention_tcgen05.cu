@@ -35,7 +35,7 @@ struct AttSmem {
 struct AttArgs {
   __nv_bfloat16* out;   // [B, Sq, Hq, D]
   float* lse;           // [B, Hq, Sq]  natural-log LSE of the scaled scores (-inf for a fully masked row)
-  int Sq, Skv, Hq, Hkv;
+  int Sq, Skv, Hq, Hkv, B;
   float scale_log2;     // softmax scale * log2(e)
   int causal;
   long long q_pos0, k_pos0;   // positions of query 0 and key 0 (causal: key_pos <= query_pos)
@@ -63,10 +63,13 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
-  const int q0 = blockIdx.x * AT_BQ;
-  const int h = blockIdx.y;
+  // 1-D grid, last query block first: under the causal mask it sees the most keys, so the longest CTAs are
+  // scheduled first and the launch ends with short ones.
+  const int per_block = a.Hq * a.B;
+  const int q0 = (a.Sq / AT_BQ - 1 - static_cast<int>(blockIdx.x / per_block)) * AT_BQ;
+  const int h = (blockIdx.x % per_block) % a.Hq;
   const int hk = h / (a.Hq / a.Hkv);
-  const long long b = blockIdx.z;
+  const long long b = (blockIdx.x % per_block) / a.Hq;
   const uint32_t sb = smem_u32(smem);
 
   // key blocks this query block can see
@@ -282,6 +285,7 @@ static int launch_fwd(const void* q, const void* k, const void* v, void* out, fl
     return -10;
   AttArgs a{};
   a.out = static_cast<__nv_bfloat16*>(out); a.lse = lse; a.Sq = Sq; a.Skv = Skv; a.Hq = Hq; a.Hkv = Hkv;
+  a.B = static_cast<int>(B);
   a.scale_log2 = scale * 1.4426950408889634f; a.causal = causal; a.q_pos0 = q_pos0; a.k_pos0 = k_pos0;
   a.status = status;
   static bool attr = false;
@@ -291,7 +295,7 @@ static int launch_fwd(const void* q, const void* k, const void* v, void* out, fl
       return -11;
     attr = true;
   }
-  dim3 grid(Sq / AT_BQ, Hq, static_cast<unsigned>(B));
+  dim3 grid(static_cast<unsigned>((Sq / AT_BQ) * Hq * B));
   attention_fwd_kernel<D><<<grid, AT_THREADS, AttSmem<D>::BYTES, st>>>(mq, mk, mv, a);
   return static_cast<int>(cudaGetLastError());
 }
@@ -329,7 +333,7 @@ extern "C" int cvb_attention_fwd(const void* q, const void* k, const void* v, vo
 // queries of one d), and a last kernel turns that buffer into bf16 [B, Sq, Hq, D].
 // TMEM has 512 columns: with D = 128 everything fits in one kernel (MODE 0); with D = 256 the work is
 // split into a dV kernel (MODE 1: S^T, dV) and a dK / dQ kernel (MODE 2: S^T, dP^T, dK, dQ^T).
-// dK / dV are produced per QUERY head; the caller sums the heads of a GQA group.
+// A CTA walks the query blocks of EVERY query head of its GQA group, so dK / dV come out already summed.
 // =================================================================================================
 constexpr int AB_BKV = 128;  // keys per CTA
 constexpr int AB_BQ = 64;    // queries per step
@@ -358,10 +362,10 @@ struct AttBwdCfg {
 struct AttBwdArgs {
   const float* lse;      // [B, Hq, Sq] natural log
   const float* delta;    // [B, Hq, Sq] rowsum(dO * O)
-  __nv_bfloat16* dk;     // [B, Skv, Hq, D] per query head
-  __nv_bfloat16* dv;     // [B, Skv, Hq, D]
+  __nv_bfloat16* dk;     // [B, Skv, Hkv, D]
+  __nv_bfloat16* dv;     // [B, Skv, Hkv, D]
   float* dqt;            // [B, Hq, D, Sq] fp32, zero-initialised, accumulated with reductions
-  int Sq, Skv, Hq, Hkv;
+  int Sq, Skv, Hq, Hkv, B;
   float scale, scale_log2;
   int causal;
   long long q_pos0, k_pos0;
@@ -386,10 +390,13 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
-  const int k0 = blockIdx.x * AB_BKV;
-  const int h = blockIdx.y;
-  const int hk = h / (a.Hq / a.Hkv);
-  const long long b = blockIdx.z;
+  // 1-D grid with the key block slowest: causal key blocks near the start see the most queries, so the
+  // longest CTAs are scheduled first and the tail of the launch consists of short ones.
+  const int per_block = a.Hkv * a.B;                        // (kv head, batch) pairs per key block
+  const int k0 = (blockIdx.x / per_block) * AB_BKV;
+  const int hk = (blockIdx.x % per_block) % a.Hkv;
+  const long long b = (blockIdx.x % per_block) / a.Hkv;
+  const int group = a.Hq / a.Hkv;                           // query heads that share this kv head
   const uint32_t sb = smem_u32(smem);
   const long long kpos = a.k_pos0 + k0 + tid;
 
@@ -400,11 +407,13 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     m_begin = need <= 0 ? 0 : static_cast<int>((need + AB_BQ - 1) / AB_BQ);
     if (m_begin > nq) m_begin = nq;
   }
-  const int steps = nq - m_begin;
+  const int per_head = nq - m_begin;          // query blocks per head that see this key block
+  const int steps = per_head * group;         // dK / dV accumulate over every query head of the GQA group
 
   auto load_q = [&](int it) {
     const int buf = it % C::NBUF;
-    const int m = m_begin + it;
+    const int m = m_begin + it % per_head;
+    const int h = hk * group + it / per_head;
     const int qrow = static_cast<int>(b * a.Sq + static_cast<long long>(m) * AB_BQ);
     mbar_arrive_expect_tx(&bar_q[buf], 2u * D * 128u);
 #pragma unroll
@@ -452,7 +461,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   }
   for (int it = 0; it < steps && ok; ++it) {
     const int buf = it % C::NBUF;
-    const int m = m_begin + it;
+    const int m = m_begin + it % per_head;
+    const int h = hk * group + it / per_head;
     const uint32_t phq = (it / C::NBUF) & 1, pit = it & 1;
     const uint32_t qb = sb + C::Q + buf * (D * 128), dob = sb + C::DO + buf * (D * 128);
     // per-query scalars of this block
@@ -602,7 +612,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     mbar_wait_bounded(&bar_q[1], 0, &dummy);
   }
   if (ok) {
-    const long long orow = ((b * a.Skv + k0 + tid) * a.Hq + h) * D;
+    const long long orow = ((b * a.Skv + k0 + tid) * a.Hkv + hk) * D;
 #pragma unroll 1
     for (int which = 0; which < 2; ++which) {
       if ((which == 0 && !C::NEED_PT) || (which == 1 && !C::NEED_DS)) continue;
@@ -693,14 +703,14 @@ static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
       return -11;
     attr = true;
   }
-  dim3 grid(a.Skv / AB_BKV, a.Hq, static_cast<unsigned>(B));
+  dim3 grid(static_cast<unsigned>((a.Skv / AB_BKV) * a.Hkv * B));
   attention_bwd_kernel<D, MODE><<<grid, AT_THREADS, C::BYTES, st>>>(mq, mk, mv, mdo, a);
   return static_cast<int>(cudaGetLastError());
 }
 
 // q, o, d_o: bf16 [B, Sq, Hq, D]; k, v: bf16 [B, Skv, Hkv, D]; lse: fp32 [B, Hq, Sq] from the forward.
 // Scratch: delta fp32 [B, Hq, Sq]; dqt fp32 [B, Hq, D, Sq], zeroed by the caller.
-// Outputs: dq bf16 [B, Sq, Hq, D]; dk, dv bf16 [B, Skv, Hq, D] PER QUERY HEAD (sum the GQA group afterwards).
+// Outputs: dq bf16 [B, Sq, Hq, D]; dk, dv bf16 [B, Skv, Hkv, D] (summed over the query heads of each GQA group).
 // Sq % 64 == 0, Skv % 128 == 0.
 extern "C" int cvb_attention_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
                                  const float* lse, float* delta, float* dqt, void* dq, void* dk, void* dv, long long B,
@@ -720,7 +730,7 @@ extern "C" int cvb_attention_bwd(const void* q, const void* k, const void* v, co
       static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), delta, B, Sq, Hq, D);
   AttBwdArgs a{};
   a.lse = lse; a.delta = delta; a.dk = static_cast<__nv_bfloat16*>(dk); a.dv = static_cast<__nv_bfloat16*>(dv);
-  a.dqt = dqt; a.Sq = Sq; a.Skv = Skv; a.Hq = Hq; a.Hkv = Hkv; a.scale = scale;
+  a.dqt = dqt; a.Sq = Sq; a.Skv = Skv; a.Hq = Hq; a.Hkv = Hkv; a.B = static_cast<int>(B); a.scale = scale;
   a.scale_log2 = scale * 1.4426950408889634f; a.causal = causal; a.q_pos0 = q_pos0; a.k_pos0 = k_pos0; a.status = status;
   int rc;
   if (D == 128) {

@@ -49,20 +49,14 @@ def _bwd(q4, k4, v4, out, lse, dout, scale, causal, q_pos0, k_pos0):
     delta = torch.empty((B, Hq, Sq), dtype=torch.float32, device=dev)
     dqt = torch.zeros((B, Hq, D, Sq), dtype=torch.float32, device=dev)
     dq = torch.empty_like(q4)
-    dkh = torch.empty((B, Skv, Hq, D), dtype=torch.bfloat16, device=dev)
-    dvh = torch.empty((B, Skv, Hq, D), dtype=torch.bfloat16, device=dev)
+    dk = torch.empty((B, Skv, Hkv, D), dtype=torch.bfloat16, device=dev)   # summed over each GQA group in-kernel
+    dv = torch.empty((B, Skv, Hkv, D), dtype=torch.bfloat16, device=dev)
     rc = nv.cuda().cvb_attention_bwd(q4.data_ptr(), k4.data_ptr(), v4.data_ptr(), out.data_ptr(), dout.data_ptr(),
-                                     lse.data_ptr(), delta.data_ptr(), dqt.data_ptr(), dq.data_ptr(), dkh.data_ptr(),
-                                     dvh.data_ptr(), B, Sq, Skv, Hq, Hkv, D, scale, int(causal), q_pos0, k_pos0,
+                                     lse.data_ptr(), delta.data_ptr(), dqt.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+                                     dv.data_ptr(), B, Sq, Skv, Hq, Hkv, D, scale, int(causal), q_pos0, k_pos0,
                                      nv.status_word(dev).data_ptr(), nv.stream())
     nv.check(rc, "cvb_attention_bwd")
     count_launch(4 if D == 128 else 5)
-    g = Hq // Hkv
-    if g > 1:   # the kernels produce dK / dV per query head: sum each GQA group
-        dk = dkh.view(B, Skv, Hkv, g, D).float().sum(3).to(torch.bfloat16)
-        dv = dvh.view(B, Skv, Hkv, g, D).float().sum(3).to(torch.bfloat16)
-    else:
-        dk, dv = dkh, dvh
     return dq, dk, dv
 
 

@@ -108,8 +108,8 @@ def ring_backward(ctx, do):
         delta = torch.empty((B, Hq, L), dtype=torch.float32, device=q4.device)
         dqt = torch.zeros((B, Hq, D, L), dtype=torch.float32, device=q4.device)
         dq_h = torch.empty_like(q4)
-        dkh = torch.empty((B, L, Hq, D), dtype=torch.bfloat16, device=q4.device)
-        dvh = torch.empty((B, L, Hq, D), dtype=torch.bfloat16, device=q4.device)
+        dkh = torch.empty((B, L, Hkv, D), dtype=torch.bfloat16, device=q4.device)
+        dvh = torch.empty((B, L, Hkv, D), dtype=torch.bfloat16, device=q4.device)
         rc = lib.cvb_attention_bwd(q4.data_ptr(), bk.peer_ptrs[owner], bv.peer_ptrs[owner], out.data_ptr(),
                                    do4.data_ptr(), lse.data_ptr(), delta.data_ptr(), dqt.data_ptr(), dq_h.data_ptr(),
                                    dkh.data_ptr(), dvh.data_ptr(), B, L, L, Hq, Hkv, D, scale, int(owner == cp_rank),
@@ -118,9 +118,8 @@ def ring_backward(ctx, do):
         nv.check(rc, "cvb_attention_bwd (peer pull)")
         count_launch(5)
         dq += dq_h.float()
-        g = Hq // Hkv
-        stage[owner, 0] = dkh.view(B, L, Hkv, g, D).float().sum(3)
-        stage[owner, 1] = dvh.view(B, L, Hkv, g, D).float().sum(3)
+        stage[owner, 0] = dkh.float()
+        stage[owner, 1] = dvh.float()
     cps.barrier()                                   # every contribution is staged
     dkv = torch.empty((2,) + tuple(kshape), dtype=torch.float32, device=q4.device)
     sq = torch.zeros(1, dtype=torch.float32, device=q4.device)
