@@ -285,10 +285,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         tmem_ld_32x32(taddr + c, r);
         tmem_ld_wait();
         const int col0 = n0 + c;
-        if (p.n_mirror > 0) {
-          // Mirrored bf16 store (N % 64 == 0): two 32-column chunks of this warp's 32 rows are staged in
+        if (p.staged_store) {
+          // Staged bf16 store (N % 64 == 0): two 32-column chunks of this warp's 32 rows are staged in
           // shared memory, then written out as 128-byte row segments (8 lanes per row) to the local C and
-          // to every mirror: full-line stores keep the NVLink writes efficient.
+          // to every mirror: full-line stores keep the L2 / NVLink writes efficient.
           if (col0 < p.N) {
             uint8_t* stg = smem + Cfg::STG_OFF + q * Cfg::STG_WARP;
             uint8_t* mine = stg + lane * Cfg::STG_ROW + (c & 32) * 2;
@@ -535,6 +535,12 @@ extern "C" int cvb_gemm_bf16(const CvbGemmArgs* a, void* stream_v) {
   if (a->n_mirror < 0 || a->n_mirror > 7 || (a->n_mirror > 0 && (a->epi != EPI_STORE_BF16 || a->N % 64 != 0)))
     return -6;
   p.n_mirror = a->n_mirror;
+  {
+    // Default: stage every bf16 store whose N allows it.  CVERL_B200_GEMM_DIRECT_STORE=1 keeps the
+    // register -> global path for comparison.
+    static const bool direct = [] { const char* e = getenv("CVERL_B200_GEMM_DIRECT_STORE"); return e && e[0] == '1'; }();
+    p.staged_store = (a->epi == EPI_STORE_BF16 && a->N % 64 == 0 && (a->n_mirror > 0 || !direct)) ? 1 : 0;
+  }
   for (int m = 0; m < a->n_mirror; ++m) {
     if (!a->mirror[m] || (reinterpret_cast<uintptr_t>(a->mirror[m]) & 15)) return -6;
     p.mirror[m] = a->mirror[m];

@@ -83,6 +83,7 @@ struct GemmParams {
   int* status;
   void* mirror[7];
   int n_mirror;
+  int staged_store;  // bf16 epilogue through shared memory (coalesced 128-byte segments)
 };
 int make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
                        uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);

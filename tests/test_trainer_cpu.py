@@ -91,6 +91,32 @@ def test_checkpoint_resume_equality_and_formats(tmp_path):
     assert bad.returncode != 0
 
 
+def test_resume_refuses_damaged_checkpoints(tmp_path):
+    """Host-side fault injection on the checkpoint: an incomplete manifest, a manifest whose step disagrees with
+    the archive, and a missing rank file must each stop the resume with an error instead of training on."""
+    import shutil
+    ck = tmp_path / "ck"
+    _run(1, "--steps", "2", "--checkpoint-dir", str(ck), "--checkpoint-every", "2", port=29686)
+    step_dir = ck / "step_000002"
+    good = json.loads((step_dir / "manifest.json").read_text())
+
+    def resume_fails(mutate):
+        work = tmp_path / "work"
+        if work.exists():
+            shutil.rmtree(work)
+        shutil.copytree(ck, work)
+        mutate(work / "step_000002")
+        p = _run(1, "--steps", "3", "--resume-checkpoint", str(work), port=29687, check=False)
+        assert p.returncode != 0, p.stdout[-500:]
+
+    resume_fails(lambda d: (d / "manifest.json").write_text(json.dumps(dict(good, complete=False))))
+    resume_fails(lambda d: (d / "manifest.json").write_text(json.dumps(dict(good, step=7))))
+    resume_fails(lambda d: (d / "rank_0.pt").unlink())
+    # the untouched checkpoint still resumes
+    ok = _lines(_run(1, "--steps", "3", "--resume-checkpoint", str(ck), port=29688))
+    assert [r["step"] for r in ok] == ["2"]
+
+
 def test_sft_jsonl_mode(tmp_path):
     data = tmp_path / "sft.jsonl"
     data.write_text("\n".join(json.dumps({"prompt": f"q{i}?", "answer": f"a{i}"}) for i in range(8)))
