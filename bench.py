@@ -37,7 +37,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("CVERL_BENCH_MICRO_BATCH", "16")))
+    ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("CVERL_BENCH_MICRO_BATCH", "32")))
     ap.add_argument("--tp", type=int, default=int(os.environ.get("CVERL_BENCH_TP", "0")))
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
     ap.add_argument("--tp-comm", default=os.environ.get("CVERL_BENCH_TP_COMM", "symm"), choices=["symm", "nccl"],
@@ -229,6 +229,7 @@ def main():
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": launches,
             "loss": float(last["m"][0]),
+            "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 1),
         }
         if args.layers:
             out["invalid"] = "debug run with fewer layers"
