@@ -37,7 +37,8 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("CVERL_BENCH_MICRO_BATCH", "32")))
+    ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("CVERL_BENCH_MICRO_BATCH", "0")),
+                    help="sequences per micro-batch; 0 = 32 per tensor-parallel rank (about 100 GB of the 180 GB HBM)")
     ap.add_argument("--tp", type=int, default=int(os.environ.get("CVERL_BENCH_TP", "0")))
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
     ap.add_argument("--tp-comm", default=os.environ.get("CVERL_BENCH_TP_COMM", "symm"), choices=["symm", "nccl"],
@@ -140,6 +141,8 @@ def main():
 
     tp = args.tp if args.tp > 0 else (2 if world >= 2 else 1)
     dp = world // tp
+    if args.micro_batch <= 0:
+        args.micro_batch = 32 * tp
     ctx = build_context(world, rank, tp=tp, dp=dp)
     cfg = Qwen35TextConfig.qwen3_5_0_8b()
     if args.layers:
