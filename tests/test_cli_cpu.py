@@ -114,3 +114,28 @@ def test_static_trainer_rollout_split_gloo():
     assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-3000:]
     assert "weights_in_sync=True" in p.stdout and "trainer rank 0 step 2" in p.stdout
     assert "rollout rank 2 step 2 sent 16 sequences weight_version=1" in p.stdout     # generated with pushed weights
+
+
+def test_online_grpo_oracle_dumps_rollouts_that_the_trainer_consumes(tiny_dir, tmp_path, capsys):
+    from cverl_b200.cli import online_grpo
+    data = tmp_path / "gsm.jsonl"
+    data.write_text("\n".join(json.dumps({"prompt": f"What is {i}+{i}?", "answer": f"#### {2 * i}"}) for i in range(6)))
+    rdir = tmp_path / "rollouts"
+    rc = online_grpo.main(["--model-dir", str(tiny_dir), "--dataset", str(data), "--rollout", "oracle", "--steps", "2",
+                           "--prompts", "2", "--n", "4", "--max-prompt-tokens", "16", "--max-response-tokens", "12",
+                           "--lr", "1e-3", "--dump-rollout-dir", str(rdir), "--push-weights"])
+    assert rc == 0
+    rows = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
+    assert [r["step"] for r in rows] == [0, 1] and rows[0]["total_seq"] == 8.0 and rows[0]["pushed_bytes"] > 0
+    assert 0.0 < rows[0]["mean_reward"] < 1.0 and rows[0]["param_delta"] > 0
+    f0 = json.loads((rdir / "rollout_step_000000.json").read_text())
+    assert f0["step"] == 0 and len(f0["sequences"]) == 8 and {"prompt_ids", "response_ids", "advantage"} <= set(f0["sequences"][0])
+    # the distributed trainer reads these files step by step
+    cmd = [sys.executable, "-m", "cverl_b200.trainer.ppo_trainer", "--backend", "gloo", "--dtype", "float32",
+           "--steps", "2", "--rollout-dir", str(rdir), "--prompt-len", "16", "--response-len", "12",
+           "--micro-batches", "2", "--micro-batch-seqs", "2"]
+    env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1", MASTER_ADDR="127.0.0.1", MASTER_PORT="29779",
+               RANK="0", WORLD_SIZE="1", LOCAL_RANK="0")
+    p = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=240)
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-3000:]
+    assert p.stdout.count("step=") == 2
