@@ -60,6 +60,7 @@ _CUDA_PROTOS = {
     "cvb_siggate_bwd": "ppppp l i ll ii ll i p",
     "cvb_conv1d_silu_fwd": "ppp l iii l p",
     "cvb_conv1d_silu_bwd": "ppppp l iii ll p",
+    "cvb_conv1d_silu_bwd_tma": "ppppp l iii ll p p",
     "cvb_embedding_fwd": "ppp l i ll p",
     "cvb_embedding_bwd": "ppp l i ll p",
     "cvb_cast_f32_to_bf16": "pp l f p",

@@ -45,15 +45,17 @@ struct PrepArgs {
 struct PrepSmem {
   static constexpr int KQ = 0;            // K box0 | Q box0 | K box1 | Q box1   (4 x 8 KB)
   static constexpr int V = 32768;         // V box0 | V box1
+  static constexpr int AM = 49152;        // fp32 [64][64]; dead after the substitution, then reused as:
   static constexpr int TP = 49152;        // T'  bf16 [64 x 64]
   static constexpr int TPP = 57344;       // T'' bf16 [64 x 64]
-  static constexpr int AM = 65536;        // fp32 [64][64]
-  static constexpr int SC = 81920;        // scalars: c, beta, rk, rq, partial sums
+  static constexpr int SC = 65536;        // scalars: c, beta, rk, rq, partial sums
   static constexpr int BARS = SC + 2048;
   static constexpr int BYTES = BARS + 128 + 1024;
 };
 
-__global__ void __launch_bounds__(CTHREADS, 2)
+// Three CTAs per SM (168 registers, 68 KB of shared memory, 128 TMEM columns each): every CTA is one serial
+// chain load -> MMA -> substitution -> MMA -> store, so the SM is kept busy by the other CTAs' phases.
+__global__ void __launch_bounds__(CTHREADS, 3)
 gdn_chunk_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const PrepArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -94,7 +96,7 @@ gdn_chunk_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   }
   if (warp == 0) {
     __syncwarp();
-    tmem_alloc(tmem_slot, 256);
+    tmem_alloc(tmem_slot, 128);  // columns 0-63: D1, then W^T; 64-127: U^T
     tmem_relinquish();
   }
   if (tid < CC) {
@@ -206,20 +208,24 @@ gdn_chunk_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     float col[CC];
 #pragma unroll
     for (int r = 0; r < CC; ++r) {
-      float acc = (r == j) ? 1.f : 0.f;
+      // four partial sums: the dot product of row r with the solved prefix is a reduction, and one
+      // accumulator would make it a chain of r dependent FMAs
+      float a0 = (r == j) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
       const float4* arow = reinterpret_cast<const float4*>(Am + r * CC);
 #pragma unroll
       for (int m4 = 0; m4 < (r + 3) / 4; ++m4) {
         const float4 av = arow[m4];
-        if (4 * m4 + 0 < r) acc -= av.x * col[4 * m4 + 0];
-        if (4 * m4 + 1 < r) acc -= av.y * col[4 * m4 + 1];
-        if (4 * m4 + 2 < r) acc -= av.z * col[4 * m4 + 2];
-        if (4 * m4 + 3 < r) acc -= av.w * col[4 * m4 + 3];
+        if (4 * m4 + 0 < r) a0 -= av.x * col[4 * m4 + 0];
+        if (4 * m4 + 1 < r) a1 -= av.y * col[4 * m4 + 1];
+        if (4 * m4 + 2 < r) a2 -= av.z * col[4 * m4 + 2];
+        if (4 * m4 + 3 < r) a3 -= av.w * col[4 * m4 + 3];
       }
-      col[r] = acc;
+      col[r] = (a0 + a1) + (a2 + a3);
     }
     const float fj = s_beta[j];
     const float fk = fj * __expf(s_c[j]) * s_rk[j];
+    // T' and T'' overwrite A: wait until both substitution warps have read their last row of it
+    asm volatile("bar.sync 1, 64;" ::: "memory");
     uint8_t* tp = smem + PrepSmem::TP;
     uint8_t* tpp = smem + PrepSmem::TPP;
 #pragma unroll
@@ -279,12 +285,12 @@ gdn_chunk_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const uint32_t tp = smem_u32(smem + PrepSmem::TP), tpp = smem_u32(smem + PrepSmem::TPP);
 #pragma unroll
     for (int k = 0; k < CC / 16; ++k) {
-      umma_bf16(tmem_base + 64, umma_smem_desc(kq + k * 2048, 16384, 1024), umma_smem_desc(tp + k * 32, 16, 1024),
+      umma_bf16(tmem_base, umma_smem_desc(kq + k * 2048, 16384, 1024), umma_smem_desc(tp + k * 32, 16, 1024),
                 idesc, k > 0);
     }
 #pragma unroll
     for (int k = 0; k < CC / 16; ++k) {
-      umma_bf16(tmem_base + 128, umma_smem_desc(vv + k * 2048, 8192, 1024), umma_smem_desc(tpp + k * 32, 16, 1024),
+      umma_bf16(tmem_base + 64, umma_smem_desc(vv + k * 2048, 8192, 1024), umma_smem_desc(tpp + k * 32, 16, 1024),
                 idesc, k > 0);
     }
     umma_commit(bar_m2);
@@ -305,7 +311,7 @@ gdn_chunk_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll 1
       for (int c0 = 0; c0 < CC; c0 += 32) {
         uint32_t r[32];
-        tmem_ld_32x32(tmem + 64 + which * 64 + c0, r);
+        tmem_ld_32x32(tmem + which * 64 + c0, r);
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) stage[(c0 + j) * CD + tid] = __float2bfloat16_rn(__uint_as_float(r[j]));
@@ -325,7 +331,7 @@ done:
   __syncthreads();
   if (warp == 0) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 256);
+    tmem_dealloc(tmem_base, 128);
   }
 }
 

@@ -6,6 +6,8 @@ Reference math: src/model/qwen3_5_text.cc:791-793, :1077-1079, :1241-1243, :692.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.nn.functional as F
 
@@ -140,9 +142,17 @@ class _ConvSilu(torch.autograd.Function):
         dy = dy.contiguous()
         dx = torch.empty((B, S, Cc), dtype=x3.dtype, device=x3.device)
         dwbuf, is_main = _wgrad_buffer(w)
-        nv.check(nv.cuda().cvb_conv1d_silu_bwd(dy.data_ptr(), x3.data_ptr(), wc.data_ptr(), dx.data_ptr(),
+        # the TMA-tiled kernel answers -2 for layouts it does not take (C not a multiple of 64, odd strides)
+        rc = -2
+        if os.environ.get("CVERL_B200_CONV_BWD", "tma") == "tma":
+            rc = nv.cuda().cvb_conv1d_silu_bwd_tma(dy.data_ptr(), x3.data_ptr(), wc.data_ptr(), dx.data_ptr(),
+                                                   dwbuf.data_ptr(), B, S, Cc, wc.shape[1], x3.stride(1), Cc,
+                                                   nv.status_word(x3.device).data_ptr(), nv.stream())
+        if rc == -2:
+            rc = nv.cuda().cvb_conv1d_silu_bwd(dy.data_ptr(), x3.data_ptr(), wc.data_ptr(), dx.data_ptr(),
                                                dwbuf.data_ptr(), B, S, Cc, wc.shape[1], x3.stride(1), Cc,
-                                               nv.stream()), "cvb_conv1d_silu_bwd")
+                                               nv.stream())
+        nv.check(rc, "cvb_conv1d_silu_bwd")
         count_launch()
         return dx, (None if is_main else dwbuf.to(w.dtype))
 

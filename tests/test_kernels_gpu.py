@@ -141,20 +141,28 @@ def test_siggate_strided_gate():
     assert _rel_err(g.grad, gr.grad) < 8e-3
 
 
-@pytest.mark.parametrize("S", [5, 64, 200])
-def test_conv1d_silu(S):
+@pytest.mark.parametrize("path", ["tma", "plain"])
+@pytest.mark.parametrize("S,Cc,KW", [(5, 256, 4), (64, 256, 4), (200, 256, 4), (131, 320, 3), (70, 40, 4), (129, 64, 2)])
+def test_conv1d_silu(S, Cc, KW, path, monkeypatch):
+    """Both backward kernels (the TMA-tiled one takes C % 64 == 0 and falls back otherwise), partial channel
+    tiles, sequence lengths that end inside a tile, a column slice of a wider tensor as the input."""
     from cverl_b200.ops import conv1d_silu
     from cverl_b200.ops.activation import conv1d_silu_ref
+    from cverl_b200 import _native as nv
+    monkeypatch.setenv("CVERL_B200_CONV_BWD", path)
     torch.manual_seed(10)
-    B, Cc = 3, 256
-    x = torch.randn(B, S, Cc, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
-    w = (0.5 * torch.randn(Cc, 4, device=_dev())).to(torch.bfloat16).requires_grad_(True)
+    B = 3
+    wide = torch.randn(B, S, Cc + 64, device=_dev(), dtype=torch.bfloat16)
+    x = wide[:, :, 32:32 + Cc].detach().requires_grad_(True)
+    w = (0.5 * torch.randn(Cc, KW, device=_dev())).to(torch.bfloat16).requires_grad_(True)
     y = conv1d_silu(x, w)
+    nv.check_status(_dev())
     dy = torch.randn_like(y)
     y.backward(dy)
     xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
     yr = conv1d_silu_ref(xr, wr)
     yr.backward(dy.float())
+    nv.check_status(_dev())
     assert _rel_err(y, yr) < 8e-3
     assert _rel_err(x.grad, xr.grad) < 1e-2
     assert _rel_err(w.grad, wr.grad) < 2e-2
