@@ -85,7 +85,7 @@ _CUDA_PROTOS = {
     "cvb_can_access_peer": "ii",
     "cvb_gdn_chunk_prep": "ppp l pp l ii ff pppppppp p p",
     "cvb_gdn_chunk_out": "ppppp l ii p p",
-    "cvb_gdn_chunk_bwd": "ppp l p ppp pp pp p p l ii f ppp pp p p",
+    "cvb_gdn_chunk_bwd": "ppp l p ppp pp pp p p l ii f ppp l pp p p",
     "cvb_gdn_scan_fwd": "pppppppp l i p p",
     "cvb_gdn_scan_bwd": "pppppppppp l i p p",
     "cvb_symm_barrier": "p iii p p",

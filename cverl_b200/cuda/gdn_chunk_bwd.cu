@@ -41,7 +41,8 @@ struct BwdArgs {
   const float* Tm;     // [items, 64, 64]
   const float* aux;    // [items, 3, 64]: c, rq (with scale), rk
   const float* dgam;   // [items]
-  __nv_bfloat16 *dq, *dk, *dv;  // [B, T, H, 128]
+  __nv_bfloat16 *dq, *dk, *dv;  // [B, T, H, 128] with token stride d_stride (elements)
+  long long d_stride;
   float* dbeta;        // [B, T, H]
   float* dg;           // [B, T, H]
   int T, H, n_chunks;
@@ -324,7 +325,7 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   // ---- stage 4 (lanes 0-63): dv, <dVb, v>, <dKb, k>; dVb and dKb rows go back as bf16 operands -------------
   if (warp < 2) {
     const float bt = s_beta[t];
-    __nv_bfloat16* dvrow = a.dv + ((row0 + t) * a.H + h) * BD;
+    __nv_bfloat16* dvrow = a.dv + (row0 + t) * a.d_stride + h * BD;
     float dbv = 0.f;
 #pragma unroll 1
     for (int c0 = 0; c0 < BD; c0 += 32) {
@@ -483,7 +484,7 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
     tmem_st_wait();
     const float coef = rkt * rkt * bk;
-    __nv_bfloat16* dkrow = a.dk + ((row0 + t) * a.H + h) * BD;
+    __nv_bfloat16* dkrow = a.dk + (row0 + t) * a.d_stride + h * BD;
 #pragma unroll 1
     for (int c0 = 0; c0 < BD; c0 += 32) {
       uint32_t r[32];
@@ -513,7 +514,7 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       for (int j = 0; j < 32; ++j) aq += __uint_as_float(r[j]) * x[j];
     }
     const float coef = rq_ns * rq_ns * aq;
-    __nv_bfloat16* dqrow = a.dq + ((row0 + t) * a.H + h) * BD;
+    __nv_bfloat16* dqrow = a.dq + (row0 + t) * a.d_stride + h * BD;
 #pragma unroll 1
     for (int c0 = 0; c0 < BD; c0 += 32) {
       uint32_t r[32];
@@ -598,15 +599,20 @@ using namespace cvb;
 // q, k, v: bf16 views [B, T, H, 128] as for cvb_gdn_chunk_prep (common token stride `tok_stride`); dO: bf16
 // [B, T, H, 128] contiguous; beta: fp32 [B, T, H]; Tm, aux: the prep kernel's outputs; Vn, dVn: bf16
 // [BH, n, 64, 128]; ST, dST: bf16 [BH, n, 128, 128] (chunk-start state and dS_next, both transposed); Sf: fp32
-// [BH, 128, 128] final state; dgam: fp32 [BH, n] scratch.  Outputs dq, dk, dv: bf16 [B, T, H, 128]; dbeta, dg:
-// fp32 [B, T, H].
+// [BH, 128, 128] final state; dgam: fp32 [BH, n] scratch.  Outputs dq, dk, dv: bf16 [B, T, H, 128] whose rows lie
+// `d_tok_stride` elements apart (0 = H * 128; a larger stride writes the three straight into their column ranges
+// of one packed gradient buffer); dbeta, dg: fp32 [B, T, H].
 extern "C" int cvb_gdn_chunk_bwd(const void* q, const void* k, const void* v, long long tok_stride, const void* dO,
                                  const float* beta, const float* Tm, const float* aux, const void* Vn, const void* dVn,
                                  const void* ST, const void* dST, const float* Sf, float* dgam, long long B, int T, int H,
-                                 float scale, void* dq, void* dk, void* dv, float* dbeta, float* dg, int* status,
-                                 void* stream) {
+                                 float scale, void* dq, void* dk, void* dv, long long d_tok_stride, float* dbeta,
+                                 float* dg, int* status, void* stream) {
   if (B <= 0 || T <= 0) return 0;
-  if (T % BC != 0 || (tok_stride % 8) != 0) return -1;
+  if (d_tok_stride == 0) d_tok_stride = static_cast<long long>(H) * BD;
+  if (T % BC != 0 || (tok_stride % 8) != 0 || (d_tok_stride % 8) != 0 || d_tok_stride < static_cast<long long>(H) * BD)
+    return -1;
+  if ((reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) | reinterpret_cast<uintptr_t>(dv)) & 15)
+    return -1;  // the rows are written as 16-byte vectors
   const long long rows = B * T;
   const int n = T / BC;
   const long long items = B * H * n;
@@ -627,6 +633,7 @@ extern "C" int cvb_gdn_chunk_bwd(const void* q, const void* k, const void* v, lo
   BwdArgs a{};
   a.beta = beta; a.Tm = Tm; a.aux = aux; a.dgam = dgam;
   a.dq = static_cast<__nv_bfloat16*>(dq); a.dk = static_cast<__nv_bfloat16*>(dk); a.dv = static_cast<__nv_bfloat16*>(dv);
+  a.d_stride = d_tok_stride;
   a.dbeta = dbeta; a.dg = dg; a.T = T; a.H = H; a.n_chunks = n; a.scale = scale; a.status = status;
   static bool attr = false;
   if (!attr) {

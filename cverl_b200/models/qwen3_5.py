@@ -323,19 +323,27 @@ class Qwen35Model(torch.nn.Module):
             like = torch.zeros(batch, vh, kd, vd, dtype=torch.float32, device=x.device)
             initial_state = recv_initial_state(proj, like, ctx.cp_group, ctx.cp_rank)
         else:
-            mixed = ops.conv1d_silu(mixed.view(batch, seq, conv_dim), conv_w)
-        q, k, v = mixed.split([key_dim, key_dim, value_dim], dim=-1)
-        q = q.reshape(batch, seq, kh, kd)
-        k = k.reshape(batch, seq, kh, kd)
-        v = v.reshape(batch, seq, vh, vd)
+            # one op for "split, then convolve the first group": its backward fills the projection's gradient in
+            # place instead of concatenating the groups' gradients
+            mixed, z, b, a = ops.conv1d_silu_split(proj.view(batch, seq, proj.shape[-1]), conv_w,
+                                                   [conv_dim, value_dim, vh, vh])
         beta = torch.sigmoid(b.float()).view(batch, seq, vh)
         g = (-torch.exp(self.param(p + "A_log").float()) *
              F.softplus(a.float() + self.param(p + "dt_bias").float())).view(batch, seq, vh)
-        if vh // kh > 1:
-            q = q.repeat_interleave(vh // kh, dim=2)
-            k = k.repeat_interleave(vh // kh, dim=2)
         # l2norm of q/k and the 1/sqrt(dk) scale on q are applied inside the fused op
-        core, state = gdn_ops.gated_delta_rule_fused(q, k, v, beta, g, initial_state, scale=1.0 / math.sqrt(kd))
+        if vh == kh and kd == vd:
+            # q | k | v stay packed: the backward kernel writes their gradients into one buffer
+            core, state = gdn_ops.gated_delta_rule_packed(mixed, beta, g, initial_state, scale=1.0 / math.sqrt(kd),
+                                                          heads=vh)
+        else:
+            q, k, v = mixed.split([key_dim, key_dim, value_dim], dim=-1)
+            q = q.reshape(batch, seq, kh, kd)
+            k = k.reshape(batch, seq, kh, kd)
+            v = v.reshape(batch, seq, vh, vd)
+            if vh // kh > 1:
+                q = q.repeat_interleave(vh // kh, dim=2)
+                k = k.repeat_interleave(vh // kh, dim=2)
+            core, state = gdn_ops.gated_delta_rule_fused(q, k, v, beta, g, initial_state, scale=1.0 / math.sqrt(kd))
         core = core.to(x.dtype).reshape(T, vh, vd)
         if ctx.cp_size > 1:  # hand the state on; the zero token ties the send into the backward pass
             core = core + send_final_state(state, ctx.cp_group, ctx.cp_rank, ctx.cp_size).to(core.dtype)

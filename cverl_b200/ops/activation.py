@@ -138,29 +138,88 @@ class _ConvSilu(torch.autograd.Function):
     def backward(ctx, dy):
         x3, w = ctx.saved_tensors
         B, S, Cc = x3.shape
-        wc = w.contiguous()
-        dy = dy.contiguous()
         dx = torch.empty((B, S, Cc), dtype=x3.dtype, device=x3.device)
-        dwbuf, is_main = _wgrad_buffer(w)
-        # the TMA-tiled kernel answers -2 for layouts it does not take (C not a multiple of 64, odd strides)
-        rc = -2
-        if os.environ.get("CVERL_B200_CONV_BWD", "tma") == "tma":
-            rc = nv.cuda().cvb_conv1d_silu_bwd_tma(dy.data_ptr(), x3.data_ptr(), wc.data_ptr(), dx.data_ptr(),
-                                                   dwbuf.data_ptr(), B, S, Cc, wc.shape[1], x3.stride(1), Cc,
-                                                   nv.status_word(x3.device).data_ptr(), nv.stream())
-        if rc == -2:
-            rc = nv.cuda().cvb_conv1d_silu_bwd(dy.data_ptr(), x3.data_ptr(), wc.data_ptr(), dx.data_ptr(),
-                                               dwbuf.data_ptr(), B, S, Cc, wc.shape[1], x3.stride(1), Cc,
-                                               nv.stream())
-        nv.check(rc, "cvb_conv1d_silu_bwd")
+        dw = _conv_bwd_launch(dy, x3, w, dx)
+        return dx, dw
+
+
+def _conv_bwd_launch(dy, x3, w, dx):
+    """Runs the convolution backward: ``x3`` [B,S,C] and ``dx`` [B,S,C] may be column ranges of wider tensors
+    (unit inner stride, row strides multiples of 8).  Returns the weight gradient, or None when it was
+    accumulated into the weight's fp32 main gradient."""
+    B, S, Cc = x3.shape
+    wc = w.contiguous()
+    dy = dy.contiguous()
+    dwbuf, is_main = _wgrad_buffer(w)
+    # the TMA-tiled kernel answers -2 for layouts it does not take (C not a multiple of 64, odd strides)
+    rc = -2
+    if os.environ.get("CVERL_B200_CONV_BWD", "tma") == "tma":
+        rc = nv.cuda().cvb_conv1d_silu_bwd_tma(dy.data_ptr(), x3.data_ptr(), wc.data_ptr(), dx.data_ptr(),
+                                               dwbuf.data_ptr(), B, S, Cc, wc.shape[1], x3.stride(1), dx.stride(1),
+                                               nv.status_word(x3.device).data_ptr(), nv.stream())
+    if rc == -2:
+        rc = nv.cuda().cvb_conv1d_silu_bwd(dy.data_ptr(), x3.data_ptr(), wc.data_ptr(), dx.data_ptr(),
+                                           dwbuf.data_ptr(), B, S, Cc, wc.shape[1], x3.stride(1), dx.stride(1),
+                                           nv.stream())
+    nv.check(rc, "cvb_conv1d_silu_bwd")
+    count_launch()
+    return None if is_main else dwbuf.to(w.dtype)
+
+
+class _ConvSiluSplit(torch.autograd.Function):
+    """``proj`` [B,S,W] = [x | r1 | r2 ...]: returns (conv1d_silu(x), r1, r2, ...) with the r's as views.  The
+    backward writes the convolution's input gradient straight into the first columns of one [B,S,W] buffer and
+    copies the other gradients beside it, instead of concatenating W columns."""
+
+    @staticmethod
+    def forward(ctx, proj, w, *sizes):
+        B, S, W = proj.shape
+        Cc = sizes[0]
+        x3 = proj[..., :Cc]
+        y = torch.empty((B, S, Cc), dtype=proj.dtype, device=proj.device)
+        nv.check(nv.cuda().cvb_conv1d_silu_fwd(x3.data_ptr(), w.contiguous().data_ptr(), y.data_ptr(), B, S, Cc,
+                                               w.shape[1], W, nv.stream()), "cvb_conv1d_silu_fwd")
         count_launch()
-        return dx, (None if is_main else dwbuf.to(w.dtype))
+        ctx.save_for_backward(proj, w)
+        ctx.sizes = sizes
+        rest, at = [], Cc
+        for n in sizes[1:]:
+            rest.append(proj[..., at:at + n])
+            at += n
+        return (y, *rest)
+
+    @staticmethod
+    def backward(ctx, dy, *drest):
+        proj, w = ctx.saved_tensors
+        sizes = ctx.sizes
+        Cc = sizes[0]
+        dproj = torch.empty(proj.shape, dtype=proj.dtype, device=proj.device)
+        dw = _conv_bwd_launch(dy, proj[..., :Cc], w, dproj[..., :Cc])
+        at = Cc
+        for n, d in zip(sizes[1:], drest):
+            if d is None:
+                dproj[..., at:at + n].zero_()
+            else:
+                dproj[..., at:at + n].copy_(d)
+            at += n
+        return (dproj, dw, *([None] * len(sizes)))
 
 
 def conv1d_silu(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     if _native(x) and x.shape[-1] % 8 == 0 and w.shape[1] in (2, 3, 4):
         return _ConvSilu.apply(x, w)
     return conv1d_silu_ref(x, w)
+
+
+def conv1d_silu_split(proj: torch.Tensor, w: torch.Tensor, sizes):
+    """``proj`` [B,S,sum(sizes)]: conv1d + SiLU on the first ``sizes[0]`` columns, the other column groups are
+    returned unchanged: ``(y, r1, r2, ...)``.  Same values and gradients as splitting first."""
+    sizes = tuple(int(s) for s in sizes)
+    if (_native(proj) and proj.is_contiguous() and sizes[0] % 8 == 0 and proj.shape[-1] % 8 == 0
+            and w.shape[1] in (2, 3, 4) and proj.data_ptr() % 16 == 0):
+        return _ConvSiluSplit.apply(proj, w, *sizes)
+    parts = proj.split(list(sizes), dim=-1)
+    return (conv1d_silu(parts[0], w), *parts[1:])
 
 
 # ------------------------------- embedding ----------------------------------

@@ -322,6 +322,53 @@ class _GdnChunked(torch.autograd.Function):
                 unblk(dg, False, g), (dS0 if has_s0 else None), None, None)
 
 
+class _GdnPacked(torch.autograd.Function):
+    """The native chunk kernels on a packed activation ``[B,T,3*H*128]`` (column ranges q | k | v, as the
+    convolution writes them).  The backward kernel stores dq, dk, dv straight into the column ranges of one
+    gradient buffer, so no concatenation runs between it and the convolution's backward."""
+
+    @staticmethod
+    def _views(t, H):
+        B, T, _ = t.shape
+        return tuple(t[..., j * H * 128:(j + 1) * H * 128].view(B, T, H, 128) for j in range(3))
+
+    @staticmethod
+    def forward(ctx, mixed, beta, g, S0, scale, H):
+        from . import gdn_native
+        q, k, v = _GdnPacked._views(mixed, H)
+        o, Sf, Vn, SsT, pre = gdn_native.chunk_forward(q, k, v, beta, g, S0, scale, keep_prep=True)
+        ctx.cfg = (scale, H, S0 is not None)
+        ctx.save_for_backward(mixed, beta, g, Vn, SsT, Sf, pre["W"], pre["Kd"], pre["Qd"], pre["P"], pre["egam"],
+                              pre["Tm"], pre["aux"])
+        return o, Sf
+
+    @staticmethod
+    def backward(ctx, do, dSf):
+        from . import gdn_native
+        scale, H, has_s0 = ctx.cfg
+        mixed, beta, g, Vn, SsT, Sf, W_, Kd_, Qd_, P_, eg_, Tm_, aux_ = ctx.saved_tensors
+        q, k, v = _GdnPacked._views(mixed, H)
+        d_mixed = torch.empty(mixed.shape, dtype=mixed.dtype, device=mixed.device)
+        pre = dict(W=W_, Kd=Kd_, Qd=Qd_, P=P_, egam=eg_, Tm=Tm_, aux=aux_)
+        _, _, _, dbeta, dg, dS0 = gdn_native.chunk_backward(q, k, v, beta, scale, pre, Vn, SsT, Sf, do, dSf,
+                                                            out=_GdnPacked._views(d_mixed, H))
+        return d_mixed, dbeta.to(beta.dtype), dg.to(g.dtype), (dS0 if has_s0 else None), None, None
+
+
+def gated_delta_rule_packed(mixed, beta, g, initial_state=None, *, scale: float, heads: int):
+    """``gated_delta_rule_fused`` on the packed ``[B,T,3*heads*d]`` tensor whose column ranges are q | k | v
+    (equal numbers of key and value heads).  With the native chunk kernels the gradient of ``mixed`` is
+    written in place by the backward kernel; otherwise this splits and calls the general entry."""
+    B, T, Cm = mixed.shape
+    d = Cm // (3 * heads)
+    q, k, v = (part.reshape(B, T, heads, d) for part in mixed.split(heads * d, dim=-1))
+    if mixed.is_cuda and d == 128 and Cm == 3 * heads * 128:
+        from . import gdn_native
+        if gdn_native.chunk_supported(q, k, v) and gdn_native.chunk_bwd_enabled():
+            return _GdnPacked.apply(mixed, beta, g, initial_state, scale, heads)
+    return gated_delta_rule_fused(q, k, v, beta, g, initial_state, scale=scale)
+
+
 def gated_delta_rule_fused(q, k, v, beta, g, initial_state=None, *, scale: float, chunk: int = 64):
     """Gated delta rule on raw (un-normalised) q, k ``[B,T,H,d]``; l2norm and the ``scale`` on q are
     applied inside.  Returns ``(o [B,T,H,dv], final_state [B,H,dk,dv] fp32)``."""

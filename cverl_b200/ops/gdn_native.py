@@ -128,9 +128,10 @@ def chunk_forward(q, k, v, beta, g, S0, scale: float, keep_prep: bool = False):
     return o, Sf, Vn, SsT, pre
 
 
-def chunk_backward(q, k, v, beta, scale: float, pre, Vn, SsT, Sf, do, dSf):
+def chunk_backward(q, k, v, beta, scale: float, pre, Vn, SsT, Sf, do, dSf, out=None):
     """Backward of ``chunk_forward`` on two kernels: the reverse state scan and the chunk-local backward.
-    ``pre`` holds the forward's prep outputs (W, Kd, Qd, P, egam, Tm, aux).
+    ``pre`` holds the forward's prep outputs (W, Kd, Qd, P, egam, Tm, aux).  ``out`` may give three bf16
+    [B,T,H,128] views with one common token stride (column ranges of a packed gradient buffer) for dq, dk, dv.
     Returns (dq, dk, dv [B,T,H,128] bf16, dbeta, dg [B,T,H] fp32, dS0 fp32)."""
     B, T, H, _ = q.shape
     n = T // 64
@@ -147,7 +148,15 @@ def chunk_backward(q, k, v, beta, scale: float, pre, Vn, SsT, Sf, do, dSf):
                               dOb.data_ptr(), pre["egam"].data_ptr(), nv.ptr(dsf), dS0.data_ptr(), dVn.data_ptr(),
                               dSnT.data_ptr(), B * H, n, st, nv.stream())
     nv.check(rc, "cvb_gdn_scan_bwd")
-    dq, dk, dv = (torch.empty((B, T, H, 128), dtype=torch.bfloat16, device=dev) for _ in range(3))
+    if out is None:
+        dq, dk, dv = (torch.empty((B, T, H, 128), dtype=torch.bfloat16, device=dev) for _ in range(3))
+        d_stride = 0
+    else:
+        dq, dk, dv = out
+        d_stride = dq.stride(1)
+        for t in out:
+            assert t.dtype == torch.bfloat16 and t.shape == (B, T, H, 128) and t.stride(3) == 1 and \
+                t.stride(2) == 128 and t.stride(1) == d_stride and t.stride(0) == T * d_stride, "packed dq/dk/dv layout"
     dbeta = torch.empty((B, T, H), dtype=torch.float32, device=dev)
     dg = torch.empty((B, T, H), dtype=torch.float32, device=dev)
     dgam = torch.empty((B, H, n), dtype=torch.float32, device=dev)
@@ -156,8 +165,8 @@ def chunk_backward(q, k, v, beta, scale: float, pre, Vn, SsT, Sf, do, dSf):
     rc = lib.cvb_gdn_chunk_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(1), do.data_ptr(), bf.data_ptr(),
                                pre["Tm"].data_ptr(), pre["aux"].data_ptr(), Vn.data_ptr(), dVn.data_ptr(),
                                SsT.data_ptr(), dSnT.data_ptr(), Sf.data_ptr(), dgam.data_ptr(), B, T, H, scale,
-                               dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dbeta.data_ptr(), dg.data_ptr(), st,
-                               nv.stream())
+                               dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), d_stride, dbeta.data_ptr(),
+                               dg.data_ptr(), st, nv.stream())
     nv.check(rc, "cvb_gdn_chunk_bwd")
     count_launch(3)
     return dq, dk, dv, dbeta, dg, dS0

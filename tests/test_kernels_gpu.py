@@ -345,3 +345,30 @@ def test_attention_block_offsets_merge_to_full_attention():
     full = attention.causal_attention_ref(q.reshape(S, H, D), k.reshape(S, H, D), v.reshape(S, H, D), B, S)
     ref = full.view(B, S, H, D)[:, 128:].float()
     assert ((merged - ref).norm() / ref.norm()).item() < 1e-2
+
+
+def test_conv1d_silu_split_matches_split_then_conv():
+    """conv1d_silu_split (the backward fills one [B,S,W] gradient buffer in place) against splitting first."""
+    from cverl_b200.ops import conv1d_silu, conv1d_silu_split
+    from cverl_b200 import _native as nv
+    torch.manual_seed(12)
+    B, S, sizes = 2, 150, [384, 128, 8, 8]
+    base = torch.randn(B, S, sum(sizes), device=_dev(), dtype=torch.bfloat16)
+    w0 = (0.5 * torch.randn(sizes[0], 4, device=_dev())).to(torch.bfloat16)
+    res = []
+    for fused in (True, False):
+        proj = base.clone().requires_grad_(True)
+        w = w0.clone().requires_grad_(True)
+        if fused:
+            y, z, b, a = conv1d_silu_split(proj, w, sizes)
+            assert type(y.grad_fn).__name__.startswith("_ConvSiluSplit")
+        else:
+            x, z, b, a = proj.split(sizes, dim=-1)
+            y = conv1d_silu(x, w)
+        loss = (y.float() * torch.linspace(-1, 1, sizes[0], device=_dev())).sum() + \
+            (z.reshape(B * S, 2, 64).float() ** 2).sum() + torch.sigmoid(b.float()).sum()      # `a` gets no gradient
+        loss.backward()
+        nv.check_status(_dev())
+        res.append((y.detach(), proj.grad, w.grad))
+    assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
+    assert _rel_err(res[0][2], res[1][2]) < 1e-3          # atomics: summation order differs between runs
