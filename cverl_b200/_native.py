@@ -87,7 +87,7 @@ _CUDA_PROTOS = {
     "cvb_gdn_chunk_out": "ppppp l ii p p",
     "cvb_gdn_chunk_bwd": "ppp l p ppp pp pp p p l ii f ppp l pp p p",
     "cvb_gdn_scan_fwd": "pppppppp l i p p",
-    "cvb_gdn_scan_bwd": "pppppppppp l i p p",
+    "cvb_gdn_scan_bwd": "pppppppppp l ii p p",
     "cvb_symm_barrier": "p iii p p",
     "cvb_reduce_scatter_sumsq": "p ii ll f pp p",
     "cvb_flat_adamw_allgather": "ppppp p ii ll fffff l p",

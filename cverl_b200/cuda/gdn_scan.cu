@@ -68,6 +68,7 @@ struct ScanArgs {
   __nv_bfloat16* out_v;       // Vn / dVn  [BH, n, C, dv]
   __nv_bfloat16* out_s;       // per-chunk state (transposed) [BH, n, dv, dk]
   int* status;
+  int do_heads;               // backward: 0 = dO is [BH, n, C, dv]; H > 0 = dO is [B, n*C, H, dv] (token-major)
 };
 
 // issue the two 64x64 boxes of a [64 x 128] tile
@@ -330,8 +331,16 @@ gdn_scan_bwd_kernel(const __grid_constant__ CUtensorMap tmKd, const __grid_const
     mbar_arrive_expect_tx(bar_a, 16384 + 16384 + 8192);
     tma_load_2d(s_kd, &tmKd, bar_a, 0, r0);
     tma_load_2d(s_kd + 8192, &tmKd, bar_a, 64, r0);
-    tma_load_2d(s_do, &tmDO, bar_a, 0, r0);
-    tma_load_2d(s_do + 8192, &tmDO, bar_a, 64, r0);
+    if (a.do_heads > 0) {  // straight from the [tokens, H * dv] gradient of the layer output
+      const long long b = bh / a.do_heads;
+      const int x0 = static_cast<int>(bh % a.do_heads) * GD;
+      const int tr = static_cast<int>((b * n + i) * GC);
+      tma_load_2d(s_do, &tmDO, bar_a, x0, tr);
+      tma_load_2d(s_do + 8192, &tmDO, bar_a, x0 + 64, tr);
+    } else {
+      tma_load_2d(s_do, &tmDO, bar_a, 0, r0);
+      tma_load_2d(s_do + 8192, &tmDO, bar_a, 64, r0);
+    }
     tma_load_2d(s_p, &tmP, bar_a, 0, r0);
     mbar_arrive_expect_tx(bar_b, 32768);
     tma_load_2d(s_qd, &tmQd, bar_b, 0, r0);
@@ -487,19 +496,25 @@ extern "C" int cvb_gdn_scan_fwd(const void* W, const void* U, const void* Kd, co
 // out_dv: dVn = P^T dO + Kd dS.  out_ds: dS_{i+1} per chunk, transposed [BH, n, dv, dk] bf16.
 extern "C" int cvb_gdn_scan_bwd(const void* P, const void* Kd, const void* Qd, const void* W, const void* dO,
                                 const float* egam, const float* ds_final, float* ds_init_out, void* out_dv,
-                                void* out_ds, long long BH, int n_chunks, int* status, void* stream) {
+                                void* out_ds, long long BH, int n_chunks, int do_heads, int* status, void* stream) {
   if (BH <= 0 || n_chunks <= 0) return 0;
   if (BH * n_chunks * GC > 0x7fffffffLL) return -2;
+  if (do_heads < 0 || (do_heads > 0 && BH % do_heads != 0)) return -1;
   CUtensorMap mK, mQ, mW, mO, mP;
   const long long rows = BH * n_chunks * GC;
-  if (make_rows128_map(&mK, Kd, rows) || make_rows128_map(&mQ, Qd, rows) || make_rows128_map(&mW, W, rows) ||
-      make_rows128_map(&mO, dO, rows) ||
+  // dO: chunk-major [BH, n, 64, 128], or (do_heads = H > 0) the token-major [B, n*64, H, 128] gradient itself
+  const int rc_do = do_heads > 0
+                        ? make_tensor_map_2d(&mO, dO, 2, static_cast<uint64_t>(do_heads) * GD,
+                                             static_cast<uint64_t>(rows / do_heads),
+                                             static_cast<uint64_t>(do_heads) * GD * 2, 64, 64)
+                        : make_rows128_map(&mO, dO, rows);
+  if (make_rows128_map(&mK, Kd, rows) || make_rows128_map(&mQ, Qd, rows) || make_rows128_map(&mW, W, rows) || rc_do ||
       make_tensor_map_2d(&mP, P, 2, GC, static_cast<uint64_t>(rows), GC * 2, 64, 64))
     return -10;
   ScanArgs a{};
   a.n_chunks = n_chunks; a.egam = egam; a.s_init = ds_final; a.s_final = ds_init_out;
   a.out_v = static_cast<__nv_bfloat16*>(out_dv); a.out_s = static_cast<__nv_bfloat16*>(out_ds);
-  a.status = status;
+  a.status = status; a.do_heads = do_heads;
   static bool attr = false;
   if (!attr) {
     if (cudaFuncSetAttribute(gdn_scan_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ScanSmem::BYTES_BWD) !=

@@ -52,7 +52,7 @@ def scan_bwd(P, Kdec, Qd, W, dO, egam, dSf):
     dS0 = torch.empty((B, H, 128, 128), dtype=torch.float32, device=dev)
     rc = nv.cuda().cvb_gdn_scan_bwd(Pb.data_ptr(), Kb.data_ptr(), Qb.data_ptr(), Wb.data_ptr(), dOb.data_ptr(),
                                     eg.data_ptr(), nv.ptr(dsf), dS0.data_ptr(), dVn.data_ptr(), dSnT.data_ptr(),
-                                    B * H, n, nv.status_word(dev).data_ptr(), nv.stream())
+                                    B * H, n, 0, nv.status_word(dev).data_ptr(), nv.stream())
     nv.check(rc, "cvb_gdn_scan_bwd")
     count_launch()
     return dVn, dSnT.transpose(-1, -2), dS0
@@ -139,14 +139,13 @@ def chunk_backward(q, k, v, beta, scale: float, pre, Vn, SsT, Sf, do, dSf, out=N
     lib = nv.cuda()
     st = nv.status_word(dev).data_ptr()
     do = do.to(torch.bfloat16).contiguous()
-    dOb = do.view(B, n, 64, H, 128).permute(0, 3, 1, 2, 4).contiguous()          # [B,H,n,64,128]
     dsf = dSf.float().contiguous() if dSf is not None else None
     dVn = torch.empty((B, H, n, 64, 128), dtype=torch.bfloat16, device=dev)
     dSnT = torch.empty((B, H, n, 128, 128), dtype=torch.bfloat16, device=dev)
     dS0 = torch.empty((B, H, 128, 128), dtype=torch.float32, device=dev)
     rc = lib.cvb_gdn_scan_bwd(pre["P"].data_ptr(), pre["Kd"].data_ptr(), pre["Qd"].data_ptr(), pre["W"].data_ptr(),
-                              dOb.data_ptr(), pre["egam"].data_ptr(), nv.ptr(dsf), dS0.data_ptr(), dVn.data_ptr(),
-                              dSnT.data_ptr(), B * H, n, st, nv.stream())
+                              do.data_ptr(), pre["egam"].data_ptr(), nv.ptr(dsf), dS0.data_ptr(), dVn.data_ptr(),
+                              dSnT.data_ptr(), B * H, n, H, st, nv.stream())   # dO read token-major, in place
     nv.check(rc, "cvb_gdn_scan_bwd")
     if out is None:
         dq, dk, dv = (torch.empty((B, T, H, 128), dtype=torch.bfloat16, device=dev) for _ in range(3))
