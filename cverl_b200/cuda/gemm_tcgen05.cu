@@ -88,6 +88,149 @@ __device__ __forceinline__ WorkItem decode_item(const GemmParams& p, int item) {
   return w;
 }
 
+// One accumulator slab of 128 rows x BN columns: the four epilogue warps drain it from TMEM (warp quadrant q
+// reads lanes 32q..32q+31 at `taddr`) and run the epilogue selected by p.epi.  m0 = first global row of the slab,
+// n0 = first global column, nb = index of the N tile (partial-softmax slot), stg_warp = this warp's staging.
+template <int BN>
+__device__ __forceinline__ void epilogue_slab(const GemmParams& p, int m0, int n0, int nb, uint32_t taddr,
+                                              long long c_off, uint8_t* stg_warp, int q, int lane) {
+  using Cfg = TileCfg<BN>;
+  const int row = m0 + q * 32 + lane;
+  const bool row_ok = row < p.M;
+
+  // per-row state of the streaming-softmax epilogues
+  float run_max = -INFINITY, run_sum = 0.f;
+  long long tgt = -1;
+  float row_lse = 0.f, row_g = 0.f;
+  if (p.epi == EPI_LSE_PARTIAL && row_ok) tgt = p.targets[row];
+  if (p.epi == EPI_SOFTMAX_GRAD && row_ok) {
+    tgt = p.targets[row];
+    row_lse = p.lse[row];
+    row_g = p.gscale[row];
+  }
+
+#pragma unroll 1
+  for (int c = 0; c < BN; c += 32) {
+    uint32_t r[32];
+    __syncwarp();
+    tmem_ld_32x32(taddr + c, r);
+    tmem_ld_wait();
+    const int col0 = n0 + c;
+    if (p.staged_store) {
+      // Staged bf16 store (N % 64 == 0): two 32-column chunks of this warp's 32 rows are staged in
+      // shared memory, then written out as 128-byte row segments (8 lanes per row) to the local C and
+      // to every mirror: full-line stores keep the L2 / NVLink writes efficient.
+      if (col0 < p.N) {
+        uint8_t* stg = stg_warp;
+        uint8_t* mine = stg + lane * Cfg::STG_ROW + (c & 32) * 2;
+#pragma unroll
+        for (int g8 = 0; g8 < 4; ++g8) {
+          uint4 o;
+          o.x = pack_bf16x2(__uint_as_float(r[g8 * 8 + 0]) * p.alpha, __uint_as_float(r[g8 * 8 + 1]) * p.alpha);
+          o.y = pack_bf16x2(__uint_as_float(r[g8 * 8 + 2]) * p.alpha, __uint_as_float(r[g8 * 8 + 3]) * p.alpha);
+          o.z = pack_bf16x2(__uint_as_float(r[g8 * 8 + 4]) * p.alpha, __uint_as_float(r[g8 * 8 + 5]) * p.alpha);
+          o.w = pack_bf16x2(__uint_as_float(r[g8 * 8 + 6]) * p.alpha, __uint_as_float(r[g8 * 8 + 7]) * p.alpha);
+          *reinterpret_cast<uint4*>(mine + g8 * 16) = o;
+        }
+        if (c & 32) {
+          __syncwarp();
+          const int cbase = n0 + (c & ~63);
+#pragma unroll 1
+          for (int it = 0; it < 8; ++it) {
+            const int rr = it * 4 + (lane >> 3), ch = lane & 7;
+            const int grow = m0 + q * 32 + rr;
+            if (grow < p.M) {
+              const uint4 o = *reinterpret_cast<const uint4*>(stg + rr * Cfg::STG_ROW + ch * 16);
+              const long long off = c_off + static_cast<long long>(grow) * p.ldc + cbase + ch * 8;
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + off) = o;
+#pragma unroll 1
+              for (int m = 0; m < p.n_mirror; ++m)
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.mirror[m]) + off) = o;
+            }
+          }
+          __syncwarp();
+        }
+      }
+      continue;
+    }
+    if (!row_ok || col0 >= p.N) continue;
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+    if (p.epi == EPI_STORE_BF16) {
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+      for (int g8 = 0; g8 < 4; ++g8) {
+        if (col0 + g8 * 8 < p.N) {
+          uint4 o;
+          o.x = pack_bf16x2(v[g8 * 8 + 0], v[g8 * 8 + 1]);
+          o.y = pack_bf16x2(v[g8 * 8 + 2], v[g8 * 8 + 3]);
+          o.z = pack_bf16x2(v[g8 * 8 + 4], v[g8 * 8 + 5]);
+          o.w = pack_bf16x2(v[g8 * 8 + 6], v[g8 * 8 + 7]);
+          *reinterpret_cast<uint4*>(dst + g8 * 8) = o;
+        }
+      }
+    } else if (p.epi == EPI_STORE_F32) {
+      float* dst = reinterpret_cast<float*>(p.C) + c_off + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+      for (int g4 = 0; g4 < 8; ++g4) {
+        if (col0 + g4 * 4 < p.N)
+          *reinterpret_cast<float4*>(dst + g4 * 4) =
+              make_float4(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2], v[g4 * 4 + 3]);
+      }
+    } else if (p.epi == EPI_ATOMIC_F32) {
+      float* dst = reinterpret_cast<float*>(p.C) + c_off + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+      for (int g4 = 0; g4 < 8; ++g4) {
+        if (col0 + g4 * 4 < p.N)
+          red_add_v4_f32(dst + g4 * 4, v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2], v[g4 * 4 + 3]);
+      }
+    } else if (p.epi == EPI_LSE_PARTIAL) {
+      // streaming max / sum-exp over this tile's columns; pick the target logit
+      float cmax = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < p.N) cmax = fmaxf(cmax, v[i]);
+      const float nmax = fmaxf(run_max, cmax);
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < p.N) s += __expf(v[i] - nmax);
+      run_sum = run_sum * __expf(run_max - nmax) + s;
+      run_max = nmax;
+      if (tgt >= col0 && tgt < col0 + 32) {
+        float tv = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (col0 + i == tgt) tv = v[i];
+        p.tgt_logit[row] = tv;
+      }
+    } else {  // EPI_SOFTMAX_GRAD: d = g * (onehot - exp(logit - lse)) as bf16
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float pr = __expf(v[i] - row_lse);
+        v[i] = row_g * (((col0 + i) == tgt ? 1.f : 0.f) - pr);
+      }
+#pragma unroll
+      for (int g8 = 0; g8 < 4; ++g8) {
+        if (col0 + g8 * 8 < p.N) {
+          uint4 o;
+          o.x = pack_bf16x2(v[g8 * 8 + 0], v[g8 * 8 + 1]);
+          o.y = pack_bf16x2(v[g8 * 8 + 2], v[g8 * 8 + 3]);
+          o.z = pack_bf16x2(v[g8 * 8 + 4], v[g8 * 8 + 5]);
+          o.w = pack_bf16x2(v[g8 * 8 + 6], v[g8 * 8 + 7]);
+          *reinterpret_cast<uint4*>(dst + g8 * 8) = o;
+        }
+      }
+    }
+  }
+  if (p.epi == EPI_LSE_PARTIAL && row_ok) {
+    p.part_max[static_cast<long long>(nb) * p.M + row] = run_max;
+    p.part_sum[static_cast<long long>(nb) * p.M + row] = run_sum;
+  }
+}
+
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -261,143 +404,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         break;
       }
       tc_fence_after();
-      const int row = w.mb * BM + q * 32 + lane;
-      const int n0 = w.nb * BN;
-      const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      const long long c_off = static_cast<long long>(w.group) * p.c_group_stride;
-
-      // per-row state of the streaming-softmax epilogues
-      float run_max = -INFINITY, run_sum = 0.f;
-      long long tgt = -1;
-      float row_lse = 0.f, row_g = 0.f;
-      if (p.epi == EPI_LSE_PARTIAL && row_ok) tgt = p.targets[row];
-      if (p.epi == EPI_SOFTMAX_GRAD && row_ok) {
-        tgt = p.targets[row];
-        row_lse = p.lse[row];
-        row_g = p.gscale[row];
-      }
-
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld_32x32(taddr + c, r);
-        tmem_ld_wait();
-        const int col0 = n0 + c;
-        if (p.staged_store) {
-          // Staged bf16 store (N % 64 == 0): two 32-column chunks of this warp's 32 rows are staged in
-          // shared memory, then written out as 128-byte row segments (8 lanes per row) to the local C and
-          // to every mirror: full-line stores keep the L2 / NVLink writes efficient.
-          if (col0 < p.N) {
-            uint8_t* stg = smem + Cfg::STG_OFF + q * Cfg::STG_WARP;
-            uint8_t* mine = stg + lane * Cfg::STG_ROW + (c & 32) * 2;
-#pragma unroll
-            for (int g8 = 0; g8 < 4; ++g8) {
-              uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(r[g8 * 8 + 0]) * p.alpha, __uint_as_float(r[g8 * 8 + 1]) * p.alpha);
-              o.y = pack_bf16x2(__uint_as_float(r[g8 * 8 + 2]) * p.alpha, __uint_as_float(r[g8 * 8 + 3]) * p.alpha);
-              o.z = pack_bf16x2(__uint_as_float(r[g8 * 8 + 4]) * p.alpha, __uint_as_float(r[g8 * 8 + 5]) * p.alpha);
-              o.w = pack_bf16x2(__uint_as_float(r[g8 * 8 + 6]) * p.alpha, __uint_as_float(r[g8 * 8 + 7]) * p.alpha);
-              *reinterpret_cast<uint4*>(mine + g8 * 16) = o;
-            }
-            if (c & 32) {
-              __syncwarp();
-              const int cbase = n0 + (c & ~63);
-#pragma unroll 1
-              for (int it = 0; it < 8; ++it) {
-                const int rr = it * 4 + (lane >> 3), ch = lane & 7;
-                const int grow = w.mb * BM + q * 32 + rr;
-                if (grow < p.M) {
-                  const uint4 o = *reinterpret_cast<const uint4*>(stg + rr * Cfg::STG_ROW + ch * 16);
-                  const long long off = c_off + static_cast<long long>(grow) * p.ldc + cbase + ch * 8;
-                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + off) = o;
-#pragma unroll 1
-                  for (int m = 0; m < p.n_mirror; ++m)
-                    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.mirror[m]) + off) = o;
-                }
-              }
-              __syncwarp();
-            }
-          }
-          continue;
-        }
-        if (!row_ok || col0 >= p.N) continue;
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-        if (p.epi == EPI_STORE_BF16) {
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + static_cast<long long>(row) * p.ldc + col0;
-#pragma unroll
-          for (int g8 = 0; g8 < 4; ++g8) {
-            if (col0 + g8 * 8 < p.N) {
-              uint4 o;
-              o.x = pack_bf16x2(v[g8 * 8 + 0], v[g8 * 8 + 1]);
-              o.y = pack_bf16x2(v[g8 * 8 + 2], v[g8 * 8 + 3]);
-              o.z = pack_bf16x2(v[g8 * 8 + 4], v[g8 * 8 + 5]);
-              o.w = pack_bf16x2(v[g8 * 8 + 6], v[g8 * 8 + 7]);
-              *reinterpret_cast<uint4*>(dst + g8 * 8) = o;
-            }
-          }
-        } else if (p.epi == EPI_STORE_F32) {
-          float* dst = reinterpret_cast<float*>(p.C) + c_off + static_cast<long long>(row) * p.ldc + col0;
-#pragma unroll
-          for (int g4 = 0; g4 < 8; ++g4) {
-            if (col0 + g4 * 4 < p.N)
-              *reinterpret_cast<float4*>(dst + g4 * 4) =
-                  make_float4(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2], v[g4 * 4 + 3]);
-          }
-        } else if (p.epi == EPI_ATOMIC_F32) {
-          float* dst = reinterpret_cast<float*>(p.C) + c_off + static_cast<long long>(row) * p.ldc + col0;
-#pragma unroll
-          for (int g4 = 0; g4 < 8; ++g4) {
-            if (col0 + g4 * 4 < p.N)
-              red_add_v4_f32(dst + g4 * 4, v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2], v[g4 * 4 + 3]);
-          }
-        } else if (p.epi == EPI_LSE_PARTIAL) {
-          // streaming max / sum-exp over this tile's columns; pick the target logit
-          float cmax = -INFINITY;
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (col0 + i < p.N) cmax = fmaxf(cmax, v[i]);
-          const float nmax = fmaxf(run_max, cmax);
-          float s = 0.f;
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (col0 + i < p.N) s += __expf(v[i] - nmax);
-          run_sum = run_sum * __expf(run_max - nmax) + s;
-          run_max = nmax;
-          if (tgt >= col0 && tgt < col0 + 32) {
-            float tv = 0.f;
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (col0 + i == tgt) tv = v[i];
-            p.tgt_logit[row] = tv;
-          }
-        } else {  // EPI_SOFTMAX_GRAD: d = g * (onehot - exp(logit - lse)) as bf16
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float pr = __expf(v[i] - row_lse);
-            v[i] = row_g * (((col0 + i) == tgt ? 1.f : 0.f) - pr);
-          }
-#pragma unroll
-          for (int g8 = 0; g8 < 4; ++g8) {
-            if (col0 + g8 * 8 < p.N) {
-              uint4 o;
-              o.x = pack_bf16x2(v[g8 * 8 + 0], v[g8 * 8 + 1]);
-              o.y = pack_bf16x2(v[g8 * 8 + 2], v[g8 * 8 + 3]);
-              o.z = pack_bf16x2(v[g8 * 8 + 4], v[g8 * 8 + 5]);
-              o.w = pack_bf16x2(v[g8 * 8 + 6], v[g8 * 8 + 7]);
-              *reinterpret_cast<uint4*>(dst + g8 * 8) = o;
-            }
-          }
-        }
-      }
-      if (p.epi == EPI_LSE_PARTIAL && row_ok) {
-        p.part_max[static_cast<long long>(w.nb) * p.M + row] = run_max;
-        p.part_sum[static_cast<long long>(w.nb) * p.M + row] = run_sum;
-      }
+      epilogue_slab<BN>(p, w.mb * BM, w.nb * BN, w.nb, taddr, static_cast<long long>(w.group) * p.c_group_stride,
+                        smem + Cfg::STG_OFF + q * Cfg::STG_WARP, q, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
@@ -410,6 +419,219 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// CTA-pair kernel: 256 x 256 x 64 tiles on two SMs (cluster of two CTAs, cta_group::2).
+//
+// A single UMMA spans the pair: CTA r stages rows [128 r, 128 r + 128) of the A tile and rows
+// [128 r, 128 r + 128) of the B (N) tile, and holds rows [128 r, 128 r + 128) of the accumulator in its own
+// TMEM.  Per k-block each SM therefore moves 32 KB through shared memory for 256 x 256 x 64 MACs of the pair,
+// against 48 KB for 128 x 256 x 64 in the single-CTA kernel: half the shared-memory traffic per FLOP, and a
+// six-stage ring in the same footprint.
+//
+// Barriers (every CTA owns a set at the same offsets):
+//   full[s]   of the even CTA: one arrival (its producer's expect_tx of both CTAs' bytes) + both CTAs' TMA bytes
+//   empty[s]  of each CTA: the even CTA's MMA thread commits to both (multicast commit)
+//   tfull[a]  of each CTA: committed to both by the MMA thread when a tile's accumulator is complete
+//   tempty[a] of the even CTA: 8 arrivals, one per epilogue warp of the pair
+// Grouped (MoE) modes and CTA-limited launches stay on the single-CTA kernel.
+// ---------------------------------------------------------------------------
+struct PairCfg {
+  static constexpr int BN = 256;
+  static constexpr int A_BYTES = 128 * BK * 2;
+  static constexpr int B_BYTES = 128 * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = 6;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int STG_WARP = TileCfg<256>::STG_WARP;
+  static constexpr int STG_OFF = STAGES * STAGE_BYTES + 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + 4 * STG_WARP;
+};
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmParams p) {
+  using Cfg = PairCfg;
+  constexpr int BN = Cfg::BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + Cfg::STAGES;
+  uint64_t* tfull_bar = bars + 2 * Cfg::STAGES;
+  uint64_t* tempty_bar = bars + 2 * Cfg::STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = even CTA (issues the MMAs), 1 = its peer
+  const int pair = blockIdx.x >> 1;
+  const int n_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 8);  // four epilogue warps in each CTA of the pair
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();  // barriers of both CTAs are initialised before either CTA signals the other
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_items = p.total_items;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int item = pair; ok && item < total_items; item += n_pairs) {
+        const WorkItem w = decode_item(p, item);
+        if (!w.valid) continue;
+        const int m0 = w.mb * 256 + static_cast<int>(rank) * 128;   // this CTA's rows of A
+        const int n0 = w.nb * BN + static_cast<int>(rank) * 128;    // this CTA's rows of B
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
+            if (!*abort_flag) atomicCAS(p.status, 0, ERR_WAIT_EMPTY);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
+          uint8_t* sb = sa + Cfg::A_BYTES;
+          if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::STAGE_BYTES);
+          const uint32_t fb = mapa_cluster(smem_u32(&full_bar[stage]), 0);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_2d_pair(sa, &tmA, fb, k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) tma_load_2d_pair(sa + j * (64 * BK * 2), &tmA, fb, m0 + 64 * j, k0);
+          }
+          if (!B_MN) {
+            tma_load_2d_pair(sb, &tmB, fb, k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) tma_load_2d_pair(sb + j * (64 * BK * 2), &tmB, fb, n0 + 64 * j, k0);
+          }
+          if (++stage == Cfg::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok || *abort_flag) {
+        // A wait ran out somewhere in the pair.  This CTA's copies report to the even CTA's barriers, so it
+        // cannot wait on them itself: give the copies in flight a bounded time to land before the CTA ends.
+        const long long t0 = clock64();
+        while (clock64() - t0 < (1ll << 21)) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (even CTA only) ------------------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc(256, BN, /*bf16*/ 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      constexpr uint32_t A_LBO = A_MN ? 64 * BK * 2 : 16;
+      constexpr uint32_t B_LBO = B_MN ? 64 * BK * 2 : 16;
+      constexpr uint32_t A_KSTEP = A_MN ? 2048 : 32;
+      constexpr uint32_t B_KSTEP = B_MN ? 2048 : 32;
+      int stage = 0;
+      uint32_t phase = 0;
+      int local_tile = 0;
+      bool ok = true;
+      for (int item = pair; ok && item < total_items; item += n_pairs) {
+        const WorkItem w = decode_item(p, item);
+        if (!w.valid) continue;
+        const int acc = local_tile & 1;
+        const uint32_t acc_phase = (local_tile >> 1) & 1;
+        if (!mbar_wait_bounded(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) {
+          if (!*abort_flag) atomicCAS(p.status, 0, ERR_WAIT_TMEM_EMPTY);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
+            if (!*abort_flag) atomicCAS(p.status, 0, ERR_WAIT_FULL);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint32_t sb = sa + Cfg::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t ad = umma_smem_desc(sa + k * A_KSTEP, A_LBO, 1024);
+            const uint64_t bd = umma_smem_desc(sb + k * B_KSTEP, B_LBO, 1024);
+            umma_bf16_pair(tmem_d, ad, bd, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(&empty_bar[stage], 3);  // frees this stage in both CTAs when the MMAs retire
+          if (++stage == Cfg::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit_pair(&tfull_bar[acc], 3);  // accumulator complete, in both CTAs
+        ++local_tile;
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (both CTAs, own 128 rows) ------------------------------
+    const int q = warp & 3;
+    int local_tile = 0;
+    for (int item = pair; item < total_items; item += n_pairs) {
+      const WorkItem w = decode_item(p, item);
+      if (!w.valid) continue;
+      const int acc = local_tile & 1;
+      const uint32_t acc_phase = (local_tile >> 1) & 1;
+      bool ok = mbar_wait_bounded(&tfull_bar[acc], acc_phase, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) {
+          if (!*abort_flag) atomicCAS(p.status, 0, ERR_WAIT_TMEM_FULL);
+          *abort_flag = 1;
+        }
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      epilogue_slab<BN>(p, w.mb * 256 + static_cast<int>(rank) * 128, w.nb * BN, w.nb, taddr, 0,
+                        smem + Cfg::STG_OFF + q * Cfg::STG_WARP, q, lane);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&tempty_bar[acc]), 0));
+      ++local_tile;
+    }
+  }
+
+  // Neither CTA may leave (or free tensor memory) while its peer can still signal its barriers or while
+  // MMAs of the pair may still write its TMEM: every role of both CTAs ends here.
+  tc_fence_before();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
   }
 }
 
@@ -491,6 +713,60 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
   return static_cast<int>(cudaGetLastError());
 }
 
+// Number of CTA pairs that can be resident at once (0 = pairs cannot be launched here).
+template <bool A_MN, bool B_MN>
+static int pair_capacity() {
+  static int cached = -1;
+  if (cached >= 0) return cached;
+  auto kern = gemm_pair_kernel<A_MN, B_MN>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM_BYTES) != cudaSuccess) {
+    cudaGetLastError();
+    return cached = 0;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * num_sms(), 1, 1);
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = PairCfg::SMEM_BYTES;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    n = 0;
+  }
+  return cached = n;
+}
+
+template <bool A_MN, bool B_MN>
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int pairs,
+                       cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = PairCfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<A_MN, B_MN>, ta, tb, p));
+}
+
+static int pair_capacity_for(bool a_mn, bool b_mn) {
+  if (!a_mn && !b_mn) return pair_capacity<false, false>();
+  if (!a_mn && b_mn) return pair_capacity<false, true>();
+  if (a_mn && b_mn) return pair_capacity<true, true>();
+  return pair_capacity<true, false>();
+}
+
 }  // namespace cvb
 
 using namespace cvb;
@@ -509,6 +785,13 @@ extern "C" int cvb_gemm_bf16(const CvbGemmArgs* a, void* stream_v) {
       ((a->lda * 2) & 15) || ((a->ldb * 2) & 15))
     return -3;
   const int bn = a->block_n == 128 ? 128 : 256;
+  // CTA-pair kernel (256 x 256 tiles over two SMs) for the plain, ungrouped shapes that fill at least one tile
+  static const bool pair_off = [] { const char* e = getenv("CVERL_B200_GEMM_PAIR"); return e && e[0] == '0'; }();
+  int pairs = 0;
+  if (!pair_off && bn == 256 && !a->tile_group && !a->k_group_offsets && a->b_total_rows == 0 && a->max_ctas <= 0 &&
+      a->M > 128 && a->N > 128)
+    pairs = pair_capacity_for(a->a_mn != 0, a->b_mn != 0);
+  const int bm = pairs > 0 ? 256 : BM;
   GemmParams p;
   memset(&p, 0, sizeof(p));
   p.M = a->M;
@@ -518,7 +801,7 @@ extern "C" int cvb_gemm_bf16(const CvbGemmArgs* a, void* stream_v) {
   p.ldc = a->ldc;
   p.alpha = a->alpha;
   p.epi = a->epi;
-  p.m_tiles = (a->M + BM - 1) / BM;
+  p.m_tiles = (a->M + bm - 1) / bm;
   p.n_tiles = (a->N + bn - 1) / bn;
   p.kblocks = (a->K + BK - 1) / BK;
   p.tile_group = a->tile_group;
@@ -545,7 +828,7 @@ extern "C" int cvb_gemm_bf16(const CvbGemmArgs* a, void* stream_v) {
     if (!a->mirror[m] || (reinterpret_cast<uintptr_t>(a->mirror[m]) & 15)) return -6;
     p.mirror[m] = a->mirror[m];
   }
-  const int sms = num_sms();
+  const int sms = pairs > 0 ? pairs : num_sms();  // concurrent tiles
   int split = a->split_k;
   const int mn_tiles = p.m_tiles * p.n_tiles;
   if (a->k_group_offsets) {
@@ -583,7 +866,7 @@ extern "C" int cvb_gemm_bf16(const CvbGemmArgs* a, void* stream_v) {
   if (rc) return -10 - (rc > 0 ? 0 : 1);
   const uint64_t b_rows = a->b_total_rows > 0 ? a->b_total_rows : (a->b_mn ? a->K : a->N);
   if (!a->b_mn)
-    rc = make_tensor_map_2d(&tb, a->B, 2, a->K, b_rows, a->ldb * 2, BK, bn);
+    rc = make_tensor_map_2d(&tb, a->B, 2, a->K, b_rows, a->ldb * 2, BK, pairs > 0 ? 128 : bn);
   else
     rc = make_tensor_map_2d(&tb, a->B, 2, a->N, b_rows, a->ldb * 2, 64, BK);
   if (rc) return -12;
@@ -591,6 +874,12 @@ extern "C" int cvb_gemm_bf16(const CvbGemmArgs* a, void* stream_v) {
   int grid = p.total_items < sms ? p.total_items : sms;
   if (a->max_ctas > 0 && grid > a->max_ctas) grid = a->max_ctas;
   if (grid <= 0) return 0;
+  if (pairs > 0) {
+    if (!a->a_mn && !a->b_mn) return launch_pair<false, false>(ta, tb, p, grid, stream);
+    if (!a->a_mn && a->b_mn) return launch_pair<false, true>(ta, tb, p, grid, stream);
+    if (a->a_mn && a->b_mn) return launch_pair<true, true>(ta, tb, p, grid, stream);
+    return launch_pair<true, false>(ta, tb, p, grid, stream);
+  }
 
 #define CVB_LAUNCH(BN_)                                                            \
   do {                                                                             \
