@@ -69,8 +69,11 @@ __device__ __forceinline__ WorkItem decode_item(const GemmParams& p, int item) {
     w.kb1 = p.k_group_offsets[w.group + 1] / BK;
     if (w.kb1 <= w.kb0) w.valid = false;
   } else {
-    const int ks = item % p.split_k;
-    t = item / p.split_k;
+    // tile-fastest: the items that run at the same time are different tiles over the same K range, so they
+    // share A and B panels in L2
+    const int mn = p.m_tiles * p.n_tiles;
+    const int ks = item / mn;
+    t = item - ks * mn;
     w.kb0 = ks * p.kb_per_split;
     w.kb1 = min(p.kblocks, w.kb0 + p.kb_per_split);
   }
@@ -87,6 +90,21 @@ __device__ __forceinline__ WorkItem decode_item(const GemmParams& p, int item) {
   }
   return w;
 }
+
+// The work items of one CTA pair, in the order in which its three roles walk them: items first, first + count,
+// first + 2 count, ... of p.total_items, skipping the invalid ones.
+struct ItemWalk {
+  int item, stride;
+  __device__ ItemWalk(int first, int count) : item(first), stride(count) {}
+  __device__ bool next(const GemmParams& p, WorkItem& w) {
+    while (item < p.total_items) {
+      w = decode_item(p, item);
+      item += stride;
+      if (w.valid) return true;
+    }
+    return false;
+  }
+};
 
 // One accumulator slab of 128 rows x BN columns: the four epilogue warps drain it from TMEM (warp quadrant q
 // reads lanes 32q..32q+31 at `taddr`) and run the epilogue selected by p.epi.  m0 = first global row of the slab,
@@ -494,7 +512,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   cluster_sync_all();  // barriers of both CTAs are initialised before either CTA signals the other
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int total_items = p.total_items;
 
   if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) ------------------------------
@@ -502,9 +519,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int item = pair; ok && item < total_items; item += n_pairs) {
-        const WorkItem w = decode_item(p, item);
-        if (!w.valid) continue;
+      ItemWalk walk(pair, n_pairs);
+      WorkItem w;
+      while (ok && walk.next(p, w)) {
         const int m0 = w.mb * 256 + static_cast<int>(rank) * 128;   // this CTA's rows of A
         const int n0 = w.nb * BN + static_cast<int>(rank) * 128;    // this CTA's rows of B
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
@@ -557,9 +574,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       int local_tile = 0;
       bool ok = true;
-      for (int item = pair; ok && item < total_items; item += n_pairs) {
-        const WorkItem w = decode_item(p, item);
-        if (!w.valid) continue;
+      ItemWalk walk(pair, n_pairs);
+      WorkItem w;
+      while (ok && walk.next(p, w)) {
         const int acc = local_tile & 1;
         const uint32_t acc_phase = (local_tile >> 1) & 1;
         if (!mbar_wait_bounded(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) {
@@ -600,9 +617,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------ epilogue (both CTAs, own 128 rows) ------------------------------
     const int q = warp & 3;
     int local_tile = 0;
-    for (int item = pair; item < total_items; item += n_pairs) {
-      const WorkItem w = decode_item(p, item);
-      if (!w.valid) continue;
+    ItemWalk walk(pair, n_pairs);
+    WorkItem w;
+    while (walk.next(p, w)) {
       const int acc = local_tile & 1;
       const uint32_t acc_phase = (local_tile >> 1) & 1;
       bool ok = mbar_wait_bounded(&tfull_bar[acc], acc_phase, abort_flag);
@@ -837,10 +854,21 @@ extern "C" int cvb_gemm_bf16(const CvbGemmArgs* a, void* stream_v) {
   } else {
     if (split <= 0) {  // auto: only atomically accumulating epilogues may split K
       split = 1;
-      if (a->epi == EPI_ATOMIC_F32 && mn_tiles < sms) {
-        split = (2 * sms + mn_tiles - 1) / mn_tiles;
-        const int max_split = p.kblocks / 4 > 0 ? p.kblocks / 4 : 1;
-        if (split > max_split) split = max_split;
+      if (a->epi == EPI_ATOMIC_F32 && mn_tiles < 8 * sms) {
+        // Few tiles and a long K (weight gradients): pick the split whose number of waves x k-blocks per item
+        // is smallest; every item also pays for its pipeline fill and atomic epilogue (measured on the weight-
+        // gradient shapes of the 0.8B model: worth about 24 k-blocks, a smaller figure over-splits wide outputs).
+        static const int item_cost = [] { const char* e = getenv("CVERL_B200_GEMM_SPLIT_COST"); return e ? atoi(e) : 24; }();
+        const int max_split = p.kblocks / 8 > 16 ? 16 : (p.kblocks / 8 > 0 ? p.kblocks / 8 : 1);
+        long long best = -1;
+        for (int s = 1; s <= max_split; ++s) {
+          const long long waves = (static_cast<long long>(mn_tiles) * s + sms - 1) / sms;
+          const long long cost = waves * ((p.kblocks + s - 1) / s + item_cost);
+          if (best < 0 || cost < best) {
+            best = cost;
+            split = s;
+          }
+        }
       }
     }
     if (split > 1 && a->epi != EPI_ATOMIC_F32) return -4;
