@@ -50,8 +50,8 @@ _CODES = {"p": c_void_p, "l": c_ll, "i": c_int, "f": c_float, "d": C.c_double}
 
 # name -> argument codes (p pointer, l long long, i int, f float); every launcher returns int
 _CUDA_PROTOS = {
-    "cvb_rmsnorm_fwd": "ppppppplillff p",
-    "cvb_rmsnorm_bwd": "ppppppppplilllf p",
+    "cvb_rmsnorm_fwd": "ppppppplillff il p",
+    "cvb_rmsnorm_bwd": "ppppppppplilllf illl p",
     "cvb_headnorm_rope_fwd": "ppppp lii ll i pp i ff i p",
     "cvb_headnorm_rope_bwd": "ppppppp lii ll i pp i f i p",
     "cvb_swiglu_fwd": "pp l i l p",

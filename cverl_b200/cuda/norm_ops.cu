@@ -53,13 +53,22 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf
 // ---------------------------------------------------------------------------
 // forward: optional residual add, optional gate
 // ---------------------------------------------------------------------------
+// Element offset of gate row `row`.  block = 0: rows lie `stride` apart.  block > 0: the rows are (token, head)
+// pairs of a column range of a wider [tokens, ...] tensor: `block` heads per token lie `stride` apart and the
+// tokens `block_stride` apart.
+__device__ __forceinline__ long long gate_off(long long row, long long stride, int block, long long block_stride) {
+  if (block <= 0) return row * stride;
+  const long long tok = row / block;
+  return tok * block_stride + (row - tok * block) * stride;
+}
+
 template <int NVEC>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ resid_in,
                    const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ gate,
                    __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ resid_out,
                    float* __restrict__ rstd_out, long long rows, int D, long long x_stride,
-                   long long gate_stride, float eps, float w_offset) {
+                   long long gate_stride, float eps, float w_offset, int gate_block, long long gate_block_stride) {
   const int lanes = min(32, D / 8);
   const int rows_per_warp = 32 / lanes;
   const int lane = threadIdx.x & 31;
@@ -106,7 +115,7 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 #pragma unroll
         for (int j = 0; j < 8; ++j) o.v[j] = a.v[j] * rstd * (w_offset + ww.v[j]);
         if (gate) {
-          Vec8 g = load8(gate + row * gate_stride + c);
+          Vec8 g = load8(gate + gate_off(row, gate_stride, gate_block, gate_block_stride) + c);
 #pragma unroll
           for (int j = 0; j < 8; ++j) o.v[j] *= silu_f(g.v[j]);
         }
@@ -128,7 +137,8 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
                    const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ dres,
                    __nv_bfloat16* __restrict__ dx, __nv_bfloat16* __restrict__ dgate,
                    float* __restrict__ dw, long long rows, int D, long long x_stride,
-                   long long gate_stride, long long dx_stride, float w_offset) {
+                   long long gate_stride, long long dx_stride, float w_offset, int gate_block,
+                   long long gate_block_stride, long long dgate_stride, long long dgate_block_stride) {
   extern __shared__ float s_dw[];  // [D]
   for (int i = threadIdx.x; i < D; i += NORM_THREADS) s_dw[i] = 0.f;
   __syncthreads();
@@ -157,7 +167,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
         Vec8 g = load8(dy + row * D + c);
         Vec8 ww = load8(w + c);
         Vec8 z;
-        if (gate) z = load8(gate + row * gate_stride + c);
+        if (gate) z = load8(gate + gate_off(row, gate_stride, gate_block, gate_block_stride) + c);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           float gg = g.v[j] * (w_offset + ww.v[j]);
@@ -175,7 +185,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
         Vec8 g = load8(dy + row * D + c);
         Vec8 ww = load8(w + c);
         Vec8 z, o, dz;
-        if (gate) z = load8(gate + row * gate_stride + c);
+        if (gate) z = load8(gate + gate_off(row, gate_stride, gate_block, gate_block_stride) + c);
         Vec8 dr;
         if (dres) dr = load8(dres + row * D + c);
 #pragma unroll
@@ -194,7 +204,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
           dw_acc[i][j] += gy * xhat;
         }
         store8(dx + row * dx_stride + c, o);
-        if (gate) store8(dgate + row * gate_stride + c, dz);
+        if (gate) store8(dgate + gate_off(row, dgate_stride, gate_block, dgate_block_stride) + c, dz);
       }
     }
   }
@@ -401,10 +411,13 @@ static inline bool cvb_misaligned(std::initializer_list<const void*> ptrs) {
 
 extern "C" int cvb_rmsnorm_fwd(const void* x, const void* resid_in, const void* w, const void* gate, void* y,
                                void* resid_out, float* rstd, long long rows, int D, long long x_stride,
-                               long long gate_stride, float eps, float w_offset, void* stream) {
+                               long long gate_stride, float eps, float w_offset, int gate_block,
+                               long long gate_block_stride, void* stream) {
   const int nvec = norm_nvec(D);
   if (nvec < 0) return -1;
-  if (cvb_misaligned({x, resid_in, w, gate, y, resid_out}) || x_stride % 8 || gate_stride % 8) return -2;
+  if (cvb_misaligned({x, resid_in, w, gate, y, resid_out}) || x_stride % 8 || gate_stride % 8 ||
+      gate_block_stride % 8 || gate_block < 0)
+    return -2;
   if (rows <= 0) return 0;
   const int lanes = D / 8 < 32 ? D / 8 : 32;
 #define CVB_FWD(NV)                                                                                          \
@@ -413,7 +426,7 @@ extern "C" int cvb_rmsnorm_fwd(const void* x, const void* resid_in, const void* 
         static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(resid_in),                   \
         static_cast<const __nv_bfloat16*>(w), static_cast<const __nv_bfloat16*>(gate),                       \
         static_cast<__nv_bfloat16*>(y), static_cast<__nv_bfloat16*>(resid_out), rstd, rows, D, x_stride,     \
-        gate_stride, eps, w_offset);                                                                         \
+        gate_stride, eps, w_offset, gate_block, gate_block_stride);                                          \
     break;
   switch (nvec) {
     CVB_FWD(1) CVB_FWD(2) CVB_FWD(3) CVB_FWD(4) CVB_FWD(5) CVB_FWD(6) CVB_FWD(7) CVB_FWD(8) CVB_FWD(12)
@@ -427,10 +440,13 @@ extern "C" int cvb_rmsnorm_fwd(const void* x, const void* resid_in, const void* 
 extern "C" int cvb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* gate,
                                const void* dres, void* dx, void* dgate, float* dw, long long rows, int D,
                                long long x_stride, long long gate_stride, long long dx_stride, float w_offset,
-                               void* stream) {
+                               int gate_block, long long gate_block_stride, long long dgate_stride,
+                               long long dgate_block_stride, void* stream) {
+  // gate rows: see gate_off(); dgate has the same row grouping with its own two strides
   const int nvec = norm_nvec(D);
   if (nvec < 0) return -1;
-  if (cvb_misaligned({dy, x, w, gate, dres, dx, dgate}) || x_stride % 8 || gate_stride % 8 || dx_stride % 8)
+  if (cvb_misaligned({dy, x, w, gate, dres, dx, dgate}) || x_stride % 8 || gate_stride % 8 || dx_stride % 8 ||
+      gate_block_stride % 8 || dgate_stride % 8 || dgate_block_stride % 8 || gate_block < 0)
     return -2;
   if (rows <= 0) return 0;
   const int lanes = D / 8 < 32 ? D / 8 : 32;
@@ -442,7 +458,8 @@ extern "C" int cvb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
         static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),                        \
         static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(gate),                \
         static_cast<const __nv_bfloat16*>(dres), static_cast<__nv_bfloat16*>(dx),                           \
-        static_cast<__nv_bfloat16*>(dgate), dw, rows, D, x_stride, gate_stride, dx_stride, w_offset);       \
+        static_cast<__nv_bfloat16*>(dgate), dw, rows, D, x_stride, gate_stride, dx_stride, w_offset,        \
+        gate_block, gate_block_stride, dgate_stride, dgate_block_stride);                                   \
     break;
   switch (nvec) {
     CVB_BWD(1) CVB_BWD(2) CVB_BWD(3) CVB_BWD(4) CVB_BWD(5) CVB_BWD(6) CVB_BWD(7) CVB_BWD(8) CVB_BWD(12)

@@ -347,7 +347,8 @@ class Qwen35Model(torch.nn.Module):
         core = core.to(x.dtype).reshape(T, vh, vd)
         if ctx.cp_size > 1:  # hand the state on; the zero token ties the send into the backward pass
             core = core + send_final_state(state, ctx.cp_group, ctx.cp_rank, ctx.cp_size).to(core.dtype)
-        y = ops.gated_rmsnorm(core, z.reshape(T, vh, vd), self.param(p + "norm.weight"), cfg.rms_norm_eps)
+        # z goes in as the projection's column range: the norm reads it (and writes its gradient) in place
+        y = ops.gated_rmsnorm(core, z, self.param(p + "norm.weight"), cfg.rms_norm_eps)
         out = self._row_linear(y.reshape(T, value_dim), self.param(p + "out_proj.weight"))
         if cache is not None:
             cache["state"] = state

@@ -166,6 +166,29 @@ def _conv_bwd_launch(dy, x3, w, dx):
     return None if is_main else dwbuf.to(w.dtype)
 
 
+class _GradSink:
+    """The [B,S,W] projection-gradient buffer of one ``_ConvSiluSplit`` node, created by whoever needs it first
+    in the backward pass: a consumer of one of the passed-through column groups may write its gradient straight
+    into the group's columns (``view_for``) instead of returning a tensor that is copied there later."""
+
+    def __init__(self, shape, dtype, device, sizes):
+        self.shape, self.dtype, self.device, self.sizes = shape, dtype, device, sizes
+        self.buf = None
+
+    def buffer(self):
+        if self.buf is None:
+            self.buf = torch.empty(self.shape, dtype=self.dtype, device=self.device)
+        return self.buf
+
+    def columns(self, group):
+        at = sum(self.sizes[:group])
+        return self.buffer()[..., at:at + self.sizes[group]]
+
+    def view_for(self, group, shape):
+        v = self.columns(group)
+        return v if tuple(v.shape) == tuple(shape) else None
+
+
 class _ConvSiluSplit(torch.autograd.Function):
     """``proj`` [B,S,W] = [x | r1 | r2 ...]: returns (conv1d_silu(x), r1, r2, ...) with the r's as views.  The
     backward writes the convolution's input gradient straight into the first columns of one [B,S,W] buffer and
@@ -182,6 +205,7 @@ class _ConvSiluSplit(torch.autograd.Function):
         count_launch()
         ctx.save_for_backward(proj, w)
         ctx.sizes = sizes
+        ctx.sink = _GradSink(proj.shape, proj.dtype, proj.device, sizes)
         rest, at = [], Cc
         for n in sizes[1:]:
             rest.append(proj[..., at:at + n])
@@ -193,14 +217,16 @@ class _ConvSiluSplit(torch.autograd.Function):
         proj, w = ctx.saved_tensors
         sizes = ctx.sizes
         Cc = sizes[0]
-        dproj = torch.empty(proj.shape, dtype=proj.dtype, device=proj.device)
+        dproj = ctx.sink.buffer()
+        ctx.sink.buf = None   # a second backward through this node gets a fresh buffer
         dw = _conv_bwd_launch(dy, proj[..., :Cc], w, dproj[..., :Cc])
         at = Cc
         for n, d in zip(sizes[1:], drest):
+            dst = dproj[..., at:at + n]
             if d is None:
-                dproj[..., at:at + n].zero_()
-            else:
-                dproj[..., at:at + n].copy_(d)
+                dst.zero_()
+            elif not (d.data_ptr() == dst.data_ptr() and d.stride() == dst.stride() and d.shape == dst.shape):
+                dst.copy_(d)  # (a consumer that wrote through the sink returns this very view: nothing to copy)
             at += n
         return (dproj, dw, *([None] * len(sizes)))
 
@@ -217,7 +243,12 @@ def conv1d_silu_split(proj: torch.Tensor, w: torch.Tensor, sizes):
     sizes = tuple(int(s) for s in sizes)
     if (_native(proj) and proj.is_contiguous() and sizes[0] % 8 == 0 and proj.shape[-1] % 8 == 0
             and w.shape[1] in (2, 3, 4) and proj.data_ptr() % 16 == 0):
-        return _ConvSiluSplit.apply(proj, w, *sizes)
+        outs = _ConvSiluSplit.apply(proj, w, *sizes)
+        node = outs[0].grad_fn
+        if node is not None and hasattr(node, "sink"):
+            for g, r in enumerate(outs[1:], start=1):
+                r._grad_sink = (node.sink, g)
+        return outs
     parts = proj.split(list(sizes), dim=-1)
     return (conv1d_silu(parts[0], w), *parts[1:])
 

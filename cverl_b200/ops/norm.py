@@ -91,7 +91,7 @@ class _AddRmsNorm(torch.autograd.Function):
         rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
         r2 = resid.reshape(-1, D).contiguous() if resid is not None else None
         rc = nv.cuda().cvb_rmsnorm_fwd(x2.data_ptr(), nv.ptr(r2), w.data_ptr(), None, y.data_ptr(), nv.ptr(h),
-                                       rstd.data_ptr(), rows, D, x2.stride(0), 0, eps, w_offset, nv.stream())
+                                       rstd.data_ptr(), rows, D, x2.stride(0), 0, eps, w_offset, 0, 0, nv.stream())
         nv.check(rc, "cvb_rmsnorm_fwd")
         count_launch()
         hh = h if h is not None else x2
@@ -114,7 +114,7 @@ class _AddRmsNorm(torch.autograd.Function):
         dwbuf, is_main = _wgrad_buffer(w)
         rc = nv.cuda().cvb_rmsnorm_bwd(dy2.data_ptr(), h.data_ptr(), w.data_ptr(), rstd.data_ptr(), None,
                                        nv.ptr(dres), dx.data_ptr(), None, dwbuf.data_ptr(), rows, D,
-                                       h.stride(0), 0, D, ctx.w_offset, nv.stream())
+                                       h.stride(0), 0, D, ctx.w_offset, 0, 0, 0, 0, nv.stream())
         nv.check(rc, "cvb_rmsnorm_bwd")
         count_launch()
         dxv = dx.view(ctx.shape)
@@ -139,53 +139,80 @@ def rmsnorm(x, w, eps: float = 1e-6, w_offset: float = 1.0):
 # ----------------------------------------------------------------------------
 # gated RMSNorm: y = rmsnorm(x) * w * silu(z)   (rows = tokens*heads, D = head dim)
 # ----------------------------------------------------------------------------
+def _gate_layout(z, rows, D):
+    """(tensor to read, row stride, block, block stride) for the gate of a [rows, D] gated norm.  A column range
+    of a wider [tokens, width] tensor (the z group of the linear-attention projection) is read in place: its rows
+    are (token, head) pairs, ``block`` heads per token."""
+    if z.dim() >= 2 and z.stride(-1) == 1 and z.shape[-1] % D == 0 and z.shape[-1] != D:
+        z2 = z.reshape(-1, z.shape[-1]) if z.dim() != 2 else z
+        heads = z2.shape[1] // D
+        if (z2.shape[0] * heads == rows and z2.stride(1) == 1 and z2.stride(0) % 8 == 0 and z2.data_ptr() % 16 == 0
+                and z2.data_ptr() == z.data_ptr()):
+            return z2, D, heads, z2.stride(0)
+    z2 = z.reshape(-1, D)
+    if z2.stride(1) != 1 or z2.stride(0) % 8:
+        z2 = z2.contiguous()
+    return z2, z2.stride(0), 0, 0
+
+
 class _GatedRmsNorm(torch.autograd.Function):
+    """y = rmsnorm(x) * w * silu(z).  ``z`` is [..., D] like ``x`` or [tokens..., heads * D] (a column range of
+    the projection output, read in place).  If ``z`` carries ``_grad_sink`` (set by ``conv1d_silu_split``) its
+    gradient is written straight into that op's projection-gradient buffer."""
+
     @staticmethod
-    def forward(ctx, x, z, w, eps):
+    def forward(ctx, x, z, w, eps, sink):
         D = x.shape[-1]
         x2 = x.reshape(-1, D)
-        z2 = z.reshape(-1, D)
         if x2.stride(1) != 1 or x2.stride(0) % 8:
             x2 = x2.contiguous()
-        if z2.stride(1) != 1 or z2.stride(0) % 8:
-            z2 = z2.contiguous()
         rows = x2.shape[0]
+        z2, zs, zb, zbs = _gate_layout(z, rows, D)
         y = torch.empty((rows, D), dtype=x.dtype, device=x.device)
         rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
         rc = nv.cuda().cvb_rmsnorm_fwd(x2.data_ptr(), None, w.data_ptr(), z2.data_ptr(), y.data_ptr(), None,
-                                       rstd.data_ptr(), rows, D, x2.stride(0), z2.stride(0), eps, 0.0,
-                                       nv.stream())
+                                       rstd.data_ptr(), rows, D, x2.stride(0), zs, eps, 0.0, zb, zbs, nv.stream())
         nv.check(rc, "cvb_rmsnorm_fwd(gated)")
         count_launch()
         ctx.save_for_backward(x2, z2, w, rstd)
         ctx.xshape, ctx.zshape = x.shape, z.shape
+        ctx.zlayout = (zs, zb, zbs)
+        ctx.sink = sink
         return y.view(x.shape)
 
     @staticmethod
     def backward(ctx, dy):
         x2, z2, w, rstd = ctx.saved_tensors
         rows, D = x2.shape
+        zs, zb, zbs = ctx.zlayout
         dy2 = dy.reshape(-1, D).contiguous()
         dx = torch.empty((rows, D), dtype=x2.dtype, device=x2.device)
-        dz = torch.empty((rows, D), dtype=x2.dtype, device=x2.device)
-        dwbuf, is_main = _wgrad_buffer(w)
-        # dgate is written with the gate's row stride; give it a dense buffer of that stride
-        if z2.stride(0) != D:
-            z2c = z2.contiguous()
+        dz = None
+        if zb > 0 and ctx.sink is not None:
+            dz = ctx.sink[0].view_for(ctx.sink[1], ctx.zshape)      # a column range of the projection gradient
+        if dz is not None:
+            ds, dbs = D, dz.reshape(-1, dz.shape[-1]).stride(0)
+        elif zb > 0:
+            dz = torch.empty(ctx.zshape, dtype=x2.dtype, device=x2.device)
+            ds, dbs = D, zb * D
         else:
-            z2c = z2
+            dz = torch.empty((rows, D), dtype=x2.dtype, device=x2.device)
+            ds, dbs = D, 0
+        dwbuf, is_main = _wgrad_buffer(w)
         rc = nv.cuda().cvb_rmsnorm_bwd(dy2.data_ptr(), x2.data_ptr(), w.data_ptr(), rstd.data_ptr(),
-                                       z2c.data_ptr(), None, dx.data_ptr(), dz.data_ptr(), dwbuf.data_ptr(),
-                                       rows, D, x2.stride(0), D, D, 0.0, nv.stream())
+                                       z2.data_ptr(), None, dx.data_ptr(), dz.data_ptr(), dwbuf.data_ptr(),
+                                       rows, D, x2.stride(0), zs, D, 0.0, zb, zbs, ds, dbs, nv.stream())
         nv.check(rc, "cvb_rmsnorm_bwd(gated)")
         count_launch()
         dw = None if is_main else dwbuf.to(w.dtype)
-        return dx.view(ctx.xshape), dz.view(ctx.zshape), dw, None
+        return dx.view(ctx.xshape), (dz if zb > 0 else dz.view(ctx.zshape)), dw, None, None
 
 
 def gated_rmsnorm(x, z, w, eps: float = 1e-6):
     if _native(x):
-        return _GatedRmsNorm.apply(x, z, w, eps)
+        return _GatedRmsNorm.apply(x, z, w, eps, getattr(z, "_grad_sink", None))
+    if z.shape != x.shape:
+        z = z.reshape(x.shape)
     return rmsnorm_ref(x, w, eps, 0.0, gate=z)
 
 

@@ -365,10 +365,16 @@ def test_conv1d_silu_split_matches_split_then_conv():
         else:
             x, z, b, a = proj.split(sizes, dim=-1)
             y = conv1d_silu(x, w)
+        # z gates an RMSNorm over 2 heads of 64: fused, the norm reads z in place from the projection and writes
+        # dz straight into the projection-gradient buffer; unfused, both go through copies
+        core = torch.linspace(-2, 2, B * S * 128, device=_dev()).view(B * S, 2, 64).to(torch.bfloat16)
+        gw = torch.linspace(0.5, 1.5, 64, device=_dev()).to(torch.bfloat16)
+        from cverl_b200.ops import gated_rmsnorm
+        n = gated_rmsnorm(core, z if fused else z.reshape(B * S, 2, 64), gw, 1e-6)
         loss = (y.float() * torch.linspace(-1, 1, sizes[0], device=_dev())).sum() + \
-            (z.reshape(B * S, 2, 64).float() ** 2).sum() + torch.sigmoid(b.float()).sum()      # `a` gets no gradient
+            (n.float() * torch.linspace(-1, 1, 64, device=_dev())).sum() + torch.sigmoid(b.float()).sum()  # `a`: no grad
         loss.backward()
         nv.check_status(_dev())
-        res.append((y.detach(), proj.grad, w.grad))
-    assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
+        res.append((y.detach(), proj.grad, w.grad, n.detach()))
+    assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1]) and torch.equal(res[0][3], res[1][3])
     assert _rel_err(res[0][2], res[1][2]) < 1e-3          # atomics: summation order differs between runs
