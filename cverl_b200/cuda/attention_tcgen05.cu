@@ -337,6 +337,9 @@ extern "C" int cvb_attention_fwd(const void* q, const void* k, const void* v, vo
 // =================================================================================================
 constexpr int AB_BKV = 128;  // keys per CTA
 constexpr int AB_BQ = 64;    // queries per step
+// Two warpgroups: warps w and w + 4 share TMEM lane quadrant w (the same 32 keys) and split the 32-column chunks
+// of every TMEM -> registers hand-off between the two MMA rounds of a step.
+constexpr int AB_THREADS = 256;
 
 template <int D, int MODE>
 struct AttBwdCfg {
@@ -373,7 +376,7 @@ struct AttBwdArgs {
 };
 
 template <int D, int MODE>
-__global__ void __launch_bounds__(AT_THREADS, 1)
+__global__ void __launch_bounds__(AB_THREADS, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                      const AttBwdArgs a) {
@@ -389,7 +392,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   float* s_delta = s_lse2 + 2 * AB_BQ;
 
   const int tid = threadIdx.x;
-  const int warp = tid >> 5;
+  const int wg = tid >> 7;      // warpgroup: every second 32-column chunk
+  const int lt = tid & 127;     // key row of this thread = its TMEM lane
+  const int warp = lt >> 5;     // TMEM lane quadrant
   // 1-D grid with the key block slowest: causal key blocks near the start see the most queries, so the
   // longest CTAs are scheduled first and the tail of the launch consists of short ones.
   const int per_block = a.Hkv * a.B;                        // (kv head, batch) pairs per key block
@@ -398,7 +403,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const long long b = (blockIdx.x % per_block) / a.Hkv;
   const int group = a.Hq / a.Hkv;                           // query heads that share this kv head
   const uint32_t sb = smem_u32(smem);
-  const long long kpos = a.k_pos0 + k0 + tid;
+  const long long kpos = a.k_pos0 + k0 + lt;
 
   const int nq = a.Sq / AB_BQ;
   int m_begin = 0;
@@ -439,7 +444,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if (C::NBUF == 2 && steps > 1) load_q(1);
     }
   }
-  if (warp == 0) {
+  if (tid < 32) {
     __syncwarp();
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
@@ -514,7 +519,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         first_vis = f > AB_BQ ? AB_BQ : static_cast<int>(f);
       }
 #pragma unroll 1
-      for (int c0 = 0; c0 < AB_BQ; c0 += 32) {
+      for (int c0 = wg * 32; c0 < AB_BQ; c0 += 64) {
         uint32_t rs[32], rp[32];
         tmem_ld_32x32(tmem + C::TC_S + c0, rs);
         if (C::NEED_DS) tmem_ld_32x32(tmem + C::TC_DP + c0, rp);
@@ -530,7 +535,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          const uint32_t off = asw128(tid, (c0 >> 3) + c);
+          const uint32_t off = asw128(lt, (c0 >> 3) + c);
           if (C::NEED_PT) {
             uint4 u;
             u.x = pack_bf16x2(p[8 * c + 0], p[8 * c + 1]); u.y = pack_bf16x2(p[8 * c + 2], p[8 * c + 3]);
@@ -588,10 +593,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       // dQ^T chunk rows: lane = d, 64 consecutive queries -> vector reductions into [B, Hq, D, Sq]
 #pragma unroll 1
       for (int ch = 0; ch < D / 128; ++ch) {
-        float* dst = a.dqt + ((b * a.Hq + h) * D + ch * 128 + tid) * static_cast<long long>(a.Sq) +
+        float* dst = a.dqt + ((b * a.Hq + h) * D + ch * 128 + lt) * static_cast<long long>(a.Sq) +
                      static_cast<long long>(m) * AB_BQ;
 #pragma unroll 1
-        for (int c0 = 0; c0 < AB_BQ; c0 += 32) {
+        for (int c0 = wg * 32; c0 < AB_BQ; c0 += 64) {
           uint32_t r[32];
           tmem_ld_32x32(tmem + C::TC_DQ + ch * AB_BQ + c0, r);
           tmem_ld_wait();
@@ -612,14 +617,14 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     mbar_wait_bounded(&bar_q[1], 0, &dummy);
   }
   if (ok) {
-    const long long orow = ((b * a.Skv + k0 + tid) * a.Hkv + hk) * D;
+    const long long orow = ((b * a.Skv + k0 + lt) * a.Hkv + hk) * D;
 #pragma unroll 1
     for (int which = 0; which < 2; ++which) {
       if ((which == 0 && !C::NEED_PT) || (which == 1 && !C::NEED_DS)) continue;
       __nv_bfloat16* dst = (which == 0 ? a.dv : a.dk) + orow;
       const uint32_t tc = which == 0 ? C::TC_DV : C::TC_DK;
 #pragma unroll 1
-      for (int c0 = 0; c0 < D; c0 += 32) {
+      for (int c0 = wg * 32; c0 < D; c0 += 64) {
         uint32_t o[32];
         if (steps > 0) {
           tmem_ld_32x32(tmem + tc + c0, o);
@@ -642,7 +647,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) {
+  if (tid < 32) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
@@ -704,7 +709,7 @@ static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
     attr = true;
   }
   dim3 grid(static_cast<unsigned>((a.Skv / AB_BKV) * a.Hkv * B));
-  attention_bwd_kernel<D, MODE><<<grid, AT_THREADS, C::BYTES, st>>>(mq, mk, mv, mdo, a);
+  attention_bwd_kernel<D, MODE><<<grid, AB_THREADS, C::BYTES, st>>>(mq, mk, mv, mdo, a);
   return static_cast<int>(cudaGetLastError());
 }
 

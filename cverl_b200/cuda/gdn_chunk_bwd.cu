@@ -19,7 +19,10 @@
 // gdn_state_dot.  Every product runs as M = 128 tcgen05 MMAs: two 64-row operands are stacked
 // ([Q;K], [dVn;dO], [Gs';dPd']) or the unused half reads don't-care rows (a zero tile where the
 // accumulator is shared).  TMEM lanes 0-63 carry the key-side results, lanes 64-127 the query-side
-// and 64 x 64 ones, so each thread finishes one token row without cross-thread reductions.
+// and 64 x 64 ones.  The CTA has two warpgroups: warps w and w + 4 may both read TMEM lane quadrant w, so
+// every TMEM -> registers -> shared-memory hand-off between two MMA rounds is split by columns (each
+// warpgroup takes every second 32-column chunk), and a token row's scalar results are the sum of two
+// partial sums exchanged through shared memory.
 // Intermediate operands go back to shared memory as bf16 rows in the 128-byte swizzle.
 //
 // The reference back-propagates token by token (cuda/qwen_linear_attention_cuda.cu:212-330).
@@ -30,7 +33,7 @@ namespace cvb {
 
 constexpr int BC = 64;
 constexpr int BD = 128;
-constexpr int BTHREADS = 128;
+constexpr int BTHREADS = 256;  // two warpgroups: warps w and w + 4 share TMEM lane quadrant w and split the columns
 
 __device__ __forceinline__ uint32_t bsw128(uint32_t row, uint32_t chunk) {
   return row * 128u + ((chunk ^ (row & 7u)) << 4);
@@ -65,8 +68,8 @@ struct BwdSmem {
   static constexpr int SS = 180224;       // S^T: 2 x [128 x 64], later dW (16 KB; then dVb1) | Gs' | dPd'  (32 KB)
   static constexpr int DW = SS;
   static constexpr int GP = SS + 16384;
-  static constexpr int SC = 212992;       // scalars                             (2 KB)
-  static constexpr int BARS = SC + 2048;
+  static constexpr int SC = 212992;       // scalars                             (6 KB)
+  static constexpr int BARS = SC + 6144;
   static constexpr int BYTES = BARS + 256 + 1024;
 };
 
@@ -146,14 +149,20 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   float* s_rk = s_c + 128;
   float* s_rq = s_c + 192;
   float* s_ec = s_c + 256;
-  float* s_rowdgg = s_c + 320;
-  float* s_dba = s_c + 384;
-  float* s_dc = s_c + 448;  // [2][64]: query side, key side
+  float* s_rowdgg = s_c + 320;  // [2][64]: per-warpgroup partial row sums from here on
+  float* s_dba = s_c + 448;
+  float* s_dc = s_c + 576;      // [2][64]: query side, key side
+  float* s_dbv = s_c + 704;
+  float* s_dotkb = s_c + 832;
+  float* s_bk = s_c + 960;
+  float* s_aq = s_c + 1088;
 
   const int tid = threadIdx.x;
-  const int warp = tid >> 5;
-  const bool lo = tid < BC;
-  const int t = tid & 63;
+  const int wg = tid >> 7;     // warpgroup: takes every second 32-column chunk of each stage
+  const int lt = tid & 127;
+  const int warp = lt >> 5;    // TMEM lane quadrant
+  const bool lo = lt < BC;
+  const int t = lt & 63;
   const long long item = blockIdx.x;
   const int i = static_cast<int>(item % a.n_chunks);
   const long long bh = item / a.n_chunks;
@@ -162,7 +171,6 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const long long row0 = b * a.T + static_cast<long long>(i) * BC;
   const uint32_t sb = smem_u32(smem);
   uint32_t tmem_base = 0, tmem = 0;
-  float dot_kb = 0.f, dbeta_t = 0.f;  // per-token partial results of lanes 0-63, kept to the end
 
   if (tid == 0) {
     for (int k = 0; k < 6; ++k) mbar_init(bars + k, 1);
@@ -188,12 +196,12 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     tma_load_2d(smem + BwdSmem::DS, &tmDS, bar_load, 0, srow);
     tma_load_2d(smem + BwdSmem::DS + 16384, &tmDS, bar_load, 64, srow);
   }
-  if (warp == 0) {
+  if (tid < 32) {
     __syncwarp();
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
-  if (lo) {
+  if (tid < BC) {
     const float* ax = a.aux + item * 3 * BC;
     const float c = ax[t];
     s_c[t] = c;
@@ -204,20 +212,20 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   }
   {
     // zero tile, and T (fp32, row-major) -> bf16 tile in the 128-byte swizzle
-    uint4* z = reinterpret_cast<uint4*>(smem + BwdSmem::Z0) + tid * 4;
+    uint4* z = reinterpret_cast<uint4*>(smem + BwdSmem::Z0) + tid * 2;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) z[j] = make_uint4(0u, 0u, 0u, 0u);
-    const int r = tid >> 1, half = tid & 1;
-    const float4* src = reinterpret_cast<const float4*>(a.Tm + (item * BC + r) * BC + half * 32);
-    float f[32];
+    for (int j = 0; j < 2; ++j) z[j] = make_uint4(0u, 0u, 0u, 0u);
+    const int r = tid >> 2, quarter = tid & 3;
+    const float4* src = reinterpret_cast<const float4*>(a.Tm + (item * BC + r) * BC + quarter * 16);
+    float f[16];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < 4; ++j) {
       const float4 x = src[j];
       f[4 * j] = x.x, f[4 * j + 1] = x.y, f[4 * j + 2] = x.z, f[4 * j + 3] = x.w;
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      *reinterpret_cast<uint4*>(smem + BwdSmem::T + bsw128(r, half * 4 + j)) = pack8(f + 8 * j);
+    for (int j = 0; j < 2; ++j)
+      *reinterpret_cast<uint4*>(smem + BwdSmem::T + bsw128(r, quarter * 2 + j)) = pack8(f + 8 * j);
   }
   BWD_PUBLISH();
   tmem_base = *tmem_slot;
@@ -256,7 +264,7 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (!lo) {  // Ks_j = e^{c_j} rk_j k_j while the tensor cores run
     const float fk = s_ec[t] * s_rk[t];
 #pragma unroll 1
-    for (int c0 = 0; c0 < BD; c0 += 32) {
+    for (int c0 = wg * 32; c0 < BD; c0 += 64) {
       float f[32];
       load_row32(smem + BwdSmem::QK + 8192, 16384, t, c0, f);
 #pragma unroll
@@ -270,7 +278,7 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   {
     const float e = s_ec[t];
 #pragma unroll 1
-    for (int c0 = 0; c0 < BD; c0 += 32) {
+    for (int c0 = wg * 32; c0 < BD; c0 += 64) {
       uint32_t r[32];
       tmem_ld_32x32(tmem + TC_ACC + c0, r);
       tmem_ld_wait();
@@ -303,7 +311,7 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (warp < 2) {
     const float ct = s_c[t], rqt = s_rq[t];
 #pragma unroll 1
-    for (int c0 = 0; c0 < BC; c0 += 32) {
+    for (int c0 = wg * 32; c0 < BC; c0 += 64) {
       uint32_t r[32];
       tmem_ld_32x32(tmem + TC_SL + c0, r);
       tmem_ld_wait();
@@ -326,9 +334,9 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (warp < 2) {
     const float bt = s_beta[t];
     __nv_bfloat16* dvrow = a.dv + (row0 + t) * a.d_stride + h * BD;
-    float dbv = 0.f;
+    float dbv = 0.f, dot_kb = 0.f;
 #pragma unroll 1
-    for (int c0 = 0; c0 < BD; c0 += 32) {
+    for (int c0 = wg * 32; c0 < BD; c0 += 64) {
       uint32_t r[32];
       tmem_ld_32x32(tmem + TC_DX + c0, r);
       tmem_ld_wait();
@@ -346,7 +354,7 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       store_global32(dvrow + c0, f);
     }
 #pragma unroll 1
-    for (int c0 = 0; c0 < BD; c0 += 32) {
+    for (int c0 = wg * 32; c0 < BD; c0 += 64) {
       uint32_t r[32];
       tmem_ld_32x32(tmem + TC_DK + c0, r);
       tmem_ld_wait();
@@ -359,7 +367,8 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       store_row32(smem + BwdSmem::DD + 8192, 8192, t, c0, f);  // dKb k-blocks at DD + 8 KB and DD + 16 KB
     }
-    dbeta_t = dbv + s_ec[t] * s_rk[t] * dot_kb;
+    s_dbv[wg * BC + t] = dbv;      // this warpgroup's half of <dVb, v> and <dKb, k>
+    s_dotkb[wg * BC + t] = dot_kb;
   }
   BWD_PUBLISH();
 
@@ -380,7 +389,7 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   // ---- stage 6 (lanes 64-127): M1 diag(beta) -> bf16 rows -------------------------------------------------
   if (warp >= 2) {
 #pragma unroll 1
-    for (int c0 = 0; c0 < BC; c0 += 32) {
+    for (int c0 = wg * 32; c0 < BC; c0 += 64) {
       uint32_t r[32];
       tmem_ld_32x32(tmem + TC_SL + c0, r);
       tmem_ld_wait();
@@ -416,7 +425,7 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     float rowdgg = 0.f, dba = 0.f;
     uint8_t* gs = smem + BwdSmem::GP;
 #pragma unroll 1
-    for (int c0 = 0; c0 < BC; c0 += 32) {
+    for (int c0 = wg * 32; c0 < BC; c0 += 64) {
       uint32_t ra[32], rg[32];
       tmem_ld_32x32(tmem + TC_SL + c0, ra);
       tmem_ld_32x32(tmem + TC_D1 + c0, rg);
@@ -438,8 +447,8 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
       }
     }
-    s_rowdgg[t] = rowdgg;
-    s_dba[t] = dba;
+    s_rowdgg[wg * BC + t] = rowdgg;
+    s_dba[wg * BC + t] = dba;
   }
   BWD_PUBLISH();
 
@@ -458,15 +467,15 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   }
   BWD_WAIT(bar_acc, ERR_WAIT_TMEM_FULL);
 
-  // ---- stage 10: finish one token row per thread -----------------------------------------------------------
+  // ---- stage 10: finish one token row per thread pair (the two warpgroups split the columns) ---------------
+  // pass 1: the row's dot product with its own (normalised) input, half per warpgroup
   if (warp < 2) {
-    // key side: dK^ = ACC + e^{c_C - c_t} dKdec + beta_t e^{c_t} dKb, then the l2-norm backward
+    // key side: dK^ = ACC + e^{c_C - c_t} dKdec + beta_t e^{c_t} dKb
     const float edec = __expf(s_c[BC - 1] - s_c[t]);
     const float bek = s_beta[t] * s_ec[t];
-    const float rkt = s_rk[t];
     float bk = 0.f;
 #pragma unroll 1
-    for (int c0 = 0; c0 < BD; c0 += 32) {
+    for (int c0 = wg * 32; c0 < BD; c0 += 64) {
       uint32_t r[32], r3[32], r7[32];
       tmem_ld_32x32(tmem + TC_ACC + c0, r);
       tmem_ld_32x32(tmem + TC_DX + c0, r3);
@@ -483,10 +492,31 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tmem_st_32x32(tmem + TC_ACC + c0, r);
     }
     tmem_st_wait();
+    s_bk[wg * BC + t] = bk;
+  } else {
+    // query side: dQ~ is complete in ACC
+    float aq = 0.f;
+#pragma unroll 1
+    for (int c0 = wg * 32; c0 < BD; c0 += 64) {
+      uint32_t r[32];
+      tmem_ld_32x32(tmem + TC_ACC + c0, r);
+      tmem_ld_wait();
+      float x[32];
+      load_row32(smem + BwdSmem::QK, 16384, t, c0, x);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) aq += __uint_as_float(r[j]) * x[j];
+    }
+    s_aq[wg * BC + t] = aq;
+  }
+  __syncthreads();
+  // pass 2: the l2-norm backward with the full dot product
+  if (warp < 2) {
+    const float rkt = s_rk[t];
+    const float bk = s_bk[t] + s_bk[BC + t];
     const float coef = rkt * rkt * bk;
     __nv_bfloat16* dkrow = a.dk + (row0 + t) * a.d_stride + h * BD;
 #pragma unroll 1
-    for (int c0 = 0; c0 < BD; c0 += 32) {
+    for (int c0 = wg * 32; c0 < BD; c0 += 64) {
       uint32_t r[32];
       tmem_ld_32x32(tmem + TC_ACC + c0, r);
       tmem_ld_wait();
@@ -496,27 +526,21 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       for (int j = 0; j < 32; ++j) f[j] = rkt * (__uint_as_float(r[j]) - x[j] * coef);
       store_global32(dkrow + c0, f);
     }
-    s_dc[BC + t] = 2.f * (s_rowdgg[t] + bek * rkt * dot_kb) - rkt * bk;
-    a.dbeta[(row0 + t) * a.H + h] = dbeta_t + s_dba[t];
+    if (wg == 0) {
+      const float bek = s_beta[t] * s_ec[t];
+      const float dot_kb = s_dotkb[t] + s_dotkb[BC + t];
+      s_dc[BC + t] = 2.f * (s_rowdgg[t] + s_rowdgg[BC + t] + bek * rkt * dot_kb) - rkt * bk;
+      a.dbeta[(row0 + t) * a.H + h] =
+          s_dbv[t] + s_dbv[BC + t] + s_ec[t] * rkt * dot_kb + s_dba[t] + s_dba[BC + t];
+    }
   } else {
-    // query side: dQ~ is complete in ACC
     const float rqt = s_rq[t];
     const float rq_ns = rqt / a.scale;
-    float aq = 0.f;
-#pragma unroll 1
-    for (int c0 = 0; c0 < BD; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld_32x32(tmem + TC_ACC + c0, r);
-      tmem_ld_wait();
-      float x[32];
-      load_row32(smem + BwdSmem::QK, 16384, t, c0, x);
-#pragma unroll
-      for (int j = 0; j < 32; ++j) aq += __uint_as_float(r[j]) * x[j];
-    }
+    const float aq = s_aq[t] + s_aq[BC + t];
     const float coef = rq_ns * rq_ns * aq;
     __nv_bfloat16* dqrow = a.dq + (row0 + t) * a.d_stride + h * BD;
 #pragma unroll 1
-    for (int c0 = 0; c0 < BD; c0 += 32) {
+    for (int c0 = wg * 32; c0 < BD; c0 += 64) {
       uint32_t r[32];
       tmem_ld_32x32(tmem + TC_ACC + c0, r);
       tmem_ld_wait();
@@ -526,10 +550,10 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       for (int j = 0; j < 32; ++j) f[j] = rqt * (__uint_as_float(r[j]) - x[j] * coef);
       store_global32(dqrow + c0, f);
     }
-    s_dc[t] = rqt * aq;
+    if (wg == 0) s_dc[t] = rqt * aq;
   }
   __syncthreads();
-  if (warp == 0) {
+  if (tid < 32) {
     // dg = suffix sum of dc: lane l owns the reversed positions 2l and 2l+1
     const int l = tid;
     const int t0 = BC - 1 - 2 * l, t1 = t0 - 1;
@@ -549,7 +573,7 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 done:
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) {
+  if (tid < 32) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
