@@ -49,6 +49,7 @@ struct BwdArgs {
   float* dbeta;        // [B, T, H]
   float* dg;           // [B, T, H]
   int T, H, n_chunks;
+  long long items;     // B * H * n_chunks
   float scale;
   int* status;
 };
@@ -82,7 +83,7 @@ constexpr uint32_t TC_DK = 384;   // dKb
 
 #define BWD_WAIT(bar, code)                                    \
   {                                                            \
-    const bool ok_ = mbar_wait_bounded(bar, 0, abort_flag);    \
+    const bool ok_ = mbar_wait_bounded(bar, ph, abort_flag);   \
     if (!ok_) {                                                \
       if (!*abort_flag) atomicCAS(a.status, 0, code);          \
       *abort_flag = 1;                                         \
@@ -163,44 +164,70 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const int warp = lt >> 5;    // TMEM lane quadrant
   const bool lo = lt < BC;
   const int t = lt & 63;
-  const long long item = blockIdx.x;
-  const int i = static_cast<int>(item % a.n_chunks);
-  const long long bh = item / a.n_chunks;
-  const int h = static_cast<int>(bh % a.H);
-  const long long b = bh / a.H;
-  const long long row0 = b * a.T + static_cast<long long>(i) * BC;
   const uint32_t sb = smem_u32(smem);
   uint32_t tmem_base = 0, tmem = 0;
+  uint32_t ph = 0;  // every barrier completes once per item: wait parity = item counter & 1
+
+  // TMA loads of one item, in two parts on the same barrier: `rest` (everything but the Q | K tiles) can be
+  // issued as soon as the previous item's last MMA round has retired, `qk` only after its final row pass.
+  auto issue_loads = [&](long long it_, bool rest, bool qk) {
+    const int ci = static_cast<int>(it_ % a.n_chunks);
+    const long long cbh = it_ / a.n_chunks;
+    const int col = static_cast<int>(cbh % a.H) * BD;
+    const int r0 = static_cast<int>((cbh / a.H) * a.T + static_cast<long long>(ci) * BC);
+    const int crow = static_cast<int>(it_ * BC), srow = static_cast<int>(it_ * BD);
+    if (rest) {
+      mbar_arrive_expect_tx(bar_load, 163840);  // the whole item, Q | K included
+      tma_load_2d(smem + BwdSmem::V, &tmV, bar_load, col, r0);
+      tma_load_2d(smem + BwdSmem::V + 8192, &tmV, bar_load, col + 64, r0);
+      tma_load_2d(smem + BwdSmem::DD, &tmDVn, bar_load, 0, crow);
+      tma_load_2d(smem + BwdSmem::DD + 8192, &tmDO, bar_load, col, r0);
+      tma_load_2d(smem + BwdSmem::DD + 16384, &tmDVn, bar_load, 64, crow);
+      tma_load_2d(smem + BwdSmem::DD + 24576, &tmDO, bar_load, col + 64, r0);
+      tma_load_2d(smem + BwdSmem::VN, &tmVn, bar_load, 0, crow);
+      tma_load_2d(smem + BwdSmem::VN + 8192, &tmVn, bar_load, 64, crow);
+      tma_load_2d(smem + BwdSmem::SS, &tmS, bar_load, 0, srow);
+      tma_load_2d(smem + BwdSmem::SS + 16384, &tmS, bar_load, 64, srow);
+      tma_load_2d(smem + BwdSmem::DS, &tmDS, bar_load, 0, srow);
+      tma_load_2d(smem + BwdSmem::DS + 16384, &tmDS, bar_load, 64, srow);
+    }
+    if (qk) {
+      tma_load_2d(smem + BwdSmem::QK, &tmQ, bar_load, col, r0);
+      tma_load_2d(smem + BwdSmem::QK + 8192, &tmK, bar_load, col, r0);
+      tma_load_2d(smem + BwdSmem::QK + 16384, &tmQ, bar_load, col + 64, r0);
+      tma_load_2d(smem + BwdSmem::QK + 24576, &tmK, bar_load, col + 64, r0);
+    }
+  };
 
   if (tid == 0) {
     for (int k = 0; k < 6; ++k) mbar_init(bars + k, 1);
     *abort_flag = 0;
     mbar_fence_init();
-    mbar_arrive_expect_tx(bar_load, 163840);
-    const int col = h * BD, r0 = static_cast<int>(row0);
-    const int crow = static_cast<int>(item * BC), srow = static_cast<int>(item * BD);
-    tma_load_2d(smem + BwdSmem::QK, &tmQ, bar_load, col, r0);
-    tma_load_2d(smem + BwdSmem::QK + 8192, &tmK, bar_load, col, r0);
-    tma_load_2d(smem + BwdSmem::QK + 16384, &tmQ, bar_load, col + 64, r0);
-    tma_load_2d(smem + BwdSmem::QK + 24576, &tmK, bar_load, col + 64, r0);
-    tma_load_2d(smem + BwdSmem::V, &tmV, bar_load, col, r0);
-    tma_load_2d(smem + BwdSmem::V + 8192, &tmV, bar_load, col + 64, r0);
-    tma_load_2d(smem + BwdSmem::DD, &tmDVn, bar_load, 0, crow);
-    tma_load_2d(smem + BwdSmem::DD + 8192, &tmDO, bar_load, col, r0);
-    tma_load_2d(smem + BwdSmem::DD + 16384, &tmDVn, bar_load, 64, crow);
-    tma_load_2d(smem + BwdSmem::DD + 24576, &tmDO, bar_load, col + 64, r0);
-    tma_load_2d(smem + BwdSmem::VN, &tmVn, bar_load, 0, crow);
-    tma_load_2d(smem + BwdSmem::VN + 8192, &tmVn, bar_load, 64, crow);
-    tma_load_2d(smem + BwdSmem::SS, &tmS, bar_load, 0, srow);
-    tma_load_2d(smem + BwdSmem::SS + 16384, &tmS, bar_load, 64, srow);
-    tma_load_2d(smem + BwdSmem::DS, &tmDS, bar_load, 0, srow);
-    tma_load_2d(smem + BwdSmem::DS + 16384, &tmDS, bar_load, 64, srow);
+    if (static_cast<long long>(blockIdx.x) < a.items) issue_loads(blockIdx.x, true, true);
   }
   if (tid < 32) {
     __syncwarp();
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
+  {
+    uint4* z = reinterpret_cast<uint4*>(smem + BwdSmem::Z0) + tid * 2;   // the zero tile, written once
+#pragma unroll
+    for (int j = 0; j < 2; ++j) z[j] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  BWD_PUBLISH();
+  tmem_base = *tmem_slot;
+  tmem = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+
+  // Persistent CTA: items blockIdx.x, blockIdx.x + gridDim.x, ...  Barriers, TMEM and the zero tile are set up
+  // once, and most of the next item's 160 KB is in flight while the current item's last stage runs.
+#pragma unroll 1
+  for (long long item = blockIdx.x; item < a.items; item += gridDim.x, ph ^= 1u) {
+  const int i = static_cast<int>(item % a.n_chunks);
+  const long long bh = item / a.n_chunks;
+  const int h = static_cast<int>(bh % a.H);
+  const long long b = bh / a.H;
+  const long long row0 = b * a.T + static_cast<long long>(i) * BC;
   if (tid < BC) {
     const float* ax = a.aux + item * 3 * BC;
     const float c = ax[t];
@@ -211,10 +238,7 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     s_beta[t] = a.beta[(row0 + t) * a.H + h];
   }
   {
-    // zero tile, and T (fp32, row-major) -> bf16 tile in the 128-byte swizzle
-    uint4* z = reinterpret_cast<uint4*>(smem + BwdSmem::Z0) + tid * 2;
-#pragma unroll
-    for (int j = 0; j < 2; ++j) z[j] = make_uint4(0u, 0u, 0u, 0u);
+    // T (fp32, row-major) -> bf16 tile in the 128-byte swizzle
     const int r = tid >> 2, quarter = tid & 3;
     const float4* src = reinterpret_cast<const float4*>(a.Tm + (item * BC + r) * BC + quarter * 16);
     float f[16];
@@ -228,8 +252,6 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       *reinterpret_cast<uint4*>(smem + BwdSmem::T + bsw128(r, quarter * 2 + j)) = pack8(f + 8 * j);
   }
   BWD_PUBLISH();
-  tmem_base = *tmem_slot;
-  tmem = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
   BWD_WAIT(bar_load, ERR_WAIT_FULL);
 
   // ---- stage 1: D1 = [Q;K] K^T, dP = dO Vn^T, [-dW ; dQd] = [dVn;dO] S^T, dVb = T^T dVn -------------------
@@ -466,6 +488,12 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     umma_commit(bar_acc);  // also covers dKdec
   }
   BWD_WAIT(bar_acc, ERR_WAIT_TMEM_FULL);
+  // Every shared-memory region but Q | K is dead from here on (the final stage reads Q | K, TMEM and scalars):
+  // start the next item's loads into them.
+  if (tid == 0 && item + gridDim.x < a.items) {
+    fence_proxy_async_smem();
+    issue_loads(item + gridDim.x, true, false);
+  }
 
   // ---- stage 10: finish one token row per thread pair (the two warpgroups split the columns) ---------------
   // pass 1: the row's dot product with its own (normalised) input, half per warpgroup
@@ -552,7 +580,9 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
     if (wg == 0) s_dc[t] = rqt * aq;
   }
-  __syncthreads();
+  tc_fence_before();
+  __syncthreads();   // all reads of Q | K, of TMEM and of this item's scalars are done
+  if (tid == 0 && item + gridDim.x < a.items) issue_loads(item + gridDim.x, false, true);
   if (tid < 32) {
     // dg = suffix sum of dc: lane l owns the reversed positions 2l and 2l+1
     const int l = tid;
@@ -570,7 +600,14 @@ gdn_chunk_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     a.dg[(row0 + t0) * a.H + h] = excl + v0;
     a.dg[(row0 + t1) * a.H + h] = excl + pair;
   }
+  }  // items
 done:
+  if (*abort_flag && tid == 0) {
+    // a wait ran out: the next item's loads may still be in flight; give them a bounded time to land
+    const long long t0 = clock64();
+    while (clock64() - t0 < (1ll << 21)) {
+    }
+  }
   tc_fence_before();
   __syncthreads();
   if (tid < 32) {
@@ -659,6 +696,7 @@ extern "C" int cvb_gdn_chunk_bwd(const void* q, const void* k, const void* v, lo
   a.dq = static_cast<__nv_bfloat16*>(dq); a.dk = static_cast<__nv_bfloat16*>(dk); a.dv = static_cast<__nv_bfloat16*>(dv);
   a.d_stride = d_tok_stride;
   a.dbeta = dbeta; a.dg = dg; a.T = T; a.H = H; a.n_chunks = n; a.scale = scale; a.status = status;
+  a.items = items;
   static bool attr = false;
   if (!attr) {
     if (cudaFuncSetAttribute(gdn_chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::BYTES) !=
@@ -666,7 +704,13 @@ extern "C" int cvb_gdn_chunk_bwd(const void* q, const void* k, const void* v, lo
       return -11;
     attr = true;
   }
-  gdn_chunk_bwd_kernel<<<static_cast<unsigned>(items), BTHREADS, BwdSmem::BYTES, st>>>(mq, mk, mv, mdo, mdvn, mvn, ms,
-                                                                                        mds, a);
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  const unsigned grid = static_cast<unsigned>(items < sms ? items : sms);  // persistent: one CTA per SM
+  gdn_chunk_bwd_kernel<<<grid, BTHREADS, BwdSmem::BYTES, st>>>(mq, mk, mv, mdo, mdvn, mvn, ms, mds, a);
   return static_cast<int>(cudaGetLastError());
 }
