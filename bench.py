@@ -147,6 +147,10 @@ def main():
     cfg = Qwen35TextConfig.qwen3_5_0_8b()
     if args.layers:
         cfg = Qwen35TextConfig(num_hidden_layers=args.layers)
+    if tp > 2 and args.tp_comm == "symm":
+        # measured (cverl_b200.bench_collectives): the mirror-store all-reduce beats NCCL at TP=2 (0.25 vs 0.32 ms
+        # on the out_proj shape) and loses from TP=4 on, where every rank would store its full partial N-1 times
+        args.tp_comm = "nccl"
     if tp > 1 and args.tp_comm == "symm":
         from cverl_b200.parallel.tp_symm import TpSymm
         ctx.tp_symm = TpSymm(ctx.tp_group, dev, args.micro_batch * (PROMPT_LEN + RESPONSE_LEN), cfg.hidden_size)

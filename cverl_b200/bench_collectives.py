@@ -1,0 +1,181 @@
+"""Micro-benchmarks of the fused compute + collective kernels against their NCCL counterparts.
+
+``torchrun --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 -m cverl_b200.bench_collectives [--numel E]``
+
+One process per GPU.  Every case is timed with CUDA events on the launching stream after a barrier, 3 warm-ups,
+``--iters`` timed runs, and reported as the MAX over ranks (rank 0 prints one JSON line per case):
+
+* ``zero_rs``   reduce-scatter (mean) of the fp32 gradient buffer + squared norm of the shard:
+                one pull kernel over peer memory (``cvb_reduce_scatter_sumsq``, between two flag barriers)
+                vs ``reduce_scatter_tensor`` + a norm kernel.
+* ``zero_ag``   AdamW on the shard + all-gather of the bf16 parameters: one kernel whose stores go to every
+                peer (``cvb_flat_adamw_allgather``) vs the local AdamW kernel + ``all_gather_into_tensor``.
+* ``tp_gemm``   row-parallel linear, GEMM + all-reduce: the tcgen05 GEMM whose epilogue stores each tile into
+                every peer's slot, a flag barrier and a local sum, vs the same GEMM + NCCL all-reduce.
+* ``push``      weight push of the bf16 parameter buffer from rank i to rank i + N/2 by peer stores
+                (``cvb_broadcast_store``) vs NCCL send / recv.
+
+``link_frac`` is the bytes that must cross NVLink per GPU and direction divided by the time and by 770 GB/s (the
+measured peer-copy bandwidth of this pool); for ``tp_gemm`` the roofline time is the slower of FLOPs / measured
+GEMM peak and bytes / 770 GB/s, and ``roofline_frac`` = that time / measured time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+LINK_GBS = 770.0
+
+
+def _time(fn, iters, group):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    ms = []
+    for _ in range(iters):
+        dist.barrier(group)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms.append(e0.elapsed_time(e1))
+    t = torch.tensor([sum(ms) / len(ms)], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    return float(t.item())
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--numel", type=int, default=752 * 1024 * 1024, help="parameters (0.8B model: 7.5e8)")
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--tokens", type=int, default=40960)
+    ap.add_argument("--what", default="zero_rs,zero_ag,tp_gemm,push")
+    a = ap.parse_args(argv)
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    group = dist.group.WORLD
+    from . import _native as nv
+    from .ops import optim as optim_ops
+    from .optim import AdamWOptions
+    from .optim.adamw import FlatAdamW
+    from .parallel.symm import FusedZeroComm, P2pBroadcaster, SymmetricHeap
+
+    def report(**kw):
+        if rank == 0:
+            print(json.dumps(kw), flush=True)
+
+    n = a.numel // (world * 8) * (world * 8)
+    shard = n // world
+    begin = rank * shard
+    what = set(a.what.split(","))
+    heap = SymmetricHeap(group, dev)
+
+    if what & {"zero_rs", "zero_ag"} and world > 1:
+        fc = FusedZeroComm(heap)
+        params = fc.allocator(n, torch.bfloat16)
+        grads = fc.allocator(n, torch.float32)
+        params.normal_(0, 0.02)
+        gshard = torch.empty(shard, dtype=torch.float32, device=dev)
+        out = torch.empty(shard, dtype=torch.float32, device=dev)
+        adam = FlatAdamW(params[begin:begin + shard], AdamWOptions(lr=1e-6, beta2=0.95, use_master_weights=False))
+        if "zero_rs" in what:
+            def fused_rs():
+                grads.fill_(1e-3)   # (the fused call zeroes the buffer afterwards, as the optimizer needs)
+                fc.reduce_scatter_mean_sumsq(gshard, begin)
+
+            def nccl_rs():
+                grads.fill_(1e-3)
+                dist.reduce_scatter_tensor(out, grads, op=dist.ReduceOp.AVG, group=group)
+                optim_ops.sumsq(out)
+                grads.zero_()
+
+            def fill_only():
+                grads.fill_(1e-3)
+            t_fill = _time(fill_only, a.iters, group)
+            tf, tn = _time(fused_rs, a.iters, group) - t_fill, _time(nccl_rs, a.iters, group) - t_fill
+            link_bytes = (world - 1) * shard * 4          # pulled from every peer
+            report(case="zero_rs", n_gpus=world, numel=n, fused_ms=tf, nccl_ms=tn,
+                   link_gbs=link_bytes / tf / 1e6, link_frac=link_bytes / tf / 1e6 / LINK_GBS,
+                   note="reduce-scatter(mean) + sumsq + zeroing of the 4-byte gradient buffer")
+        if "zero_ag" in what:
+            clip = torch.ones(1, device=dev)
+
+            def fused_ag():
+                fc.adamw_allgather(adam, gshard, clip, begin)
+
+            def nccl_ag():
+                adam.step(gshard, clip=clip)
+                dist.all_gather_into_tensor(params, params[begin:begin + shard], group=group)
+            gshard.fill_(1e-3)
+            tf, tn = _time(fused_ag, a.iters, group), _time(nccl_ag, a.iters, group)
+            link_bytes = (world - 1) * shard * 2          # stored to every peer
+            report(case="zero_ag", n_gpus=world, numel=n, fused_ms=tf, nccl_ms=tn,
+                   link_gbs=link_bytes / tf / 1e6, link_frac=link_bytes / tf / 1e6 / LINK_GBS,
+                   note="AdamW on the shard (24 B / element local traffic) + all-gather of bf16 parameters")
+        nv.check_status(dev)
+
+    if "tp_gemm" in what and world > 1:
+        from .ops import gemm_nt
+        from .parallel.tp_symm import TpSymm
+        M, N, K = a.tokens, 1024, max(64, 2048 // world)  # out_proj of the 0.8B model: K = 2048 split over TP
+        tp = TpSymm(group, dev, M, N)
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
+
+        def fused():
+            tp.reduce_gemm_nt(x, w)
+
+        def nccl():
+            y = gemm_nt(x, w)
+            dist.all_reduce(y, group=group)
+        tf, tn = _time(fused, a.iters, group), _time(nccl, a.iters, group)
+        flops = 2.0 * M * N * K
+        link_bytes = (world - 1) * M * N * 2
+        peak = 1627e12
+        try:
+            from .bench_kernels import _peaks
+            peak = _peaks()["bf16_tflops"] * 1e12
+        except Exception:
+            pass
+        roof_ms = max(flops / peak, link_bytes / (LINK_GBS * 1e9)) * 1e3
+        report(case="tp_gemm", n_gpus=world, M=M, N=N, K=K, fused_ms=tf, nccl_ms=tn, roofline_ms=roof_ms,
+               roofline_frac=roof_ms / tf, link_gbs=link_bytes / tf / 1e6)
+        nv.check_status(dev)
+
+    if "push" in what and world > 1 and world % 2 == 0:
+        nbytes = n * 2
+        pb = P2pBroadcaster(heap, nbytes)
+        src = torch.empty(n, dtype=torch.bfloat16, device=dev).normal_()
+        dst = pb.tensor(n, torch.bfloat16)
+        half = world // 2
+
+        def fused():
+            if rank < half:
+                pb.push(src, [rank + half])
+            pb.sync()
+
+        def nccl():
+            if rank < half:
+                dist.send(src, rank + half, group=group)
+            else:
+                dist.recv(dst, rank - half, group=group)
+        tf, tn = _time(fused, a.iters, group), _time(nccl, a.iters, group)
+        report(case="push", n_gpus=world, bytes=nbytes, fused_ms=tf, nccl_ms=tn, link_gbs=nbytes / tf / 1e6,
+               link_frac=nbytes / tf / 1e6 / LINK_GBS, note=f"{half} trainers -> {half} rollout ranks, one copy each")
+        nv.check_status(dev)
+    dist.barrier(group)
+    dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
