@@ -4,7 +4,7 @@
 // out of the convolution output), beta and g it produces everything the state scan and the
 // output kernel consume:
 //     rq, rk      l2-norm factors            c        cumulative log-decay inside the chunk
-//     A[t,u]    = beta_t e^{c_t-c_u} <k^_t,k^_u> (u<t)      T = (I + A)^-1   (forward substitution)
+//     A[t,u]    = beta_t e^{c_t-c_u} <k^_t,k^_u> (u<t)      T = (I + A)^-1   (blocked triangular inverse, fp32)
 //     W  = T diag(beta e^c) K^     U = T diag(beta) V       (pseudo keys / values, WY form)
 //     P[t,u]    = e^{c_t-c_u} <q~_t,k^_u> (u<=t)            Kd = e^{c_C-c} K^      Qd = e^{c} Q~
 // All products run with M = 128 on the tensor cores: [K;Q] K^T stacks the two 64-row tiles, and
@@ -49,12 +49,13 @@ struct PrepSmem {
   static constexpr int TP = 49152;        // T'  bf16 [64 x 64]
   static constexpr int TPP = 57344;       // T'' bf16 [64 x 64]
   static constexpr int SC = 65536;        // scalars: c, beta, rk, rq, partial sums
-  static constexpr int BARS = SC + 2048;
+  static constexpr int XS = SC + 2048;     // fp32 [3][16][16]: block products of the triangular inverse
+  static constexpr int BARS = XS + 3072;
   static constexpr int BYTES = BARS + 128 + 1024;
 };
 
-// Three CTAs per SM (168 registers, 68 KB of shared memory, 128 TMEM columns each): every CTA is one serial
-// chain load -> MMA -> substitution -> MMA -> store, so the SM is kept busy by the other CTAs' phases.
+// Three CTAs per SM (168 registers, 71 KB of shared memory, 128 TMEM columns each): every CTA is one serial
+// chain load -> MMA -> triangular inverse -> MMA -> store, so the SM is kept busy by the other CTAs' phases.
 __global__ void __launch_bounds__(CTHREADS, 3)
 gdn_chunk_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const PrepArgs a) {
@@ -179,10 +180,18 @@ gdn_chunk_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       tmem_ld_wait();
       if (tid < CC) {
         const float bt = s_beta[t] * s_rk[t];
+        // Row t as 16 float4 whose positions are XOR-ed with (t & 15): the threads of a quarter-warp (rows 256
+        // bytes apart) then hit different banks; scalar stores in row order would be a 32-way conflict.
+        float4* arow_w = reinterpret_cast<float4*>(Am + t * CC);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int u = c0 + j;
-          Am[t * CC + u] = (u < t) ? bt * __expf(ct - s_c[u]) * s_rk[u] * __uint_as_float(r[j]) : 0.f;
+        for (int q = 0; q < 8; ++q) {
+          float f[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int j = 4 * q + e, u = c0 + j;
+            f[e] = (u < t) ? bt * __expf(ct - s_c[u]) * s_rk[u] * __uint_as_float(r[j]) : 0.f;
+          }
+          arow_w[((c0 >> 2) + q) ^ (t & 15)] = make_float4(f[0], f[1], f[2], f[3]);
         }
       } else {
         const float qt = s_rq[t];
@@ -202,26 +211,63 @@ gdn_chunk_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
   }
   __syncthreads();
+  {
+    // 3. T = (I + A)^-1 by 16 x 16 blocks, in place over A (fp32 rows, float4 positions XOR-ed with row & 15).
+    //    Diagonal blocks: forward substitution inside the block, one column per thread.  Then block row by block
+    //    row: X_ij = sum_{k=j..i-1} A_ik T_kj and T_ij = -T_ii X_ij for j < i.  A column-by-column substitution
+    //    over all 64 rows is a chain of 2,016 dependent FMAs per thread; here every dot product is independent.
+    auto am = [&](int r, int c) -> float& { return Am[r * CC + ((((c >> 2) ^ (r & 15)) << 2) | (c & 3))]; };
+    float* Xs = reinterpret_cast<float*>(smem + PrepSmem::XS);
+    if (tid < CC) {
+      const int b0 = (tid >> 4) * 16, jc = tid & 15;
+      float dcol[16];
+#pragma unroll
+      for (int r = 0; r < 16; ++r) {
+        float acc = (r == jc) ? 1.f : 0.f;
+#pragma unroll
+        for (int m = 0; m < r; ++m) acc -= am(b0 + r, b0 + m) * dcol[m];
+        dcol[r] = acc;
+      }
+      __syncwarp();   // a block's 16 columns sit in one warp: all have read A_bb before anyone overwrites it
+#pragma unroll
+      for (int r = 0; r < 16; ++r) am(b0 + r, b0 + jc) = dcol[r];
+    }
+    __syncthreads();
+#pragma unroll 1
+    for (int i = 1; i < 4; ++i) {
+      for (int e = tid; e < i * 256; e += CTHREADS) {
+        const int jb = e >> 8, r = (e >> 4) & 15, c = e & 15;
+        float acc0 = 0.f, acc1 = 0.f;
+        for (int k = jb; k < i; ++k) {
+#pragma unroll
+          for (int m = 0; m < 16; m += 2) {
+            acc0 += am(16 * i + r, 16 * k + m) * am(16 * k + m, 16 * jb + c);
+            acc1 += am(16 * i + r, 16 * k + m + 1) * am(16 * k + m + 1, 16 * jb + c);
+          }
+        }
+        Xs[e] = acc0 + acc1;
+      }
+      __syncthreads();
+      for (int e = tid; e < i * 256; e += CTHREADS) {
+        const int jb = e >> 8, r = (e >> 4) & 15, c = e & 15;
+        float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+        for (int m = 0; m < 16; m += 2) {   // T_ii is lower triangular: its upper entries are stored zeros
+          acc0 += am(16 * i + r, 16 * i + m) * Xs[(jb << 8) + (m << 4) + c];
+          acc1 += am(16 * i + r, 16 * i + m + 1) * Xs[(jb << 8) + ((m + 1) << 4) + c];
+        }
+        am(16 * i + r, 16 * jb + c) = -(acc0 + acc1);
+      }
+      __syncthreads();
+    }
+  }
   if (tid < CC) {
-    // 3. forward substitution, one column of T per thread, fully in registers
+    // column j of T into registers, then the scaled bf16 operand tiles (they overwrite A) and the fp32 copy
     const int j = tid;
     float col[CC];
 #pragma unroll
-    for (int r = 0; r < CC; ++r) {
-      // four partial sums: the dot product of row r with the solved prefix is a reduction, and one
-      // accumulator would make it a chain of r dependent FMAs
-      float a0 = (r == j) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-      const float4* arow = reinterpret_cast<const float4*>(Am + r * CC);
-#pragma unroll
-      for (int m4 = 0; m4 < (r + 3) / 4; ++m4) {
-        const float4 av = arow[m4];
-        if (4 * m4 + 0 < r) a0 -= av.x * col[4 * m4 + 0];
-        if (4 * m4 + 1 < r) a1 -= av.y * col[4 * m4 + 1];
-        if (4 * m4 + 2 < r) a2 -= av.z * col[4 * m4 + 2];
-        if (4 * m4 + 3 < r) a3 -= av.w * col[4 * m4 + 3];
-      }
-      col[r] = (a0 + a1) + (a2 + a3);
-    }
+    for (int r = 0; r < CC; ++r)
+      col[r] = Am[r * CC + ((((j >> 2) ^ (r & 15)) << 2) | (j & 3))];
     const float fj = s_beta[j];
     const float fk = fj * __expf(s_c[j]) * s_rk[j];
     // T' and T'' overwrite A: wait until both substitution warps have read their last row of it
