@@ -476,7 +476,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       s_lse2[buf * AB_BQ + tid] = a.lse[qi] * 1.4426950408889634f;
       s_delta[buf * AB_BQ + tid] = a.delta[qi];
     }
-    // ---- round 1: S^T = K Q^T (and dP^T = V dO^T) ----------------------------------------------------------
+    // ---- MMA phase 1: S^T = K Q^T (and dP^T = V dO^T) ---------------------------------------------------------
     if (tid == 0) {
       if (mbar_wait_bounded(&bar_q[buf], phq, abort_flag)) {
         tc_fence_after();
@@ -555,7 +555,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    // ---- round 2: dV += P^T dO, dK += dS^T Q, dQ^T = K^T dS^T --------------------------------------------
+    // ---- MMA phase 2: dV += P^T dO, dK += dS^T Q, dQ^T = K^T dS^T -------------------------------------------
     if (tid == 0) {
       constexpr uint32_t id_acc = umma_idesc(128, D, 1, 0, 1);
       if (C::NEED_PT) {
