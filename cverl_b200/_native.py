@@ -86,6 +86,8 @@ _CUDA_PROTOS = {
     "cvb_gdn_chunk_prep": "ppp l pp l ii ff pppppppp p p",
     "cvb_gdn_chunk_out": "ppppp l ii p p",
     "cvb_gdn_chunk_bwd": "ppp l p ppp pp pp p p l ii f ppp l pp p p",
+    "cvb_gdn_gates_fwd": "pppp pp l i l p",
+    "cvb_gdn_gates_bwd": "pp pppp pp pp l i ll p",
     "cvb_gdn_scan_fwd": "pppppppp l i p p",
     "cvb_gdn_scan_bwd": "pppppppppp l ii p p",
     "cvb_symm_barrier": "p iii p p",

@@ -327,9 +327,9 @@ class Qwen35Model(torch.nn.Module):
             # place instead of concatenating the groups' gradients
             mixed, z, b, a = ops.conv1d_silu_split(proj.view(batch, seq, proj.shape[-1]), conv_w,
                                                    [conv_dim, value_dim, vh, vh])
-        beta = torch.sigmoid(b.float()).view(batch, seq, vh)
-        g = (-torch.exp(self.param(p + "A_log").float()) *
-             F.softplus(a.float() + self.param(p + "dt_bias").float())).view(batch, seq, vh)
+        # beta = sigmoid(b), g = -exp(A_log) softplus(a + dt_bias): one kernel each way on the projection's columns
+        beta, g = gdn_ops.gdn_gates(b, a, self.param(p + "A_log"), self.param(p + "dt_bias"))
+        beta, g = beta.view(batch, seq, vh), g.view(batch, seq, vh)
         # l2norm of q/k and the 1/sqrt(dk) scale on q are applied inside the fused op
         if vh == kh and kd == vd:
             # q | k | v stay packed: the backward kernel writes their gradients into one buffer

@@ -322,6 +322,83 @@ class _GdnChunked(torch.autograd.Function):
                 unblk(dg, False, g), (dS0 if has_s0 else None), None, None)
 
 
+def gdn_gates_ref(b, a, A_log, dt_bias):
+    """beta = sigmoid(b), g = -exp(A_log) * softplus(a + dt_bias), both fp32."""
+    beta = torch.sigmoid(b.float())
+    g = -torch.exp(A_log.float()) * F.softplus(a.float() + dt_bias.float())
+    return beta, g
+
+
+class _GdnGates(torch.autograd.Function):
+    """``gdn_gates_ref`` as one kernel each way on bf16 column groups ``b``, ``a`` [..., H] of the fused
+    projection (read in place).  If they carry ``_grad_sink`` (set by ``conv1d_silu_split``) their gradients
+    are written straight into the projection-gradient buffer."""
+
+    @staticmethod
+    def forward(ctx, b, a, A_log, dt_bias, sink_b, sink_a):
+        from .. import _native as nv
+        from .gemm import count_launch
+        H = b.shape[-1]
+        rows = b.numel() // H
+        beta = torch.empty(b.shape, dtype=torch.float32, device=b.device)
+        g = torch.empty(b.shape, dtype=torch.float32, device=b.device)
+        nv.check(nv.cuda().cvb_gdn_gates_fwd(b.data_ptr(), a.data_ptr(), A_log.data_ptr(), dt_bias.data_ptr(),
+                                             beta.data_ptr(), g.data_ptr(), rows, H, b.stride(-2), nv.stream()),
+                 "cvb_gdn_gates_fwd")
+        count_launch()
+        ctx.save_for_backward(b, a, A_log, dt_bias)
+        ctx.sinks = (sink_b, sink_a)
+        return beta, g
+
+    @staticmethod
+    def backward(ctx, dbeta, dg):
+        from .. import _native as nv
+        from .gemm import count_launch
+        from .norm import _wgrad_buffer
+        b, a, A_log, dt_bias = ctx.saved_tensors
+        H = b.shape[-1]
+        rows = b.numel() // H
+        dbeta = dbeta.float().contiguous()
+        dg = dg.float().contiguous()
+        db = da = None
+        sb, sa = ctx.sinks
+        if sb is not None and sa is not None and sb[0] is sa[0]:
+            db, da = sb[0].view_for(sb[1], b.shape), sa[0].view_for(sa[1], a.shape)
+        if db is None or da is None or db.stride(-2) != da.stride(-2):
+            db = torch.empty(b.shape, dtype=b.dtype, device=b.device)
+            da = torch.empty(a.shape, dtype=a.dtype, device=a.device)
+        gA, mainA = _wgrad_buffer(A_log)
+        gB, mainB = _wgrad_buffer(dt_bias)
+        nv.check(nv.cuda().cvb_gdn_gates_bwd(dbeta.data_ptr(), dg.data_ptr(), b.data_ptr(), a.data_ptr(),
+                                             A_log.data_ptr(), dt_bias.data_ptr(), db.data_ptr(), da.data_ptr(),
+                                             gA.data_ptr(), gB.data_ptr(), rows, H, b.stride(-2), db.stride(-2),
+                                             nv.stream()), "cvb_gdn_gates_bwd")
+        count_launch()
+        return (db, da, None if mainA else gA.to(A_log.dtype), None if mainB else gB.to(dt_bias.dtype), None, None)
+
+
+def gdn_gates(b, a, A_log, dt_bias):
+    """(beta, g) of the Gated-DeltaNet block, fp32, shaped like ``b``.  bf16 CUDA column groups with a common
+    row stride run the fused kernels; anything else runs the torch statement."""
+    H = b.shape[-1]
+
+    def rows_view_ok(t):
+        if t.dim() < 2 or t.stride(-1) != 1:
+            return False
+        s = t.stride(-2)
+        for d in range(t.dim() - 2):        # leading dims must fold into the row index
+            if t.stride(d) != t.stride(d + 1) * t.shape[d + 1]:
+                return False
+        return s >= H
+
+    if (b.is_cuda and b.dtype == torch.bfloat16 and a.dtype == torch.bfloat16 and a.shape == b.shape
+            and A_log.dtype == torch.bfloat16 and dt_bias.dtype == torch.bfloat16 and A_log.is_contiguous()
+            and dt_bias.is_contiguous() and 0 < H <= 256 and (H & (H - 1)) == 0 and rows_view_ok(b) and rows_view_ok(a)
+            and a.stride(-2) == b.stride(-2)):
+        return _GdnGates.apply(b, a, A_log, dt_bias, getattr(b, "_grad_sink", None), getattr(a, "_grad_sink", None))
+    return gdn_gates_ref(b, a, A_log, dt_bias)
+
+
 class _GdnPacked(torch.autograd.Function):
     """The native chunk kernels on a packed activation ``[B,T,3*H*128]`` (column ranges q | k | v, as the
     convolution writes them).  The backward kernel stores dq, dk, dv straight into the column ranges of one

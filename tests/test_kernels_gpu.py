@@ -378,3 +378,41 @@ def test_conv1d_silu_split_matches_split_then_conv():
         res.append((y.detach(), proj.grad, w.grad, n.detach()))
     assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1]) and torch.equal(res[0][3], res[1][3])
     assert _rel_err(res[0][2], res[1][2]) < 1e-3          # atomics: summation order differs between runs
+
+
+@pytest.mark.parametrize("through_split", [True, False])
+def test_gdn_gates_kernel(through_split):
+    """beta = sigmoid(b), g = -exp(A_log) softplus(a + dt_bias): the fused kernels against the torch statement,
+    on column groups of a projection (gradients written through the split op's sink) and on a plain 2-D split."""
+    from cverl_b200.ops import conv1d_silu_split
+    from cverl_b200.ops import gdn
+    from cverl_b200 import _native as nv
+    torch.manual_seed(13)
+    B, S, H = 2, 96, 16
+    sizes = [128, 64, H, H]
+    base = (2.0 * torch.randn(B, S, sum(sizes), device=_dev())).to(torch.bfloat16)
+    base[0, 0, -1] = 30.0                                  # softplus above its linear threshold
+    cw = (0.5 * torch.randn(sizes[0], 4, device=_dev())).to(torch.bfloat16)
+    A0 = torch.log(torch.empty(H, device=_dev()).uniform_(1, 8)).to(torch.bfloat16)
+    D0 = torch.empty(H, device=_dev()).uniform_(-1, 1).to(torch.bfloat16)
+    wb = torch.randn(B, S, H, device=_dev())
+    wg = torch.randn(B, S, H, device=_dev())
+    res = []
+    for fused in (True, False):
+        proj = base.clone().requires_grad_(True)
+        A_log, dt_bias = A0.clone().requires_grad_(True), D0.clone().requires_grad_(True)
+        if through_split:
+            y, z, b, a = conv1d_silu_split(proj, cw, sizes)
+        else:
+            y, z, b, a = proj.view(B * S, -1).split(sizes, dim=-1)
+        beta, g = gdn.gdn_gates(b, a, A_log, dt_bias) if fused else gdn.gdn_gates_ref(b, a, A_log, dt_bias)
+        if fused:
+            assert type(beta.grad_fn).__name__.startswith("_GdnGates")
+        loss = (beta.reshape(B, S, H) * wb).sum() + (g.reshape(B, S, H) * wg).sum() + y.float().sum()
+        loss.backward()
+        nv.check_status(_dev())
+        res.append((beta.detach().reshape(-1), g.detach().reshape(-1), proj.grad[..., -2 * H:].float(),
+                    A_log.grad.float(), dt_bias.grad.float()))
+    for k, tol in zip(range(5), (1e-5, 1e-5, 1e-2, 2e-2, 2e-2)):
+        assert torch.isfinite(res[0][k]).all()
+        assert _rel_err(res[0][k], res[1][k]) < tol, (k, _rel_err(res[0][k], res[1][k]))
