@@ -451,8 +451,12 @@ extern "C" int cvb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
   if (rows <= 0) return 0;
   const int lanes = D / 8 < 32 ? D / 8 : 32;
   int grid = norm_grid(rows, 32 / lanes);
-  if (grid > 148 * 2) grid = 148 * 2;  // fewer CTAs = fewer global atomics on dw
-#define CVB_BWD(NV)                                                                                         \
+  // One resident wave (fewer CTAs = fewer global atomics on dw): the 128-wide rows of the head norms need 80
+  // registers, so three CTAs fit per SM; the wider instantiations fit two.
+  static const int per_sm_env = [] { const char* e = getenv("CVERL_B200_NORM_BWD_CTAS_PER_SM"); return e ? atoi(e) : 0; }();
+  const int per_sm = per_sm_env > 0 ? per_sm_env : (nvec <= 1 ? 3 : 2);
+  if (grid > 148 * per_sm) grid = 148 * per_sm;
+#define CVB_BWD(NV)                                                                                        \
   case NV:                                                                                                  \
     rmsnorm_bwd_kernel<NV><<<grid, NORM_THREADS, D * sizeof(float), static_cast<cudaStream_t>(stream)>>>(   \
         static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),                        \
