@@ -139,3 +139,12 @@ def test_online_grpo_oracle_dumps_rollouts_that_the_trainer_consumes(tiny_dir, t
     p = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=240)
     assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-3000:]
     assert p.stdout.count("step=") == 2
+
+
+def test_benchmark_modules_parse_their_flags():
+    """The kernel and collective benchmarks import without a GPU and describe their flags."""
+    for mod in ("cverl_b200.bench_kernels", "cverl_b200.bench_collectives"):
+        p = subprocess.run([sys.executable, "-m", mod, "--help"], cwd=ROOT, env=dict(os.environ, PYTHONPATH=str(ROOT)),
+                           capture_output=True, text=True, timeout=120)
+        assert p.returncode == 0, p.stderr[-2000:]
+        assert "--iters" in p.stdout
