@@ -251,6 +251,11 @@ def run(argv=None) -> int:
     symm_ok = use_cuda and dtype == torch.bfloat16
     seq_local = (args.prompt_len + args.response_len) // max(args.cp, 1)
     rows = args.micro_batch_seqs * seq_local
+    if args.tp_comm == "symm" and args.tp > 2 and symm_ok:
+        # the mirror-store all-reduce sends every partial N-1 times: measured faster than NCCL at TP=2 only
+        if rank == 0:
+            print("note: --tp-comm symm is used at --tp 2 only; falling back to NCCL all-reduces", flush=True)
+        args.tp_comm = "nccl"
     if args.tp_comm == "symm" and args.tp > 1 and symm_ok:
         from ..parallel.tp_symm import TpSymm
         ctx.tp_symm = TpSymm(ctx.tp_group, device, rows, cfg.hidden_size)
