@@ -104,12 +104,11 @@ class ClockSampler(threading.Thread):
 
 
 def reference_arm(args):
-    """The reference is a CMake/LibTorch C++ project without Python packaging; the offline pip install
-    fails, so the reference arm reports itself unavailable."""
-    print(json.dumps({"impl": "reference",
-                      "unavailable": "reference is a CMake C++ project with no setup.py/pyproject; offline pip "
-                                     "install fails and its CMake needs pcre2.h, which this image lacks"}))
-    return 0
+    """Runs the unmodified reference trainer (built out of tree by ``baseline/build_ref.py``) on this
+    benchmark's configuration; nothing of this framework is imported on that path."""
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+    import ref_arm
+    return ref_arm.run(args)
 
 
 def main():

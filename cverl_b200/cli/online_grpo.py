@@ -85,16 +85,24 @@ def group_advantages(rewards: Sequence[float], pidx: Sequence[int], eps: float =
 
 
 def dump_rollout(path: Path, step: int, tokenizer, prompts, responses, pidx, rewards, advantages,
-                 max_prompt_tokens: int, max_response_tokens: int) -> None:
+                 max_prompt_tokens: int, max_response_tokens: int, answers=None, sidx=None) -> None:
+    """Writes ``rollout_step_%06d.json`` for the trainer's zero-based ``step``: file number and ``"step"`` field
+    are ``step + 1`` (reference: tools/model/qwen3_5_pp_tp_ppo_trainer.cc:745-757,1496-1503).  The file carries
+    both the token-id rows this package's trainer reads and the reference's text fields."""
     seqs = []
     for text, i, rew, adv in zip(responses, pidx, rewards, advantages):
         seqs.append({"prompt_index": i, "prompt_ids": tokenizer.encode(prompts[i])[-max_prompt_tokens:],
                      "response_ids": tokenizer.encode(text)[:max_response_tokens], "reward": rew, "advantage": adv,
                      "response_text": text})
     path.mkdir(parents=True, exist_ok=True)
-    tmp = path / f"rollout_step_{step:06d}.json.tmp"
-    tmp.write_text(json.dumps({"step": step, "sequences": seqs}))
-    tmp.rename(path / f"rollout_step_{step:06d}.json")
+    doc = {"step": step + 1, "sequences": seqs, "prompts": list(prompts), "responses": list(responses),
+           "prompt_indices": [int(i) for i in pidx],
+           "sample_indices": [int(i) for i in (sidx if sidx is not None else range(len(responses)))]}
+    if answers is not None:
+        doc["answers"] = list(answers)
+    tmp = path / f"rollout_step_{step + 1:06d}.json.tmp"
+    tmp.write_text(json.dumps(doc))
+    tmp.rename(path / f"rollout_step_{step + 1:06d}.json")
 
 
 def main(argv=None) -> int:
@@ -145,7 +153,7 @@ def main(argv=None) -> int:
         rewards = [compute_gsm8k_reward(r, answers[i], ropt) for r, i in zip(responses, pidx)]
         if a.dump_rollout_dir:
             dump_rollout(Path(a.dump_rollout_dir), step, policy.tokenizer, prompts, responses, pidx, rewards,
-                         group_advantages(rewards, pidx), a.max_prompt_tokens, a.max_response_tokens)
+                         group_advantages(rewards, pidx), a.max_prompt_tokens, a.max_response_tokens, answers, sidx)
         metrics = {"total_seq": float(len(responses)), "mean_reward": sum(rewards) / max(1, len(rewards))}
         if not a.skip_train:
             metrics = policy.gsm8k_grpo_update(prompts, responses, answers, pidx, sidx, a.max_prompt_tokens,

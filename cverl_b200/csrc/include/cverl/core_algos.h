@@ -2,8 +2,9 @@
  * outcome advantages and the PPO clipped policy loss, on fp32 [rows, cols]
  * views.  Symbol names, argument order and enum values follow the reference
  * (include/cverl/core_algos.h:12-100).  The `_f32_cpu` entry points are served
- * by a dependency-free C++ implementation; the `_f32_cuda` siblings (declared
- * in cverl/core_algos_cuda.h) run fused sm_100a kernels on device pointers.
+ * by a dependency-free C++ implementation; the device versions are the `cvb_*`
+ * launchers declared in cverl_b200/cuda/core_algos_cuda.h (fused sm_100a kernels
+ * on device pointers, exported from libcverl_b200_cuda.so).
  *
  * Every function validates its views (non-null data, F32, expected device,
  * non-negative and matching shapes) and returns CVERL_ERR_INVALID_ARGUMENT

@@ -102,15 +102,24 @@ class Fp32MasterAdamW:
     """Per-tensor AdamW with optional fp32 master weights and fp32 main-grad accumulation
     (reference: fp32_master_adamw.cc:68-268)."""
 
-    def __init__(self, params: Sequence[torch.Tensor], options: AdamWOptions):
+    def __init__(self, params: Sequence[torch.Tensor], options: AdamWOptions,
+                 main_grads: Optional[Sequence[torch.Tensor]] = None):
+        """``main_grads``: existing fp32 gradient accumulators to adopt (views of a flat gradient buffer that
+        the backward kernels fill) instead of allocating one per parameter."""
         options.validate("Fp32MasterAdamW")
         self.options = options
         self.params = list(params)
         self.master = [p.detach().float().clone() if options.use_master_weights else None for p in self.params]
         self.exp_avg = [torch.zeros(p.shape, dtype=torch.float32, device=p.device) for p in self.params]
         self.exp_avg_sq = [torch.zeros(p.shape, dtype=torch.float32, device=p.device) for p in self.params]
-        self.main_grad = [torch.zeros(p.shape, dtype=torch.float32, device=p.device) for p in self.params]
-        self.has_main_grad = False
+        if main_grads is not None:
+            if len(main_grads) != len(self.params) or any(g.shape != p.shape or g.dtype != torch.float32
+                                                          for g, p in zip(main_grads, self.params)):
+                raise ValueError("Fp32MasterAdamW: main_grads must be fp32 tensors shaped like the parameters")
+            self.main_grad = list(main_grads)
+        else:
+            self.main_grad = [torch.zeros(p.shape, dtype=torch.float32, device=p.device) for p in self.params]
+        self.has_main_grad = main_grads is not None
         self.step_count = 0
 
     # --- gradients -----------------------------------------------------------

@@ -23,6 +23,8 @@ class ParallelContext:
     dp_size: int = 1
     pp_rank: int = 0
     pp_size: int = 1
+    # the ranks of one model replica (pp x cp x tp x ep): the non-sharded optimizer modes sum their gradient norm here
+    model_group: Optional[Any] = None
     # fused NVLink kernels (symmetric-memory paths) instead of NCCL for TP / ZeRO
     fused_comm: bool = False
     # ``parallel.tp_symm.TpSymm`` when tensor-parallel linears fuse their all-reduce into the GEMM

@@ -40,6 +40,11 @@ def build_context(world: int, rank: int, *, tp: int = 1, dp: Optional[int] = Non
             if rank in ranks:
                 mine = g
         setattr(ctx, attr, mine)
+    if dp > 1 and world // dp > 1:
+        for ranks in topo.all_groups("model"):
+            g = dist.new_group(ranks)
+            if rank in ranks:
+                ctx.model_group = g
     # first and last pipeline stage of every pipeline group: they share the tied embedding
     ctx.embed_group = None
     if pp > 1:

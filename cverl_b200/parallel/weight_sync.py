@@ -5,9 +5,10 @@ root rank to every rank of a group, in place, in buckets (25 MB by default) that
 dtypes or devices; a bucket of one tensor is sent without the flatten copy; one optional
 barrier closes the sync.  ``send_parameter_shards`` / ``recv_parameter_shards`` move the
 same buckets point to point.  Semantics follow the reference
-(src/distributed/weight_sync.cc:56-272).  On a single NVSwitch node the production path is
-``cverl_b200.parallel.symm.NvlsBroadcaster`` (multicast stores, one pass over the weights);
-this module is the portable path over any ``Collectives`` backend.
+(src/distributed/weight_sync.cc:56-272).  On a single NVSwitch node the fast path is
+``cverl_b200.parallel.symm.P2pBroadcaster`` (one kernel whose stores land in every receiver's
+peer-mapped copy, one pass over the weights); this module is the portable path over any
+``Collectives`` backend.
 """
 from __future__ import annotations
 

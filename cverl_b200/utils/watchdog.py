@@ -2,10 +2,14 @@
 
 The reference has no failure detection: a rank that throws exits and its peers block in NCCL
 forever (tools/distributed/run_qwen_pp_tp_ppo_trainer.sh:123-128).  Here every rank writes a
-heartbeat (monotonic counter + wall time) to a store between steps; before each step the
-trainer asks the watchdog whether a peer went silent or reported a failure, and if so raises
-``PeerFailure`` on the host BEFORE launching further kernels or collectives, so that no GPU
-work is left waiting.  A failing rank records its exception in the store on the way out.
+heartbeat (a counter that only grows) to a store from a small host thread, so a long step or a
+checkpoint write does not look like a dead process; before each step the trainer asks the watchdog
+whether a peer went silent or reported a failure, and if so raises ``PeerFailure`` on the host
+BEFORE launching further kernels or collectives, so that no GPU work is left waiting.  Silence is
+judged on the OBSERVER's monotonic clock (how long since this rank last saw the peer's counter
+move), never by comparing wall clocks of two machines.  A peer that has not written its first
+beat yet (still building its model) is waited for, not reported.  A failing rank records its
+exception in the store on the way out.
 The store is a ``torch.distributed.TCPStore`` / ``FileStore`` or the in-memory ``DictStore``
 used by tests; nothing here touches a GPU.
 """
@@ -49,13 +53,41 @@ class Heartbeat:
     def __init__(self, store, rank: int, world: int, prefix: str = "cverl/hb"):
         self.store, self.rank, self.world, self.prefix = store, rank, world, prefix
         self.count = 0
+        self._lock = threading.Lock()
+        self._thread: Optional[threading.Thread] = None
+        self._halt = threading.Event()
+        self._step = -1
 
     def _key(self, rank: int, what: str) -> str:
         return f"{self.prefix}/{what}/{rank}"
 
     def beat(self, step: Optional[int] = None) -> None:
-        self.count += 1
-        self.store.set(self._key(self.rank, "beat"), f"{self.count}:{time.time()}:{-1 if step is None else step}")
+        with self._lock:
+            self.count += 1
+            if step is not None:
+                self._step = step
+            self.store.set(self._key(self.rank, "beat"), f"{self.count}:{time.time()}:{self._step}")
+
+    def start_background(self, period_s: float) -> None:
+        """Beats every ``period_s`` seconds from a daemon thread (host only; touches no GPU) until ``stop``."""
+        if self._thread is not None:
+            return
+        self._halt.clear()
+
+        def loop():
+            while not self._halt.wait(period_s):
+                try:
+                    self.beat()
+                except Exception:          # the store went away: the process is shutting down
+                    return
+        self._thread = threading.Thread(target=loop, name="cverl-heartbeat", daemon=True)
+        self._thread.start()
+
+    def stop(self) -> None:
+        self._halt.set()
+        if self._thread is not None:
+            self._thread.join(timeout=5.0)
+            self._thread = None
 
     def report_failure(self, message: str) -> None:
         self.store.set(self._key(self.rank, "fail"), message[:2000])
@@ -75,8 +107,30 @@ class Heartbeat:
 class Watchdog:
     """Declares a peer lost when its heartbeat is older than ``timeout_s`` or it reported a failure."""
 
-    def __init__(self, heartbeat: Heartbeat, timeout_s: float = 30.0, clock=time.time):
+    def __init__(self, heartbeat: Heartbeat, timeout_s: float = 30.0, clock=time.monotonic):
         self.hb, self.timeout_s, self.clock = heartbeat, timeout_s, clock
+        self._seen: Dict[int, tuple] = {}      # peer -> (last counter seen, observer time when it last moved)
+        self._armed_at = clock()
+
+    def wait_for_peers(self, timeout_s: float, poll_s: float = 0.05) -> None:
+        """Blocks until every peer has written its first beat (start-up skew: model construction, weight
+        loading); raises ``PeerFailure`` for the ones still missing after ``timeout_s``."""
+        deadline = self.clock() + timeout_s
+        while True:
+            failed = self.failed_ranks()
+            if failed:
+                raise PeerFailure(sorted(failed), "reported a failure: " + "; ".join(failed.values())[:500])
+            missing = [r for r in range(self.hb.world) if r != self.hb.rank and self.hb.read(r) is None]
+            if not missing:
+                break
+            if self.clock() > deadline:
+                raise PeerFailure(missing, f"never wrote a first heartbeat within {timeout_s} s")
+            time.sleep(poll_s)
+        now = self.clock()
+        self._armed_at = now
+        for r in range(self.hb.world):
+            if r != self.hb.rank:
+                self._seen[r] = (self.hb.read(r)[0], now)
 
     def silent_ranks(self) -> List[int]:
         now = self.clock()
@@ -85,7 +139,15 @@ class Watchdog:
             if r == self.hb.rank:
                 continue
             beat = self.hb.read(r)
-            if beat is None or now - beat[1] > self.timeout_s:
+            if beat is None:
+                # no first beat yet: silent only once the grace period since arming has run out
+                if now - self._armed_at > self.timeout_s:
+                    out.append(r)
+                continue
+            last = self._seen.get(r)
+            if last is None or beat[0] != last[0]:
+                self._seen[r] = (beat[0], now)
+            elif now - last[1] > self.timeout_s:
                 out.append(r)
         return out
 

@@ -128,8 +128,9 @@ def test_online_grpo_oracle_dumps_rollouts_that_the_trainer_consumes(tiny_dir, t
     rows = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
     assert [r["step"] for r in rows] == [0, 1] and rows[0]["total_seq"] == 8.0 and rows[0]["pushed_bytes"] > 0
     assert 0.0 < rows[0]["mean_reward"] < 1.0 and rows[0]["param_delta"] > 0
-    f0 = json.loads((rdir / "rollout_step_000000.json").read_text())
-    assert f0["step"] == 0 and len(f0["sequences"]) == 8 and {"prompt_ids", "response_ids", "advantage"} <= set(f0["sequences"][0])
+    f0 = json.loads((rdir / "rollout_step_000001.json").read_text())     # 1-based, as the reference numbers them
+    assert f0["step"] == 1 and len(f0["responses"]) == 8 and len(f0["prompts"]) == 2
+    assert len(f0["sequences"]) == 8 and {"prompt_ids", "response_ids", "advantage"} <= set(f0["sequences"][0])
     # the distributed trainer reads these files step by step
     cmd = [sys.executable, "-m", "cverl_b200.trainer.ppo_trainer", "--backend", "gloo", "--dtype", "float32",
            "--steps", "2", "--rollout-dir", str(rdir), "--prompt-len", "16", "--response-len", "12",
@@ -139,6 +140,20 @@ def test_online_grpo_oracle_dumps_rollouts_that_the_trainer_consumes(tiny_dir, t
     p = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=240)
     assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-3000:]
     assert p.stdout.count("step=") == 2
+    row = dict(kv.split("=", 1) for kv in p.stdout.splitlines()[0].split() if "=" in kv)
+    assert 0.0 < float(row["mean_reward"]) < 1.0 and float(row["adv_abs_sum"]) > 0 and row["rollout_rows"] == "8"
+    # the same files in the reference's text form (no token-id rows): tokenised, scored and GRPO-normalised here
+    tdir = tmp_path / "text_rollouts"
+    tdir.mkdir()
+    for f in rdir.glob("rollout_step_*.json"):
+        doc = json.loads(f.read_text())
+        doc.pop("sequences")
+        (tdir / f.name).write_text(json.dumps(doc))
+    cmd[cmd.index(str(rdir))] = str(tdir)
+    p = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=240)
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-3000:]
+    row2 = dict(kv.split("=", 1) for kv in p.stdout.splitlines()[0].split() if "=" in kv)
+    assert float(row2["mean_reward"]) == pytest.approx(float(row["mean_reward"])) and row2["rollout_rows"] == "8"
 
 
 def test_benchmark_modules_parse_their_flags():

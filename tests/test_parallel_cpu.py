@@ -209,3 +209,83 @@ def test_adamw_master_keeps_small_updates_and_load_state():
     torch.testing.assert_close(opt.master, opt2.master)
     with pytest.raises(ValueError):
         opt2.load_state(opt.master[:4], opt.exp_avg, opt.exp_avg_sq, 1)
+
+
+class _ScriptedDp:
+    """Plays rank ``rank`` of a data-parallel group of ``n``: every peer's gradient is this rank's scaled by a
+    known factor, so reductions have closed forms; calls and their dtypes / sizes are recorded."""
+
+    def __init__(self, rank, n, factors):
+        from cverl_b200.parallel.collectives import Collectives
+        self._rank, self._n, self.factors, self.calls = rank, n, factors, []
+
+    def rank(self):
+        return self._rank
+
+    def world_size(self):
+        return self._n
+
+    def all_reduce(self, t, op, group):
+        from cverl_b200.parallel.collectives import ReduceOp
+        self.calls.append(("all_reduce", t.dtype, t.numel()))
+        total = t.float() * sum(self.factors) / self.factors[self._rank]
+        return (total / self._n if op == ReduceOp.MEAN else total).to(t.dtype)
+
+    def reduce_scatter(self, t, op, group):
+        from cverl_b200.parallel.collectives import ReduceOp
+        self.calls.append(("reduce_scatter", t.dtype, t.numel()))
+        total = t.float() * sum(self.factors) / self.factors[self._rank]
+        total = total / self._n if op == ReduceOp.MEAN else total
+        k = t.numel() // self._n
+        return total[self._rank * k:(self._rank + 1) * k].to(t.dtype)
+
+    def broadcast(self, t, root, group):
+        self.calls.append(("broadcast", root, t.numel()))
+        return t.clone() if root == self._rank else torch.full_like(t, float(root + 100))
+
+
+def test_bucketed_dp_gradient_sync_and_owner_broadcast():
+    """Bucket boundaries, single-tensor buckets, forced communication dtype, a group of one, reduce-scatter
+    padding and the ZeRO-1 owner broadcast, each against a scripted rank (reference behaviour:
+    src/distributed/parallel_ops.cc:226-321)."""
+    from cverl_b200.parallel import dp_sync
+    torch.manual_seed(0)
+    params = [torch.nn.Parameter(torch.randn(n)) for n in (100, 300, 50, 1000, 7)]
+    for p in params:
+        p.grad = torch.randn_like(p)
+    want = [p.grad.clone() * (1.0 + 3.0) / 2.0 for p in params]
+    fake = _ScriptedDp(0, 2, [1.0, 3.0])
+    calls = dp_sync.data_parallel_sync_gradients(params, fake, [0, 1], True, bucket_bytes=1700)
+    # 100+300 floats fit 1700 bytes, 50 opens the next bucket with nothing else fitting beside 1000, then 7
+    assert calls == 4 and [c[2] for c in fake.calls] == [400, 50, 1000, 7]
+    for p, w in zip(params, want):
+        assert torch.allclose(p.grad, w, atol=1e-6)
+    # forced bf16 communication halves the bytes per element, so more fits a bucket, and the wire dtype is bf16
+    fake = _ScriptedDp(1, 2, [1.0, 3.0])
+    dp_sync.data_parallel_sync_gradients(params, fake, [0, 1], False, bucket_bytes=1700, comm_dtype=torch.bfloat16)
+    assert all(c[1] == torch.bfloat16 for c in fake.calls) and [c[2] for c in fake.calls] == [450, 1000, 7]
+    # a data group of one issues nothing; a non-member is refused
+    lone = _ScriptedDp(0, 1, [1.0])
+    assert dp_sync.data_parallel_sync_gradients(params, lone, [0]) == 0 and not lone.calls
+    with pytest.raises(ValueError):
+        dp_sync.data_parallel_sync_gradients(params, _ScriptedDp(5, 2, [1.0, 1.0]), [0, 1])
+    with pytest.raises(ValueError):
+        dp_sync.data_parallel_sync_gradients(params, fake, [0, 1], bucket_bytes=0)
+    # reduce-scatter buckets: padded to the group size, this rank's slice of the mean
+    for p in params:
+        p.grad = torch.ones_like(p)
+    fake = _ScriptedDp(1, 2, [1.0, 1.0])
+    buckets = dp_sync.data_parallel_reduce_scatter_gradients(params, fake, [0, 1], True, bucket_bytes=10 ** 9)
+    assert len(buckets) == 1 and buckets[0].original_numel == 1457 and buckets[0].padded_numel == 1458
+    assert buckets[0].parameter_indices == [0, 1, 2, 3, 4] and buckets[0].shard.numel() == 729
+    assert float(buckets[0].shard[:-1].min()) == 1.0 and float(buckets[0].shard[-1]) == 0.0     # the padding
+    # owner broadcast: rank 0 owns parameters 0 and 3, rank 1 the rest; rank 0 keeps its own and receives the others
+    owners = [0, 1, 1, 0, 1]
+    vals = [torch.full((n,), float(i)) for i, n in enumerate((100, 300, 50, 1000, 7))]
+    fake = _ScriptedDp(0, 2, [1.0, 1.0])
+    calls = dp_sync.broadcast_owner_parameters(vals, owners, fake, [0, 1], bucket_bytes=10 ** 9)
+    assert calls == 2 and [c[1] for c in fake.calls] == [0, 1]
+    assert float(vals[0][0]) == 0.0 and float(vals[3][0]) == 3.0 and all(float(vals[i][0]) == 101.0 for i in (1, 2, 4))
+    # flat bucket ranges cut at parameter boundaries
+    assert dp_sync.flat_bucket_ranges([100, 300, 50, 1000, 7], [0, 104, 408, 464, 1464], 1700, 4) == \
+        [(0, 404), (408, 458), (464, 1464), (1464, 1471)]

@@ -68,11 +68,21 @@ def test_checkpoint_resume_equality_and_formats(tmp_path):
     step_dir = ck / "step_000002"
     manifest = json.loads((step_dir / "manifest.json").read_text())
     assert manifest["complete"] and manifest["format"] == "cverl_pp_tp_flat_shard_checkpoint_v4"
-    assert manifest["rank_files"] == ["rank_0.pt", "rank_1.pt"] and manifest["parallel_dims"]["dp"] == 2
-    assert (ck / "latest_checkpoint.txt").read_text() == "step_000002"
+    # the reference's key names and values (tools/model/qwen3_5_pp_tp_ppo_trainer.cc:1045-1104)
+    assert manifest["step"] == 2 and manifest["optimizer_kind"] == "FlatAdamW" and manifest["use_master_weights"]
+    assert manifest["model_parameters_saved"] is False and manifest["world_size"] == 2
+    assert manifest["data_parallel"] == 2 and manifest["tensor_parallel"] == 1 and manifest["pipeline_parallel"] == 1
+    assert manifest["optimizer"]["type"] == "FlatAdamW" and manifest["optimizer"]["step"] == 2
+    assert manifest["rank_files"][1] == {"global_rank": 1, "expert_rank": 0, "tensor_rank": 0, "context_rank": 0,
+                                         "pipeline_rank": 0, "data_rank": 1, "param_file": "rank_1.pt",
+                                         "metadata_file": "rank_1.json"}
+    assert (ck / "latest_checkpoint.txt").read_text().strip() == "step_000002"
     meta = json.loads((step_dir / "rank_1.json").read_text())
     fs = meta["flat_parameter_shard"]
     assert fs["shard_end"] - fs["shard_begin"] == fs["numel"] and meta["use_master_weights"] is True
+    assert meta["optimizer_kind"] == "FlatAdamW" and meta["optimizer_step"] == 2 and meta["param_file"] == "rank_1.pt"
+    assert fs["dtype"] == "Float" and meta["parameters"][0]["dtype"] in ("BFloat16", "Float") and meta["data_rank"] == 1
+    assert meta["optimizer_param_indices"] == list(range(len(meta["parameters"])))
     from cverl_b200.utils.checkpoint import load_archive
     arch = load_archive(step_dir / "rank_0.pt")
     assert set(arch) == {"flat_param_shard", "flat_exp_avg", "flat_exp_avg_sq", "optim_step"}
@@ -89,6 +99,25 @@ def test_checkpoint_resume_equality_and_formats(tmp_path):
     # a different topology must be refused
     bad = _run(1, "--steps", "3", "--resume-checkpoint", str(ck), port=29684, check=False)
     assert bad.returncode != 0
+
+
+def test_reads_an_archive_written_by_libtorch():
+    """``tests/fixtures/libtorch_output_archive.pt`` was written by LibTorch's ``OutputArchive`` (tensors stored
+    as module parameters; the generating program sits beside it): the reader must return every tensor."""
+    from pathlib import Path
+    from cverl_b200.utils.checkpoint import c10_dtype_name, load_archive, save_archive
+    arch = load_archive(Path(__file__).parent / "fixtures" / "libtorch_output_archive.pt")
+    assert set(arch) == {"flat_param_shard", "flat_exp_avg", "flat_exp_avg_sq", "param_0", "optim_step"}
+    assert int(arch["optim_step"]) == 3 and arch["flat_param_shard"].dtype == torch.bfloat16
+    assert torch.equal(arch["flat_exp_avg"], torch.arange(8).float() * 0.5)
+    assert arch["param_0"].shape == (2, 3)
+    assert c10_dtype_name(torch.bfloat16) == "BFloat16" and c10_dtype_name(torch.float32) == "Float"
+    # and what this package writes has the same container layout: parameters, no buffers
+    import tempfile
+    with tempfile.TemporaryDirectory() as d:
+        save_archive(Path(d) / "a.pt", arch)
+        mod = torch.jit.load(str(Path(d) / "a.pt"))
+        assert sorted(n for n, _ in mod.named_parameters()) == sorted(arch) and not list(mod.named_buffers())
 
 
 def test_resume_refuses_damaged_checkpoints(tmp_path):
@@ -110,7 +139,9 @@ def test_resume_refuses_damaged_checkpoints(tmp_path):
         assert p.returncode != 0, p.stdout[-500:]
 
     resume_fails(lambda d: (d / "manifest.json").write_text(json.dumps(dict(good, complete=False))))
-    resume_fails(lambda d: (d / "manifest.json").write_text(json.dumps(dict(good, step=7))))
+    resume_fails(lambda d: (d / "manifest.json").write_text(
+        json.dumps(dict(good, optimizer=dict(good["optimizer"], step=7)))))
+    resume_fails(lambda d: (d / "manifest.json").write_text(json.dumps(dict(good, optimizer_kind="flat_adamw"))))
     resume_fails(lambda d: (d / "rank_0.pt").unlink())
     # the untouched checkpoint still resumes
     ok = _lines(_run(1, "--steps", "3", "--resume-checkpoint", str(ck), port=29688))
@@ -132,22 +163,29 @@ def test_watchdog_detects_silent_and_failed_peers():
     hbs = [Heartbeat(store, r, 3) for r in range(3)]
     for h in hbs:
         h.beat(0)
-    wd = Watchdog(hbs[0], timeout_s=5.0, clock=lambda: now[0] + 0.0)
-    import time as _t
-    wd.clock = lambda: _t.time()
+    wd = Watchdog(hbs[0], timeout_s=5.0, clock=lambda: now[0])
     wd.check()                                     # everybody alive
-    wd.clock = lambda: _t.time() + 60.0            # peers stop beating: a rank that never joins the step
+    now[0] += 60.0                                 # peers stop beating: a rank that never joins the step
     with pytest.raises(PeerFailure) as e:
         wd.check()
     assert e.value.ranks == [1, 2]
+    # silence is judged by the observer's clock: a peer whose own wall clock is far off is fine while it beats
+    hbs[1].beat(1)
+    hbs[2].beat(1)
+    wd.check()
     # a dropped message: rank 2's heartbeat key is lost in the store
     store2 = DictStore()
     store2.dropped.add("cverl/hb/beat/2")
     hb2 = [Heartbeat(store2, r, 3) for r in range(3)]
     for h in hb2:
         h.beat(0)
+    t2 = [0.0]
+    wd2 = Watchdog(hb2[0], 5.0, clock=lambda: t2[0])
+    wd2.check()                                    # inside the grace period a missing first beat is not a failure
+    t2[0] = 6.0
+    hb2[1].beat(1)                                 # rank 1 is alive and its message arrives; rank 2's never does
     with pytest.raises(PeerFailure) as e:
-        Watchdog(hb2[0], 5.0).check()
+        wd2.check()
     assert e.value.ranks == [2]
     # a rank that raises publishes the failure before exiting
 
@@ -156,10 +194,41 @@ def test_watchdog_detects_silent_and_failed_peers():
         raise ValueError("bad batch")
     with pytest.raises(ValueError):
         failing_rank()
-    wd.clock = lambda: _t.time()
     with pytest.raises(PeerFailure) as e:
         wd.check()
     assert e.value.ranks == [1] and "bad batch" in e.value.reason
+
+
+def test_watchdog_startup_race_and_long_steps():
+    """A peer still building its model has no beat yet: the first check waits for it instead of reporting
+    it; and a step far longer than the timeout is not a failure while the peer's host thread keeps beating."""
+    import threading
+    import time as _t
+    from cverl_b200.utils.watchdog import DictStore, Heartbeat, PeerFailure, Watchdog
+    store = DictStore()
+    hb0, hb1 = Heartbeat(store, 0, 2), Heartbeat(store, 1, 2)
+    hb0.beat(0)
+    late = threading.Timer(0.3, lambda: hb1.beat(0))          # rank 1 arrives 0.3 s late
+    late.start()
+    wd = Watchdog(hb0, timeout_s=0.2)
+    wd.wait_for_peers(timeout_s=5.0)                            # returns once rank 1 has beaten
+    late.join()
+    wd.check()
+    # rank 1 now runs a "step" of 1 s (5x the timeout) with its background thread beating
+    hb1.start_background(0.05)
+    _t.sleep(1.0)
+    wd.check()
+    hb1.stop()
+    _t.sleep(0.5)                                               # the thread is gone: now it is silent
+    with pytest.raises(PeerFailure) as e:
+        wd.check()
+    assert e.value.ranks == [1]
+    # a peer that never shows up at all is reported by the start-up wait
+    store3 = DictStore()
+    lone = Watchdog(Heartbeat(store3, 0, 2), timeout_s=0.2)
+    with pytest.raises(PeerFailure) as e:
+        lone.wait_for_peers(timeout_s=0.3)
+    assert e.value.ranks == [1]
 
 
 def test_simple_grpo_trainer_learns_and_resumes(tmp_path):
@@ -216,3 +285,71 @@ def test_grpo_update_moves_parameters_toward_rewarded_responses():
     after = pol.response_log_probs(batch.prompt_ids, batch.response_ids).detach().sum(-1)
     assert m["param_delta"] > 0 and m["kl_loss"] >= 0
     assert (after - before)[::2].mean() > (after - before)[1::2].mean()        # rewarded responses gained likelihood
+
+
+def test_optimizer_modes_agree_and_v2_checkpoint_resumes(tmp_path):
+    """Flat ZeRO shard, ZeRO-1 with per-parameter owners and the unsharded bucketed all-reduce are the same
+    AdamW: two data-parallel ranks reach the same losses in all three modes; the non-flat mode writes the
+    rank-local v2 checkpoint and resumes from it to the same trajectory."""
+    base = ["--dp", "2", "--micro-batches", "2", "--steps", "4", "--dp-grad-bucket-mb", "1"]
+    flat = _lines(_run(2, *base, port=29701))
+    zero1 = _lines(_run(2, *base, "--dp-shard-optimizer", "true", "--dp-flat-shard-optimizer", "false", port=29702))
+    dense = _lines(_run(2, *base, "--dp-shard-optimizer", "false", port=29703))
+    assert [r["flat_shard_optimizer"] for r in (flat[0], zero1[0], dense[0])] == ["true", "false", "false"]
+    assert [r["dp_shard_optimizer"] for r in (flat[0], zero1[0], dense[0])] == ["true", "true", "false"]
+    for a, b, c in zip(flat, zero1, dense):
+        for other in (b, c):
+            assert float(a["loss_sum"]) == pytest.approx(float(other["loss_sum"]), rel=2e-4, abs=1e-6)
+            assert float(a["global_grad_norm"]) == pytest.approx(float(other["global_grad_norm"]), rel=1e-3)
+    ck = tmp_path / "ck2"
+    mode = ["--dp-shard-optimizer", "true", "--dp-flat-shard-optimizer", "false", "--master-weights", "true"]
+    full = _lines(_run(2, *base, *mode, port=29704))
+    _run(2, *base[:-4], "--steps", "2", "--dp-grad-bucket-mb", "1", *mode, "--checkpoint-dir", str(ck),
+         "--checkpoint-every", "2", port=29705)
+    d = ck / "step_000002"
+    manifest = json.loads((d / "manifest.json").read_text())
+    assert manifest["format"] == "cverl_pp_tp_rank_local_checkpoint_v2" and manifest["optimizer"]["type"] == "Fp32MasterAdamW"
+    metas = [json.loads((d / f"rank_{r}.json").read_text()) for r in range(2)]
+    owned = [set(m["optimizer_param_indices"]) for m in metas]
+    assert owned[0] and owned[1] and not (owned[0] & owned[1])          # every parameter has exactly one owner
+    assert owned[0] | owned[1] == set(range(len(metas[0]["parameters"])))
+    from cverl_b200.utils.checkpoint import load_archive
+    arch = load_archive(d / "rank_0.pt")
+    assert "param_0" in arch and "optim_exp_avg_0" in arch and int(arch["optim_step"]) == 2
+    k = metas[0]["optimizer_param_indices"][0]
+    assert arch[f"param_{k}"].dtype == torch.float32                    # the owner's fp32 master copy
+    resumed = _lines(_run(2, *base, *mode, "--resume-checkpoint", str(ck), port=29706))
+    assert [r["step"] for r in resumed] == ["2", "3"]
+    for ra, rb in zip(full[2:], resumed):
+        assert float(ra["loss_sum"]) == pytest.approx(float(rb["loss_sum"]), rel=1e-5, abs=1e-7)
+
+
+def test_rollout_batches_over_a_file_rendezvous_communicator(tmp_path):
+    """A rollout source started on its own sends ``GpuRolloutBatch`` to two trainer ranks over a communicator
+    that rendezvouses through a file; the trainer reports the batch's reward metrics, and uses the reference
+    log-probs it carries for the KL term."""
+    idf = tmp_path / "rollout_world.id"
+    env = dict(os.environ, OMP_NUM_THREADS="1", PYTHONPATH=str(ROOT))
+    src = subprocess.Popen([sys.executable, "-m", "cverl_b200.cli.rollout_batch_source", "--id-file", str(idf),
+                            "--rank", "0", "--world-size", "3", "--target-ranks", "1,2", "--steps", "2", "--batch", "4",
+                            "--prompt-len", "8", "--response-len", "8", "--backend", "gloo", "--with-ref-log-probs"],
+                           cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    try:
+        p = _run(2, "--dp", "2", "--micro-batches", "2", "--steps", "2", "--rollout-nccl-id-file", str(idf),
+                 "--rollout-nccl-world-size", "3", "--rollout-nccl-rank-offset", "1", "--rollout-nccl-source-rank", "0",
+                 "--kl-coef", "0.1", "--kl-penalty", "k3", port=29711)
+        out, err = src.communicate(timeout=60)
+    finally:
+        if src.poll() is None:
+            src.kill()
+    assert src.returncode == 0, out[-1000:] + err[-2000:]
+    rows = _lines(p)
+    assert len(rows) == 2 and rows[0]["rollout_rows"] == "4"
+    assert float(rows[0]["mean_reward"]) == pytest.approx(0.5) and float(rows[0]["success_rate"]) == pytest.approx(0.5)
+    assert float(rows[0]["adv_abs_sum"]) == pytest.approx(32.0)          # 4 rows x 8 tokens of +-1
+    assert float(rows[0]["kl_loss_sum"]) > 0                             # reference log-probs reached the loss
+
+
+def test_kl_needs_reference_log_probs():
+    p = _run(1, "--steps", "1", "--kl-coef", "0.1", port=29713, check=False)
+    assert p.returncode != 0 and "ref_log_probs" in (p.stdout + p.stderr)
