@@ -95,8 +95,8 @@ _CUDA_PROTOS = {
     "cvb_flat_adamw_allgather": "ppppp p ii ll fffff l p",
     "cvb_broadcast_store": "pp i l p",
     "cvb_sum_parts": "p l i p l p",
-    "cvb_p2p_scatter_rows": "pp i pp ll p",
-    "cvb_p2p_gather_rows": "pp i pp ll p",
+    "cvb_p2p_scatter_rows": "pp i pp ll l p p",
+    "cvb_p2p_gather_rows": "pp i pp ll l p p",
     "cvb_attention_fwd": "ppppp l iiiii f i ll p p",
     "cvb_attention_bwd": "ppppp p pp ppp l iiiii f i ll p p",
     "cvb_router_topk_fwd": "p l iii pp p",

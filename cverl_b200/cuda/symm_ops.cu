@@ -262,15 +262,22 @@ namespace cvb {
 
 template <bool GATHER>
 __global__ void __launch_bounds__(SY_THREADS)
-p2p_rows_kernel(uint8_t* local, PeerPtrs peers, const int* __restrict__ peer_rank,
-                const long long* __restrict__ peer_row, long long n, int row_vec /* 16-byte vectors per row */) {
+p2p_rows_kernel(uint8_t* local, PeerPtrs peers, int world, const int* __restrict__ peer_rank,
+                const long long* __restrict__ peer_row, long long n, int row_vec /* 16-byte vectors per row */,
+                long long capacity_rows, int* status) {
   const long long row = (static_cast<long long>(blockIdx.x) * SY_THREADS + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (row >= n) return;
   const int pr = peer_rank[row];
-  if (pr < 0 || pr >= MAX_PEERS) return;
+  if (pr < 0) return;                                   // an entry marked "not routed"
+  const long long dst = peer_row[row];
+  // a rank outside the group or a row outside the peer's buffer is skipped and reported, never dereferenced
+  if (pr >= world || dst < 0 || dst >= capacity_rows) {
+    if (lane == 0 && status != nullptr) atomicCAS(status, 0, ERR_BAD_ARG);
+    return;
+  }
   uint4* mine = reinterpret_cast<uint4*>(local) + row * row_vec;
-  uint4* theirs = reinterpret_cast<uint4*>(peers.p[pr]) + peer_row[row] * row_vec;
+  uint4* theirs = reinterpret_cast<uint4*>(peers.p[pr]) + dst * row_vec;
   for (int c = lane; c < row_vec; c += 32) {
     if (GATHER) mine[c] = theirs[c];
     else theirs[c] = mine[c];
@@ -279,24 +286,33 @@ p2p_rows_kernel(uint8_t* local, PeerPtrs peers, const int* __restrict__ peer_ran
 
 }  // namespace cvb
 
+// Row movers.  `capacity_rows` is the number of rows of every peer buffer and `status` the device status word:
+// an entry whose rank is not in [0, world) or whose row is not in [0, capacity_rows) is skipped and sets
+// ERR_BAD_ARG there; a negative rank marks an entry to leave out silently.
 extern "C" int cvb_p2p_scatter_rows(const void* local, void* const* peer_ptrs, int world, const int* peer_rank,
-                                    const long long* peer_row, long long n, long long row_bytes, void* stream) {
+                                    const long long* peer_row, long long n, long long row_bytes,
+                                    long long capacity_rows, int* status, void* stream) {
   PeerPtrs pp;
-  if (!fill(&pp, peer_ptrs, world) || row_bytes % 16 || (reinterpret_cast<uintptr_t>(local) & 15)) return -1;
+  if (!fill(&pp, peer_ptrs, world) || row_bytes % 16 || (reinterpret_cast<uintptr_t>(local) & 15) ||
+      capacity_rows <= 0) return -1;
   if (n <= 0) return 0;
   const long long blocks = (n * 32 + SY_THREADS - 1) / SY_THREADS;
   p2p_rows_kernel<false><<<static_cast<unsigned>(blocks), SY_THREADS, 0, ST(stream)>>>(
-      static_cast<uint8_t*>(const_cast<void*>(local)), pp, peer_rank, peer_row, n, static_cast<int>(row_bytes / 16));
+      static_cast<uint8_t*>(const_cast<void*>(local)), pp, world, peer_rank, peer_row, n,
+      static_cast<int>(row_bytes / 16), capacity_rows, status);
   return static_cast<int>(cudaGetLastError());
 }
 
 extern "C" int cvb_p2p_gather_rows(void* local, void* const* peer_ptrs, int world, const int* peer_rank,
-                                   const long long* peer_row, long long n, long long row_bytes, void* stream) {
+                                   const long long* peer_row, long long n, long long row_bytes,
+                                   long long capacity_rows, int* status, void* stream) {
   PeerPtrs pp;
-  if (!fill(&pp, peer_ptrs, world) || row_bytes % 16 || (reinterpret_cast<uintptr_t>(local) & 15)) return -1;
+  if (!fill(&pp, peer_ptrs, world) || row_bytes % 16 || (reinterpret_cast<uintptr_t>(local) & 15) ||
+      capacity_rows <= 0) return -1;
   if (n <= 0) return 0;
   const long long blocks = (n * 32 + SY_THREADS - 1) / SY_THREADS;
   p2p_rows_kernel<true><<<static_cast<unsigned>(blocks), SY_THREADS, 0, ST(stream)>>>(
-      static_cast<uint8_t*>(local), pp, peer_rank, peer_row, n, static_cast<int>(row_bytes / 16));
+      static_cast<uint8_t*>(local), pp, world, peer_rank, peer_row, n, static_cast<int>(row_bytes / 16),
+      capacity_rows, status);
   return static_cast<int>(cudaGetLastError());
 }

@@ -15,11 +15,39 @@ The reference exchanges rows with four NCCL all-to-alls per layer (src/distribut
 """
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
 from .. import _native as nv
 from ..ops.gemm import count_launch
 from .symm import SymmBarrier, SymmetricHeap
+
+
+def plan_rows(table: torch.Tensor, rank: int, dst_rank: torch.Tensor, capacity_rows: int):
+    """Destination row of every routed entry, from the count table ``table[src, dst]`` (int64) that the ranks
+    exchanged: entries for one destination land after the rows of all lower source ranks, in their original
+    order.  Returns ``(peer_rank int32 [n], peer_row int64 [n], overflow int32 [1])``.  A destination that would
+    receive more than ``capacity_rows`` rows sets ``overflow``, and the entries that do not fit get rank -1,
+    which the row kernels leave out - nothing is ever written past a buffer.  Pure tensor arithmetic: runs on
+    any device."""
+    world = table.shape[0]
+    n = dst_rank.numel()
+    dev = dst_rank.device
+    counts = torch.bincount(dst_rank, minlength=world)[:world].to(torch.int64)
+    base = table[:rank].sum(0)
+    order = torch.argsort(dst_rank, stable=True)
+    starts = torch.zeros(world + 1, dtype=torch.int64, device=dev)
+    starts[1:] = counts.cumsum(0)
+    sorted_dst = dst_rank[order]
+    idx_in_seg = torch.arange(n, device=dev) - starts[sorted_dst]
+    peer_row = torch.empty(n, dtype=torch.int64, device=dev)
+    peer_row[order] = base[sorted_dst] + idx_in_seg
+    fits = peer_row < capacity_rows
+    peer_rank = torch.where(fits, dst_rank.to(torch.int32), torch.full_like(dst_rank, -1, dtype=torch.int32))
+    peer_row = torch.where(fits, peer_row, torch.zeros_like(peer_row))
+    overflow = (table.sum(0).max() > capacity_rows).to(torch.int32).reshape(1)
+    return peer_rank, peer_row, overflow
 
 
 class EpSymm:
@@ -49,10 +77,13 @@ class EpSymm:
 
     # -- raw row movement ------------------------------------------------------------------------------
     def _move(self, gather: bool, local: torch.Tensor, buf, peer_rank: torch.Tensor, peer_row: torch.Tensor,
-              row_bytes: int) -> None:
+              row_bytes: int, capacity_rows: Optional[int] = None) -> None:
+        """One warp per row between ``local`` and the peers' copies of ``buf``.  The kernel skips (and reports in
+        the device status word) any entry whose rank or row lies outside the group / the buffer."""
         fn = nv.cuda().cvb_p2p_gather_rows if gather else nv.cuda().cvb_p2p_scatter_rows
         nv.check(fn(local.data_ptr(), buf.ptr_array(), self.world, peer_rank.data_ptr(), peer_row.data_ptr(),
-                    peer_rank.numel(), row_bytes, nv.stream()), "cvb_p2p_rows")
+                    peer_rank.numel(), row_bytes, self.cap if capacity_rows is None else capacity_rows,
+                    nv.status_word(self.device).data_ptr(), nv.stream()), "cvb_p2p_rows")
         count_launch()
 
     def plan(self, dst_rank: torch.Tensor, local_expert: torch.Tensor, num_local: int):
@@ -68,20 +99,12 @@ class EpSymm:
         src = mine.unsqueeze(0).expand(self.world, 8).contiguous()
         peers = torch.arange(self.world, dtype=torch.int32, device=dev)
         slot = torch.full((self.world,), self.rank, dtype=torch.int64, device=dev)
-        self._move(False, src, self.b_cnt, peers, slot, 32)
+        self._move(False, src, self.b_cnt, peers, slot, 32, capacity_rows=self.world)
         self.barrier()
         table = self.cnt[:, :self.world].to(torch.int64)         # [src, dst]
-        base = table[:self.rank].sum(0)                          # rows that lower ranks send to each destination
-        received = table[:, self.rank].sum()
-        self.overflow.copy_(torch.maximum(self.overflow, (table.sum(0).max() > self.cap).to(torch.int32).reshape(1)))
-        order = torch.argsort(dst_rank, stable=True)
-        starts = torch.zeros(self.world + 1, dtype=torch.int64, device=dev)
-        starts[1:] = counts.to(torch.int64).cumsum(0)
-        sorted_dst = dst_rank[order]
-        idx_in_seg = torch.arange(n, device=dev) - starts[sorted_dst]
-        peer_row = torch.empty(n, dtype=torch.int64, device=dev)
-        peer_row[order] = (base[sorted_dst] + idx_in_seg).clamp_(max=self.cap - 1)
-        peer_rank = dst_rank.to(torch.int32)
+        received = table[:, self.rank].sum().clamp(max=self.cap)
+        peer_rank, peer_row, over = plan_rows(table, self.rank, dst_rank, self.cap)
+        self.overflow.copy_(torch.maximum(self.overflow, over))
         # expert ids travel as 16-byte rows
         idrow = torch.zeros((n, 4), dtype=torch.int32, device=dev)
         idrow[:, 0] = local_expert.to(torch.int32)

@@ -289,3 +289,25 @@ def test_bucketed_dp_gradient_sync_and_owner_broadcast():
     # flat bucket ranges cut at parameter boundaries
     assert dp_sync.flat_bucket_ranges([100, 300, 50, 1000, 7], [0, 104, 408, 464, 1464], 1700, 4) == \
         [(0, 404), (408, 458), (464, 1464), (1464, 1471)]
+
+
+def test_ep_row_plan_and_overflow_flag():
+    """Destination rows of the peer-memory expert dispatch: rows for one destination are stacked by source
+    rank; a destination that would overflow its buffer raises the flag and the surplus entries are left out
+    (rank -1) instead of being written over the last row."""
+    from cverl_b200.parallel.ep_symm import plan_rows
+    dst = [torch.tensor([0, 1, 1, 0, 1]), torch.tensor([1, 1, 0, 1, 1])]         # routed entries of ranks 0 and 1
+    table = torch.stack([torch.bincount(d, minlength=2) for d in dst]).to(torch.int64)   # [src, dst]
+    r0 = plan_rows(table, 0, dst[0], capacity_rows=16)
+    r1 = plan_rows(table, 1, dst[1], capacity_rows=16)
+    assert r0[0].tolist() == [0, 1, 1, 0, 1] and r0[1].tolist() == [0, 0, 1, 1, 2] and int(r0[2]) == 0
+    assert r1[1].tolist() == [3, 4, 2, 5, 6]            # after rank 0's 3 rows at destination 1, 2 rows at 0
+    rows_at_1 = sorted([r for k, r in zip(r0[0].tolist(), r0[1].tolist()) if k == 1] +
+                       [r for k, r in zip(r1[0].tolist(), r1[1].tolist()) if k == 1])
+    assert rows_at_1 == list(range(7))                  # dense, no collisions
+    # capacity 5 < 7 rows bound for rank 1: flag set on every rank, surplus entries dropped, none clamped
+    o0 = plan_rows(table, 0, dst[0], capacity_rows=5)
+    o1 = plan_rows(table, 1, dst[1], capacity_rows=5)
+    assert int(o0[2]) == 1 and int(o1[2]) == 1
+    assert o1[0].tolist() == [1, 1, 0, -1, -1] and o1[1].tolist() == [3, 4, 2, 0, 0]
+    assert all(r < 5 for r in o0[1].tolist() + o1[1].tolist())

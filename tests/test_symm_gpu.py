@@ -69,6 +69,34 @@ def test_broadcast_store_emulated():
         assert torch.equal(d, src)
 
 
+def test_p2p_rows_skip_entries_outside_the_group_or_the_buffer():
+    """Row scatter / gather with two "ranks" that are buffers of one device: an entry whose rank is not in the
+    group (2 of a world of 2, although the pointer table has 8 slots) or whose row is past the buffer is skipped
+    and reported through the status word; rank -1 is left out silently; the good entries move."""
+    from cverl_b200 import _native as nv
+    cap, hidden = 8, 64
+    bufs = [torch.zeros(cap, hidden, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+    rows = torch.arange(5 * hidden, device="cuda", dtype=torch.float32).view(5, hidden).bfloat16()
+    st = nv.status_word()
+    st.zero_()
+    prank = torch.tensor([0, 1, 2, 1, -1], dtype=torch.int32, device="cuda")      # 2: outside the group
+    prow = torch.tensor([3, 7, 0, 8, 0], dtype=torch.int64, device="cuda")        # 8: past the 8-row buffer
+    nv.check(nv.cuda().cvb_p2p_scatter_rows(rows.data_ptr(), _ptrs(bufs), 2, prank.data_ptr(), prow.data_ptr(), 5,
+                                            hidden * 2, cap, st.data_ptr(), nv.stream()), "scatter")
+    torch.cuda.synchronize()
+    assert torch.equal(bufs[0][3], rows[0]) and torch.equal(bufs[1][7], rows[1])
+    assert int((bufs[0] != 0).any(1).sum()) == 1 and int((bufs[1] != 0).any(1).sum()) == 1   # nothing else written
+    with pytest.raises(RuntimeError, match="status 7"):
+        nv.check_status()
+    # gather the two good rows back; no status this time
+    back = torch.zeros(2, hidden, device="cuda", dtype=torch.bfloat16)
+    nv.check(nv.cuda().cvb_p2p_gather_rows(back.data_ptr(), _ptrs(bufs), 2, prank[:2].contiguous().data_ptr(),
+                                           prow[:2].contiguous().data_ptr(), 2, hidden * 2, cap, st.data_ptr(),
+                                           nv.stream()), "gather")
+    torch.cuda.synchronize()
+    assert torch.equal(back, rows[:2]) and nv.check_status() == 0
+
+
 def test_barrier_wait_runs_out_to_status():
     """A flag that nothing sets: the wait gives up within its clock budget, the kernel returns and the
     host reads the status word; the context stays usable."""
