@@ -41,12 +41,15 @@ def parse_args():
                     help="sequences per micro-batch; 0 = 32 per tensor-parallel rank (about 100 GB of the 180 GB HBM)")
     ap.add_argument("--tp", type=int, default=int(os.environ.get("CVERL_BENCH_TP", "0")))
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
-    ap.add_argument("--tp-comm", default=os.environ.get("CVERL_BENCH_TP_COMM", "symm"), choices=["symm", "nccl"],
-                    help="tensor-parallel all-reduces: symm = fused into the GEMM epilogue over peer-mapped "
-                         "memory, nccl = library collectives")
+    ap.add_argument("--tp-comm", default=os.environ.get("CVERL_BENCH_TP_COMM", "sp"), choices=["sp", "symm", "nccl"],
+                    help="tensor-parallel communication: sp = token-sharded residual stream, reduce-scatter in the "
+                         "GEMM epilogue and all-gather in the norm kernels over peer-mapped memory; symm = all-reduce "
+                         "by mirror stores from the GEMM epilogue; nccl = library collectives")
     ap.add_argument("--zero-comm", default=os.environ.get("CVERL_BENCH_ZERO", "symm"), choices=["symm", "nccl"],
                     help="ZeRO communication: symm = own kernels over peer-mapped memory, nccl = library collectives")
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (result marked invalid)")
+    ap.add_argument("--no-check", action="store_true",
+                    help="skip the untimed comparison of the fused communication kernels with the NCCL path")
     return ap.parse_args()
 
 
@@ -111,6 +114,52 @@ def reference_arm(args):
     return ref_arm.run(args)
 
 
+def consistency_check(model, ctx, opt, fused_comm, dev_batch, micro_batch, world, dev):
+    """One forward / backward of the first micro-batch through this package's fused communication kernels and
+    once more through NCCL, on the same weights and tokens: returns the differences in the loss-side quantity
+    (mean response log-prob) and in the global gradient norm, and (with data parallelism) of the fused ZeRO
+    reduce-scatter against ``reduce_scatter_tensor``.  Runs before warm-up; leaves the gradients zeroed."""
+    import torch.distributed as dist
+    ids = dev_batch["input_ids"][:micro_batch]
+    g = torch.Generator(device=dev).manual_seed(99)
+    seed = torch.randn(ids.shape[0], RESPONSE_LEN, device=dev, generator=g) / ids.shape[0]
+
+    def one_pass():
+        model.flat.main_grad.zero_()
+        lp = model.response_logprobs(ids, PROMPT_LEN)
+        lp.backward(seed)
+        model.sync_replicated_grads()
+        sq = model.flat.main_grad.double().pow(2).sum()
+        dist.all_reduce(sq)
+        return float(lp.detach().double().mean()), float(sq.sqrt())
+
+    fused = one_pass()
+    saved = (ctx.tp_sp, ctx.tp_symm)
+    ctx.tp_sp = ctx.tp_symm = None
+    try:
+        plain = one_pass()
+    finally:
+        ctx.tp_sp, ctx.tp_symm = saved
+    out = {"loss_abs_diff": abs(fused[0] - plain[0]),
+           "grad_norm_rel_diff": abs(fused[1] - plain[1]) / max(plain[1], 1e-30)}
+    if fused_comm is not None:
+        # the gradients of the NCCL pass are still in the buffer: reduce-scatter them both ways
+        want = torch.empty(opt.shard_numel, dtype=torch.float32, device=dev)
+        dist.reduce_scatter_tensor(want, model.flat.main_grad.clone(), op=dist.ReduceOp.AVG, group=ctx.dp_group)
+        got = torch.empty_like(want)
+        sq = fused_comm.reduce_scatter_mean_sumsq(got, opt.begin).clone()      # zeroes the gradient buffer
+        out["zero_rs_rel_diff"] = float((got - want).norm() / want.norm().clamp_min(1e-30))
+        out["zero_sumsq_rel_diff"] = float((sq[0] - want.pow(2).sum()).abs() / want.pow(2).sum().clamp_min(1e-30))
+    model.flat.main_grad.zero_()
+    worst = torch.tensor([out["loss_abs_diff"], out["grad_norm_rel_diff"], out.get("zero_rs_rel_diff", 0.0)],
+                         device=dev)
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    out["loss_abs_diff"], out["grad_norm_rel_diff"] = float(worst[0]), float(worst[1])
+    # bf16 activations summed in another order: a few 1e-3 is rounding, more is a wrong kernel
+    out["ok"] = bool(worst[0] < 2e-2 and worst[1] < 5e-2 and worst[2] < 1e-4)
+    return out
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -150,6 +199,10 @@ def main():
         # measured (cverl_b200.bench_collectives): the mirror-store all-reduce beats NCCL at TP=2 (0.25 vs 0.32 ms
         # on the out_proj shape) and loses from TP=4 on, where every rank would store its full partial N-1 times
         args.tp_comm = "nccl"
+    if tp > 1 and args.tp_comm == "sp":
+        from cverl_b200.parallel.tp_sp import TpSp
+        ctx.tp_sp = TpSp(ctx.tp_group, dev, args.micro_batch * (PROMPT_LEN + RESPONSE_LEN), cfg.hidden_size,
+                         arena_slots=2 * cfg.num_hidden_layers + 1)
     if tp > 1 and args.tp_comm == "symm":
         from cverl_b200.parallel.tp_symm import TpSymm
         ctx.tp_symm = TpSymm(ctx.tp_group, dev, args.micro_batch * (PROMPT_LEN + RESPONSE_LEN), cfg.hidden_size)
@@ -191,6 +244,14 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return ms.item()
 
+    check = None
+    if world > 1 and not args.no_check:
+        check = consistency_check(model, ctx, opt, fused_comm, dev_batch, args.micro_batch, world, dev)
+        nv.check_status(dev)
+        if not check["ok"]:
+            if rank == 0:
+                print(json.dumps({"error": "fused communication kernels disagree with the NCCL path", "check": check}))
+            return 1
     for _ in range(max(args.warmup, 0)):
         engine.update(dev_batch, PROMPT_LEN)
     nv.check_status(dev)
@@ -237,6 +298,8 @@ def main():
             "loss": float(last["m"][0]),
             "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 1),
         }
+        if check is not None:
+            out["check"] = check
         if args.layers:
             out["invalid"] = "debug run with fewer layers"
         print(json.dumps(out))

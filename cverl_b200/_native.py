@@ -40,6 +40,7 @@ class GemmArgs(C.Structure):
         ("targets", c_void_p), ("part_max", c_void_p), ("part_sum", c_void_p), ("tgt_logit", c_void_p),
         ("lse", c_void_p), ("gscale", c_void_p), ("status", c_void_p),
         ("mirror", c_void_p * 7), ("n_mirror", C.c_int32),
+        ("scatter_base", c_void_p * 8), ("scatter_rows", C.c_int32),
     ]
 
 
@@ -52,6 +53,8 @@ _CODES = {"p": c_void_p, "l": c_ll, "i": c_int, "f": c_float, "d": C.c_double}
 _CUDA_PROTOS = {
     "cvb_rmsnorm_fwd": "ppppppplillff il p",
     "cvb_rmsnorm_bwd": "ppppppppplilllf illl p",
+    "cvb_sp_add_rmsnorm_fwd": "p l i pp p i l pp l i ff p",
+    "cvb_sp_add_rmsnorm_bwd": "p l i pppp p p i l p l i f p",
     "cvb_headnorm_rope_fwd": "ppppp lii ll i pp i ff i p",
     "cvb_headnorm_rope_bwd": "ppppppp lii ll i pp i f i p",
     "cvb_swiglu_fwd": "pp l i l p",

@@ -160,10 +160,16 @@ __device__ __forceinline__ void epilogue_slab(const GemmParams& p, int m0, int n
             if (grow < p.M) {
               const uint4 o = *reinterpret_cast<const uint4*>(stg + rr * Cfg::STG_ROW + ch * 16);
               const long long off = c_off + static_cast<long long>(grow) * p.ldc + cbase + ch * 8;
-              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + off) = o;
+              if (p.scatter_rows > 0) {
+                // reduce-scatter epilogue: the row block's owner gets the tile, nobody else
+                *reinterpret_cast<uint4*>(
+                    reinterpret_cast<__nv_bfloat16*>(p.scatter_base[grow / p.scatter_rows]) + off) = o;
+              } else {
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + off) = o;
 #pragma unroll 1
-              for (int m = 0; m < p.n_mirror; ++m)
-                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.mirror[m]) + off) = o;
+                for (int m = 0; m < p.n_mirror; ++m)
+                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.mirror[m]) + off) = o;
+              }
             }
           }
           __syncwarp();
@@ -839,7 +845,21 @@ extern "C" int cvb_gemm_bf16(const CvbGemmArgs* a, void* stream_v) {
     // Default: stage every bf16 store whose N allows it.  CVERL_B200_GEMM_DIRECT_STORE=1 keeps the
     // register -> global path for comparison.
     static const bool direct = [] { const char* e = getenv("CVERL_B200_GEMM_DIRECT_STORE"); return e && e[0] == '1'; }();
-    p.staged_store = (a->epi == EPI_STORE_BF16 && a->N % 64 == 0 && (a->n_mirror > 0 || !direct)) ? 1 : 0;
+    p.staged_store = (a->epi == EPI_STORE_BF16 && a->N % 64 == 0 &&
+                      (a->n_mirror > 0 || a->scatter_rows > 0 || !direct)) ? 1 : 0;
+  }
+  p.scatter_rows = 0;
+  if (a->scatter_rows != 0) {
+    // every 128-row slab of a tile must have one owner, and the table must cover all M rows
+    if (a->scatter_rows < 0 || a->scatter_rows % 128 != 0 || a->epi != EPI_STORE_BF16 || a->N % 64 != 0 ||
+        a->n_mirror != 0 || a->tile_group != nullptr || (a->M + a->scatter_rows - 1) / a->scatter_rows > 8)
+      return -6;
+    p.scatter_rows = a->scatter_rows;
+    for (int b = 0; b < 8; ++b) p.scatter_base[b] = nullptr;
+    for (int b = 0; b < (a->M + a->scatter_rows - 1) / a->scatter_rows; ++b) {
+      if (!a->scatter_base[b] || (reinterpret_cast<uintptr_t>(a->scatter_base[b]) & 15)) return -6;
+      p.scatter_base[b] = a->scatter_base[b];
+    }
   }
   for (int m = 0; m < a->n_mirror; ++m) {
     if (!a->mirror[m] || (reinterpret_cast<uintptr_t>(a->mirror[m]) & 15)) return -6;

@@ -51,6 +51,12 @@ typedef struct CvbGemmArgs {
   // GPUs' mapped copies of C (plain stores over NVLink from the epilogue warps, tile by tile)
   void* mirror[7];
   int32_t n_mirror;
+  // EPI_STORE_BF16, scatter_rows > 0 (a multiple of 128): row block `row / scatter_rows` of the output is stored
+  // ONLY at scatter_base[block] + row * ldc + col, and C is not written - the reduce-scatter of a tensor-parallel
+  // partial product: every row block goes straight to the rank that owns those rows (its own memory or a peer's,
+  // over NVLink).  The caller folds the owner's row origin into each base pointer.
+  void* scatter_base[8];
+  int32_t scatter_rows;
 } CvbGemmArgs;
 
 // Launches on `stream` (a cudaStream_t).  Returns 0 or a negative/CUDA error.
@@ -83,6 +89,8 @@ struct GemmParams {
   int* status;
   void* mirror[7];
   int n_mirror;
+  void* scatter_base[8];
+  int scatter_rows;
   int staged_store;  // bf16 epilogue through shared memory (coalesced 128-byte segments)
 };
 int make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,

@@ -382,6 +382,165 @@ headnorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat
 }
 
 // vectors of 8 per lane for a row of D elements, or -1 when D is not supported
+
+// ---------------------------------------------------------------------------
+// Sequence-parallel residual add + RMSNorm (tensor parallelism with the residual stream sharded by token rows).
+//
+// forward:  x = sum_p parts[p] (+ resid_in) over this rank's rows; resid_out = x; y = rmsnorm(x) is stored at row
+//           `dst_row0 + row` of EVERY buffer in `ydst` - the local copy and, through peer-mapped pointers over
+//           NVLink, the copy on every other rank of the tensor-parallel group: the stores ARE the all-gather that
+//           the following column-parallel GEMM needs.  `parts` are the `nparts` partial products that the
+//           row-parallel GEMMs of all ranks scattered into this rank's buffer (their reduce-scatter), lying
+//           `part_stride` elements apart.
+// backward: dy = sum_p dy_parts[p] (the column-parallel input-gradient partials, scattered the same way);
+//           dx = dres + rstd * (g - xhat * mean(g * xhat)), g = dy * (w0 + w); dx goes to `dx_local` and to row
+//           `dst_row0 + row` of every buffer in `dxdst` (the all-gather of the row-parallel GEMM's output gradient).
+// ---------------------------------------------------------------------------
+struct SpDst {
+  __nv_bfloat16* p[8];
+};
+
+template <int NVEC>
+__global__ void __launch_bounds__(NORM_THREADS)
+sp_add_rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ parts, long long part_stride, int nparts,
+                          const __nv_bfloat16* __restrict__ resid_in, const __nv_bfloat16* __restrict__ w,
+                          SpDst ydst, int ndst, long long dst_row0, __nv_bfloat16* __restrict__ resid_out,
+                          float* __restrict__ rstd_out, long long rows, int D, float eps, float w_offset) {
+  const int lanes = min(32, D / 8);
+  const int rows_per_warp = 32 / lanes;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / lanes;
+  const int sl = lane % lanes;
+  const long long warp_global = (static_cast<long long>(blockIdx.x) * NORM_THREADS + threadIdx.x) >> 5;
+  const long long warps_total = (static_cast<long long>(gridDim.x) * NORM_THREADS) >> 5;
+  for (long long r0 = warp_global * rows_per_warp; r0 < rows; r0 += warps_total * rows_per_warp) {
+    const long long row = r0 + sub;
+    const bool ok = row < rows;
+    float ss = 0.f;
+    Vec8 h[NVEC];
+    if (ok) {
+#pragma unroll
+      for (int i = 0; i < NVEC; ++i) {
+        const int c = (i * lanes + sl) * 8;
+        Vec8 a = load8(parts + row * D + c);
+        for (int q = 1; q < nparts; ++q) {
+          Vec8 b = load8(parts + q * part_stride + row * D + c);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a.v[j] += b.v[j];
+        }
+        if (resid_in) {
+          Vec8 b = load8(resid_in + row * D + c);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a.v[j] += b.v[j];
+        }
+        store8(resid_out + row * D + c, a);
+        // the norm sees the bf16-rounded residual stream, as a consumer reading it back would
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          a.v[j] = __bfloat162float(__float2bfloat16_rn(a.v[j]));
+          ss += a.v[j] * a.v[j];
+        }
+        h[i] = a;
+      }
+    }
+    ss = seg_sum(ss, lanes);
+    const float rstd = rsqrtf(ss / D + eps);
+    if (ok) {
+      if (sl == 0) rstd_out[row] = rstd;
+#pragma unroll
+      for (int i = 0; i < NVEC; ++i) {
+        const int c = (i * lanes + sl) * 8;
+        const Vec8 a = h[i];
+        Vec8 ww = load8(w + c);
+        Vec8 o;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o.v[j] = a.v[j] * rstd * (w_offset + ww.v[j]);
+        for (int d = 0; d < ndst; ++d) store8(ydst.p[d] + (dst_row0 + row) * D + c, o);
+      }
+    }
+  }
+}
+
+template <int NVEC>
+__global__ void __launch_bounds__(NORM_THREADS)
+sp_add_rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy_parts, long long part_stride, int nparts,
+                          const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                          const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
+                          __nv_bfloat16* __restrict__ dx_local, SpDst dxdst, int ndst, long long dst_row0,
+                          float* __restrict__ dw, long long rows, int D, float w_offset) {
+  extern __shared__ float s_dw[];  // [D]
+  for (int i = threadIdx.x; i < D; i += NORM_THREADS) s_dw[i] = 0.f;
+  __syncthreads();
+  const int lanes = min(32, D / 8);
+  const int rows_per_warp = 32 / lanes;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / lanes;
+  const int sl = lane % lanes;
+  const long long warp_global = (static_cast<long long>(blockIdx.x) * NORM_THREADS + threadIdx.x) >> 5;
+  const long long warps_total = (static_cast<long long>(gridDim.x) * NORM_THREADS) >> 5;
+  float dw_acc[NVEC][8];
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw_acc[i][j] = 0.f;
+  for (long long r0 = warp_global * rows_per_warp; r0 < rows; r0 += warps_total * rows_per_warp) {
+    const long long row = r0 + sub;
+    const bool ok = row < rows;
+    const float rstd = ok ? rstd_in[row] : 0.f;
+    float dot = 0.f;
+    Vec8 gsum[NVEC];
+    if (ok) {
+#pragma unroll
+      for (int i = 0; i < NVEC; ++i) {
+        const int c = (i * lanes + sl) * 8;
+        Vec8 a = load8(x + row * D + c);
+        Vec8 g = load8(dy_parts + row * D + c);
+        for (int q = 1; q < nparts; ++q) {
+          Vec8 b = load8(dy_parts + q * part_stride + row * D + c);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) g.v[j] += b.v[j];
+        }
+        Vec8 ww = load8(w + c);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dot += g.v[j] * (w_offset + ww.v[j]) * a.v[j] * rstd;
+        gsum[i] = g;
+      }
+    }
+    dot = seg_sum(dot, lanes) / D;
+    if (ok) {
+#pragma unroll
+      for (int i = 0; i < NVEC; ++i) {
+        const int c = (i * lanes + sl) * 8;
+        Vec8 a = load8(x + row * D + c);
+        const Vec8 g = gsum[i];
+        Vec8 ww = load8(w + c);
+        Vec8 o, dr;
+        if (dres) dr = load8(dres + row * D + c);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xhat = a.v[j] * rstd;
+          const float gg = g.v[j] * (w_offset + ww.v[j]);
+          o.v[j] = rstd * (gg - xhat * dot) + (dres ? dr.v[j] : 0.f);
+          dw_acc[i][j] += g.v[j] * xhat;
+        }
+        if (dx_local) store8(dx_local + row * D + c, o);
+        for (int d = 0; d < ndst; ++d) store8(dxdst.p[d] + (dst_row0 + row) * D + c, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int c = (i * lanes + sl) * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) atomicAdd(&s_dw[c + j], dw_acc[i][j]);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < D; i += NORM_THREADS) {
+    const float v = s_dw[i];
+    if (v != 0.f) atomicAdd(&dw[i], v);
+  }
+}
+
 static int norm_nvec(int D) {
   if (D % 8 != 0 || D <= 0) return -1;
   const int v = D / 8;
@@ -471,6 +630,74 @@ extern "C" int cvb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
     default: return -1;
   }
 #undef CVB_BWD
+  return static_cast<int>(cudaGetLastError());
+}
+
+
+static bool sp_fill(SpDst* d, void* const* ptrs, int n) {
+  if (n < 0 || n > 8) return false;
+  for (int i = 0; i < 8; ++i) d->p[i] = nullptr;
+  for (int i = 0; i < n; ++i) {
+    if (!ptrs || !ptrs[i] || (reinterpret_cast<uintptr_t>(ptrs[i]) & 15)) return false;
+    d->p[i] = static_cast<__nv_bfloat16*>(ptrs[i]);
+  }
+  return true;
+}
+
+// `ydst`: `ndst` device pointers (host array), the copies of the gathered output on the ranks of the group; this
+// rank's rows land at row `dst_row0` of each.  `parts`: `nparts` partial inputs `part_stride` elements apart.
+extern "C" int cvb_sp_add_rmsnorm_fwd(const void* parts, long long part_stride, int nparts, const void* resid_in,
+                                      const void* w, void* const* ydst, int ndst, long long dst_row0,
+                                      void* resid_out, float* rstd, long long rows, int D, float eps,
+                                      float w_offset, void* stream) {
+  const int nvec = norm_nvec(D);
+  SpDst dst;
+  if (nvec < 0 || nparts < 1 || nparts > 8 || !sp_fill(&dst, ydst, ndst) || !resid_out || !rstd) return -1;
+  if (cvb_misaligned({parts, resid_in, w, resid_out}) || part_stride % 8 || dst_row0 < 0) return -2;
+  if (rows <= 0) return 0;
+  const int lanes = D / 8 < 32 ? D / 8 : 32;
+#define CVB_SPF(NV)                                                                                           \
+  case NV:                                                                                                    \
+    sp_add_rmsnorm_fwd_kernel<NV><<<norm_grid(rows, 32 / lanes), NORM_THREADS, 0,                             \
+                                    static_cast<cudaStream_t>(stream)>>>(                                     \
+        static_cast<const __nv_bfloat16*>(parts), part_stride, nparts,                                        \
+        static_cast<const __nv_bfloat16*>(resid_in), static_cast<const __nv_bfloat16*>(w), dst, ndst,         \
+        dst_row0, static_cast<__nv_bfloat16*>(resid_out), rstd, rows, D, eps, w_offset);                      \
+    break;
+  switch (nvec) {
+    CVB_SPF(1) CVB_SPF(2) CVB_SPF(3) CVB_SPF(4) CVB_SPF(5) CVB_SPF(6) CVB_SPF(7) CVB_SPF(8) CVB_SPF(12)
+    CVB_SPF(14) CVB_SPF(16)
+    default: return -1;
+  }
+#undef CVB_SPF
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int cvb_sp_add_rmsnorm_bwd(const void* dy_parts, long long part_stride, int nparts, const void* x,
+                                      const void* w, const float* rstd, const void* dres, void* dx_local,
+                                      void* const* dxdst, int ndst, long long dst_row0, float* dw,
+                                      long long rows, int D, float w_offset, void* stream) {
+  const int nvec = norm_nvec(D);
+  SpDst dst;
+  if (nvec < 0 || nparts < 1 || nparts > 8 || !sp_fill(&dst, dxdst, ndst) || !dw || !rstd) return -1;
+  if (cvb_misaligned({dy_parts, x, w, dres, dx_local}) || part_stride % 8 || dst_row0 < 0) return -2;
+  if (rows <= 0) return 0;
+  const int lanes = D / 8 < 32 ? D / 8 : 32;
+  int grid = norm_grid(rows, 32 / lanes);
+  if (grid > 148 * 2) grid = 148 * 2;
+#define CVB_SPB(NV)                                                                                           \
+  case NV:                                                                                                    \
+    sp_add_rmsnorm_bwd_kernel<NV><<<grid, NORM_THREADS, D * sizeof(float), static_cast<cudaStream_t>(stream)>>>( \
+        static_cast<const __nv_bfloat16*>(dy_parts), part_stride, nparts, static_cast<const __nv_bfloat16*>(x), \
+        static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(dres),                  \
+        static_cast<__nv_bfloat16*>(dx_local), dst, ndst, dst_row0, dw, rows, D, w_offset);                   \
+    break;
+  switch (nvec) {
+    CVB_SPB(1) CVB_SPB(2) CVB_SPB(3) CVB_SPB(4) CVB_SPB(5) CVB_SPB(6) CVB_SPB(7) CVB_SPB(8) CVB_SPB(12)
+    CVB_SPB(14) CVB_SPB(16)
+    default: return -1;
+  }
+#undef CVB_SPB
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -74,6 +74,7 @@ class Qwen35Model(torch.nn.Module):
         self._build_fused_views()
         self._rope_cache: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
         self._cp_original_len: Optional[int] = None
+        self._sp_active = False     # inside a sequence-parallel forward (see ``sequence_parallel``)
 
     # ------------------------------------------------------------------ layout
     def _flat_entries(self) -> List[Tuple[str, Tuple[int, ...]]]:
@@ -204,7 +205,18 @@ class Qwen35Model(torch.nn.Module):
                 names += [p + "self_attn.q_norm.weight", p + "self_attn.k_norm.weight"]
             else:
                 names.append(p + "linear_attn.norm.weight")
+            if self.sequence_parallel:
+                # token-sharded layer norms: every rank holds the gradient of its rows only
+                names += [p + "input_layernorm.weight", p + "post_attention_layernorm.weight"]
+        if self.sequence_parallel and self.last_stage:
+            names.append(cfg.final_norm_name)
         return names
+
+    @property
+    def sequence_parallel(self) -> bool:
+        """True when the tensor-parallel group runs with the residual stream sharded by token rows
+        (``parallel/tp_sp.py``); the training forward then requires shapes that path accepts."""
+        return getattr(self.ctx, "tp_sp", None) is not None and self.ctx.tp_size > 1
 
     @torch.no_grad()
     def sync_replicated_grads(self) -> None:
@@ -242,6 +254,9 @@ class Qwen35Model(torch.nn.Module):
     def _col_linear(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         """Column-parallel linear on a replicated input: the input gradient is all-reduced over TP."""
         ctx = self.ctx
+        if self._sp_active:
+            from ..parallel import tp_sp
+            return tp_sp.col_linear(x, w, ctx.tp_sp)
         if ctx.tp_size > 1 and ctx.tp_symm is not None:
             from ..parallel import tp_symm
             if tp_symm.usable(ctx.tp_symm, x, x.reshape(-1, x.shape[-1]).shape[0], x.shape[-1]):
@@ -251,6 +266,10 @@ class Qwen35Model(torch.nn.Module):
     def _row_linear(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         """Row-parallel linear on a sharded input: the output is all-reduced over TP."""
         ctx = self.ctx
+        if self._sp_active:
+            # left reduce-scattered: the result is a handle that only ``tp_sp.norm_gather`` may consume
+            from ..parallel import tp_sp
+            return tp_sp.row_linear(x, w, ctx.tp_sp)
         if ctx.tp_size > 1 and ctx.tp_symm is not None:
             from ..parallel import tp_symm
             if tp_symm.usable(ctx.tp_symm, x, x.reshape(-1, x.shape[-1]).shape[0], w.shape[0]):
@@ -371,7 +390,34 @@ class Qwen35Model(torch.nn.Module):
         table = self.param(cfg.embed_name)
         lo = ctx.tp_rank * table.shape[0] if ctx.tp_size > 1 else 0
         e = ops.embedding(input_ids.reshape(-1), table, lo)
+        if self._sp_active:
+            from ..parallel.autograd_collectives import reduce_scatter_rows
+            return reduce_scatter_rows(e, ctx.tp_group)          # this rank's token rows of the sum
         return reduce_from_tp(e, ctx.tp_group)
+
+    def _forward_layers_sp(self, x_local: torch.Tensor, batch: int, seq: int) -> torch.Tensor:
+        """Sequence-parallel layer stack: ``x_local`` holds this rank's token rows; every residual add + RMSNorm
+        runs on those rows only and hands the gathered result to the next column-parallel GEMM; every
+        row-parallel GEMM leaves its output reduce-scattered for the next norm.  Returns the final-normed
+        hidden states of ALL tokens ``[B*S, H]``."""
+        from ..parallel import tp_sp
+        cfg, sp = self.cfg, self.ctx.tp_sp
+        eps, off = cfg.rms_norm_eps, cfg.norm_weight_offset
+        delta, resid, from_parts = x_local, None, False
+        for i in range(self.layer_begin, self.layer_end):
+            p = f"{cfg.layer_root}{i}."
+            n1, resid = tp_sp.norm_gather(delta, resid, self.param(p + "input_layernorm.weight"), eps, off, sp,
+                                          from_parts)
+            if cfg.layer_types[i] == "full_attention":
+                a = self.full_attention(n1, i, batch, seq)
+            else:
+                a = self.linear_attention(n1, i, batch, seq)
+            n2, resid = tp_sp.norm_gather(a, resid, self.param(p + "post_attention_layernorm.weight"), eps, off, sp,
+                                          True)
+            delta, from_parts = self.mlp(n2, i), True
+        out, _ = tp_sp.norm_gather(delta, resid, self.param(cfg.final_norm_name), eps, off, sp, from_parts,
+                                   grad_in_tensor=True)
+        return out
 
     def forward_layers(self, x: torch.Tensor, batch: int, seq: int, final_norm: bool = True,
                        caches: Optional[list] = None) -> torch.Tensor:
@@ -400,6 +446,20 @@ class Qwen35Model(torch.nn.Module):
     def forward_hidden(self, input_ids: torch.Tensor) -> torch.Tensor:
         """[B, S] ids -> final-normed hidden states ``[B, S, H]`` (single-stage model)."""
         batch, seq = input_ids.shape
+        if self.sequence_parallel:
+            sp = self.ctx.tp_sp
+            if not (self.first_stage and self.last_stage) or self.cfg.is_qwen3_moe or self.ctx.cp_size > 1:
+                raise RuntimeError("the sequence-parallel tensor-parallel path needs a dense single-stage model")
+            if not (sp.fits(batch * seq, self.cfg.hidden_size) and input_ids.is_cuda):
+                raise RuntimeError(f"sequence-parallel path: {batch} x {seq} tokens do not fit its buffers "
+                                   f"(a multiple of {128 * sp.world} and at most {sp.max_rows})")
+            self._sp_active = True
+            try:
+                sp.begin_pass()
+                x = self.embed(input_ids)
+                return self._forward_layers_sp(x, batch, seq).view(batch, seq, -1)
+            finally:
+                self._sp_active = False
         x = self.embed(input_ids)
         return self.forward_layers(x, batch, seq).view(batch, seq, -1)
 

@@ -73,13 +73,18 @@ def gemm_raw(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, M: int, N: int
              b_mn: bool, epi: int, alpha: float = 1.0, split_k: int = 0, block_n: int = 0,
              tile_group=None, b_group_rows: int = 0, b_total_rows: int = 0, k_group_offsets=None,
              num_groups: int = 0, c_group_stride: int = 0, targets=None, part_max=None, part_sum=None,
-             tgt_logit=None, lse=None, gscale=None, max_ctas: int = 0, mirrors=()) -> None:
-    """One launch of the tcgen05 GEMM. Operands are 2-D bf16 tensors with unit inner stride."""
+             tgt_logit=None, lse=None, gscale=None, max_ctas: int = 0, mirrors=(), scatter=None,
+             ldc: int = 0) -> None:
+    """One launch of the tcgen05 GEMM. Operands are 2-D bf16 tensors with unit inner stride.
+
+    ``scatter=(bases, rows_per_owner)``: reduce-scatter epilogue - row block ``row // rows_per_owner`` of the
+    bf16 result is stored only at raw address ``bases[block] + (row * ldc + col) * 2`` (``out`` is None and ``ldc``
+    is given)."""
     lib = nv.cuda()
     args = nv.GemmArgs()
     args.A, args.B, args.C = a.data_ptr(), b.data_ptr(), out.data_ptr() if out is not None else None
     args.lda, args.ldb = a.stride(0), b.stride(0)
-    args.ldc = out.stride(0) if out is not None else 0
+    args.ldc = out.stride(0) if out is not None else ldc
     args.M, args.N, args.K = M, N, K
     args.a_mn, args.b_mn = int(a_mn), int(b_mn)
     args.epi, args.alpha = epi, alpha
@@ -94,6 +99,11 @@ def gemm_raw(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, M: int, N: int
     args.n_mirror = len(mirrors)
     for i, m in enumerate(mirrors):   # raw addresses of peers' copies of ``out``
         args.mirror[i] = m
+    if scatter is not None:
+        bases, rows_per_owner = scatter
+        args.scatter_rows = rows_per_owner
+        for i, base in enumerate(bases):
+            args.scatter_base[i] = base
     rc = lib.cvb_gemm_bf16(C.byref(args), nv.stream())
     nv.check(rc, "cvb_gemm_bf16")
     count_launch()

@@ -96,9 +96,10 @@ class _LmHeadLogProb(torch.autograd.Function):
                      block_n=256, targets=local_t[r0:r1], lse=lse[r0:r1], gscale=g[r0:r1])
             gemm_nn(d, emb2, out=dh[r0:r1])          # dh = d @ E
             gemm_tn_acc(d, h2[r0:r1], dE)            # dE += d.T @ h
-        if ctx.group is not None:
-            import torch.distributed as dist
-            dist.all_reduce(dh, group=ctx.group)
+        # With a vocab-parallel group ``dh`` is this rank's partial sum over its vocabulary shard.  It is NOT
+        # all-reduced here: the caller feeds ``h`` through ``copy_to_tp`` (identity forward, all-reduce backward),
+        # as the PyTorch statement of this op does; reducing in both places would scale the gradient by the
+        # group size.
         dEret = None if main_grad is not None else dE.to(emb.dtype)
         return dh.view(ctx.hshape), dEret, None, None, None
 

@@ -29,6 +29,9 @@ class ParallelContext:
     fused_comm: bool = False
     # ``parallel.tp_symm.TpSymm`` when tensor-parallel linears fuse their all-reduce into the GEMM
     tp_symm: Optional[Any] = None
+    # ``parallel.tp_sp.TpSp`` when the tensor-parallel group shards the residual stream by token rows and fuses the
+    # reduce-scatter / all-gather halves of every all-reduce into the GEMM epilogue and the norm kernels
+    tp_sp: Optional[Any] = None
     # ``parallel.ep_symm.EpSymm`` when expert-parallel dispatch / combine run over peer-mapped memory
     ep_symm: Optional[Any] = None
     # ``parallel.cp_symm.CpSymm`` when context-parallel attention pulls K / V from peers instead of a ring

@@ -119,8 +119,11 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--zero-comm", default="nccl", choices=["nccl", "symm"],
                    help="ZeRO gradient reduce-scatter / parameter all-gather: library collectives, or this "
                         "package's kernels over peer-mapped memory (CUDA, bf16 parameters, same node)")
-    g.add_argument("--tp-comm", default="nccl", choices=["nccl", "symm"],
-                   help="tensor-parallel all-reduces: NCCL, or fused into the GEMM epilogue over peer-mapped memory")
+    g.add_argument("--tp-comm", default="nccl", choices=["nccl", "symm", "sp"],
+                   help="tensor-parallel communication: NCCL all-reduces; symm = all-reduce fused into the GEMM "
+                        "epilogue over peer-mapped memory; sp = token-sharded residual stream with the "
+                        "reduce-scatter in the GEMM epilogue and the all-gather in the norm kernels (dense models, "
+                        "--pp 1 --cp 1, tokens per micro-batch a multiple of 128 * tp)")
     g.add_argument("--ep-comm", default="nccl", choices=["nccl", "symm"],
                    help="expert-parallel dispatch / combine: NCCL all-to-all, or row scatter / gather kernels over "
                         "peer-mapped memory (no host read)")
@@ -510,6 +513,12 @@ def run(argv=None) -> int:
         if rank == 0:
             print("note: --tp-comm symm is used at --tp 2 only; falling back to NCCL all-reduces", flush=True)
         args.tp_comm = "nccl"
+    if args.tp_comm == "sp" and args.tp > 1:
+        if not symm_ok or args.pp > 1 or args.cp > 1 or cfg.is_qwen3_moe or rows % (128 * args.tp):
+            raise SystemExit("--tp-comm sp needs CUDA, bf16, a dense model, --pp 1 --cp 1 and a micro-batch whose "
+                             "token count is a multiple of 128 * tp")
+        from ..parallel.tp_sp import TpSp
+        ctx.tp_sp = TpSp(ctx.tp_group, device, rows, cfg.hidden_size, arena_slots=2 * cfg.num_hidden_layers + 1)
     if args.tp_comm == "symm" and args.tp > 1 and symm_ok:
         from ..parallel.tp_symm import TpSymm
         ctx.tp_symm = TpSymm(ctx.tp_group, device, rows, cfg.hidden_size)
