@@ -86,6 +86,7 @@ _CUDA_PROTOS = {
     "cvb_device_free": "p",
     "cvb_device_memset": "pilp",
     "cvb_can_access_peer": "ii",
+    "cvb_device_memcpy_async": "pp l p",
     "cvb_gdn_chunk_prep": "ppp l pp l ii ff pppppppp p p",
     "cvb_gdn_chunk_out": "ppppp l ii p p",
     "cvb_gdn_chunk_bwd": "ppp l p ppp pp pp p p l ii f ppp l pp p p",

@@ -12,6 +12,10 @@ One process per GPU.  Every case is timed with CUDA events on the launching stre
                 peer (``cvb_flat_adamw_allgather``) vs the local AdamW kernel + ``all_gather_into_tensor``.
 * ``tp_gemm``   row-parallel linear, GEMM + all-reduce: the tcgen05 GEMM whose epilogue stores each tile into
                 every peer's slot, a flag barrier and a local sum, vs the same GEMM + NCCL all-reduce.
+* ``tp_sp``     one tensor-parallel layer half with the token-sharded residual stream: row-parallel GEMM whose
+                epilogue reduce-scatters its tiles to their owners, residual add + RMSNorm on this rank's rows,
+                all-gather of the normalised rows overlapped with the column-parallel GEMM on the local rows
+                (``parallel/tp_sp.py``), vs GEMM + NCCL all-reduce + add-RMSNorm on all rows + GEMM.
 * ``push``      weight push of the bf16 parameter buffer from rank i to rank i + N/2 by peer stores
                 (``cvb_broadcast_store``) vs NCCL send / recv.
 
@@ -55,7 +59,7 @@ def main(argv=None) -> int:
     ap.add_argument("--numel", type=int, default=752 * 1024 * 1024, help="parameters (0.8B model: 7.5e8)")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--tokens", type=int, default=40960)
-    ap.add_argument("--what", default="zero_rs,zero_ag,tp_gemm,push")
+    ap.add_argument("--what", default="zero_rs,zero_ag,tp_gemm,tp_sp,push")
     a = ap.parse_args(argv)
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -149,6 +153,48 @@ def main(argv=None) -> int:
         roof_ms = max(flops / peak, link_bytes / (LINK_GBS * 1e9)) * 1e3
         report(case="tp_gemm", n_gpus=world, M=M, N=N, K=K, fused_ms=tf, nccl_ms=tn, roofline_ms=roof_ms,
                roofline_frac=roof_ms / tf, link_gbs=link_bytes / tf / 1e6)
+        nv.check_status(dev)
+
+    if "tp_sp" in what and world > 1 and a.tokens % (128 * world) == 0:
+        from . import ops
+        from .ops import gemm_nt
+        from .parallel import tp_sp
+        M, H, K, N2 = a.tokens, 1024, max(64, 2048 // world), 7168 // world   # out_proj -> norm -> gate|up
+        sp = tp_sp.TpSp(group, dev, M, H, arena_slots=1)
+        rl = M // world
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w1 = torch.randn(H, K, device=dev, dtype=torch.bfloat16) * 0.02
+        w2 = torch.randn(N2, H, device=dev, dtype=torch.bfloat16) * 0.02
+        wn = torch.zeros(H, device=dev, dtype=torch.bfloat16)
+        resid_l = torch.randn(rl, H, device=dev, dtype=torch.bfloat16)
+        resid_f = torch.randn(M, H, device=dev, dtype=torch.bfloat16)
+
+        def fused():
+            with torch.no_grad():
+                sp.slot = 0
+                parts = tp_sp.row_linear(x, w1, sp)
+                full, _ = tp_sp.norm_gather(parts, resid_l, wn, 1e-6, 1.0, sp, True)
+                tp_sp.col_linear(full, w2, sp)
+
+        def nccl():
+            with torch.no_grad():
+                y = gemm_nt(x, w1)
+                dist.all_reduce(y, group=group)
+                n1, _ = ops.add_rmsnorm(y, resid_f, wn, 1e-6, 1.0)
+                gemm_nt(n1, w2)
+        tf, tn = _time(fused, a.iters, group), _time(nccl, a.iters, group)
+        flops = 2.0 * M * H * K + 2.0 * M * N2 * H
+        link_bytes = 2 * (world - 1) * rl * H * 2         # reduce-scatter out + all-gather out, per GPU
+        peak = 1627e12
+        try:
+            from .bench_kernels import _peaks
+            peak = _peaks()["bf16_tflops"] * 1e12
+        except Exception:
+            pass
+        roof_ms = max(flops / peak, link_bytes / (LINK_GBS * 1e9)) * 1e3
+        report(case="tp_sp", n_gpus=world, M=M, H=H, K=K, N2=N2, fused_ms=tf, nccl_ms=tn, roofline_ms=roof_ms,
+               roofline_frac=roof_ms / tf, compute_ms=flops / peak * 1e3, link_ms=link_bytes / (LINK_GBS * 1e6),
+               note="row GEMM -> RS (epilogue) -> add+RMSNorm on T/n rows -> AG (copy engines) || column GEMM")
         nv.check_status(dev)
 
     if "push" in what and world > 1 and world % 2 == 0:

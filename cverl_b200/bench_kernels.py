@@ -74,6 +74,28 @@ def case_gemm(a, dev, kind):
     return fn, 2.0 * M * N * K, None
 
 
+def case_gemm_scatter(a, dev):
+    """The reduce-scatter epilogue of the tensor-parallel row-parallel GEMM on ONE device: the row blocks of the
+    partial product go to two different buffers (the "owners"), both in local memory here, exactly as they would
+    go to this rank's and a peer's buffer over NVLink.  Serves profiler captures of that kernel, which must not
+    run under a multi-rank command."""
+    from . import _native as nv
+    from .ops import gemm as G
+    M, N, K = a.m, a.n, a.k
+    if M % 256 or N % 64:
+        raise SystemExit("gemm_scatter needs m % 256 == 0 and n % 64 == 0")
+    x, w = _bf(M, K, dev=dev), _bf(N, K, dev=dev)
+    rl = M // 2
+    owners = [torch.empty(2, rl, N, device=dev, dtype=torch.bfloat16) for _ in range(2)]   # [slot][rows, N]
+    me = 0
+    bases = [owners[o].data_ptr() + (me * rl - o * rl) * N * 2 for o in range(2)]
+
+    def fn():
+        G.gemm_raw(x, w, None, M, N, K, a_mn=False, b_mn=False, epi=nv.EPI_STORE_BF16,
+                   block_n=G._pick_block_n(M, N), scatter=(bases, rl), ldc=N)
+    return fn, 2.0 * M * N * K, None
+
+
 def case_lmhead(a, dev, backward):
     from . import ops
     T, H, V = a.m, a.k, a.n
@@ -234,6 +256,8 @@ def main(argv=None) -> int:
     k = a.kernel
     if k in ("gemm_nt", "gemm_nn", "gemm_tn"):
         fn, flops, nbytes = case_gemm(a, dev, k)
+    elif k == "gemm_scatter":
+        fn, flops, nbytes = case_gemm_scatter(a, dev)
     elif k in ("lmhead_fwd", "lmhead_bwd"):
         fn, flops, nbytes = case_lmhead(a, dev, k.endswith("bwd"))
     elif k in ("gdn_prep", "gdn_fwd", "gdn_bwd"):

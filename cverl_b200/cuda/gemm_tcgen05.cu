@@ -680,8 +680,81 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 // 2-D bf16 tensor map with 128-byte swizzle. `inner` is the contiguous extent.
+static int encode_tensor_map_2d_impl(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner,
+                                     uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner,
+                                     uint32_t box_outer);
+static inline int encode_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner,
+                                       uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner,
+                                       uint32_t box_outer) {
+  return encode_tensor_map_2d_impl(out, base, elem_bytes, inner, outer, row_stride_bytes, box_inner, box_outer);
+}
+
+// A tensor map is a pure function of (base, element size, extents, row stride, box): training re-issues the same
+// few hundred (pointer, shape) pairs every step - weights, the flat gradient, cached activation buffers - so the
+// encoded maps are kept in a small per-thread table (the forward and the autograd thread each have one; no lock)
+// and the driver call is made only on a miss.
+namespace {
+struct MapKey {
+  const void* base;
+  uint64_t inner, outer, stride;
+  uint32_t box_inner, box_outer;
+  int elem;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && inner == o.inner && outer == o.outer && stride == o.stride &&
+           box_inner == o.box_inner && box_outer == o.box_outer && elem == o.elem;
+  }
+};
+struct MapSlot {
+  MapKey key;
+  CUtensorMap map;
+  bool used;
+};
+constexpr int MAP_CACHE_SLOTS = 8192;  // power of two
+inline uint64_t map_hash(const MapKey& k) {
+  uint64_t h = reinterpret_cast<uint64_t>(k.base) * 0x9E3779B97F4A7C15ull;
+  h ^= (k.inner + 0x632BE59BD9B4E019ull) * 0xC2B2AE3D27D4EB4Full;
+  h ^= (k.outer << 20) ^ (k.stride << 7) ^ (static_cast<uint64_t>(k.box_inner) << 40) ^
+       (static_cast<uint64_t>(k.box_outer) << 52) ^ static_cast<uint64_t>(k.elem);
+  h ^= h >> 29;
+  return h * 0xBF58476D1CE4E5B9ull;
+}
+}  // namespace
+
 int make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
                        uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+  static const bool cache_on = [] { const char* e = getenv("CVERL_B200_TMAP_CACHE"); return !(e && e[0] == '0'); }();
+  static thread_local MapSlot* table = nullptr;
+  const MapKey key{base, inner, outer, row_stride_bytes, box_inner, box_outer, elem_bytes};
+  MapSlot* slot = nullptr;
+  if (cache_on) {
+    if (!table) table = static_cast<MapSlot*>(calloc(MAP_CACHE_SLOTS, sizeof(MapSlot)));
+    if (table) {
+      uint64_t i = map_hash(key) & (MAP_CACHE_SLOTS - 1);
+      for (int probe = 0; probe < 8; ++probe, i = (i + 1) & (MAP_CACHE_SLOTS - 1)) {
+        if (table[i].used && table[i].key == key) {
+          *out = table[i].map;
+          return 0;
+        }
+        if (!table[i].used) {
+          slot = &table[i];
+          break;
+        }
+      }
+      if (!slot) slot = &table[map_hash(key) & (MAP_CACHE_SLOTS - 1)];  // full neighbourhood: overwrite
+    }
+  }
+  const int rc = encode_tensor_map_2d(out, base, elem_bytes, inner, outer, row_stride_bytes, box_inner, box_outer);
+  if (rc == 0 && slot) {
+    slot->key = key;
+    slot->map = *out;
+    slot->used = true;
+  }
+  return rc;
+}
+
+static int encode_tensor_map_2d_impl(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner,
+                                     uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner,
+                                     uint32_t box_outer) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;
   // The driver call needs this thread to have a current context.  Autograd runs backward on

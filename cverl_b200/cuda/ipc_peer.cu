@@ -50,6 +50,12 @@ int cvb_device_free(void* p) { return static_cast<int>(cudaFree(p)); }
 int cvb_device_memset(void* p, int value, long long bytes, void* stream) {
   return static_cast<int>(cudaMemsetAsync(p, value, static_cast<size_t>(bytes), static_cast<cudaStream_t>(stream)));
 }
+// Device-to-device copy on `stream`; either side may be a peer-mapped address (the copy engines move the bytes
+// over NVLink without occupying an SM).
+int cvb_device_memcpy_async(void* dst, const void* src, long long bytes, void* stream) {
+  return static_cast<int>(cudaMemcpyAsync(dst, src, static_cast<size_t>(bytes), cudaMemcpyDeviceToDevice,
+                                          static_cast<cudaStream_t>(stream)));
+}
 int cvb_can_access_peer(int device, int peer) {
   int ok = 0;
   if (cudaDeviceCanAccessPeer(&ok, device, peer) != cudaSuccess) return 0;

@@ -126,11 +126,14 @@ class SymmBarrier:
         self.flags = heap.alloc(256)
         self.epoch = 0
 
-    def __call__(self) -> None:
+        self._ptrs = self.flags.ptr_array()
+        self._status = nv.status_word(heap.device).data_ptr()
+
+    def __call__(self, stream: Optional[int] = None) -> None:
+        """Enqueues the barrier on the current stream, or on the raw ``cudaStream_t`` handle given."""
         self.epoch += 1
-        dev = self.heap.device
-        nv.check(nv.cuda().cvb_symm_barrier(self.flags.ptr_array(), self.heap.index, self.heap.world, self.epoch,
-                                            nv.status_word(dev).data_ptr(), nv.stream()), "cvb_symm_barrier")
+        nv.check(nv.cuda().cvb_symm_barrier(self._ptrs, self.heap.index, self.heap.world, self.epoch, self._status,
+                                            nv.stream() if stream is None else stream), "cvb_symm_barrier")
         count_launch()
 
 

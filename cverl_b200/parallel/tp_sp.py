@@ -11,11 +11,14 @@ its two halves, each fused into the kernel next to it:
   partial product ONLY to the rank that owns those rows - into slot ``me`` of that rank's ``parts`` buffer,
   its own memory or a peer's over NVLink (``scatter`` mode of ``cuda/gemm_tcgen05.cu``) - tile by tile while
   the tensor cores run the next tile.  Nothing else is sent: ``(n-1)/n`` of the tile bytes cross the link.
-* **norm -> all-gather.**  After one flag barrier, ``sp_add_rmsnorm_fwd`` (``cuda/norm_ops.cu``) sums the
-  ``n`` slots of its own rows with the residual, normalises ``T/n`` rows instead of ``T``, and stores the
-  normalised rows into the gathered activation on every rank of the group.  After a second barrier the
-  column-parallel GEMM reads the gathered rows from local memory (each remote row crossed the link once; no
-  TMA load ever targets peer memory).
+* **norm -> all-gather -> GEMM.**  After one flag barrier, ``sp_add_rmsnorm_fwd`` (``cuda/norm_ops.cu``) sums
+  the ``n`` slots of its own rows with the residual, normalises ``T/n`` rows instead of ``T`` and writes them
+  into its row range of the gathered activation.  The rows then travel to the peers' copies over NVLink on a
+  side stream (copy engines, no SM) while the column-parallel GEMM already runs on the rows this rank
+  produced; a second barrier on that side stream tells each rank that its peers' rows have landed, and the
+  GEMM's remaining row blocks follow.  Each remote row crosses the link once and is read from local memory;
+  no TMA load ever targets peer memory.  (``overlap=False`` makes the norm kernel store to every rank
+  directly and the GEMM wait for all rows: one launch more exposed to the link, fewer launches.)
 
 The backward pass is the mirror image: the column-parallel linear's input-gradient GEMM scatters its partial
 product the same way, ``sp_add_rmsnorm_bwd`` sums the slots, runs the norm backward on ``T/n`` rows and
@@ -29,6 +32,7 @@ flight at a time: no pipeline parallelism on this path).  All waits are the boun
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import List, Optional
 
 import torch
@@ -41,7 +45,7 @@ from .tp_symm import _acc_dw
 
 
 class TpSp:
-    def __init__(self, group, device, max_rows: int, hidden: int, arena_slots: int):
+    def __init__(self, group, device, max_rows: int, hidden: int, arena_slots: int, overlap: bool = True):
         """``max_rows``: tokens of one micro-batch over the whole group (a multiple of ``128 * world``)."""
         self.heap = SymmetricHeap(group, device)
         self.world, self.rank = self.heap.world, self.heap.index
@@ -56,12 +60,29 @@ class TpSp:
         self.arena = self.heap.alloc(self.slot_bytes * arena_slots)           # gathered forward activations
         self.arena_slots = arena_slots
         self.barrier = SymmBarrier(self.heap)
+        # the gather travels on a side stream with a barrier of its own (flag epochs are per barrier object:
+        # two streams must not share one)
+        self.overlap = overlap = overlap and os.environ.get("CVERL_B200_TP_SP_OVERLAP", "1") != "0"
+        self.side = torch.cuda.Stream(device=self.device) if overlap else None
+        self.side_barrier = SymmBarrier(self.heap) if overlap else None
+        self.pending = None            # (event, first row, end row) of a gather still in flight
+        self._views = {}               # (buffer id, byte offset, rows) -> cached tensor view
         self.cur_parts = 0
         self.cur_gath = 0
         self.slot = 0
         self.active = False
 
     # ------------------------------------------------------------------------------------------------
+    def view(self, buf, rows: int, offset_bytes: int = 0) -> torch.Tensor:
+        """``[rows, hidden]`` bf16 view of a symmetric buffer; the views are cached (building one from a raw pointer
+        costs tens of microseconds of host time, and there are four per norm)."""
+        key = (id(buf), offset_bytes, rows)
+        t = self._views.get(key)
+        if t is None:
+            t = buf.tensor(rows * self.hidden, torch.bfloat16, offset_bytes).view(rows, self.hidden)
+            self._views[key] = t
+        return t
+
     def fits(self, rows: int, hidden: int) -> bool:
         return (hidden == self.hidden and rows <= self.max_rows and rows % (128 * self.world) == 0
                 and hidden % 64 == 0)
@@ -90,10 +111,40 @@ class TpSp:
         a, b = G._row_major_2d(a), G._row_major_2d(b)
         G.gemm_raw(a, b, None, rows, self.hidden, K, a_mn=False, b_mn=b_mn, epi=nv.EPI_STORE_BF16,
                    block_n=G._pick_block_n(rows, self.hidden), scatter=(bases, rl), ldc=ldc)
-        return buf.tensor(rows * self.hidden, torch.bfloat16).view(rows, self.hidden)
+        return self.view(buf, rows)
+
+    def push_rows(self, buf, offset_bytes: int, rl: int) -> None:
+        """This rank's ``rl`` rows at ``offset_bytes`` of ``buf`` were just written locally (on the current
+        stream): send them to the same place in every peer's copy on the side stream, then barrier there.  Leaves
+        ``pending`` for the consumer, which may use rows ``[rank*rl, (rank+1)*rl)`` at once and the others after
+        waiting for the event."""
+        wrote = torch.cuda.Event()
+        wrote.record(torch.cuda.current_stream(self.device))
+        nbytes = rl * self.hidden * 2
+        off = offset_bytes + self.rank * nbytes
+        side = self.side.cuda_stream
+        self.side.wait_event(wrote)
+        copy = nv.cuda().cvb_device_memcpy_async
+        for j in range(self.world):
+            if j != self.rank:
+                nv.check(copy(buf.peer_ptrs[j] + off, buf.peer_ptrs[self.rank] + off, nbytes, side),
+                         "cudaMemcpyAsync(peer)")
+        self.side_barrier(side)
+        landed = torch.cuda.Event()
+        landed.record(self.side)
+        self.pending = (landed, self.rank * rl, (self.rank + 1) * rl)
+
+    def take_pending(self):
+        p, self.pending = self.pending, None
+        return p
+
+    def wait_pending(self) -> None:
+        p = self.take_pending()
+        if p is not None:
+            torch.cuda.current_stream(self.device).wait_event(p[0])
 
     def parts_view(self, rows: int) -> torch.Tensor:
-        return self.parts[self.cur_parts].tensor(rows * self.hidden, torch.bfloat16).view(rows, self.hidden)
+        return self.view(self.parts[self.cur_parts], rows)
 
 
 def _ptr_array(ptrs: List[int]):
@@ -107,16 +158,35 @@ class _SpRowLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, sp: TpSp):
         ctx.save_for_backward(x, w)
+        ctx.sp = sp
         x2 = x.reshape(-1, x.shape[-1])
         return sp.scatter_gemm(x2, w, x2.shape[0], x2.shape[1], False)
 
     @staticmethod
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
+        sp = ctx.sp
         x2 = x.reshape(-1, x.shape[-1])
-        dx = G.gemm_nn(dy, w).reshape(x.shape) if ctx.needs_input_grad[0] else None
-        dw = _acc_dw(ctx, dy, x2, w) if ctx.needs_input_grad[1] else None
-        return dx, dw, None
+        pend = sp.take_pending()
+        if pend is None or getattr(w, "main_grad", None) is None:
+            if pend is not None:
+                torch.cuda.current_stream(sp.device).wait_event(pend[0])
+            dx = G.gemm_nn(dy, w).reshape(x.shape) if ctx.needs_input_grad[0] else None
+            dw = _acc_dw(ctx, dy, x2, w) if ctx.needs_input_grad[1] else None
+            return dx, dw, None
+        # the rows this rank produced are here already: start on them while the peers' rows arrive
+        landed, r0, r1 = pend
+        T = dy.shape[0]
+        dx2 = torch.empty((T, w.shape[1]), dtype=torch.bfloat16, device=dy.device) if ctx.needs_input_grad[0] else None
+        blocks = [(r0, r1)] + [b for b in ((0, r0), (r1, T)) if b[1] > b[0]]
+        for k, (a, b) in enumerate(blocks):
+            if k == 1:
+                torch.cuda.current_stream(sp.device).wait_event(landed)
+            if dx2 is not None:
+                G.gemm_nn(dy[a:b], w, out=dx2[a:b])
+            if ctx.needs_input_grad[1]:
+                G.gemm_tn_acc(dy[a:b], x2[a:b], w.main_grad)
+        return (dx2.reshape(x.shape) if dx2 is not None else None), None, None
 
 
 class _SpColLinear(torch.autograd.Function):
@@ -127,7 +197,20 @@ class _SpColLinear(torch.autograd.Function):
     def forward(ctx, x, w, sp: TpSp):
         ctx.save_for_backward(x, w)
         ctx.sp = sp
-        return G.gemm_nt(x, w)
+        pend = sp.take_pending()
+        if pend is None:
+            return G.gemm_nt(x, w)
+        # the rows this rank normalised are here already: start on them while the peers' rows arrive
+        landed, r0, r1 = pend
+        T = x.shape[0]
+        y = G._alloc_out(T, w.shape[0], torch.bfloat16, x.device)
+        G.gemm_nt(x[r0:r1], w, out=y[r0:r1])
+        torch.cuda.current_stream(sp.device).wait_event(landed)
+        if r0 > 0:
+            G.gemm_nt(x[:r0], w, out=y[:r0])
+        if r1 < T:
+            G.gemm_nt(x[r1:], w, out=y[r1:])
+        return y
 
     @staticmethod
     def backward(ctx, dy):
@@ -163,17 +246,24 @@ class _SpNormGather(torch.autograd.Function):
         r2 = resid.contiguous() if resid is not None else None
         if from_parts:
             sp.barrier()                     # every rank's scatter stores into my parts buffer have landed
-        dst = _ptr_array([p + slot_off for p in sp.arena.peer_ptrs])
+        if sp.overlap:
+            dst, ndst = _ptr_array([sp.arena.peer_ptrs[sp.rank] + slot_off]), 1
+        else:
+            dst, ndst = _ptr_array([p + slot_off for p in sp.arena.peer_ptrs]), sp.world
         nv.check(nv.cuda().cvb_sp_add_rmsnorm_fwd(src.data_ptr(), stride, nparts, nv.ptr(r2), w.data_ptr(), dst,
-                                                  sp.world, sp.rank * rl, resid_out.data_ptr(), rstd.data_ptr(),
+                                                  ndst, sp.rank * rl, resid_out.data_ptr(), rstd.data_ptr(),
                                                   rl, H, eps, w_offset, nv.stream()), "cvb_sp_add_rmsnorm_fwd")
         count_launch()
-        sp.barrier()                         # every rank's rows of the gathered activation are in place
+        if sp.overlap:
+            sp.push_rows(sp.arena, slot_off, rl)
+            if grad_in_tensor:               # the consumer is not one of this module's GEMMs: wait here
+                sp.wait_pending()
+        else:
+            sp.barrier()                     # every rank's rows of the gathered activation are in place
         ctx.save_for_backward(resid_out, w, rstd)
         ctx.sp, ctx.w_offset, ctx.rl = sp, w_offset, rl
         ctx.from_parts, ctx.has_resid, ctx.grad_in_tensor = from_parts, resid is not None, grad_in_tensor
-        full = sp.arena.tensor(rows * H, torch.bfloat16, slot_off).view(rows, H)
-        return full, resid_out
+        return sp.view(sp.arena, rows, slot_off), resid_out
 
     @staticmethod
     def backward(ctx, d_full, d_resid_out):
@@ -195,7 +285,10 @@ class _SpNormGather(torch.autograd.Function):
         if ctx.from_parts:
             sp.cur_gath ^= 1
             gbuf = sp.gath[sp.cur_gath]
-            dst, ndst = _ptr_array(list(gbuf.peer_ptrs)), sp.world
+            if sp.overlap:
+                dst, ndst = _ptr_array([gbuf.peer_ptrs[sp.rank]]), 1
+            else:
+                dst, ndst = _ptr_array(list(gbuf.peer_ptrs)), sp.world
         else:
             dst, ndst = None, 0
         nv.check(nv.cuda().cvb_sp_add_rmsnorm_bwd(src.data_ptr(), stride, nparts, h.data_ptr(), w.data_ptr(),
@@ -205,8 +298,11 @@ class _SpNormGather(torch.autograd.Function):
         count_launch()
         dw = None if is_main else dwbuf.to(w.dtype)
         if ctx.from_parts:
-            sp.barrier()                     # the gathered output gradient is complete on every rank
-            d_delta = gbuf.tensor(rows * H, torch.bfloat16).view(rows, H)
+            if sp.overlap:
+                sp.push_rows(gbuf, 0, rl)    # consumed by the row-parallel linear's backward, own rows first
+            else:
+                sp.barrier()                 # the gathered output gradient is complete on every rank
+            d_delta = sp.view(gbuf, rows)
         else:
             d_delta = dx
         return d_delta, (dx if ctx.has_resid else None), dw, None, None, None, None, None
