@@ -97,6 +97,74 @@ def test_p2p_rows_skip_entries_outside_the_group_or_the_buffer():
     assert torch.equal(back, rows[:2]) and nv.check_status() == 0
 
 
+def test_gemm_reduce_scatter_epilogue_emulated():
+    """GEMM whose epilogue sends every row block only to its owner: two "ranks" on one device, each writing its
+    partial product into slot ``rank`` of both owners' buffers; the owners' slot sums equal the fp32 product."""
+    from cverl_b200 import _native as nv
+    from cverl_b200.ops import gemm as G
+    M, N, K, world = 1024, 256, 384, 2
+    rl = M // world
+    g = torch.Generator(device="cuda").manual_seed(4)
+    xs = [torch.randn(M, K, device="cuda", generator=g).bfloat16() for _ in range(world)]
+    ws = [(0.05 * torch.randn(N, K, device="cuda", generator=g)).bfloat16() for _ in range(world)]
+    owners = [torch.zeros(world, rl, N, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    for me in range(world):
+        bases = [owners[o].data_ptr() + (me * rl - o * rl) * N * 2 for o in range(world)]
+        G.gemm_raw(xs[me], ws[me], None, M, N, K, a_mn=False, b_mn=False, epi=nv.EPI_STORE_BF16,
+                   block_n=G._pick_block_n(M, N), scatter=(bases, rl), ldc=N)
+    torch.cuda.synchronize()
+    nv.check_status()
+    ref = sum(x.float() @ w.float().t() for x, w in zip(xs, ws))
+    for o in range(world):
+        for me in range(world):
+            part = xs[me].float() @ ws[me].float().t()
+            torch.testing.assert_close(owners[o][me].float(), part[o * rl:(o + 1) * rl], rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(owners[o].float().sum(0), ref[o * rl:(o + 1) * rl], rtol=2e-2, atol=4e-2)
+
+
+def test_sequence_parallel_norm_kernels_emulated():
+    """``sp_add_rmsnorm`` forward / backward against the fp32 statement: the inputs are ``n`` partial slots, the
+    outputs go to row ``dst_row0`` of several gathered buffers (here all on one device)."""
+    from cverl_b200 import _native as nv
+    from cverl_b200.ops.norm import rmsnorm_ref
+    world, rl, H, rank = 2, 384, 1024, 1
+    g = torch.Generator(device="cuda").manual_seed(8)
+    parts = torch.randn(world, rl, H, device="cuda", generator=g).bfloat16()
+    resid = torch.randn(rl, H, device="cuda", generator=g).bfloat16()
+    w = (0.1 * torch.randn(H, device="cuda", generator=g)).bfloat16()
+    gathered = [torch.zeros(world * rl, H, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    resid_out = torch.empty(rl, H, device="cuda", dtype=torch.bfloat16)
+    rstd = torch.empty(rl, device="cuda")
+    nv.check(nv.cuda().cvb_sp_add_rmsnorm_fwd(parts.data_ptr(), rl * H, world, resid.data_ptr(), w.data_ptr(),
+                                              _ptrs(gathered), world, rank * rl, resid_out.data_ptr(),
+                                              rstd.data_ptr(), rl, H, 1e-6, 1.0, nv.stream()), "sp fwd")
+    torch.cuda.synchronize()
+    hsum = (parts.float().sum(0) + resid.float()).requires_grad_(True)
+    torch.testing.assert_close(resid_out.float(), hsum.detach(), rtol=1e-2, atol=1e-2)
+    y_ref = rmsnorm_ref(resid_out.float().requires_grad_(False), w, 1e-6, 1.0)
+    for buf in gathered:
+        torch.testing.assert_close(buf[rank * rl:(rank + 1) * rl].float(), y_ref.float(), rtol=2e-2, atol=2e-2)
+        assert float(buf[:rank * rl].abs().sum()) == 0.0                      # other ranks' rows untouched
+    # backward: dy arrives as n partial slots, dres as a local tensor
+    dy_parts = torch.randn(world, rl, H, device="cuda", generator=g).bfloat16()
+    dres = torch.randn(rl, H, device="cuda", generator=g).bfloat16()
+    dx = torch.empty(rl, H, device="cuda", dtype=torch.bfloat16)
+    dxg = [torch.zeros(world * rl, H, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    dw = torch.zeros(H, device="cuda")
+    nv.check(nv.cuda().cvb_sp_add_rmsnorm_bwd(dy_parts.data_ptr(), rl * H, world, resid_out.data_ptr(), w.data_ptr(),
+                                              rstd.data_ptr(), dres.data_ptr(), dx.data_ptr(), _ptrs(dxg), world,
+                                              rank * rl, dw.data_ptr(), rl, H, 1.0, nv.stream()), "sp bwd")
+    torch.cuda.synchronize()
+    h = resid_out.float().requires_grad_(True)
+    wf = w.float().requires_grad_(True)
+    xf = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-6) * (1.0 + wf)
+    xf.backward(dy_parts.float().sum(0))
+    torch.testing.assert_close(dx.float(), h.grad + dres.float(), rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(dw, wf.grad, rtol=2e-2, atol=0.5)
+    for buf in dxg:
+        assert torch.equal(buf[rank * rl:(rank + 1) * rl], dx)
+
+
 def test_barrier_wait_runs_out_to_status():
     """A flag that nothing sets: the wait gives up within its clock budget, the kernel returns and the
     host reads the status word; the context stays usable."""
