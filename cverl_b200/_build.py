@@ -6,7 +6,10 @@ Two shared libraries are produced under ``cverl_b200/lib``:
   ``-gencode arch=compute_100a,code=sm_100a`` (cross-compiles without a GPU);
 * ``libcverl.so`` - the host-side C/C++ runtime (public C ABI of the RL math,
   topology, pipeline schedule, safetensors, tokenizers, reward, transports,
-  plugin loader).
+  plugin loader);
+* ``libcverl_nccl.so`` - the native NCCL communicator (``nccl/nccl_backend.cc``),
+  built against the ``nccl.h`` / ``libnccl.so.2`` of the installed ``nvidia-nccl``
+  wheel (the library ``torch`` itself loads), skipped when that wheel is absent.
 
 Objects are cached under ``build/`` and rebuilt when a source or header is newer.
 """
@@ -25,6 +28,7 @@ LIB_DIR = PKG / "lib"
 OBJ_DIR = ROOT / "build" / "obj"
 CUDA_LIB = LIB_DIR / "libcverl_b200_cuda.so"
 HOST_LIB = LIB_DIR / "libcverl.so"
+NCCL_LIB = LIB_DIR / "libcverl_nccl.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -121,9 +125,42 @@ def build_host(force: bool = False, verbose: bool = False) -> Path:
     return HOST_LIB
 
 
+def _nccl_paths():
+    """(include dir, library file) of the NCCL that ``torch`` uses, or (None, None)."""
+    import site
+    for sp in site.getsitepackages():
+        inc, lib = Path(sp) / "nvidia/nccl/include", Path(sp) / "nvidia/nccl/lib/libnccl.so.2"
+        if (inc / "nccl.h").exists() and lib.exists():
+            return inc, lib
+    for inc, lib in ((Path("/usr/include"), Path("/usr/lib/x86_64-linux-gnu/libnccl.so.2")),):
+        if (inc / "nccl.h").exists() and lib.exists():
+            return inc, lib
+    return None, None
+
+
+def build_nccl(force: bool = False, verbose: bool = False) -> Path | None:
+    src = PKG / "nccl" / "nccl_backend.cc"
+    inc, lib = _nccl_paths()
+    if inc is None:
+        if verbose:
+            print("[g++] nccl_backend.cc skipped: no nccl.h / libnccl.so.2 on this machine", flush=True)
+        return None
+    LIB_DIR.mkdir(parents=True, exist_ok=True)
+    if not force and NCCL_LIB.exists() and NCCL_LIB.stat().st_mtime >= src.stat().st_mtime:
+        return NCCL_LIB
+    if verbose:
+        print("[g++] nccl_backend.cc", flush=True)
+    cuda_home = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+    _run([os.environ.get("CXX", "g++"), *CXX_FLAGS, "-shared", "-I", str(inc), "-I", str(cuda_home / "include"),
+          str(src), "-o", str(NCCL_LIB), str(lib), f"-L{cuda_home / 'lib64'}", "-lcudart",
+          f"-Wl,-rpath,{lib.parent}", f"-Wl,-rpath,{cuda_home / 'lib64'}"])
+    return NCCL_LIB
+
+
 def build_all(force: bool = False, verbose: bool = False) -> None:
     build_host(force, verbose)
     build_cuda(force, verbose)
+    build_nccl(force, verbose)
 
 
 if __name__ == "__main__":
