@@ -1,0 +1,94 @@
+"""Parity against outside oracles on the CPU: the model forward against Hugging Face Transformers, the BPE
+tokenizer against Hugging Face ``tokenizers`` on a freshly trained vocabulary, and the small demo programs."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+@pytest.mark.parametrize("kind", ["qwen3_5", "qwen3_moe"])
+def test_forward_matches_transformers(kind, capsys):
+    pytest.importorskip("transformers")
+    from cverl_b200.cli import compare_hf_forward
+    rc = compare_hf_forward.main(["--random", kind, "--rtol", "1e-4", "--atol", "1e-4"])
+    report = json.loads(capsys.readouterr().out)
+    if rc == 3:
+        pytest.skip(report["unavailable"])
+    assert rc == 0 and report["allclose"] and report["max_abs"] < 1e-4, report
+    rc = compare_hf_forward.main(["--random", kind, "--logits", "--rtol", "1e-4", "--atol", "1e-4", "--seed", "3"])
+    report = json.loads(capsys.readouterr().out)
+    assert rc == 0 and report["ours_top5"] == report["hf_top5"], report
+
+
+def test_bpe_tokenizer_matches_hf_tokenizers_on_a_trained_vocabulary(tmp_path):
+    """A byte-level BPE tokenizer with a few hundred real merges, the Qwen pre-tokenizer pattern and special tokens,
+    trained here on the repository's own prose: every probe and every line of the corpus must encode to the ids
+    Hugging Face ``tokenizers`` gives, and decode back."""
+    pytest.importorskip("tokenizers")
+    from tokenizers import Tokenizer
+    from cverl_b200.cli import dump_tokenizer_fixtures as dump
+    from cverl_b200.text import HfBpeTokenizer
+    corpus = tmp_path / "corpus.txt"
+    corpus.write_text((ROOT / "README.md").read_text() + "\n" + (ROOT / "cverl_b200" / "ops" / "rl.py").read_text())
+    assert dump.main(["train", "--corpus", str(corpus), "--vocab-size", "700", "--out-dir", str(tmp_path / "tok")]) == 0
+    fixtures = json.loads((tmp_path / "tok" / "fixtures.json").read_text())
+    mine = HfBpeTokenizer(str(tmp_path / "tok" / "tokenizer.json"))
+    hf = Tokenizer.from_file(str(tmp_path / "tok" / "tokenizer.json"))
+    assert mine.vocab_size == hf.get_vocab_size() and len(fixtures) == len(dump.PROBES)
+    for row in fixtures:
+        assert mine.encode(row["text"]) == row["ids"], row["text"]
+        assert mine.decode(row["ids"], skip_special=False) == row["decoded"], row["text"]
+    lines = [ln for ln in corpus.read_text().splitlines() if ln.strip()][:300]
+    for ln in lines:
+        assert mine.encode(ln) == hf.encode(ln, add_special_tokens=False).ids, ln
+    # the fixture file of a real tokenizer (e.g. Qwen3.5's) replays the same way when one is present
+    real = os.environ.get("CVERL_QWEN_MODEL_DIR")
+    if real and (Path(real) / "tokenizer.json").exists():
+        out = tmp_path / "real.json"
+        assert dump.main(["real", "--tokenizer-json", str(Path(real) / "tokenizer.json"), "--out", str(out)]) == 0
+        big = HfBpeTokenizer(str(Path(real) / "tokenizer.json"))
+        for row in json.loads(out.read_text()):
+            assert big.encode(row["text"]) == row["ids"], row["text"]
+
+
+@pytest.fixture(scope="module")
+def tiny_dir(tmp_path_factory):
+    from cverl_b200.models.config import Qwen35TextConfig
+    from cverl_b200.models.hf_io import synthesize_model_dir
+    d = tmp_path_factory.mktemp("tiny_model_demo")
+    synthesize_model_dir(Qwen35TextConfig.tiny(), d, seed=3, dtype=torch.float32)
+    return d
+
+
+def _run(*args):
+    return subprocess.run([sys.executable, "-m", *args], cwd=ROOT, env=dict(os.environ, PYTHONPATH=str(ROOT)),
+                          capture_output=True, text=True, timeout=240)
+
+
+def test_demo_programs(tmp_path, tiny_dir):
+    p = _run("cverl_b200.cli.minimal_ppo_step")
+    assert p.returncode == 0 and "param_delta=" in p.stdout, p.stderr[-1000:]
+    prefix = str(tmp_path / "toy")
+    p = _run("cverl_b200.cli.toy_grpo_trainer", "3", "4", "4", "--save-prefix", prefix)
+    assert p.returncode == 0 and p.stdout.splitlines()[0] == "step,loss,avg_reward,success_rate,ppo_kl,clipfrac"
+    assert len(p.stdout.splitlines()) == 4 and Path(prefix + ".model.pt").exists()
+    p = _run("cverl_b200.cli.toy_grpo_trainer", "1", "4", "4", "--load-prefix", prefix)
+    assert p.returncode == 0
+    p = _run("cverl_b200.cli.hf_embedding_grpo_trainer", str(tiny_dir), "--steps", "3", "--vocab-subset", "32")
+    assert p.returncode == 0, p.stderr[-1500:]
+    rows = p.stdout.splitlines()
+    assert rows[2].startswith("embedding_subset=[32,") and rows[3].startswith("step,loss") and len(rows) == 7
+    data = tmp_path / "d.jsonl"
+    data.write_text("\n".join(json.dumps({"prompt": f"What is {i}+1?", "answer": f"#### {i + 1}"}) for i in range(9)))
+    p = _run("cverl_b200.cli.gsm8k_grpo_bench", "--dataset", str(data), "--steps", "6", "--lr", "0.01")
+    assert p.returncode == 0, p.stderr[-1500:]
+    kv = dict(ln.split(",", 1) for ln in p.stdout.splitlines())
+    assert kv["backend"] == "cverl_b200" and float(kv["train_tokens_per_second"]) > 0 and kv["dataset_rows"] == "9"
+    assert float(kv["train_tokens_per_second"]) == pytest.approx(
+        6 * 8 * 4 * 16 * 2 / float(kv["seconds"]), rel=1e-3)
