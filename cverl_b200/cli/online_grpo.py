@@ -129,6 +129,15 @@ def main(argv=None) -> int:
     ap.add_argument("--skip-train", action="store_true")
     ap.add_argument("--dump-rollout-dir", default="")
     ap.add_argument("--push-weights", action="store_true")
+    ap.add_argument("--weight-sync", default="none", choices=["none", "nccl"],
+                    help="nccl: after every update, push the live weights into the vLLM server at --server "
+                         "(pause, update manifest + NCCL transfer, resume)")
+    ap.add_argument("--weight-master-address", default="127.0.0.1")
+    ap.add_argument("--weight-master-port", type=int, default=0)
+    ap.add_argument("--weight-world-size", type=int, default=0, help="trainer rank + all vLLM worker ranks")
+    ap.add_argument("--weight-rank-offset", type=int, default=1)
+    ap.add_argument("--sleep-during-train", action="store_true",
+                    help="put the server to sleep (level 1) while the actor update runs and wake it before the sync")
     ap.add_argument("--http-timeout", type=float, default=120.0)
     ap.add_argument("--seed", type=int, default=17)
     a = ap.parse_args(argv)
@@ -139,6 +148,15 @@ def main(argv=None) -> int:
         raise SystemExit("dataset is empty")
     policy = QwenPolicy(a.model_dir, device=a.device, param_dtype=a.param_dtype, max_layers=a.max_layers)
     ropt = Gsm8kRewardOptions(method="flexible")
+    sync = control = None
+    if a.weight_sync == "nccl" or a.sleep_during_train:
+        from ..rollout.vllm_control import VllmControl, VllmNcclSync
+        control = VllmControl(a.server, a.http_timeout)
+        if a.weight_sync == "nccl":
+            if a.weight_master_port <= 0 or a.weight_world_size <= 1:
+                raise SystemExit("--weight-sync nccl needs --weight-master-port and --weight-world-size >= 2")
+            sync = VllmNcclSync(control, a.weight_master_address, a.weight_master_port, a.weight_world_size,
+                                a.weight_rank_offset)
     cursor = 0
     for step in range(a.first_step, a.first_step + a.steps):
         t0 = time.time()
@@ -155,12 +173,18 @@ def main(argv=None) -> int:
             dump_rollout(Path(a.dump_rollout_dir), step, policy.tokenizer, prompts, responses, pidx, rewards,
                          group_advantages(rewards, pidx), a.max_prompt_tokens, a.max_response_tokens, answers, sidx)
         metrics = {"total_seq": float(len(responses)), "mean_reward": sum(rewards) / max(1, len(rewards))}
+        if a.sleep_during_train and control is not None and not a.skip_train:
+            control.sleep(1, "wait")
         if not a.skip_train:
             metrics = policy.gsm8k_grpo_update(prompts, responses, answers, pidx, sidx, a.max_prompt_tokens,
                                                a.max_response_tokens, a.ppo_epochs, a.lr, 0.0, 0.2, a.kl_coef,
                                                "flexible", True)
+        if a.sleep_during_train and control is not None and not a.skip_train:
+            control.wake()
         pushed = 0
-        if a.push_weights and not a.skip_train:
+        if sync is not None and not a.skip_train:
+            pushed = sync.sync(policy.named_parameters(), policy.update_info())["bytes"]
+        elif a.push_weights and not a.skip_train:
             info = policy.update_info()
             pushed = sum(t.numel() * t.element_size() for _, t in policy.named_parameters())
             assert len(info["names"]) == len(policy.named_parameters())

@@ -139,3 +139,20 @@ def test_actor_loss_cpu_path_matches_c_abi():
     metrics, grad = rl.actor_loss(old, lp, adv, mask, None)
     assert metrics[0].item() == pytest.approx(c_abi.ppo_loss(old, lp, adv, mask)[0], rel=1e-5, abs=1e-6)
     torch.testing.assert_close(grad, c_abi.ppo_loss_backward(old, lp, adv, mask), rtol=1e-5, atol=1e-6)
+
+
+def test_cpu_loss_step_bench_and_cross_check_with_another_abi_library(capsys):
+    """The CPU loss-step benchmark runs on the built library; when an ABI-compatible second library is present
+    (the out-of-tree build of the reference writes one) the two must agree on every output of the step."""
+    import json
+    from pathlib import Path
+    from cverl_b200 import bench_cpu_loss
+    other = Path(__file__).resolve().parents[1] / "baseline" / "_ref" / "lib" / "libcverl_ref.so"
+    args = ["--iters", "3", "--batch", "16", "--seq", "64"]
+    if other.exists():
+        args += ["--other", str(other)]
+    assert bench_cpu_loss.main(args) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["ours_us_per_step"] > 0
+    if other.exists():
+        assert rep["max_abs_diff"] < 1e-5, rep["max_abs_diff_by_output"]

@@ -265,3 +265,86 @@ def _gpu_batch_worker(rank, world, mode):
 @pytest.mark.parametrize("mode", ["direct", "slab"])
 def test_gpu_batch_transport_over_gloo(mode):
     run_ranks(_gpu_batch_worker, 2, mode)
+
+
+def test_vllm_control_plane_and_weight_sync_sequence():
+    """The control client against a local fake server, and the order of one weight push: engine init on both
+    sides, pause, the update manifest in flight while the tensors are sent, resume - with a fake transfer engine
+    standing in for vLLM's."""
+    import json as _json
+    import threading
+    from http.server import BaseHTTPRequestHandler, HTTPServer
+    import torch
+    from cverl_b200.rollout.vllm_control import VllmControl, VllmNcclSync, normalize_dtype_name
+    calls = []
+    update_seen = threading.Event()
+
+    class Handler(BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+
+        def _reply(self, obj):
+            body = _json.dumps(obj).encode()
+            self.send_response(200)
+            self.send_header("Content-Length", str(len(body)))
+            self.end_headers()
+            self.wfile.write(body)
+
+        def do_POST(self):
+            n = int(self.headers.get("Content-Length", "0"))
+            payload = _json.loads(self.rfile.read(n) or b"{}")
+            calls.append((self.path, payload))
+            if self.path == "/update_weights":
+                update_seen.set()
+            self._reply({"ok": True, "path": self.path})
+
+        def do_GET(self):
+            calls.append((self.path, None))
+            self._reply({"world_size": 2} if "world_size" in self.path else {"is_sleeping": False})
+
+    server = HTTPServer(("127.0.0.1", 0), Handler)
+    t = threading.Thread(target=server.serve_forever, daemon=True)
+    t.start()
+    try:
+        c = VllmControl(f"http://127.0.0.1:{server.server_port}", timeout=10)
+        assert c.world_size()["world_size"] == 2 and c.is_sleeping() == {"is_sleeping": False}
+        c.sleep(2, "abort")
+        c.wake(["weights"])
+        assert [p for p, _ in calls[-2:]] == ["/sleep?level=2&mode=abort", "/wake_up?tags=weights"]
+        calls.clear()
+
+        sent = []
+
+        class FakeEngine:
+            @staticmethod
+            def trainer_init(info):
+                sent.append(("init", dict(info)))
+                return "group"
+
+            @staticmethod
+            def trainer_send_weights(it, args):
+                assert update_seen.wait(5.0)              # the manifest request is in flight while tensors move
+                sent.append(("send", [n for n, _ in it], args))
+
+        params = [("model.a.weight", torch.zeros(4, 2)), ("model.b.weight", torch.zeros(3, dtype=torch.bfloat16))]
+        info = {"names": [n for n, _ in params], "dtype_names": ["torch.float32", "BFloat16".lower()],
+                "shapes": [[4, 2], [3]], "packed": True}
+        sync = VllmNcclSync(c, "127.0.0.1", 29999, 3, engine=FakeEngine, send_args=lambda **kw: kw)
+        out = sync.sync(params, info)
+        assert out["sent"] == 2 and out["bytes"] == 4 * 2 * 4 + 3 * 2 and out["server"]["ok"]
+        paths = [p for p, _ in calls]
+        assert paths == ["/init_weight_transfer_engine", "/pause?mode=wait", "/update_weights", "/resume"]
+        assert calls[0][1]["init_info"] == {"master_address": "127.0.0.1", "master_port": 29999, "rank_offset": 1,
+                                            "world_size": 3}
+        upd = calls[2][1]["update_info"]
+        assert upd["dtype_names"] == ["float32", "bfloat16"] and upd["is_checkpoint_format"] is True
+        assert sent[0] == ("init", {"master_address": "127.0.0.1", "master_port": 29999, "world_size": 3})
+        assert sent[1][1] == ["model.a.weight", "model.b.weight"] and sent[1][2]["group"] == "group"
+        assert sent[1][2]["packed_buffer_size_bytes"] == 1 << 30 and sent[1][2]["packed_num_buffers"] == 2
+        calls.clear()
+        update_seen.clear()
+        sync.sync(params, info)                               # the group is opened once
+        assert [p for p, _ in calls] == ["/pause?mode=wait", "/update_weights", "/resume"]
+        assert normalize_dtype_name("torch.bfloat16") == "bfloat16" and normalize_dtype_name("Float") == "float32"
+    finally:
+        server.shutdown()
