@@ -1,0 +1,32 @@
+"""A Hugging Face dataset split on disk as prompt / answer JSONL."""
+import pytest
+
+
+
+def test_hf_dataset_split_to_prompt_answer_jsonl(tmp_path, capsys):
+    """A dataset snapshot on disk in the Hub's parquet layout (``<config>/<split>-0000i-of-0000n.parquet``) becomes
+    a prompt / answer JSONL that the native reader loads; ``None`` fields become empty strings, ``max_examples``
+    truncates, a missing field is an error that lists the keys."""
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+    from cverl_b200.cli import hf_dataset_download
+    from cverl_b200.data import download_hf_dataset, load_prompt_answer_jsonl
+    snap = tmp_path / "snap" / "main"
+    snap.mkdir(parents=True)
+    pq.write_table(pa.table({"question": ["What is 1+1?", "Ünïcode?"], "answer": ["#### 2", None]}),
+                   snap / "train-00000-of-00002.parquet")
+    pq.write_table(pa.table({"question": ["Third?"], "answer": ["#### 3"]}), snap / "train-00001-of-00002.parquet")
+    pq.write_table(pa.table({"question": ["test q"], "answer": ["t"]}), snap / "test-00000-of-00001.parquet")
+    out = tmp_path / "out" / "train.jsonl"
+    res = download_hf_dataset(str(tmp_path / "snap"), out, name="main", split="train")
+    assert res.rows == 3 and res.output_file == out
+    rows = load_prompt_answer_jsonl(out)
+    assert [r.prompt for r in rows] == ["What is 1+1?", "Ünïcode?", "Third?"] and rows[1].answer == ""
+    assert hf_dataset_download.main(["--dataset", str(tmp_path / "snap"), "--name", "main", "--split", "test",
+                                     "--output-file", str(tmp_path / "t.jsonl"), "--max-examples", "1"]) == 0
+    printed = capsys.readouterr().out
+    assert f"CVERL_HF_DATASET_FILE={tmp_path / 't.jsonl'}" in printed and "CVERL_HF_DATASET_ROWS=1" in printed
+    with pytest.raises(KeyError, match="available keys"):
+        download_hf_dataset(str(tmp_path / "snap"), tmp_path / "x.jsonl", name="main", prompt_field="prompt")
+    with pytest.raises(FileNotFoundError):
+        download_hf_dataset(str(tmp_path / "snap"), tmp_path / "x.jsonl", name="main", split="validation")
