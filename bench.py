@@ -300,6 +300,8 @@ def main():
         }
         if check is not None:
             out["check"] = check
+        from cverl_b200.utils import fallbacks
+        out["library_fallbacks"] = fallbacks.total()     # hot ops that left their native kernel (0 expected)
         if args.layers:
             out["invalid"] = "debug run with fewer layers"
         print(json.dumps(out))

@@ -51,5 +51,8 @@ def causal_attention(q, k, v, batch: int, seq: int, scale: float | None = None):
             from . import attention_native
             if attention_native.supported(q, k, v, seq):
                 return attention_native.causal_attention(q, k, v, batch, seq, scale)
+            from ..utils import fallbacks
+            fallbacks.note("causal_attention", f"dtype {q.dtype}, head dim {q.shape[-1]}, sequence length {seq}: the "
+                                               f"tcgen05 kernels take bf16, head dim 128 / 256, length % 128 == 0")
         return _sdpa(q, k, v, batch, seq, scale)
     return causal_attention_ref(q, k, v, batch, seq, scale)

@@ -221,6 +221,10 @@ class _GdnChunked(torch.autograd.Function):
                 else:
                     ctx.save_for_backward(q, k, v, beta, g, Vn, SsT.transpose(-1, -2), Sf)
                 return o, Sf
+        if q.is_cuda:
+            from ..utils import fallbacks
+            fallbacks.note("gated_delta_rule", f"dtype {q.dtype}, shape {tuple(q.shape)}, chunk {chunk}: the chunk "
+                                               f"kernels take bf16 [B, T, H, 128] with T % 64 == 0 read in place")
         ctx.native = False
         pad = (-T) % chunk
         n = (T + pad) // chunk

@@ -30,6 +30,9 @@ def count_launch(k: int = 1) -> None:
 
 
 def use_native(t: torch.Tensor) -> bool:
+    if t.is_cuda and t.dtype != torch.bfloat16 and not _FORCE_LIBRARY:
+        from ..utils import fallbacks
+        fallbacks.note("gemm", f"dtype {t.dtype}: the tcgen05 GEMM takes bf16 operands")
     return t.is_cuda and t.dtype == torch.bfloat16 and not _FORCE_LIBRARY
 
 

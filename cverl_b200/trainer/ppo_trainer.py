@@ -46,6 +46,7 @@ from ..parallel.pipeline import PipelineStage, pipeline_peers
 from ..parallel.dp_sync import TensorwiseOptimizer
 from ..parallel.zero import FlatZeroOptimizer
 from ..utils import checkpoint as ckpt
+from ..utils import fallbacks as _fallbacks
 from ..utils.metrics import MetricsCsv, format_line
 from ..utils.watchdog import Heartbeat, PeerFailure, Watchdog
 from .actor import ActorConfig, ActorEngine
@@ -719,6 +720,7 @@ def run(argv=None) -> int:
             "global_grad_norm": float(g[0, 5]), "grad_clip_scale": float(g[0, 6]),
             "param_delta_sum": float(g[:, 7].sum()), "all_ranks_have_grad": have_grad,
             "all_ranks_updated": updated, "any_rank_updated": any_updated,
+            "native_fallbacks": _fallbacks.total(),
         }
         exit_ok = exit_ok and have_grad and (args.skip_optimizer_step or any_updated)
         if rank == 0:

@@ -416,3 +416,29 @@ def test_gdn_gates_kernel(through_split):
     for k, tol in zip(range(5), (1e-5, 1e-5, 1e-2, 2e-2, 2e-2)):
         assert torch.isfinite(res[0][k]).all()
         assert _rel_err(res[0][k], res[1][k]) < tol, (k, _rel_err(res[0][k], res[1][k]))
+
+
+def test_library_fallbacks_are_counted_and_announced():
+    """A CUDA call that a native kernel cannot serve warns once per (op, reason), is counted every time, and is an
+    error under ``CVERL_B200_STRICT=1``."""
+    import os
+    import warnings
+    from cverl_b200.ops import attention
+    from cverl_b200.utils import fallbacks
+    fallbacks.reset()
+    q = torch.randn(96, 2, 128, device="cuda", dtype=torch.bfloat16)      # sequence length 96: not a multiple of 128
+    with warnings.catch_warnings(record=True) as seen:
+        warnings.simplefilter("always")
+        attention.causal_attention(q, q, q, 1, 96)
+        attention.causal_attention(q, q, q, 1, 96)
+    assert fallbacks.total() == 2 and len([w for w in seen if issubclass(w.category, fallbacks.NativeKernelFallback)]) == 1
+    os.environ["CVERL_B200_STRICT"] = "1"
+    try:
+        with pytest.raises(RuntimeError, match="STRICT"):
+            attention.causal_attention(q, q, q, 1, 96)
+    finally:
+        del os.environ["CVERL_B200_STRICT"]
+    fallbacks.reset()
+    ok = torch.randn(128, 2, 128, device="cuda", dtype=torch.bfloat16)
+    attention.causal_attention(ok, ok, ok, 1, 128)
+    assert fallbacks.total() == 0

@@ -59,3 +59,19 @@ def test_static_scratch_rejects_oversized_batch():
     rc = fn(x.data_ptr(), x.data_ptr(), x.data_ptr(), 1e-6, 1, x.data_ptr(), None, MAX_ROWS + 1, 1, nv.stream())
     assert rc == ERR_LIMIT                          # refused on the host: nothing was launched
     torch.cuda.synchronize()
+
+
+def test_static_scratch_at_its_exact_limit():
+    """``rows == 16384`` is the largest batch the fixed array holds: accepted, and correct to the last row."""
+    from cverl_b200 import _native as nv
+    from cverl_b200.ops import rl
+    fn = _entry()
+    rows, cols = MAX_ROWS, 8
+    rew, mask, gid = _case(rows, cols, 5, 8)
+    adv = torch.full((rows, cols), float("nan"), device="cuda")
+    rc = fn(rew.data_ptr(), mask.data_ptr(), gid.data_ptr(), 1e-6, 1, adv.data_ptr(), None, rows, cols, nv.stream())
+    assert rc == 0
+    ref_adv, _ = rl.fused_grpo_advantage(rew, mask, gid, 1e-6, True)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(adv, ref_adv, rtol=1e-6, atol=1e-6)
+    assert torch.isfinite(adv[-8:]).all()
