@@ -34,7 +34,7 @@ def test_trainer_cli_bf16_steps_checkpoint_resume(tmp_path):
         for key in ("loss_sum", "global_grad_norm", "step_time_s"):
             v = float(r[key])
             assert v == v and abs(v) < 1e9
-    assert (ck / "latest_checkpoint.txt").read_text() == "step_000002"
+    assert (ck / "latest_checkpoint.txt").read_text().strip() == "step_000002"
     resumed = _run("--steps", "4", "--resume-checkpoint", str(ck))
     assert [r["step"] for r in resumed] == ["2", "3"]
     assert float(resumed[0]["loss_sum"]) == pytest.approx(float(rows[2]["loss_sum"]), rel=2e-2, abs=1e-3)
