@@ -5,12 +5,19 @@ token (src/rollout/policy_worker.cc:99-102, O(N^2)).  Here ``prefill`` runs the 
 and keeps, per layer, either the rotated keys and the values (full attention) or the last
 ``conv_kernel-1`` pre-convolution rows plus the ``[dk, dv]`` recurrent state (Gated DeltaNet);
 ``decode_step`` then advances every sequence by one token with one token of compute.
+
+On a GPU with bf16 parameters the step runs on the native kernels (``decode_step_native``): tcgen05 GEMMs for
+every projection and the LM head, the fused norm / RoPE / gate kernels of training, ``cvb_decode_attention``
+(appends the token's key / value to the cache and attends over it, reading the length from device memory) and
+``cvb_gdn_decode_step`` (one read and one write of the recurrent state).  Nothing in that step depends on a
+host-side shape or scalar, so ``GraphedDecoder`` captures it once in a CUDA graph and replays it per token.
+The fp32 PyTorch statement below stays as the CPU path and the test oracle.
 """
 from __future__ import annotations
 
 import math
 from dataclasses import dataclass, field
-from typing import List
+from typing import List, Optional
 
 import torch
 import torch.nn.functional as F
@@ -24,6 +31,26 @@ from ..ops.norm import apply_rope_ref, rmsnorm_ref
 class DecodeState:
     length: int                      # tokens already in the caches
     layers: List[dict] = field(default_factory=list)
+    dev: Optional[dict] = None       # device-side step counters and tables of the native path
+
+    def to_native(self, model) -> None:
+        """Device copies of what the native step reads: the length after this step (int32 [1]), the position of
+        the new token per sequence (int32 [B]), the rotary tables up to the cache length."""
+        cfg = model.cfg
+        dev = model.flat.flat.device
+        max_len = max([c["k"].shape[1] for c in self.layers if "k" in c] or [self.length + 1])
+        B = next(iter(self.layers[0].values())).shape[0]
+        cos, sin = ops.rope_tables(max_len, cfg.rotary_dim, cfg.rope_theta, dev)
+        self.dev = {"len": torch.full((1,), self.length + 1, dtype=torch.int32, device=dev),
+                    "pos": torch.full((B,), self.length, dtype=torch.int32, device=dev), "cos": cos, "sin": sin,
+                    "max_len": max_len}
+        for c in self.layers:
+            if "state" in c:
+                c["state"] = c["state"].float().contiguous()
+            if "conv" in c:
+                c["conv"] = c["conv"].to(model.dtype).contiguous()
+            if "k" in c:
+                c["k"], c["v"] = c["k"].contiguous(), c["v"].contiguous()
 
 
 def _lin(x, w):
@@ -48,9 +75,22 @@ def prefill(model, prompt_ids: torch.Tensor, max_len: int):
     return DecodeState(S, caches), logits
 
 
+def native_decode_supported(model) -> bool:
+    cfg = model.cfg
+    p = model.flat.flat
+    return (p.is_cuda and p.dtype == torch.bfloat16 and model.ctx.tp_size == 1 and not cfg.is_qwen3_moe
+            and cfg.head_dim in (128, 256) and cfg.linear_key_head_dim == 128 and cfg.linear_value_head_dim == 128
+            and cfg.num_attention_heads // cfg.num_key_value_heads in (1, 2, 4, 8)
+            and model.first_stage and model.last_stage)
+
+
 @torch.no_grad()
 def decode_step(model, state: DecodeState, tokens: torch.Tensor) -> torch.Tensor:
     """Feeds one token per sequence; returns the logits ``[B, V]`` of the following token."""
+    if native_decode_supported(model) and tokens.is_cuda:
+        if state.dev is None:
+            state.to_native(model)
+        return decode_step_native(model, state, tokens)
     cfg = model.cfg
     B = tokens.shape[0]
     pos = state.length
@@ -133,3 +173,138 @@ def _linear_attention_step(model, x, i, c):
     o = (S * q.unsqueeze(-1)).sum(-2)
     y = rmsnorm_ref(o, model.param(p + "norm.weight"), cfg.rms_norm_eps, 0.0, gate=z.view(B, vh, vd))
     return _lin(y.reshape(B, value_dim), model.param(p + "out_proj.weight"))
+
+
+# ---------------------------------------------------------------------------------------------------------
+# native one-token step
+# ---------------------------------------------------------------------------------------------------------
+def _native_full_attention(model, x, i, c, dv):
+    from .. import _native as nv
+    from ..ops.gemm import count_launch
+    cfg = model.cfg
+    p = f"{cfg.layer_root}{i}.self_attn."
+    d, h, kvh = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+    B = x.shape[0]
+    qkv = ops.linear(x, model.fused[f"{i}.qkv"])                       # [B, h*d*2 + 2*kvh*d] bf16
+    q_all, k, v = qkv.split([h * d * 2, kvh * d, kvh * d], dim=-1)
+    q, gate = q_all.view(B, h, 2 * d).split([d, d], dim=-1)            # strided views into the projection
+    off = cfg.norm_weight_offset
+    q = ops.headnorm_rope(q, model.param(p + "q_norm.weight"), dv["cos"], dv["sin"], dv["pos"], cfg.rotary_dim,
+                          cfg.rms_norm_eps, off)
+    k = ops.headnorm_rope(k.view(B, kvh, d), model.param(p + "k_norm.weight"), dv["cos"], dv["sin"], dv["pos"],
+                          cfg.rotary_dim, cfg.rms_norm_eps, off)
+    v = v.contiguous().view(B, kvh, d)
+    o = torch.empty((B, h, d), dtype=x.dtype, device=x.device)
+    nv.check(nv.cuda().cvb_decode_attention(q.data_ptr(), q.stride(0), q.stride(1), k.data_ptr(), v.data_ptr(),
+                                            kvh * d, c["k"].data_ptr(), c["v"].data_ptr(), o.data_ptr(),
+                                            dv["len"].data_ptr(), B, c["k"].shape[1], h, kvh, d,
+                                            1.0 / math.sqrt(d), nv.status_word(x.device).data_ptr(), nv.stream()),
+             "cvb_decode_attention")
+    count_launch()
+    o = ops.siggate(o, gate)
+    return ops.linear(o.reshape(B, h * d), model.param(p + "o_proj.weight"))
+
+
+def _native_linear_attention(model, x, i, c):
+    from .. import _native as nv
+    from ..ops.gemm import count_launch
+    cfg = model.cfg
+    p = f"{cfg.layer_root}{i}.linear_attn."
+    kh, vh = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+    kd, vd = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+    key_dim, value_dim = kh * kd, vh * vd
+    conv_dim = 2 * key_dim + value_dim
+    B = x.shape[0]
+    proj = ops.linear(x, model.fused[f"{i}.lin_in"])                   # [B, conv_dim + value_dim + 2 vh]
+    mixed, z, b, a = proj.split([conv_dim, value_dim, vh, vh], dim=-1)
+    w = model.param(p + "conv1d.weight").view(conv_dim, cfg.linear_conv_kernel_dim)
+    window = torch.cat([c["conv"], mixed.unsqueeze(1)], dim=1)         # [B, KW, C] bf16
+    c["conv"].copy_(window[:, 1:])                                     # in place: the captured graph keeps the buffer
+    conv = F.silu((window.float() * w.float().t().unsqueeze(0)).sum(1)).to(x.dtype)   # [B, C]
+    o = torch.empty((B, vh, vd), dtype=x.dtype, device=x.device)
+    nv.check(nv.cuda().cvb_gdn_decode_step(conv.data_ptr(), conv.stride(0), kh, vh, b.data_ptr(), a.data_ptr(),
+                                           proj.stride(0), model.param(p + "A_log").data_ptr(),
+                                           model.param(p + "dt_bias").data_ptr(), c["state"].data_ptr(),
+                                           o.data_ptr(), B, nv.stream()), "cvb_gdn_decode_step")
+    count_launch()
+    y = ops.gated_rmsnorm(o, z, model.param(p + "norm.weight"), cfg.rms_norm_eps)
+    return ops.linear(y.reshape(B, value_dim), model.param(p + "out_proj.weight"))
+
+
+@torch.no_grad()
+def decode_step_native(model, state: DecodeState, tokens: torch.Tensor, advance: bool = True) -> torch.Tensor:
+    """One token per sequence on the native kernels; logits ``[B, V]`` fp32.  Every length / position is read
+    from ``state.dev`` on the device and advanced there, so the same launches serve every step."""
+    cfg = model.cfg
+    dv = state.dev
+    B = tokens.shape[0]
+    eps, off = cfg.rms_norm_eps, cfg.norm_weight_offset
+    delta = ops.embedding(tokens.view(B), model.param(cfg.embed_name))
+    resid = None
+    for li, i in enumerate(range(model.layer_begin, model.layer_end)):
+        p = f"{cfg.layer_root}{i}."
+        c = state.layers[li]
+        n1, resid = ops.add_rmsnorm(delta, resid, model.param(p + "input_layernorm.weight"), eps, off)
+        if cfg.layer_types[i] == "full_attention":
+            a = _native_full_attention(model, n1, i, c, dv)
+        else:
+            a = _native_linear_attention(model, n1, i, c)
+        n2, resid = ops.add_rmsnorm(a, resid, model.param(p + "post_attention_layernorm.weight"), eps, off)
+        delta = model.mlp(n2, i)
+    out, _ = ops.add_rmsnorm(delta, resid, model.param(cfg.final_norm_name), eps, off)
+    logits = ops.gemm_nt(out, model.lm_head_weight(), out_dtype=torch.float32)
+    if advance:
+        dv["len"] += 1
+        dv["pos"] += 1
+        state.length += 1
+    return logits
+
+
+class GraphedDecoder:
+    """The native decode step captured once in a CUDA graph and replayed per token.
+
+    ``step(tokens)`` copies the tokens into the graph's input buffer, replays, and returns the graph's logits
+    buffer (valid until the next ``step``).  The caches, the recurrent states, the length counter and the position
+    vector are the tensors of ``state``; the graph updates them in place.
+    """
+
+    def __init__(self, model, state: DecodeState, batch: int, warmup: int = 2):
+        if not native_decode_supported(model):
+            raise RuntimeError("the native decode path does not support this model / device")
+        if state.dev is None:
+            state.to_native(model)
+        self.model, self.state = model, state
+        dev = model.flat.flat.device
+        self.tokens = torch.zeros(batch, dtype=torch.long, device=dev)
+        # warm-up steps run for real on a side stream (lazy initialisation, allocator pools) and are then undone:
+        # the caches / states they touched are restored, the counters rewound
+        snapshot = [{k: v.clone() for k, v in c.items() if k in ("state", "conv")} for c in state.layers]
+        len0, pos0, host_len = state.dev["len"].clone(), state.dev["pos"].clone(), state.length
+        s = torch.cuda.Stream(device=dev)
+        s.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(s):
+            for _ in range(warmup):
+                decode_step_native(model, state, self.tokens)
+        torch.cuda.current_stream(dev).wait_stream(s)
+        self._restore(snapshot, len0, pos0, host_len)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = decode_step_native(model, state, self.tokens)
+        # capturing executed nothing, but the host-side counter moved: rewind it
+        state.length = host_len
+        self._restore(snapshot, len0, pos0, host_len)
+
+    def _restore(self, snapshot, len0, pos0, host_len) -> None:
+        for c, snap in zip(self.state.layers, snapshot):
+            for k, v in snap.items():
+                c[k].copy_(v)
+        self.state.dev["len"].copy_(len0)
+        self.state.dev["pos"].copy_(pos0)
+        self.state.length = host_len
+
+    @torch.no_grad()
+    def step(self, tokens: torch.Tensor) -> torch.Tensor:
+        self.tokens.copy_(tokens.view(-1))
+        self.graph.replay()
+        self.state.length += 1
+        return self.logits

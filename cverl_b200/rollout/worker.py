@@ -152,6 +152,11 @@ class CachedQwenRolloutWorker(RolloutWorker):
         finished = torch.zeros(B, dtype=torch.bool, device=dev)
         gen = _generator(dev, config.seed)
         state, logits = prefill(self.model, prompts, max_len=prompts.shape[1] + N)
+        graphed = None
+        if prompts.is_cuda and N > 4:
+            from ..models.decode import GraphedDecoder, native_decode_supported
+            if native_decode_supported(self.model):
+                graphed = GraphedDecoder(self.model, state, B)     # one CUDA graph replayed per token
         for step in range(N):
             tok, lp = sample_next_tokens(logits, config, gen)
             active = ~finished
@@ -164,5 +169,5 @@ class CachedQwenRolloutWorker(RolloutWorker):
                     if bool(finished.all()):
                         break
             if step + 1 < N:
-                logits = decode_step(self.model, state, tok)
+                logits = graphed.step(tok) if graphed is not None else decode_step(self.model, state, tok)
         return GenerationOutput(out, lps, lengths)

@@ -442,3 +442,38 @@ def test_library_fallbacks_are_counted_and_announced():
     ok = torch.randn(128, 2, 128, device="cuda", dtype=torch.bfloat16)
     attention.causal_attention(ok, ok, ok, 1, 128)
     assert fallbacks.total() == 0
+
+
+def test_native_cached_decode_matches_forward_and_fp32_step():
+    """Prefill + native one-token steps (tcgen05 GEMMs, decode attention over the cache, single-step scan state
+    update), eager and replayed from a CUDA graph, against (a) the logits of a full forward over the grown
+    sequence and (b) the fp32 PyTorch decode step on the same caches."""
+    from cverl_b200 import _native as nv
+    from cverl_b200.models import decode
+    from cverl_b200.models.config import Qwen35TextConfig
+    from cverl_b200.models.qwen3_5 import Qwen35Model
+    cfg = Qwen35TextConfig(vocab_size=2048, hidden_size=256, num_hidden_layers=4, num_attention_heads=4,
+                           num_key_value_heads=2, head_dim=256, intermediate_size=512, linear_key_head_dim=128,
+                           linear_value_head_dim=128, linear_num_key_heads=2, linear_num_value_heads=4)
+    dev = _dev()
+    model = Qwen35Model(cfg, dtype=torch.bfloat16, device=dev, with_main_grad=False)
+    model.init_weights(seed=9)
+    assert decode.native_decode_supported(model)
+    g = torch.Generator(device=dev).manual_seed(2)
+    B, P, N = 3, 128, 6
+    ids = torch.randint(1, cfg.vocab_size, (B, P + N), device=dev, generator=g)
+    with torch.no_grad():
+        full = model.forward_logits(ids).float()                       # [B, P+N, V]
+        for graphed in (False, True):
+            state, logits = decode.prefill(model, ids[:, :P], max_len=P + N)
+            assert _rel_err(logits, full[:, P - 1]) < 3e-2
+            runner = decode.GraphedDecoder(model, state, B) if graphed else None
+            for t in range(N - 1):
+                tok = ids[:, P + t]
+                logits = runner.step(tok) if graphed else decode.decode_step(model, state, tok)
+                assert state.length == P + t + 1
+                ref = full[:, P + t]
+                assert _rel_err(logits, ref) < 4e-2, (graphed, t, _rel_err(logits, ref))
+                assert (logits.argmax(-1) == ref.argmax(-1)).float().mean() >= 0.66
+            assert int(state.dev["len"]) == P + N and int(state.dev["pos"][0]) == P + N - 1
+    nv.check_status()
