@@ -104,7 +104,7 @@ _CUDA_PROTOS = {
     "cvb_attention_fwd": "ppppp l iiiii f i ll p p",
     "cvb_attention_bwd": "ppppp p pp ppp l iiiii f i ll p p",
     "cvb_decode_attention": "p ll pp l ppp p iiiii f p p",
-    "cvb_gdn_decode_step": "p l ii pp l pp pp i p",
+    "cvb_gdn_decode_step": "p l ii pp i p pp l pp pp i p",
     "cvb_router_topk_fwd": "p l iii pp p",
     "cvb_router_topk_bwd": "pppp l iii p p",
 }

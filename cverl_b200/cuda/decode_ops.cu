@@ -125,26 +125,54 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
 }
 
 // ---------------------------------------------------------------------------------------------------
-// Gated-DeltaNet single step: grid = (B, Hv), 128 threads; thread j owns column j (value dim) of the state
+// Gated-DeltaNet single step, with the depthwise causal convolution in front of it: grid = (B, Hv), 128
+// threads; thread j owns channel j of this head's q, k and v and column j (value dim) of the state
 // S [dk = 128, dv = 128] fp32 of (b, head), kept in registers for one read and one write:
-//   q^ = l2norm(q) / sqrt(dk), k^ = l2norm(k), beta = sigmoid(b), g = -exp(A_log) * softplus(a + dt_bias)
+//   x   = silu(sum_t w[c, t] * window[t, c])      window = the last KW - 1 raw rows (ring cache) + the new row
+//   q^  = l2norm(q) / sqrt(dk), k^ = l2norm(k), beta = sigmoid(b), g = -exp(A_log) * softplus(a + dt_bias)
 //   S *= e^g;  kv = S^T k^;  delta = (v - kv) beta;  S += k^ (x) delta;  o = S^T q^
-// q, k index the key head hv / (Hv / Hk); rows of qkv are [q heads | k heads | v heads] of one token.
+// `proj` rows are [q heads | k heads | v heads | ...] of one token (raw, before the convolution).  The ring cache
+// conv_ring [B, KW, C] holds raw rows; the row of token t lives in slot t % KW, so a step only WRITES slot
+// (len - 1) % KW - which nobody reads during this step (everyone takes the new row from `proj`) - and reads the
+// other KW - 1 slots.  q / k channels are shared by the Hv / Hk value heads of a key head: the first of them
+// writes their slot.  len = sequence length including the new token, read from device memory.
 // ---------------------------------------------------------------------------------------------------
+template <int KW>
 __global__ void __launch_bounds__(128)
-gdn_decode_step_kernel(const __nv_bfloat16* __restrict__ qkv, long long qkv_stride, int Hk, int Hv,
-                       const __nv_bfloat16* __restrict__ bgate, const __nv_bfloat16* __restrict__ agate,
-                       long long gate_stride, const __nv_bfloat16* __restrict__ A_log,
-                       const __nv_bfloat16* __restrict__ dt_bias, float* __restrict__ state,
-                       __nv_bfloat16* __restrict__ out) {
+gdn_decode_step_kernel(const __nv_bfloat16* __restrict__ proj, long long proj_stride, int Hk, int Hv,
+                       const __nv_bfloat16* __restrict__ conv_w, __nv_bfloat16* __restrict__ conv_ring,
+                       const int* __restrict__ len_ptr, const __nv_bfloat16* __restrict__ bgate,
+                       const __nv_bfloat16* __restrict__ agate, long long gate_stride,
+                       const __nv_bfloat16* __restrict__ A_log, const __nv_bfloat16* __restrict__ dt_bias,
+                       float* __restrict__ state, __nv_bfloat16* __restrict__ out) {
   constexpr int DK = 128, DV = 128;
   const int b = blockIdx.x, hv = blockIdx.y, j = threadIdx.x;
-  const int hk = hv / (Hv / Hk);
-  const __nv_bfloat16* row = qkv + static_cast<long long>(b) * qkv_stride;
+  const int rep = Hv / Hk;
+  const int hk = hv / rep;
+  const int C = 2 * Hk * DK + Hv * DV;
+  const int t = *len_ptr - 1;                      // index of the new token
+  const __nv_bfloat16* row = proj + static_cast<long long>(b) * proj_stride;
+  __nv_bfloat16* ring = conv_ring + static_cast<long long>(b) * KW * C;
+  const int ch[3] = {hk * DK + j, Hk * DK + hk * DK + j, 2 * Hk * DK + hv * DV + j};
+  float x[3];
+#pragma unroll
+  for (int s = 0; s < 3; ++s) {
+    const int c = ch[s];
+    const __nv_bfloat16 fresh = row[c];
+    float acc = __bfloat162float(conv_w[static_cast<long long>(c) * KW + (KW - 1)]) * __bfloat162float(fresh);
+#pragma unroll
+    for (int d = 1; d < KW; ++d) {                // token t - d, weight tap KW - 1 - d (tokens before 0 are zero)
+      if (t - d >= 0)
+        acc += __bfloat162float(conv_w[static_cast<long long>(c) * KW + (KW - 1 - d)]) *
+               __bfloat162float(ring[static_cast<long long>(((t - d) % KW)) * C + c]);
+    }
+    x[s] = acc / (1.f + __expf(-acc));
+    if (s == 2 || hv % rep == 0) ring[static_cast<long long>(t % KW) * C + c] = fresh;
+  }
   __shared__ float sq[DK], sk[DK], red[8];
-  const float qr = __bfloat162float(row[hk * DK + j]);
-  const float kr = __bfloat162float(row[static_cast<long long>(Hk) * DK + hk * DK + j]);
-  const float vr = __bfloat162float(row[2LL * Hk * DK + static_cast<long long>(hv) * DV + j]);
+  const float qr = __bfloat162float(__float2bfloat16_rn(x[0]));   // the training path rounds the conv output to bf16
+  const float kr = __bfloat162float(__float2bfloat16_rn(x[1]));
+  const float vr = __bfloat162float(__float2bfloat16_rn(x[2]));
   // two block-wide sums of squares (q and k) through warp shuffles and shared memory
   float s1 = qr * qr, s2 = kr * kr;
 #pragma unroll
@@ -210,14 +238,27 @@ extern "C" int cvb_decode_attention(const void* q, long long q_stride, long long
   return -2;  // head dim / group size without an instantiation
 }
 
-extern "C" int cvb_gdn_decode_step(const void* qkv, long long qkv_stride, int Hk, int Hv, const void* bgate,
-                                   const void* agate, long long gate_stride, const void* A_log, const void* dt_bias,
-                                   float* state, void* out, int B, void* stream) {
-  if (!qkv || !bgate || !agate || !A_log || !dt_bias || !state || !out || B <= 0 || Hk <= 0 || Hv % Hk) return -1;
+// proj: [B, >= 2*Hk*128 + Hv*128] raw projection rows; conv_w [C, KW] bf16; conv_ring [B, KW, C] bf16 (slot of token
+// t is t % KW); bgate / agate: per-head gate inputs with row stride gate_stride; state [B, Hv, 128, 128] fp32.
+extern "C" int cvb_gdn_decode_step(const void* proj, long long proj_stride, int Hk, int Hv, const void* conv_w,
+                                   void* conv_ring, int KW, const int* len_ptr, const void* bgate, const void* agate,
+                                   long long gate_stride, const void* A_log, const void* dt_bias, float* state,
+                                   void* out, int B, void* stream) {
+  if (!proj || !conv_w || !conv_ring || !len_ptr || !bgate || !agate || !A_log || !dt_bias || !state || !out ||
+      B <= 0 || Hk <= 0 || Hv % Hk)
+    return -1;
   dim3 grid(B, Hv);
-  gdn_decode_step_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(qkv), qkv_stride, Hk, Hv, static_cast<const __nv_bfloat16*>(bgate),
-      static_cast<const __nv_bfloat16*>(agate), gate_stride, static_cast<const __nv_bfloat16*>(A_log),
-      static_cast<const __nv_bfloat16*>(dt_bias), state, static_cast<__nv_bfloat16*>(out));
-  return static_cast<int>(cudaGetLastError());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define CVB_GDS(KW_)                                                                                             \
+  if (KW == KW_) {                                                                                               \
+    gdn_decode_step_kernel<KW_><<<grid, 128, 0, st>>>(                                                           \
+        static_cast<const __nv_bfloat16*>(proj), proj_stride, Hk, Hv, static_cast<const __nv_bfloat16*>(conv_w), \
+        static_cast<__nv_bfloat16*>(conv_ring), len_ptr, static_cast<const __nv_bfloat16*>(bgate),               \
+        static_cast<const __nv_bfloat16*>(agate), gate_stride, static_cast<const __nv_bfloat16*>(A_log),         \
+        static_cast<const __nv_bfloat16*>(dt_bias), state, static_cast<__nv_bfloat16*>(out));                    \
+    return static_cast<int>(cudaGetLastError());                                                                 \
+  }
+  CVB_GDS(4) CVB_GDS(3) CVB_GDS(2)
+#undef CVB_GDS
+  return -2;
 }

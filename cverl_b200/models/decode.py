@@ -48,7 +48,16 @@ class DecodeState:
             if "state" in c:
                 c["state"] = c["state"].float().contiguous()
             if "conv" in c:
-                c["conv"] = c["conv"].to(model.dtype).contiguous()
+                # ring cache of raw pre-convolution rows: the row of token t lives in slot t % KW.  The prefill
+                # left the last KW - 1 rows (tokens length-KW+1 .. length-1) in order.
+                kw = cfg.linear_conv_kernel_dim
+                tail = c["conv"].to(model.dtype)
+                ring = torch.zeros((tail.shape[0], kw, tail.shape[2]), dtype=model.dtype, device=dev)
+                for r in range(kw - 1):
+                    tok = self.length - (kw - 1) + r
+                    if tok >= 0:
+                        ring[:, tok % kw] = tail[:, r]
+                c["conv_ring"] = ring.contiguous()
             if "k" in c:
                 c["k"], c["v"] = c["k"].contiguous(), c["v"].contiguous()
 
@@ -193,10 +202,12 @@ def _native_full_attention(model, x, i, c, dv):
                           cfg.rms_norm_eps, off)
     k = ops.headnorm_rope(k.view(B, kvh, d), model.param(p + "k_norm.weight"), dv["cos"], dv["sin"], dv["pos"],
                           cfg.rotary_dim, cfg.rms_norm_eps, off)
-    v = v.contiguous().view(B, kvh, d)
     o = torch.empty((B, h, d), dtype=x.dtype, device=x.device)
+    if k.stride(0) != v.stride(0):           # the kernel takes one row stride for the new key and value
+        v = v.contiguous()
+        k = k.contiguous()
     nv.check(nv.cuda().cvb_decode_attention(q.data_ptr(), q.stride(0), q.stride(1), k.data_ptr(), v.data_ptr(),
-                                            kvh * d, c["k"].data_ptr(), c["v"].data_ptr(), o.data_ptr(),
+                                            k.stride(0), c["k"].data_ptr(), c["v"].data_ptr(), o.data_ptr(),
                                             dv["len"].data_ptr(), B, c["k"].shape[1], h, kvh, d,
                                             1.0 / math.sqrt(d), nv.status_word(x.device).data_ptr(), nv.stream()),
              "cvb_decode_attention")
@@ -205,7 +216,7 @@ def _native_full_attention(model, x, i, c, dv):
     return ops.linear(o.reshape(B, h * d), model.param(p + "o_proj.weight"))
 
 
-def _native_linear_attention(model, x, i, c):
+def _native_linear_attention(model, x, i, c, dv):
     from .. import _native as nv
     from ..ops.gemm import count_launch
     cfg = model.cfg
@@ -217,13 +228,12 @@ def _native_linear_attention(model, x, i, c):
     B = x.shape[0]
     proj = ops.linear(x, model.fused[f"{i}.lin_in"])                   # [B, conv_dim + value_dim + 2 vh]
     mixed, z, b, a = proj.split([conv_dim, value_dim, vh, vh], dim=-1)
-    w = model.param(p + "conv1d.weight").view(conv_dim, cfg.linear_conv_kernel_dim)
-    window = torch.cat([c["conv"], mixed.unsqueeze(1)], dim=1)         # [B, KW, C] bf16
-    c["conv"].copy_(window[:, 1:])                                     # in place: the captured graph keeps the buffer
-    conv = F.silu((window.float() * w.float().t().unsqueeze(0)).sum(1)).to(x.dtype)   # [B, C]
     o = torch.empty((B, vh, vd), dtype=x.dtype, device=x.device)
-    nv.check(nv.cuda().cvb_gdn_decode_step(conv.data_ptr(), conv.stride(0), kh, vh, b.data_ptr(), a.data_ptr(),
-                                           proj.stride(0), model.param(p + "A_log").data_ptr(),
+    # convolution (ring cache of raw rows) + SiLU + l2norm + gates + state update + read-out: one kernel
+    nv.check(nv.cuda().cvb_gdn_decode_step(proj.data_ptr(), proj.stride(0), kh, vh,
+                                           model.param(p + "conv1d.weight").data_ptr(), c["conv_ring"].data_ptr(),
+                                           cfg.linear_conv_kernel_dim, dv["len"].data_ptr(), b.data_ptr(),
+                                           a.data_ptr(), proj.stride(0), model.param(p + "A_log").data_ptr(),
                                            model.param(p + "dt_bias").data_ptr(), c["state"].data_ptr(),
                                            o.data_ptr(), B, nv.stream()), "cvb_gdn_decode_step")
     count_launch()
@@ -248,7 +258,7 @@ def decode_step_native(model, state: DecodeState, tokens: torch.Tensor, advance:
         if cfg.layer_types[i] == "full_attention":
             a = _native_full_attention(model, n1, i, c, dv)
         else:
-            a = _native_linear_attention(model, n1, i, c)
+            a = _native_linear_attention(model, n1, i, c, dv)
         n2, resid = ops.add_rmsnorm(a, resid, model.param(p + "post_attention_layernorm.weight"), eps, off)
         delta = model.mlp(n2, i)
     out, _ = ops.add_rmsnorm(delta, resid, model.param(cfg.final_norm_name), eps, off)
@@ -278,7 +288,7 @@ class GraphedDecoder:
         self.tokens = torch.zeros(batch, dtype=torch.long, device=dev)
         # warm-up steps run for real on a side stream (lazy initialisation, allocator pools) and are then undone:
         # the caches / states they touched are restored, the counters rewound
-        snapshot = [{k: v.clone() for k, v in c.items() if k in ("state", "conv")} for c in state.layers]
+        snapshot = [{k: v.clone() for k, v in c.items() if k in ("state", "conv_ring")} for c in state.layers]
         len0, pos0, host_len = state.dev["len"].clone(), state.dev["pos"].clone(), state.length
         s = torch.cuda.Stream(device=dev)
         s.wait_stream(torch.cuda.current_stream(dev))
