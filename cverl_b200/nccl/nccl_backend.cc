@@ -37,6 +37,7 @@ struct Comm {
   cudaEvent_t done = nullptr;    // communicator stream -> caller's stream
   int rank = 0, world = 1, device = 0;
   bool sync_after_op = true;
+  bool owns_stream = true;       // false: the stream was lent by the caller and outlives the communicator
 };
 
 #define CVN_CUDA(expr)                                                            \
@@ -92,14 +93,16 @@ int leave(Comm* c, cudaStream_t caller) {
   return 0;
 }
 
-Comm* finish_create(ncclComm_t comm, int rank, int world, int device, bool sync_after_op) {
+Comm* finish_create(ncclComm_t comm, int rank, int world, int device, bool sync_after_op, cudaStream_t lent) {
   Comm* c = new Comm;
+  c->stream = lent;
+  c->owns_stream = lent == nullptr;
   c->comm = comm;
   c->rank = rank;
   c->world = world;
   c->device = device;
   c->sync_after_op = sync_after_op;
-  if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
+  if ((c->owns_stream && cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) ||
       cudaEventCreateWithFlags(&c->ready, cudaEventDisableTiming) != cudaSuccess ||
       cudaEventCreateWithFlags(&c->done, cudaEventDisableTiming) != cudaSuccess) {
     g_err = "cannot create the communicator's stream / events";
@@ -152,7 +155,9 @@ int cvn_unique_id_read_file(const char* path, unsigned char* id128, int polls, i
   return -2;
 }
 
-void* cvn_comm_create(int rank, int world, int device, const unsigned char* id128, int sync_after_op) {
+// `stream`: a non-blocking stream lent by the caller for the communicator's lifetime and longer (a framework's
+// pooled stream, which an allocator may still touch after the communicator is gone), or null to own one.
+void* cvn_comm_create(int rank, int world, int device, const unsigned char* id128, int sync_after_op, void* stream) {
   if (rank < 0 || world <= 0 || rank >= world) {
     g_err = "rank out of range";
     return nullptr;
@@ -169,12 +174,12 @@ void* cvn_comm_create(int rank, int world, int device, const unsigned char* id12
     g_err = std::string("ncclCommInitRank: ") + ncclGetErrorString(r);
     return nullptr;
   }
-  return finish_create(comm, rank, world, device, sync_after_op != 0);
+  return finish_create(comm, rank, world, device, sync_after_op != 0, static_cast<cudaStream_t>(stream));
 }
 
 // Collective over the parent: members of one sub-group pass the same `color` (>= 0) and their index as `key`;
 // a rank outside every group passes color -1 and gets a null handle.
-void* cvn_comm_split(void* parent, int color, int key, int new_world) {
+void* cvn_comm_split(void* parent, int color, int key, int new_world, void* stream) {
   Comm* p = static_cast<Comm*>(parent);
   if (!p) return nullptr;
   cudaSetDevice(p->device);
@@ -185,7 +190,7 @@ void* cvn_comm_split(void* parent, int color, int key, int new_world) {
     return nullptr;
   }
   if (color < 0 || sub == nullptr) return nullptr;
-  return finish_create(sub, key, new_world, p->device, p->sync_after_op);
+  return finish_create(sub, key, new_world, p->device, p->sync_after_op, static_cast<cudaStream_t>(stream));
 }
 
 int cvn_comm_destroy(void* h) {
@@ -196,7 +201,7 @@ int cvn_comm_destroy(void* h) {
   ncclCommDestroy(c->comm);
   cudaEventDestroy(c->ready);
   cudaEventDestroy(c->done);
-  cudaStreamDestroy(c->stream);
+  if (c->owns_stream) cudaStreamDestroy(c->stream);
   delete c;
   return 0;
 }

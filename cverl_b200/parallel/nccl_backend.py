@@ -1,7 +1,7 @@
 """``NcclCollectives``: the framework's own NCCL backend behind the ``Collectives`` interface.
 
 One native communicator (``nccl/nccl_backend.cc``) per instance, with a dedicated non-blocking CUDA
-stream; rendezvous through a file that holds the NCCL unique id, so that processes started by
+stream (taken from torch's stream pool and lent to the native layer); rendezvous through a file that holds the NCCL unique id, so that processes started by
 any launcher - or by none - can form a communicator (the reference:
 src/distributed/nccl_collectives.cc:156-196).  Two completion modes, as in the reference
 (:278-312): ``sync_after_op=True`` waits on the host after every operation; the default async mode
@@ -43,9 +43,9 @@ def library():
         lib = C.CDLL(str(path))
         lib.cvn_last_error.restype = C.c_char_p
         lib.cvn_comm_create.restype = C.c_void_p
-        lib.cvn_comm_create.argtypes = [C.c_int, C.c_int, C.c_int, C.c_char_p, C.c_int]
+        lib.cvn_comm_create.argtypes = [C.c_int, C.c_int, C.c_int, C.c_char_p, C.c_int, C.c_void_p]
         lib.cvn_comm_split.restype = C.c_void_p
-        lib.cvn_comm_split.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int]
+        lib.cvn_comm_split.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
         lib.cvn_comm_destroy.argtypes = [C.c_void_p]
         lib.cvn_comm_stream.restype = C.c_void_p
         lib.cvn_comm_stream.argtypes = [C.c_void_p]
@@ -92,7 +92,7 @@ def read_unique_id_file(path: str, timeout_s: float = 5.0, poll_ms: int = 25) ->
 class NcclCollectives(Collectives):
     def __init__(self, rank: int, world_size: int, device, unique_id: Optional[bytes] = None,
                  id_file: Optional[str] = None, sync_after_op: bool = False, id_timeout_s: float = 5.0,
-                 _handle=None, _global_ranks: Optional[Sequence[int]] = None):
+                 _handle=None, _global_ranks: Optional[Sequence[int]] = None, _stream=None):
         """``unique_id`` (bytes from ``create_unique_id`` of rank 0) or ``id_file``: rank 0 creates the id and
         writes the file, the others poll for it."""
         self._lib = library()
@@ -102,6 +102,10 @@ class NcclCollectives(Collectives):
         self._sync = sync_after_op
         self._global_ranks = list(_global_ranks) if _global_ranks is not None else list(range(world_size))
         self._children: Dict[Tuple[int, ...], Optional["NcclCollectives"]] = {}
+        # The communicator's stream comes from torch's pool and is lent to the native layer: the caching
+        # allocator records events on it when a tensor registered by ``record_stream`` is freed, which may be
+        # after ``close()``, so the stream must never be destroyed.
+        self._stream = _stream if _stream is not None else torch.cuda.Stream(device=self.device)
         if _handle is not None:
             self._h = _handle
         else:
@@ -114,10 +118,10 @@ class NcclCollectives(Collectives):
                 else:
                     unique_id = read_unique_id_file(id_file, id_timeout_s)
             idx = self.device.index if self.device.index is not None else torch.cuda.current_device()
-            self._h = self._lib.cvn_comm_create(rank, world_size, idx, unique_id, int(sync_after_op))
+            self._h = self._lib.cvn_comm_create(rank, world_size, idx, unique_id, int(sync_after_op),
+                                                self._stream.cuda_stream)
             if not self._h:
                 raise RuntimeError("NCCL communicator: " + self._lib.cvn_last_error().decode())
-        self._stream = torch.cuda.ExternalStream(self._lib.cvn_comm_stream(self._h), device=self.device)
         self._scratch = torch.zeros(1, dtype=torch.float32, device=self.device)
 
     # ---- interface ----------------------------------------------------------------------------------------
@@ -176,13 +180,15 @@ class NcclCollectives(Collectives):
                 for r in ranks:
                     h = ((h ^ (r & 0xFFFFFFFF)) * 16777619) & 0x7FFFFFFF
                 color, key = h, ranks.index(me)
-            handle = self._lib.cvn_comm_split(self._h, color, key, len(ranks))
+            stream = torch.cuda.Stream(device=self.device) if color >= 0 else None
+            handle = self._lib.cvn_comm_split(self._h, color, key, len(ranks),
+                                              stream.cuda_stream if stream is not None else None)
             child = None
             if color >= 0:
                 if not handle:
                     raise RuntimeError("ncclCommSplit: " + self._lib.cvn_last_error().decode())
                 child = NcclCollectives(key, len(ranks), self.device, sync_after_op=self._sync, _handle=handle,
-                                        _global_ranks=ranks)
+                                        _global_ranks=ranks, _stream=stream)
                 child._root_world = self.world_size()
             self._children[ranks] = child
         if child is None:
