@@ -96,6 +96,7 @@ _CUDA_PROTOS = {
     "cvb_gdn_scan_bwd": "pppppppppp l ii p p",
     "cvb_symm_barrier": "p iii p p",
     "cvb_reduce_scatter_sumsq": "p ii ll f pp p",
+    "cvb_reduce_scatter_acc": "p ii ll f p ii p",
     "cvb_flat_adamw_allgather": "ppppp p ii ll fffff l p",
     "cvb_broadcast_store": "pp i l p",
     "cvb_sum_parts": "p l i p l p",

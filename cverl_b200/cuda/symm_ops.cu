@@ -6,6 +6,8 @@
 //  * reduce_scatter_sumsq   ZeRO gradient reduce-scatter: each rank pulls its shard of every peer's
 //                           flat fp32 gradient, sums, scales (mean) and accumulates the squared norm
 //                           for global-norm clipping, in one pass
+//  * reduce_scatter_acc     bucketed ZeRO-2: the same pull, accumulated into the shard gradient, the reader clearing
+//                           the source so that the bucket buffer can be reused
 //  * flat_adamw_allgather   FlatAdamW on the local shard whose bf16 result is stored straight into
 //                           every peer's parameter buffer: the parameter all-gather rides on the
 //                           optimizer's own stores
@@ -65,12 +67,18 @@ reduce_scatter_sumsq_kernel(PeerPtrs grads, int world, int rank, long long begin
   const long long nv = n / 4;
   for (long long i = static_cast<long long>(blockIdx.x) * SY_THREADS + threadIdx.x; i < nv;
        i += static_cast<long long>(gridDim.x) * SY_THREADS) {
+    float4 v[MAX_PEERS];               // start at home, then walk the peers; all loads issued before the first add
+#pragma unroll
+    for (int k = 0; k < MAX_PEERS; ++k) {
+      if (k < world) {
+        const int p = (rank + k) % world;
+        v[k] = *reinterpret_cast<const float4*>(static_cast<const float*>(grads.p[p]) + begin + i * 4);
+      }
+    }
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 1
-    for (int k = 0; k < world; ++k) {
-      const int p = (rank + k) % world;  // start at home, then walk the peers
-      const float4 v = *reinterpret_cast<const float4*>(static_cast<const float*>(grads.p[p]) + begin + i * 4);
-      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+#pragma unroll
+    for (int k = 0; k < MAX_PEERS; ++k) {
+      if (k < world) { s.x += v[k].x; s.y += v[k].y; s.z += v[k].z; s.w += v[k].w; }
     }
     s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
     *reinterpret_cast<float4*>(out + i * 4) = s;
@@ -83,6 +91,42 @@ reduce_scatter_sumsq_kernel(PeerPtrs grads, int world, int rank, long long begin
     float r = threadIdx.x < SY_THREADS / 32 ? sh[threadIdx.x] : 0.f;
     r = warp_sum(r);
     if (threadIdx.x == 0) atomicAdd(sq, r);
+  }
+}
+
+// Bucketed ZeRO-2: out[i] += scale * sum_p grads[p][begin + i]; with zero_src the reader also clears what it read
+// (every element of a gradient bucket is read by exactly one rank, its owner, so the clear needs no second pass
+// on the source GPU - only the barrier that tells it the bucket buffer is free again).
+__global__ void __launch_bounds__(SY_THREADS)
+reduce_scatter_acc_kernel(PeerPtrs grads, int world, int rank, long long begin, long long n, float scale,
+                          float* __restrict__ out, int zero_src) {
+  const long long nv = n / 4;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (long long i = static_cast<long long>(blockIdx.x) * SY_THREADS + threadIdx.x; i < nv;
+       i += static_cast<long long>(gridDim.x) * SY_THREADS) {
+    // all peers' loads are issued before the first use: eight independent 16-byte requests in flight per thread
+    float4 v[MAX_PEERS];
+#pragma unroll
+    for (int k = 0; k < MAX_PEERS; ++k) {
+      if (k < world) {
+        const int p = (rank + k) % world;
+        v[k] = *reinterpret_cast<const float4*>(static_cast<const float*>(grads.p[p]) + begin + i * 4);
+      }
+    }
+    float4 s = zero;
+#pragma unroll
+    for (int k = 0; k < MAX_PEERS; ++k) {
+      if (k < world) {
+        s.x += v[k].x; s.y += v[k].y; s.z += v[k].z; s.w += v[k].w;
+        if (zero_src) {
+          const int p = (rank + k) % world;
+          *reinterpret_cast<float4*>(static_cast<float*>(grads.p[p]) + begin + i * 4) = zero;
+        }
+      }
+    }
+    float4 o = *reinterpret_cast<const float4*>(out + i * 4);
+    o.x += s.x * scale; o.y += s.y * scale; o.z += s.z * scale; o.w += s.w * scale;
+    *reinterpret_cast<float4*>(out + i * 4) = o;
   }
 }
 
@@ -211,6 +255,17 @@ extern "C" int cvb_reduce_scatter_sumsq(void* const* grad_ptrs, int world, int r
   if (!fill(&g, grad_ptrs, world) || n % 4 || begin % 4) return -1;
   if (n == 0) return 0;
   reduce_scatter_sumsq_kernel<<<sy_grid(n / 4), SY_THREADS, 0, ST(stream)>>>(g, world, rank, begin, n, scale, out, sq);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int cvb_reduce_scatter_acc(void* const* grad_ptrs, int world, int rank, long long begin, long long n,
+                                      float scale, float* out, int zero_src, int max_blocks, void* stream) {
+  PeerPtrs g;
+  if (!fill(&g, grad_ptrs, world) || n % 4 || begin % 4 || (reinterpret_cast<uintptr_t>(out) & 15)) return -1;
+  if (n == 0) return 0;
+  int grid = sy_grid(n / 4);
+  if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;   // leave SMs to the backward pass it overlaps
+  reduce_scatter_acc_kernel<<<grid, SY_THREADS, 0, ST(stream)>>>(g, world, rank, begin, n, scale, out, zero_src);
   return static_cast<int>(cudaGetLastError());
 }
 

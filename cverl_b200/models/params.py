@@ -173,20 +173,38 @@ class FlatParams:
     sum of the entry sizes and ``padded_numel`` rounds it up to a multiple of
     ``pad_multiple`` (the data-parallel size, times the vector width the fused
     optimizer wants).
+
+    ``grad_buckets`` (one non-decreasing bucket id per entry) switches the gradient storage from a
+    full-size twin to per-bucket buffers, for an optimizer that reduces a bucket as soon as the
+    backward pass has finished with it: every bucket starts on a multiple of ``bucket_align``
+    elements, the buckets named in ``pinned_buckets`` own a buffer each (gradients that arrive
+    throughout the pass: embedding, head), and the others take turns on ``grad_slots`` buffers
+    of the largest bucket's size (bucket b uses slot ``b % grad_slots``).  ``main_grad`` is then
+    None; ``bucket_grad(b)`` is bucket b's fp32 buffer and each parameter's ``main_grad`` a view of it.
     """
 
     def __init__(self, entries: Sequence[Tuple[str, Tuple[int, ...]]], dtype=torch.bfloat16, device="cpu",
-                 pad_multiple: int = 1, with_main_grad: bool = True, entry_align: int = 8, allocator=None):
+                 pad_multiple: int = 1, with_main_grad: bool = True, entry_align: int = 8, allocator=None,
+                 grad_buckets: Optional[Sequence[int]] = None, bucket_align: int = 8, grad_slots: int = 2,
+                 pinned_buckets: Sequence[int] = ()):
         # Entries start on a 16-byte boundary (8 bf16 elements) so that vector loads and TMA can
         # address every tensor in place.  Every tensor of the shipped model shapes has a multiple
         # of 8 elements, for which this is exactly the gap-free concatenation of the reference.
         self.entries = [(n, tuple(s)) for n, s in entries]
         self.offsets: Dict[str, Tuple[int, int]] = {}
+        if grad_buckets is not None:
+            if len(grad_buckets) != len(self.entries) or any(b < a for a, b in zip(grad_buckets, grad_buckets[1:])):
+                raise ValueError("grad_buckets needs one non-decreasing bucket id per entry")
+            pad_multiple = _align(pad_multiple, bucket_align)
         off = 0
-        for name, shape in self.entries:
+        starts: List[Tuple[int, int]] = []              # (bucket id, first element)
+        for k, (name, shape) in enumerate(self.entries):
             n = 1
             for s in shape:
                 n *= s
+            if grad_buckets is not None and (k == 0 or grad_buckets[k] != grad_buckets[k - 1]):
+                off = _align(off, bucket_align)
+                starts.append((grad_buckets[k], off))
             self.offsets[name] = (off, n)
             off += _align(n, entry_align) if entry_align > 1 else n
         self.numel = off
@@ -195,15 +213,69 @@ class FlatParams:
         # peer-mapped memory for the symmetric-memory ZeRO path (parameters first, then gradients)
         alloc = allocator or (lambda n, dt: torch.zeros(n, dtype=dt, device=device))
         self.flat = alloc(self.padded_numel, dtype)
-        self.main_grad = alloc(self.padded_numel, torch.float32) if with_main_grad else None
+        self.main_grad = None
+        self.bucket_ids: List[int] = []
+        self.bucket_ranges: Dict[int, Tuple[int, int]] = {}
+        self._bucket_buf: Dict[int, torch.Tensor] = {}
+        self.grad_slot_of: Dict[int, int] = {}          # rotating buckets only
+        self.grad_buffers: List[torch.Tensor] = []      # every gradient allocation, in allocation order
+        if grad_buckets is None:
+            self.main_grad = alloc(self.padded_numel, torch.float32) if with_main_grad else None
+        elif with_main_grad:
+            for k, (b, begin) in enumerate(starts):
+                end = starts[k + 1][1] if k + 1 < len(starts) else self.padded_numel
+                self.bucket_ids.append(b)
+                self.bucket_ranges[b] = (begin, end)
+            pinned = set(pinned_buckets)
+            rotating = [b for b in self.bucket_ids if b not in pinned]
+            slot_len = max((self.bucket_ranges[b][1] - self.bucket_ranges[b][0] for b in rotating), default=0)
+            n_slots = min(max(grad_slots, 1), len(rotating)) if rotating else 0
+            slots = [alloc(slot_len, torch.float32) for _ in range(n_slots)]
+            self.grad_buffers += slots
+            for b in self.bucket_ids:
+                lo, hi = self.bucket_ranges[b]
+                if b in pinned:
+                    self._bucket_buf[b] = alloc(hi - lo, torch.float32)
+                    self.grad_buffers.append(self._bucket_buf[b])
+                else:
+                    self.grad_slot_of[b] = b % n_slots
+                    self._bucket_buf[b] = slots[b % n_slots][:hi - lo]
+        self._with_grad = with_main_grad
         self.params: Dict[str, torch.nn.Parameter] = {}
         for name, shape in self.entries:
             self.params[name] = self._make_param(name, *self.offsets[name], shape)
 
+    @property
+    def bucketed(self) -> bool:
+        return bool(self.bucket_ids)
+
+    def bucket_grad(self, b: int) -> torch.Tensor:
+        """Bucket b's fp32 gradient buffer (its slot's first ``end - begin`` elements)."""
+        return self._bucket_buf[b]
+
+    def bucket_of_offset(self, off: int) -> int:
+        for b in self.bucket_ids:
+            lo, hi = self.bucket_ranges[b]
+            if lo <= off < hi:
+                return b
+        raise ValueError(f"offset {off} is outside every gradient bucket")
+
+    def _grad_view(self, off: int, n: int) -> Optional[torch.Tensor]:
+        if self.main_grad is not None:
+            return self.main_grad[off:off + n]
+        if not self.bucket_ids:
+            return None
+        b = self.bucket_of_offset(off)
+        lo, hi = self.bucket_ranges[b]
+        if off + n > hi:
+            raise ValueError("a parameter view crosses a gradient-bucket boundary")
+        return self._bucket_buf[b][off - lo:off - lo + n]
+
     def _make_param(self, name, off, n, shape) -> torch.nn.Parameter:
         p = torch.nn.Parameter(self.flat[off:off + n].view(shape), requires_grad=True)
-        if self.main_grad is not None:
-            p.main_grad = self.main_grad[off:off + n].view(shape)
+        g = self._grad_view(off, n)
+        if g is not None:
+            p.main_grad = g.view(shape)
         p.flat_name = name
         return p
 
@@ -222,6 +294,8 @@ class FlatParams:
     def zero_grad(self) -> None:
         if self.main_grad is not None:
             self.main_grad.zero_()
+        for g in self.grad_buffers:
+            g.zero_()
 
     def named_tensors(self):
         for name, shape in self.entries:

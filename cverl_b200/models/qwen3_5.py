@@ -47,7 +47,11 @@ class Qwen35Model(torch.nn.Module):
     def __init__(self, cfg: Qwen35TextConfig, *, dtype=torch.bfloat16, device="cpu",
                  ctx: ParallelContext = SINGLE, layer_begin: int = 0, layer_end: Optional[int] = None,
                  first_stage: bool = True, last_stage: bool = True, pad_multiple: int = 1,
-                 with_main_grad: bool = True, flat_allocator=None):
+                 with_main_grad: bool = True, flat_allocator=None, grad_buckets: bool = False,
+                 bucket_align: int = 8, grad_slots: int = 2):
+        """``grad_buckets``: per-layer gradient buckets on ``grad_slots`` rotating buffers instead of a full fp32
+        gradient twin (for ``BucketedZero2Optimizer``, which reduces a layer's gradients while the backward pass
+        runs the next layer); the embedding and the head keep a buffer each."""
         super().__init__()
         self.cfg = cfg
         self.ctx = ctx
@@ -67,8 +71,16 @@ class Qwen35Model(torch.nn.Module):
                                                         last_stage)
         self.spec_by_name: Dict[str, ParamSpec] = {s.name: s for s in self.specs}
         entries = self._flat_entries()
+        buckets, pinned = None, ()
+        if grad_buckets:
+            buckets = [self._bucket_of_entry(n) for n, _ in entries]
+            pinned = (0,)
         self.flat = FlatParams(entries, dtype=dtype, device=device, pad_multiple=pad_multiple,
-                               with_main_grad=with_main_grad, allocator=flat_allocator)
+                               with_main_grad=with_main_grad, allocator=flat_allocator, grad_buckets=buckets,
+                               bucket_align=bucket_align, grad_slots=grad_slots, pinned_buckets=pinned)
+        # ``backward_boundary(delta, resid, bucket)``: identity on the residual stream whose backward tells a
+        # bucketed optimizer that the layers after this point have finished their backward pass
+        self.backward_boundary = None
         for name, p in self.flat.params.items():
             self.register_parameter(name.replace(".", "/"), p)
         self._build_fused_views()
@@ -77,6 +89,15 @@ class Qwen35Model(torch.nn.Module):
         self._sp_active = False     # inside a sequence-parallel forward (see ``sequence_parallel``)
 
     # ------------------------------------------------------------------ layout
+    def _bucket_of_entry(self, name: str) -> int:
+        """Gradient bucket of a flat entry: 0 = everything outside the layers (embedding, final norm, untied
+        head: they come first in the buffer), 1 + k = k-th layer of this stage."""
+        root = self.cfg.layer_root
+        for prefix in (root, "__packed_moe.layers."):
+            if name.startswith(prefix):
+                return 1 + int(name[len(prefix):].split(".")[0]) - self.layer_begin
+        return 0
+
     def _flat_entries(self) -> List[Tuple[str, Tuple[int, ...]]]:
         cfg, tp, ep = self.cfg, self.ctx.tp_size, self.ctx.ep_size
         entries: List[Tuple[str, Tuple[int, ...]]] = []
@@ -425,8 +446,11 @@ class Qwen35Model(torch.nn.Module):
         cfg = self.cfg
         eps, off = cfg.rms_norm_eps, cfg.norm_weight_offset
         delta, resid = x, None
+        boundary = self.backward_boundary if torch.is_grad_enabled() else None
         for i in range(self.layer_begin, self.layer_end):
             p = f"{cfg.layer_root}{i}."
+            if boundary is not None:       # backward: layer i (bucket 1 + i - begin) is complete when this fires
+                delta, resid = boundary(delta, resid, 1 + i - self.layer_begin)
             n1, resid = ops.add_rmsnorm(delta, resid, self.param(p + "input_layernorm.weight"), eps, off)
             cache = None
             if caches is not None:
@@ -438,6 +462,8 @@ class Qwen35Model(torch.nn.Module):
                 a = self.linear_attention(n1, i, batch, seq, cache=cache)
             n2, resid = ops.add_rmsnorm(a, resid, self.param(p + "post_attention_layernorm.weight"), eps, off)
             delta = self.mlp(n2, i)
+        if boundary is not None:           # fires before the last layer's backward starts
+            delta, resid = boundary(delta, resid, self.layer_end - self.layer_begin + 1)
         if self.last_stage and final_norm:
             out, _ = ops.add_rmsnorm(delta, resid, self.param(cfg.final_norm_name), eps, off)
             return out

@@ -117,6 +117,10 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--kl-penalty", default="k1")
     g.add_argument("--advantage-scale", type=float, default=1.0)
     g.add_argument("--max-grad-norm", type=float, default=1.0)
+    g.add_argument("--zero-stage", type=int, default=1, choices=[1, 2],
+                   help="2: per-layer gradient buckets on rotating buffers, reduce-scattered from inside the backward "
+                        "pass on a side stream (no full fp32 gradient copy; flat mode, --tp 1 --pp 1 --cp 1 --ep 1)")
+    g.add_argument("--zero-grad-slots", type=int, default=2, help="gradient bucket buffers in flight for --zero-stage 2")
     g.add_argument("--zero-comm", default="nccl", choices=["nccl", "symm"],
                    help="ZeRO gradient reduce-scatter / parameter all-gather: library collectives, or this "
                         "package's kernels over peer-mapped memory (CUDA, bf16 parameters, same node)")
@@ -501,11 +505,19 @@ def run(argv=None) -> int:
     lb, le = topo.pipeline_layer_range(cfg.num_hidden_layers, info.pipeline_rank)
     first, last = info.pipeline_rank == 0, info.pipeline_rank == args.pp - 1
     fused_comm = None
+    zero2 = args.zero_stage == 2
+    if zero2 and (opt_mode != "flat" or args.tp * args.pp * args.cp * args.ep != 1 or args.skip_optimizer_step):
+        raise SystemExit("--zero-stage 2 needs the flat sharded optimizer, --tp 1 --pp 1 --cp 1 --ep 1 and an "
+                         "optimizer step")
     if args.zero_comm == "symm" and args.dp > 1 and opt_mode == "flat":
         if not use_cuda or dtype != torch.bfloat16:
             raise SystemExit("--zero-comm symm needs CUDA and --dtype bfloat16")
         from ..parallel.symm import FusedZeroComm, SymmetricHeap
-        fused_comm = FusedZeroComm(SymmetricHeap(ctx.dp_group, device))
+        if zero2:
+            from ..parallel.zero2 import FusedZero2Comm
+            fused_comm = FusedZero2Comm(SymmetricHeap(ctx.dp_group, device))
+        else:
+            fused_comm = FusedZeroComm(SymmetricHeap(ctx.dp_group, device))
     symm_ok = use_cuda and dtype == torch.bfloat16
     seq_local = (args.prompt_len + args.response_len) // max(args.cp, 1)
     rows = args.micro_batch_seqs * seq_local
@@ -537,7 +549,8 @@ def run(argv=None) -> int:
             ctx.cp_symm = CpSymm(ctx.cp_group, device)
     model = Qwen35Model(cfg, dtype=dtype, device=device, ctx=ctx, layer_begin=lb, layer_end=le, first_stage=first,
                         last_stage=last, pad_multiple=args.dp * 8,
-                        flat_allocator=fused_comm.allocator if fused_comm else None)
+                        flat_allocator=fused_comm.allocator if fused_comm else None, grad_buckets=zero2,
+                        bucket_align=args.dp * 8, grad_slots=args.zero_grad_slots)
     if loader is not None:
         load_model_weights(model, loader)
     else:
@@ -545,7 +558,12 @@ def run(argv=None) -> int:
     comm_dtype = None if args.dp_grad_comm_dtype in ("float32", "model") else _DTYPES[args.dp_grad_comm_dtype]
     adam_opts = AdamWOptions(lr=args.lr, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=args.weight_decay,
                              use_master_weights=args.master_weights)
-    if opt_mode == "flat":
+    if zero2:
+        from ..parallel.zero2 import BucketedZero2Optimizer
+        opt = BucketedZero2Optimizer(model, adam_opts, dp_group=ctx.dp_group, dp_rank=ctx.dp_rank, dp_size=args.dp,
+                                     norm_group=None, norm_world=world, max_grad_norm=args.max_grad_norm,
+                                     fused_comm=fused_comm)
+    elif opt_mode == "flat":
         opt = FlatZeroOptimizer(model.flat, adam_opts, dp_group=ctx.dp_group, dp_rank=ctx.dp_rank, dp_size=args.dp,
                                 norm_group=None, norm_world=world, max_grad_norm=args.max_grad_norm,
                                 comm_dtype=comm_dtype, fused_comm=fused_comm)
@@ -566,8 +584,10 @@ def run(argv=None) -> int:
     if args.resume_checkpoint:
         if opt_mode == "flat":
             start_step = ckpt.load_rank_checkpoint(args.resume_checkpoint, rank, model, opt, rank_info)
-            shard = model.flat.flat[opt.begin:opt.end]
-            if args.dp > 1:  # rebuild the full parameters from the DP shards
+            shard = model.flat.flat[opt.begin:opt.end] if not zero2 else None
+            if zero2:
+                opt.all_gather_params()
+            elif args.dp > 1:  # rebuild the full parameters from the DP shards
                 if use_cuda:
                     dist.all_gather_into_tensor(model.flat.flat, shard.clone(), group=ctx.dp_group)
                 else:

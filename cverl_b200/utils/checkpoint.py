@@ -117,6 +117,8 @@ def save_rank_checkpoint(ckpt_dir, step: int, global_rank: int, model, optimizer
         params.append(entry)
     tensors.update({"flat_param_shard": sd["flat_param_shard"], "flat_exp_avg": sd["flat_exp_avg"],
                     "flat_exp_avg_sq": sd["flat_exp_avg_sq"], "optim_step": sd["optim_step"]})
+    if "bucket_chunks" in sd:      # bucket-sharded ZeRO-2: the shard is a concatenation of per-bucket pieces
+        tensors["bucket_chunks"] = sd["bucket_chunks"]
     save_archive(d / f"rank_{global_rank}.pt", tensors)
     meta = _rank_meta_common(global_rank, rank_info, int(sd["optim_step"]))
     meta.update({
@@ -129,6 +131,8 @@ def save_rank_checkpoint(ckpt_dir, step: int, global_rank: int, model, optimizer
                                  "dtype": c10_dtype_name(optimizer.adam.parameter_shard.dtype)},
         "parameters": params,
     })
+    if "bucket_chunks" in sd:
+        meta["flat_parameter_shard"]["layout"] = "bucketed"
     _write_json_atomic(d / f"rank_{global_rank}.json", meta)
     return d
 

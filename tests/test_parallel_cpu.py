@@ -311,3 +311,69 @@ def test_ep_row_plan_and_overflow_flag():
     assert int(o0[2]) == 1 and int(o1[2]) == 1
     assert o1[0].tolist() == [1, 1, 0, -1, -1] and o1[1].tolist() == [3, 4, 2, 0, 0]
     assert all(r < 5 for r in o0[1].tolist() + o1[1].tolist())
+
+
+def _zero2_worker(rank, world, moe):
+    """Bucketed ZeRO-2 (gradients reduced per layer from inside the backward pass) against the flat optimizer on
+    one rank that sees both ranks' batches."""
+    from cverl_b200.parallel.mesh import build_context
+    from cverl_b200.parallel.zero2 import BucketedZero2Optimizer
+    cfg = Qwen35TextConfig.tiny(moe=moe, layers=3)
+    ctx = build_context(world, rank, tp=1, dp=2)
+    model = Qwen35Model(cfg, dtype=torch.float32, ctx=ctx, pad_multiple=2 * 8, grad_buckets=True, bucket_align=2 * 8,
+                        grad_slots=2)
+    model.init_weights(seed=5)
+    assert model.flat.main_grad is None and model.flat.bucket_ids == list(range(cfg.num_hidden_layers + 1))
+    ref = Qwen35Model(cfg, dtype=torch.float32, pad_multiple=2 * 8)
+    ref.init_weights(seed=5)
+    opts = AdamWOptions(lr=1e-2, beta2=0.95, use_master_weights=False)
+    opt = BucketedZero2Optimizer(model, opts, dp_group=ctx.dp_group, dp_rank=rank, dp_size=2, norm_group=None,
+                                 norm_world=2, max_grad_norm=0.5)
+    ropt = FlatZeroOptimizer(ref.flat, opts, max_grad_norm=0.5)
+    gen = torch.Generator().manual_seed(11)
+    for step in range(2):
+        # two micro-batches per rank: buckets are reduced and accumulated once per backward pass
+        ids = torch.randint(0, cfg.vocab_size, (2, 2, 2, 12), generator=gen)       # [rank, micro-batch, B, S]
+        w = torch.randn(2, 2, 2, 8, generator=gen)
+        for mb in range(2):
+            lp = model.response_logprobs(ids[rank, mb], 4)
+            lp.backward(w[rank, mb] * 0.5)
+        assert opt.reduced_buckets == (step * 2 + 2) * cfg.num_hidden_layers
+        for r in range(2):
+            for mb in range(2):
+                lp = ref.response_logprobs(ids[r, mb], 4)
+                lp.backward(w[r, mb] * 0.25)
+        _fold(ref)
+        opt.step()
+        ropt.step()
+        for name, t in model.flat.named_tensors():
+            torch.testing.assert_close(t, ref.flat.params[name].data, rtol=2e-4, atol=2e-5, msg=lambda m: f"{name}: {m}")
+        assert abs(opt.last_metrics[1].item() - ropt.last_metrics[1].item()) < 1e-3 * ropt.last_metrics[1].item()
+        assert all(float(g.abs().max()) == 0.0 for g in model.flat.grad_buffers)
+        assert float(opt.grad_shard.abs().max()) == 0.0
+    # state round trip: a second optimizer loaded from the first continues identically
+    sd = opt.state_dict()
+    opt.load_state_dict(sd)
+    assert opt.step_count == 2 and int(sd["bucket_chunks"].sum()) == opt.shard_numel
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_bucketed_zero2_dp2_matches_single_rank(moe):
+    run_ranks(_zero2_worker, 2, moe)
+
+
+def test_flat_params_gradient_buckets_layout():
+    from cverl_b200.models.params import FlatParams
+    entries = [("emb", (5, 4)), ("l0.a", (3, 8)), ("l0.b", (8,)), ("l1.a", (3, 8)), ("l1.b", (8,)), ("l2.a", (3, 8))]
+    fp = FlatParams(entries, dtype=torch.float32, pad_multiple=16, grad_buckets=[0, 1, 1, 2, 2, 3], bucket_align=16,
+                    grad_slots=2, pinned_buckets=(0,))
+    assert fp.bucket_ranges == {0: (0, 32), 1: (32, 64), 2: (64, 96), 3: (96, 128)} and fp.padded_numel == 128
+    assert fp.grad_slot_of == {1: 1, 2: 0, 3: 1} and len(fp.grad_buffers) == 3
+    # buckets 1 and 3 share a slot: the same memory backs both parameters' gradients
+    assert fp.params["l0.a"].main_grad.data_ptr() == fp.params["l2.a"].main_grad.data_ptr()
+    assert fp.params["l1.a"].main_grad.data_ptr() != fp.params["l0.a"].main_grad.data_ptr()
+    assert fp.fused_view(["l0.a", "l0.b"], (32,)).main_grad.numel() == 32
+    with pytest.raises(ValueError):
+        fp.fused_view(["l0.b", "l1.a"], (32,))                  # crosses a bucket boundary
+    with pytest.raises(ValueError):
+        FlatParams(entries, grad_buckets=[0, 1, 0, 2, 2, 3])    # bucket ids must not decrease

@@ -345,6 +345,105 @@ def test_sequence_parallel_tp_model_two_gpus():
     run_ranks(_tp_sp_model_rank, 2, backend="nccl", timeout=300)
 
 
+def _zero2_gpu_rank(rank, world, fused):
+    """Bucketed ZeRO-2 on GPUs: per-layer gradient buckets reduced from inside the backward pass on a side stream
+    (peer-memory kernels or NCCL), against a full-gradient model whose gradients are all-reduced afterwards."""
+    import torch.distributed as dist
+    from cverl_b200 import _native as nv
+    from cverl_b200.models.config import Qwen35TextConfig
+    from cverl_b200.models.qwen3_5 import Qwen35Model
+    from cverl_b200.optim import AdamWOptions
+    from cverl_b200.parallel.mesh import build_context
+    from cverl_b200.parallel.symm import SymmetricHeap
+    from cverl_b200.parallel.zero import FlatZeroOptimizer
+    from cverl_b200.parallel.zero2 import BucketedZero2Optimizer, FusedZero2Comm
+    dev = torch.device("cuda", rank)
+    cfg = Qwen35TextConfig(vocab_size=4096, hidden_size=256, num_hidden_layers=4, num_attention_heads=4,
+                           num_key_value_heads=2, head_dim=128, intermediate_size=512, linear_key_head_dim=128,
+                           linear_value_head_dim=128, linear_num_key_heads=2, linear_num_value_heads=2)
+    B, S, P = 2, 256, 64
+    ctx = build_context(world, rank, tp=1, dp=world)
+    heap = SymmetricHeap(ctx.dp_group, dev) if fused else None
+    comm = FusedZero2Comm(heap) if fused else None
+    model = Qwen35Model(cfg, dtype=torch.bfloat16, device=dev, ctx=ctx, pad_multiple=world * 8, grad_buckets=True,
+                        bucket_align=world * 8, grad_slots=2, flat_allocator=comm.allocator if comm else None)
+    model.init_weights(seed=7)
+    ref = Qwen35Model(cfg, dtype=torch.bfloat16, device=dev, ctx=ctx, pad_multiple=world * 8)
+    ref.init_weights(seed=7)
+    opts = AdamWOptions(lr=1e-3, beta2=0.95, use_master_weights=False)
+    opt = BucketedZero2Optimizer(model, opts, dp_group=ctx.dp_group, dp_rank=rank, dp_size=world, norm_group=None,
+                                 norm_world=world, max_grad_norm=1.0, fused_comm=comm)
+    ropt = FlatZeroOptimizer(ref.flat, opts, dp_group=ctx.dp_group, dp_rank=rank, dp_size=world, norm_group=None,
+                             norm_world=world, max_grad_norm=1.0)
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    failures = []
+    for it in range(2):
+        for mb in range(2):
+            ids = torch.randint(1, cfg.vocab_size, (B, S), device=dev, generator=g)
+            seed = torch.randn(B, S - P, device=dev, generator=g) * 0.5
+            model.response_logprobs(ids, P).backward(seed)
+            ref.response_logprobs(ids, P).backward(seed)
+        opt.finish_backward()
+        want = ref.flat.main_grad.clone()
+        dist.all_reduce(want, group=ctx.dp_group)
+        want /= world
+        torch.cuda.synchronize()
+        nv.check_status()
+        err_sq = tot_sq = 0.0
+        for b in model.flat.bucket_ids:
+            lo, _ = model.flat.bucket_ranges[b]
+            c = opt.chunk[b]
+            got = opt.grad_shard[opt.piece_off[b]: opt.piece_off[b] + c]
+            # the same elements in the reference layout: walk the entries of this bucket that fall into the piece
+            for name, (off, n) in model.flat.offsets.items():
+                a, e = max(off, lo + rank * c), min(off + n, lo + (rank + 1) * c)
+                if a >= e:
+                    continue
+                roff = ref.flat.offsets[name][0]
+                w = want[roff + (a - off): roff + (e - off)]
+                gt = got[a - lo - rank * c: e - lo - rank * c]
+                err_sq += (gt - w).pow(2).sum().item()
+                tot_sq += w.pow(2).sum().item()
+        if not (tot_sq > 0 and (err_sq / tot_sq) ** 0.5 < 0.02):   # fp32 atomics in another order: rounding only
+            failures.append(("shard gradient", it, err_sq, tot_sq))
+        if any(float(buf.abs().max()) != 0.0 for buf in model.flat.grad_buffers):
+            failures.append(("bucket buffers not cleared", it))
+        if opt.reduced_buckets != (it + 1) * 2 * cfg.num_hidden_layers:
+            failures.append(("reductions from inside backward", opt.reduced_buckets))
+        opt.step()
+        ropt.step()
+        torch.cuda.synchronize()
+        nv.check_status()
+        # one AdamW step moves every element by about lr = 1e-3: a piece that missed its update or its all-gather
+        # would differ by that much everywhere; elements whose near-zero gradient changed sign may differ singly
+        off_cnt = tot_cnt = 0
+        for name, t in model.flat.named_tensors():
+            d = (t.float() - ref.flat.params[name].data.float()).abs()
+            if d.max().item() > 2.5e-3 * (it + 1):
+                failures.append((name, it, d.max().item()))
+            off_cnt += int((d > 5e-4).sum())
+            tot_cnt += d.numel()
+        if off_cnt > 0.02 * tot_cnt:
+            failures.append(("parameters off by a whole update", it, off_cnt, tot_cnt))
+        # every rank holds the same parameters after the all-gather
+        chk = model.flat.flat.float().sum().reshape(1)
+        both = [torch.empty_like(chk) for _ in range(world)]
+        dist.all_gather(both, chk, group=ctx.dp_group)
+        if any(float(x) != float(both[0]) for x in both):
+            failures.append(("parameters differ between ranks", it))
+    dist.barrier()
+    torch.cuda.synchronize()
+    if heap is not None:
+        heap.close()
+    assert not failures, failures[:10]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("fused", [False, True])
+def test_bucketed_zero2_two_gpus(fused):
+    run_ranks(_zero2_gpu_rank, 2, fused, backend="nccl", timeout=300)
+
+
 def _ring_native_rank(rank, world, pull=False):
     import torch.distributed as dist
     from cverl_b200 import _native as nv

@@ -353,3 +353,27 @@ def test_rollout_batches_over_a_file_rendezvous_communicator(tmp_path):
 def test_kl_needs_reference_log_probs():
     p = _run(1, "--steps", "1", "--kl-coef", "0.1", port=29713, check=False)
     assert p.returncode != 0 and "ref_log_probs" in (p.stdout + p.stderr)
+
+
+def test_zero_stage2_matches_stage1_and_resumes(tmp_path):
+    """--zero-stage 2 (per-layer gradient buckets reduced during the backward pass, bucket-sharded optimizer state)
+    is the same AdamW as the flat shard: same losses on two data-parallel ranks, and it resumes from its own
+    checkpoint onto the same trajectory."""
+    base = ["--dp", "2", "--micro-batches", "2", "--steps", "4"]
+    flat = _lines(_run(2, *base, port=29711))
+    z2 = _lines(_run(2, *base, "--zero-stage", "2", port=29712))
+    for a, b in zip(flat, z2):
+        assert float(a["loss_sum"]) == pytest.approx(float(b["loss_sum"]), rel=2e-4, abs=1e-6)
+        assert float(a["global_grad_norm"]) == pytest.approx(float(b["global_grad_norm"]), rel=1e-3)
+        assert b["all_ranks_updated"] == "true"
+    ck = tmp_path / "ckz2"
+    _run(2, "--dp", "2", "--micro-batches", "2", "--steps", "2", "--zero-stage", "2", "--checkpoint-dir", str(ck),
+         "--checkpoint-every", "2", port=29713)
+    meta = json.loads((ck / "step_000002" / "rank_1.json").read_text())
+    assert meta["flat_parameter_shard"]["layout"] == "bucketed"
+    resumed = _lines(_run(2, *base, "--zero-stage", "2", "--resume-checkpoint", str(ck), port=29714))
+    assert [r["step"] for r in resumed] == ["2", "3"]
+    for ra, rb in zip(z2[2:], resumed):
+        assert float(ra["loss_sum"]) == pytest.approx(float(rb["loss_sum"]), rel=1e-5, abs=1e-7)
+    bad = _run(2, "--tp", "2", "--zero-stage", "2", port=29715, check=False)
+    assert bad.returncode != 0 and "--zero-stage 2 needs" in (bad.stdout + bad.stderr)
