@@ -40,7 +40,17 @@ def parse_args():
     ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("CVERL_BENCH_MICRO_BATCH", "0")),
                     help="sequences per micro-batch; 0 = 32 per tensor-parallel rank (about 100 GB of the 180 GB HBM)")
     ap.add_argument("--tp", type=int, default=int(os.environ.get("CVERL_BENCH_TP", "0")))
-    ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
+    ap.add_argument("--seqs-per-gpu", type=int, default=0, help="0 = the configuration's own (128 for the headline)")
+    ap.add_argument("--config", default="grpo_0_8b",
+                    choices=["grpo_0_8b", "cpu_loss", "moe30b_ep8_sft", "cp8_attention", "zero2_dp8_push"],
+                    help="grpo_0_8b is the headline benchmark; the others are described in cverl_b200/bench_configs.py")
+    ap.add_argument("--seq-len", type=int, default=0, help="other configurations: 0 = the named sequence length")
+    ap.add_argument("--ep-comm", default="symm", choices=["symm", "nccl"])
+    ap.add_argument("--cp-comm", default="nccl", choices=["symm", "nccl"])
+    ap.add_argument("--grad-slots", type=int, default=2, help="zero2_dp8_push: gradient bucket buffers in flight")
+    ap.add_argument("--rs-blocks", type=int, default=0,
+                    help="zero2_dp8_push: CTAs of a bucket's reduce-scatter kernel while it overlaps the backward pass")
+    ap.add_argument("--no-overlap", action="store_true", help="zero2_dp8_push: reduce buckets on the main stream")
     ap.add_argument("--tp-comm", default=os.environ.get("CVERL_BENCH_TP_COMM", "sp"), choices=["sp", "symm", "nccl"],
                     help="tensor-parallel communication: sp = token-sharded residual stream, reduce-scatter in the "
                          "GEMM epilogue and all-gather in the norm kernels over peer-mapped memory; symm = all-reduce "
@@ -164,6 +174,11 @@ def main():
     args = parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.config != "grpo_0_8b":
+        from cverl_b200 import bench_configs
+        return bench_configs.run(args, ClockSampler)
+    if args.seqs_per_gpu <= 0:
+        args.seqs_per_gpu = SEQS_PER_GPU
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

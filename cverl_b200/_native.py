@@ -100,10 +100,14 @@ _CUDA_PROTOS = {
     "cvb_flat_adamw_allgather": "ppppp p ii ll fffff l p",
     "cvb_broadcast_store": "pp i l p",
     "cvb_sum_parts": "p l i p l p",
+    "cvb_multimem_broadcast_store": "pp l i p",
+    "cvb_multimem_reduce_scatter": "p ll f p i p i p",
+    "cvb_multimem_allreduce_bf16": "p ll i p",
     "cvb_p2p_scatter_rows": "pp i pp ll l p p",
     "cvb_p2p_gather_rows": "pp i pp ll l p p",
     "cvb_attention_fwd": "ppppp l iiiii f i ll p p",
     "cvb_attention_bwd": "ppppp p pp ppp l iiiii f i ll p p",
+    "cvb_attn_merge": "pppp l iiiiii p",
     "cvb_decode_attention": "p ll pp l ppp p iiiii f p p",
     "cvb_gdn_decode_step": "p l ii pp i p pp l pp pp i p",
     "cvb_router_topk_fwd": "p l iii pp p",

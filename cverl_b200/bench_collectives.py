@@ -218,6 +218,78 @@ def main(argv=None) -> int:
         report(case="push", n_gpus=world, bytes=nbytes, fused_ms=tf, nccl_ms=tn, link_gbs=nbytes / tf / 1e6,
                link_frac=nbytes / tf / 1e6 / LINK_GBS, note=f"{half} trainers -> {half} rollout ranks, one copy each")
         nv.check_status(dev)
+    if "nvls" in what and world > 1:
+        # the same collectives through the NVSwitch multicast address (multimem.st / multimem.ld_reduce)
+        from .parallel import nvls
+        try:
+            rs = nvls.NvlsReduceScatter(group, dev, n)
+        except RuntimeError as exc:
+            report(case="nvls", n_gpus=world, unavailable=str(exc))
+            rs = None
+        if rs is not None:
+            gshard = torch.empty(shard, dtype=torch.float32, device=dev)
+            out = torch.empty(shard, dtype=torch.float32, device=dev)
+
+            def mm_rs():
+                rs.reduce(gshard, begin)
+
+            def nccl_rs():
+                dist.reduce_scatter_tensor(out, rs.grad, op=dist.ReduceOp.AVG, group=group)
+                optim_ops.sumsq(out)
+            rs.grad.fill_(1e-3 * (rank + 1))
+            tf, tn = _time(mm_rs, a.iters, group), _time(nccl_rs, a.iters, group)
+            dist.reduce_scatter_tensor(out, rs.grad, op=dist.ReduceOp.AVG, group=group)
+            err = float((out - gshard).abs().max())
+            report(case="nvls_zero_rs", n_gpus=world, numel=n, fused_ms=tf, nccl_ms=tn, max_abs_diff=err,
+                   egress_gbs=(world - 1) * shard * 4 / tf / 1e6,
+                   note="reduce-scatter(mean) + sumsq; the sum is formed in the switch, each GPU receives its shard "
+                        "once and still ships (n-1)/n of its buffer")
+            del rs, gshard, out
+            torch.cuda.empty_cache()
+            nbytes = n * 2
+            bc = nvls.NvlsBroadcaster(group, dev, nbytes)
+            src = torch.empty(n, dtype=torch.bfloat16, device=dev).normal_()
+            dst = bc.tensor(n, torch.bfloat16)
+            part = n // world // 8 * 8
+
+            def mm_push():          # every rank multicasts its 1/n of the weights: the parameter all-gather
+                bc.push(src[rank * part:(rank + 1) * part], rank * part * 2)
+                bc.sync()
+
+            def mm_push_one():      # one sender, everyone receives: the 1 -> n weight broadcast
+                if rank == 0:
+                    bc.push(src, 0)
+                bc.sync()
+
+            def nccl_bcast():
+                dist.broadcast(src if rank == 0 else dst, 0, group=group)
+
+            def nccl_ag():
+                dist.all_gather_into_tensor(dst[:part * world], src[rank * part:(rank + 1) * part], group=group)
+            t1, t2 = _time(mm_push_one, a.iters, group), _time(nccl_bcast, a.iters, group)
+            report(case="nvls_push_1_to_n", n_gpus=world, bytes=nbytes, fused_ms=t1, nccl_ms=t2,
+                   egress_gbs=nbytes / t1 / 1e6, link_frac=nbytes / t1 / 1e6 / LINK_GBS,
+                   note="one multimem.st per 16 bytes on rank 0; the switch delivers to every rank")
+            t3, t4 = _time(mm_push, a.iters, group), _time(nccl_ag, a.iters, group)
+            report(case="nvls_allgather", n_gpus=world, bytes=nbytes, fused_ms=t3, nccl_ms=t4,
+                   ingress_gbs=(world - 1) * part * 2 / t3 / 1e6,
+                   link_frac=(world - 1) * part * 2 / t3 / 1e6 / LINK_GBS,
+                   note="every rank multicasts its shard: egress 1/n of the buffer, ingress (n-1)/n")
+            del bc, src, dst
+            torch.cuda.empty_cache()
+            m = a.tokens * 1024
+            ar = nvls.NvlsAllReduce(group, dev, m)
+            x = torch.empty(m, dtype=torch.bfloat16, device=dev).normal_()
+
+            def mm_ar():
+                ar.all_reduce()
+
+            def nccl_ar():
+                dist.all_reduce(x, group=group)
+            t5, t6 = _time(mm_ar, a.iters, group), _time(nccl_ar, a.iters, group)
+            report(case="nvls_allreduce_bf16", n_gpus=world, numel=m, fused_ms=t5, nccl_ms=t6,
+                   note="[tokens, 1024] bf16 partial sums: ld_reduce + multimem.st of each rank's slice")
+        nv.check_status(dev)
     dist.barrier(group)
     dist.destroy_process_group()
     return 0

@@ -169,6 +169,41 @@ class Qwen35Model(torch.nn.Module):
             self.load_full_tensor(s.name, full)
 
     @torch.no_grad()
+    def init_weights_on_device(self, seed: int = 1234, std: float = 0.02) -> None:
+        """Random initialisation written straight into the flat buffer on its device, tensor by tensor: no full
+        tensor is ever built on the host, so a 30 B-parameter model initialises in seconds.  The distributions are
+        those of ``init_weights``; the values are not (each local tensor has its own generator, seeded by its
+        name, plus the tensor-parallel rank for sharded tensors and the expert-parallel rank for packed expert
+        weights, so replicas agree across data-parallel ranks)."""
+        import zlib
+        cfg, ctx = self.cfg, self.ctx
+        dev = self.flat.flat.device
+        gen = torch.Generator(device=dev)
+        for name, p in self.flat.params.items():
+            salt = zlib.crc32(name.encode())
+            if name.startswith("__packed_moe"):
+                salt ^= 0x9E3779B1 * (ctx.ep_rank + 1) & 0xFFFFFFFF
+                sharded = ctx.tp_size > 1
+            else:
+                spec = self.spec_by_name[name]
+                sharded = ctx.tp_size > 1 and tuple(spec.local_shape(ctx.tp_size)) != tuple(spec.full_shape)
+            if sharded:
+                salt ^= 0x85EBCA6B * (ctx.tp_rank + 1) & 0xFFFFFFFF
+            gen.manual_seed((seed * 1000003 + salt) & 0x7FFFFFFFFFFFFFFF)
+            t = p.data
+            if name.endswith("A_log"):
+                t.copy_(torch.log(torch.empty(t.shape, device=dev).uniform_(1.0, 8.0, generator=gen)))
+            elif name.endswith("dt_bias"):
+                t.copy_(torch.empty(t.shape, device=dev).uniform_(-1.0, 1.0, generator=gen))
+            elif name.endswith("norm.weight") or name.endswith("layernorm.weight"):
+                gated = name.endswith("linear_attn.norm.weight")
+                t.fill_(1.0 if (cfg.is_qwen3_moe or gated) else 0.0)
+            elif name.endswith("conv1d.weight"):
+                t.copy_(torch.empty(t.shape, device=dev).uniform_(-0.5, 0.5, generator=gen))
+            else:
+                t.normal_(0.0, std, generator=gen)
+
+    @torch.no_grad()
     def load_full_tensor(self, name: str, full: torch.Tensor) -> None:
         """Shard a full Hugging Face tensor for this rank and copy it into the flat buffer."""
         spec = self.spec_by_name[name]
@@ -322,7 +357,23 @@ class Qwen35Model(torch.nn.Module):
         k = ops.headnorm_rope(k, self.param(p + "k_norm.weight"), cos, sin, pos, cfg.rotary_dim, cfg.rms_norm_eps, off)
         if cache is not None:  # prefill of a cached decode: keep the rotated keys and the values
             cache["k"], cache["v"] = k.view(batch, seq, kvh, d), v.reshape(batch, seq, kvh, d)
-        if ctx.cp_size > 1:
+        zig = False
+        if ctx.cp_size > 1 and ctx.cp_zigzag and ctx.cp_symm is None:
+            from ..parallel import cp_zigzag as zz
+            zig = zz.zigzag_supported(seq, self._cp_original_len or seq * ctx.cp_size, ctx.cp_size) and (
+                not q.is_cuda or (seq // 2) % 128 == 0)
+        if zig:
+            # q | k | v travel to the zig-zag layout as one tensor, the output comes back the same way
+            packed = torch.cat([q.reshape(batch, seq, h * d), k.reshape(batch, seq, kvh * d),
+                                v.reshape(batch, seq, kvh * d)], dim=-1)
+            packed = zz.zigzag_reshard(packed, ctx.cp_group, ctx.cp_rank, ctx.cp_size, True)
+            zq, zk, zv = packed.split([h * d, kvh * d, kvh * d], dim=-1)
+            o = zz.zigzag_ring_attention(zq.reshape(batch, seq, h, d), zk.reshape(batch, seq, kvh, d),
+                                         zv.reshape(batch, seq, kvh, d), ctx.cp_group, ctx.cp_rank, ctx.cp_size,
+                                         1.0 / math.sqrt(d))
+            o = zz.zigzag_reshard(o.reshape(batch, seq, h * d), ctx.cp_group, ctx.cp_rank, ctx.cp_size, False)
+            o = o.reshape(T, h, d)
+        elif ctx.cp_size > 1:
             from ..parallel.context_parallel import ring_attention
             o = ring_attention(q.view(batch, seq, h, d).transpose(1, 2), k.view(batch, seq, kvh, d).transpose(1, 2),
                                v.reshape(batch, seq, kvh, d).transpose(1, 2), ctx.cp_group, ctx.cp_rank, ctx.cp_size,

@@ -36,6 +36,9 @@ class ParallelContext:
     ep_symm: Optional[Any] = None
     # ``parallel.cp_symm.CpSymm`` when context-parallel attention pulls K / V from peers instead of a ring
     cp_symm: Optional[Any] = None
+    # context-parallel attention over a zig-zag resharding of q | k | v (``parallel.cp_zigzag``): every rank does
+    # the same amount of causal attention work; off = contiguous shards, rank r attends r + 1/2 key blocks
+    cp_zigzag: bool = False
 
     @property
     def single(self) -> bool:

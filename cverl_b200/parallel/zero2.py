@@ -63,7 +63,7 @@ class FusedZero2Comm:
     bf16 parameter buffer first, then each fp32 gradient buffer.
     """
 
-    def __init__(self, heap, max_blocks: int = 296):
+    def __init__(self, heap, max_blocks: int = 96):
         from .symm import SymmBarrier
         self.heap = heap
         self.params = None

@@ -134,6 +134,9 @@ def build_parser() -> argparse.ArgumentParser:
                         "peer-mapped memory (no host read)")
     g.add_argument("--cp-comm", default="nccl", choices=["nccl", "symm"],
                    help="context-parallel attention: ring send/recv, or K / V pulled from the owners by the kernels")
+    g.add_argument("--cp-attn", default="zigzag", choices=["zigzag", "ring"],
+                   help="context-parallel attention: zigzag = q | k | v resharded so that every rank does the same "
+                        "causal work (with --cp-comm nccl); ring = contiguous shards")
     g.add_argument("--ep-capacity-factor", type=float, default=2.0,
                    help="receive-buffer rows per rank for --ep-comm symm, as a multiple of the balanced load")
     _add_flag(g, "--master-weights")
@@ -539,6 +542,7 @@ def run(argv=None) -> int:
         from ..parallel.ep_symm import EpSymm
         cap = int(rows * cfg.num_experts_per_tok * args.ep_capacity_factor) + 128
         ctx.ep_symm = EpSymm(ctx.ep_group, device, cap, cfg.hidden_size)
+    ctx.cp_zigzag = args.cp > 1 and args.cp_attn == "zigzag" and args.cp_comm != "symm"
     if args.cp_comm == "symm" and args.cp > 1 and symm_ok:
         if args.pp > 1:
             # the peer-mapped K / V buffers hold ONE micro-batch per layer; 1F1B keeps several in flight

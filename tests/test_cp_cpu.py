@@ -94,3 +94,72 @@ def _model_cp_worker(rank, world):
 
 def test_hybrid_model_context_parallel_matches_dense():
     run_ranks(_model_cp_worker, 2)
+
+
+def _zigzag_worker(rank, world):
+    """Zig-zag sharded ring attention (one equally sized launch per hop and rank) against dense causal attention:
+    outputs and all three gradients, through the resharding in both directions."""
+    import torch.distributed as dist
+    from cverl_b200.parallel.cp_zigzag import zigzag_chunks, zigzag_reshard, zigzag_ring_attention
+    torch.manual_seed(1)
+    B, Hq, Hkv, D = 2, 4, 2, 8
+    h = 3
+    S = 2 * h * world
+    q, k, v = (torch.randn(B, S, n, D) for n in (Hq, Hkv, Hkv))
+    qd, kd, vd = (t.clone().requires_grad_(True) for t in (q, k, v))
+    dense = causal_attention_ref(qd.reshape(B * S, Hq, D), kd.reshape(B * S, Hkv, D), vd.reshape(B * S, Hkv, D), B,
+                                 S).view(B, S, Hq, D)
+    w = torch.randn(B, S, Hq, D)
+    (dense * w).sum().backward()
+    T = S // world
+    cont = slice(rank * T, (rank + 1) * T)
+    ql, kl, vl = (t[:, cont].clone().requires_grad_(True) for t in (q, k, v))
+    packed = torch.cat([ql.reshape(B, T, -1), kl.reshape(B, T, -1), vl.reshape(B, T, -1)], dim=-1)
+    z = zigzag_reshard(packed, dist.group.WORLD, rank, world, True)
+    c0, c1 = zigzag_chunks(rank, world)
+    want_rows = torch.cat([torch.arange(c0 * h, (c0 + 1) * h), torch.arange(c1 * h, (c1 + 1) * h)])
+    torch.testing.assert_close(z[..., :Hq * D], q[:, want_rows].reshape(B, T, -1))      # the layout itself
+    zq, zk, zv = z.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
+    out = zigzag_ring_attention(zq.reshape(B, T, Hq, D), zk.reshape(B, T, Hkv, D), zv.reshape(B, T, Hkv, D),
+                                dist.group.WORLD, rank, world)
+    torch.testing.assert_close(out, dense.detach()[:, want_rows], rtol=1e-4, atol=1e-5)
+    back = zigzag_reshard(out.reshape(B, T, -1), dist.group.WORLD, rank, world, False).reshape(B, T, Hq, D)
+    torch.testing.assert_close(back, dense.detach()[:, cont], rtol=1e-4, atol=1e-5)
+    (back * w[:, cont]).sum().backward()
+    for got, full in ((ql, qd), (kl, kd), (vl, vd)):
+        torch.testing.assert_close(got.grad, full.grad[:, cont], rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_zigzag_ring_attention_matches_dense(world):
+    run_ranks(_zigzag_worker, world)
+
+
+def _model_zigzag_worker(rank, world):
+    from cverl_b200.parallel.mesh import build_context
+    cfg = Qwen35TextConfig.tiny(layers=4)
+    ctx = build_context(world, rank, cp=world, dp=1)
+    ctx.cp_zigzag = True
+    cp_model = Qwen35Model(cfg, dtype=torch.float32, ctx=ctx)
+    cp_model.init_weights(seed=6)
+    dense = Qwen35Model(cfg, dtype=torch.float32)
+    dense.init_weights(seed=6)
+    ids = torch.randint(0, cfg.vocab_size, (2, 24), generator=torch.Generator().manual_seed(2))
+    w = torch.randn(2, 16, generator=torch.Generator().manual_seed(3))
+    lp = cp_model.response_logprobs(ids, 8)
+    lpd = dense.response_logprobs(ids, 8)
+    torch.testing.assert_close(lp, lpd, rtol=2e-4, atol=2e-4)
+    ((lp * w).sum() / world).backward()
+    (lpd * w).sum().backward()
+    for m in (cp_model, dense):
+        for p in list(m.flat.params.values()) + list(m.fused.values()):
+            if p.grad is not None:
+                p.main_grad.add_(p.grad)
+                p.grad = None
+    import torch.distributed as dist
+    dist.all_reduce(cp_model.flat.main_grad)
+    torch.testing.assert_close(cp_model.flat.main_grad, dense.flat.main_grad, rtol=5e-3, atol=5e-5)
+
+
+def test_hybrid_model_zigzag_context_parallel_matches_dense():
+    run_ranks(_model_zigzag_worker, 2)

@@ -383,6 +383,10 @@ def _zero2_gpu_rank(rank, world, fused):
             seed = torch.randn(B, S - P, device=dev, generator=g) * 0.5
             model.response_logprobs(ids, P).backward(seed)
             ref.response_logprobs(ids, P).backward(seed)
+        for p in list(ref.flat.params.values()) + list(ref.fused.values()):   # gradients that came through autograd
+            if p.grad is not None:
+                p.main_grad.add_(p.grad.float())
+                p.grad = None
         opt.finish_backward()
         want = ref.flat.main_grad.clone()
         dist.all_reduce(want, group=ctx.dp_group)
@@ -404,7 +408,7 @@ def _zero2_gpu_rank(rank, world, fused):
                 gt = got[a - lo - rank * c: e - lo - rank * c]
                 err_sq += (gt - w).pow(2).sum().item()
                 tot_sq += w.pow(2).sum().item()
-        if not (tot_sq > 0 and (err_sq / tot_sq) ** 0.5 < 0.02):   # fp32 atomics in another order: rounding only
+        if not (tot_sq > 0 and (err_sq / tot_sq) ** 0.5 < 1e-4):   # fp32 atomics in another order: rounding only
             failures.append(("shard gradient", it, err_sq, tot_sq))
         if any(float(buf.abs().max()) != 0.0 for buf in model.flat.grad_buffers):
             failures.append(("bucket buffers not cleared", it))
@@ -442,6 +446,108 @@ def _zero2_gpu_rank(rank, world, fused):
 @pytest.mark.parametrize("fused", [False, True])
 def test_bucketed_zero2_two_gpus(fused):
     run_ranks(_zero2_gpu_rank, 2, fused, backend="nccl", timeout=300)
+
+
+def _nvls_rank(rank, world):
+    """NVSwitch multicast kernels (multimem.st / multimem.ld_reduce) against the library collectives."""
+    import torch.distributed as dist
+    from cverl_b200 import _native as nv
+    from cverl_b200.parallel import nvls
+    dev = torch.device("cuda", rank)
+    group = dist.group.WORLD
+    try:
+        bc = nvls.NvlsBroadcaster(group, dev, 1 << 22)
+    except RuntimeError as exc:                       # no multicast support on this machine: nothing to test
+        print(f"NVLS unavailable: {exc}")
+        return
+    failures = []
+    g = torch.Generator(device=dev).manual_seed(5)                     # the same stream of numbers on both ranks
+    src = torch.randn(1 << 20, device=dev, generator=g).bfloat16()
+    dst = bc.tensor(1 << 20, torch.bfloat16, 1 << 21)
+    if rank == 0:
+        bc.push(src, 1 << 21)
+    bc.sync()
+    torch.cuda.synchronize()
+    if not torch.equal(dst, src):
+        failures.append("multicast store")
+    if float(bc.tensor(1 << 20, torch.bfloat16, 0).abs().max()) != 0.0:
+        failures.append("multicast store wrote outside its range")
+    n = 1 << 20
+    rs = nvls.NvlsReduceScatter(group, dev, n)
+    rs.grad.copy_(torch.randn(n, device=dev, generator=torch.Generator(device=dev).manual_seed(10 + rank)))
+    shard = n // world
+    got = torch.full((shard,), 0.5, device=dev)
+    sq = rs.reduce(got, rank * shard, accumulate=True).clone()
+    want = torch.empty(shard, device=dev)
+    dist.reduce_scatter_tensor(want, rs.grad.clone(), op=dist.ReduceOp.AVG)
+    torch.cuda.synchronize()
+    if not torch.allclose(got, want + 0.5, rtol=1e-5, atol=1e-6):
+        failures.append(("reducing load", float((got - want - 0.5).abs().max())))
+    if abs(float(sq) - float((want + 0.5).pow(2).sum())) > 1e-3 * float((want + 0.5).pow(2).sum()):
+        failures.append("squared norm")
+    ar = nvls.NvlsAllReduce(group, dev, 40 * 1024 + 8)
+    x = torch.randn(40 * 1024 + 8, device=dev, generator=torch.Generator(device=dev).manual_seed(20 + rank)).bfloat16()
+    ar.data.copy_(x)
+    y = ar.all_reduce().clone()
+    ref = x.float()
+    dist.all_reduce(ref)
+    torch.cuda.synchronize()
+    if not torch.allclose(y.float(), ref, rtol=2e-2, atol=2e-2):
+        failures.append(("all-reduce", float((y.float() - ref).abs().max())))
+    nv.check_status()
+    dist.barrier()
+    torch.cuda.synchronize()
+    for o in (bc, rs, ar):
+        o.close()
+    assert not failures, failures
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_nvls_multicast_kernels_two_gpus():
+    run_ranks(_nvls_rank, 2, backend="nccl", timeout=300)
+
+
+def _zigzag_native_rank(rank, world):
+    """Zig-zag context-parallel attention on the tcgen05 kernels (hops with unequal query / key lengths, the fp32
+    merge kernel) against dense causal attention in fp32: outputs and gradients."""
+    import torch.distributed as dist
+    from cverl_b200 import _native as nv
+    from cverl_b200.ops.attention import causal_attention_ref
+    from cverl_b200.parallel.cp_zigzag import zigzag_chunks, zigzag_ring_attention
+    from cverl_b200.utils import fallbacks
+    dev = torch.device("cuda", rank)
+    failures = []
+    for D in (128, 256):
+        B, Hq, Hkv, h = 1, 4, 2, 256
+        S = 2 * h * world
+        g = torch.Generator(device=dev).manual_seed(3)                  # the same tensors on every rank
+        q, k, v, w = (torch.randn(B, S, n, D, device=dev, generator=g).bfloat16().float() for n in (Hq, Hkv, Hkv, Hq))
+        qd, kd, vd = (t.clone().requires_grad_(True) for t in (q, k, v))
+        dense = causal_attention_ref(qd.reshape(B * S, Hq, D), kd.reshape(B * S, Hkv, D), vd.reshape(B * S, Hkv, D),
+                                     B, S).view(B, S, Hq, D)
+        (dense * w).sum().backward()
+        c0, c1 = zigzag_chunks(rank, world)
+        rows = torch.cat([torch.arange(c0 * h, (c0 + 1) * h), torch.arange(c1 * h, (c1 + 1) * h)]).to(dev)
+        ql, kl, vl = (t[:, rows].bfloat16().requires_grad_(True) for t in (q, k, v))
+        out = zigzag_ring_attention(ql, kl, vl, dist.group.WORLD, rank, world)
+        (out.float() * w[:, rows]).sum().backward()
+        torch.cuda.synchronize()
+        nv.check_status()
+        def rel(a, b):
+            return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-20)).item()
+        errs = {"out": rel(out, dense.detach()[:, rows]), "dq": rel(ql.grad, qd.grad[:, rows]),
+                "dk": rel(kl.grad, kd.grad[:, rows]), "dv": rel(vl.grad, vd.grad[:, rows])}
+        if any(e > 2e-2 for e in errs.values()):
+            failures.append((D, errs))
+    if fallbacks.total() != 0:
+        failures.append(("library fallbacks", fallbacks.total()))
+    dist.barrier()
+    assert not failures, failures
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_zigzag_ring_attention_native_two_gpus():
+    run_ranks(_zigzag_native_rank, 2, backend="nccl", timeout=300)
 
 
 def _ring_native_rank(rank, world, pull=False):
