@@ -305,7 +305,7 @@ def zero2_dp8_push(args, ClockSampler) -> int:
     ctx = build_context(world, rank, dp=world)
     comm = None
     if world > 1 and args.zero_comm == "symm":
-        comm = FusedZero2Comm(SymmetricHeap(ctx.dp_group, dev), max_blocks=args.rs_blocks or 96)
+        comm = FusedZero2Comm(SymmetricHeap(ctx.dp_group, dev), max_blocks=args.rs_blocks)
     model = Qwen35Model(cfg, dtype=torch.bfloat16, device=dev, ctx=ctx, pad_multiple=world * 8, grad_buckets=True,
                         bucket_align=world * 8, grad_slots=args.grad_slots,
                         flat_allocator=comm.allocator if comm else None)
@@ -391,7 +391,7 @@ def zero2_dp8_push(args, ClockSampler) -> int:
                       "seq_len": S, "seqs_per_gpu": seqs, "micro_batch_seqs": mb, "parallelism": f"dp{world}",
                       "zero": "stage 2, per-layer buckets reduced during backward on a side stream",
                       "zero_comm": args.zero_comm if world > 1 else "none", "overlap": not args.no_overlap,
-                      "grad_slots": args.grad_slots, "rs_blocks": (args.rs_blocks or 96) if comm else None, "params": int(model.flat.numel),
+                      "grad_slots": args.grad_slots, "rs_blocks": args.rs_blocks if comm else None, "params": int(model.flat.numel),
                       "buckets_reduced_inside_each_backward_pass": in_backward,
                       "l2": "working set far above the 126 MB L2"},
            "optimizer_tail_ms": ms_tail,

@@ -17,8 +17,7 @@ would have a single owner and its reduction would be limited by that one GPU's i
 
 Two transports: library collectives (NCCL ``reduce_scatter_tensor`` / ``all_gather_into_tensor``; gloo
 for the CPU tests), or the peer-memory kernels (``FusedZero2Comm``): ``cvb_reduce_scatter_acc`` pulls
-the piece from every peer's bucket buffer, accumulates it into the shard gradient and clears what
-it read, and ``cvb_flat_adamw_allgather`` stores the updated bf16 piece into every peer's parameter
+the piece from every peer's bucket buffer and accumulates it into the shard gradient, and ``cvb_flat_adamw_allgather`` stores the updated bf16 piece into every peer's parameter
 buffer.
 
 The reference reduce-scatters the whole flat gradient after the backward pass, optionally in
@@ -63,9 +62,10 @@ class FusedZero2Comm:
     bf16 parameter buffer first, then each fp32 gradient buffer.
     """
 
-    def __init__(self, heap, max_blocks: int = 96):
+    def __init__(self, heap, max_blocks: int = 0, zero_by_reader: bool = False):
         from .symm import SymmBarrier
         self.heap = heap
+        self.zero_by_reader = zero_by_reader
         self.params = None
         self.param_flat: Optional[torch.Tensor] = None
         self._grad_bufs: Dict[int, object] = {}          # local base pointer -> SymmBuffer
@@ -89,14 +89,18 @@ class FusedZero2Comm:
 
     def reduce_scatter_acc(self, bucket_grad: torch.Tensor, begin: int, n: int, scale: float,
                            out: torch.Tensor) -> None:
-        """On the current stream: barrier, pull + accumulate + clear, barrier (the bucket buffer is free after it)."""
+        """On the current stream: barrier, pull + accumulate, barrier, clear (the bucket buffer is free after it).
+        ``zero_by_reader`` lets the pulling kernel clear what it read instead (no separate pass over the bucket,
+        but the zeros then cross NVLink: worthwhile only while the links have room)."""
         buf = self._grad_bufs[bucket_grad.data_ptr()]
         self.barrier()
         nv.check(nv.cuda().cvb_reduce_scatter_acc(buf.ptr_array(), self.heap.world, self.heap.index, begin, n, scale,
-                                                  out.data_ptr(), 1, self.max_blocks, nv.stream()),
-                 "cvb_reduce_scatter_acc")
+                                                  out.data_ptr(), int(self.zero_by_reader), self.max_blocks,
+                                                  nv.stream()), "cvb_reduce_scatter_acc")
         count_launch()
         self.barrier()
+        if not self.zero_by_reader:
+            bucket_grad.zero_()
 
     def adamw_allgather(self, o: AdamWOptions, step: int, grad, master, m, v, clip, begin: int) -> None:
         nv.check(nv.cuda().cvb_flat_adamw_allgather(grad.data_ptr(), nv.ptr(master), m.data_ptr(), v.data_ptr(),

@@ -435,6 +435,11 @@ def _zero2_gpu_rank(rank, world, fused):
         dist.all_gather(both, chk, group=ctx.dp_group)
         if any(float(x) != float(both[0]) for x in both):
             failures.append(("parameters differ between ranks", it))
+        # start the next round from identical parameters again: a bf16 rounding that fell differently in the two
+        # optimizers would otherwise show up, amplified by the recurrent layers, as a gradient difference
+        with torch.no_grad():
+            for name, t in model.flat.named_tensors():
+                t.copy_(ref.flat.params[name].data)
     dist.barrier()
     torch.cuda.synchronize()
     if heap is not None:
