@@ -96,6 +96,69 @@ def case_gemm_scatter(a, dev):
     return fn, 2.0 * M * N * K, None
 
 
+def case_peer_emulated(a, dev, which):
+    """The self-communicating kernels with every "peer" buffer in this device's own memory: the same code and the
+    same access pattern as across NVLink (profiler captures must not run under a multi-rank command, and two
+    ranks' kernels that wait on each other must not share a GPU - these cases have no waits).
+
+    rs_acc          ZeRO-2 bucket reduce-scatter: pull this rank's piece from ``world`` gradient buffers, accumulate
+    adamw_allgather FlatAdamW on a shard whose bf16 result is stored into ``world`` parameter buffers
+    bcast_store     weight push: one read, one store per destination
+    sp_norm_fwd     sequence-parallel TP: sum of ``world`` GEMM partial slots + residual + RMSNorm on T / world rows,
+                    normalised rows stored into ``world`` gathered buffers
+    attn_merge      merge of one ring-attention hop's partial result into the fp32 accumulator
+    """
+    import ctypes as C
+    from . import _native as nv
+    world = 4
+    st = lambda: nv.stream()   # noqa: E731
+    if which in ("rs_acc", "adamw_allgather", "bcast_store"):
+        n = a.numel // (world * 8) * (world * 8)
+        shard = n // world
+        if which == "rs_acc":
+            bufs = [torch.full((n,), 1e-3 * (i + 1), dtype=torch.float32, device=dev) for i in range(world)]
+            ptrs = (C.c_void_p * world)(*[b.data_ptr() for b in bufs])
+            out = torch.zeros(shard, dtype=torch.float32, device=dev)
+            fn = lambda: nv.check(nv.cuda().cvb_reduce_scatter_acc(ptrs, world, 1, shard, shard, 1.0 / world,
+                                                                   out.data_ptr(), 0, 0, st()), "rs_acc")
+            return fn, None, (world + 2) * shard * 4, bufs
+        if which == "adamw_allgather":
+            params = [torch.zeros(n, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+            ptrs = (C.c_void_p * world)(*[b.data_ptr() for b in params])
+            g, m, v = (torch.full((shard,), 1e-3, dtype=torch.float32, device=dev) for _ in range(3))
+            fn = lambda: nv.check(nv.cuda().cvb_flat_adamw_allgather(g.data_ptr(), None, m.data_ptr(), v.data_ptr(),
+                                                                     None, ptrs, world, 1, shard, shard, 1e-6, 0.9,
+                                                                     0.95, 1e-8, 0.01, 1, st()), "adamw_allgather")
+            return fn, None, shard * (4 * 5 + 2 + 2 * world), (params, g, m, v)
+        src = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+        dsts = [torch.empty(n, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+        ptrs = (C.c_void_p * world)(*[b.data_ptr() for b in dsts])
+        fn = lambda: nv.check(nv.cuda().cvb_broadcast_store(src.data_ptr(), ptrs, world, n * 2, st()), "bcast_store")
+        return fn, None, n * 2 * (1 + world), (src, dsts)
+    if which == "sp_norm_fwd":
+        T, H = 81920, 1024            # 64 sequences x 1280 tokens: the benchmark's micro-batch at TP=2
+        rl = T // world
+        parts = _bf(world, rl, H, dev=dev)
+        resid, w = _bf(rl, H, dev=dev), _bf(H, dev=dev, scale=0.1)
+        gathered = [torch.empty(T, H, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+        dst = (C.c_void_p * world)(*[g.data_ptr() for g in gathered])
+        resid_out = torch.empty(rl, H, dtype=torch.bfloat16, device=dev)
+        rstd = torch.empty(rl, dtype=torch.float32, device=dev)
+        fn = lambda: nv.check(nv.cuda().cvb_sp_add_rmsnorm_fwd(parts.data_ptr(), rl * H, world, resid.data_ptr(),
+                                                               w.data_ptr(), dst, world, rl, resid_out.data_ptr(),
+                                                               rstd.data_ptr(), rl, H, 1e-6, 1.0, st()), "sp_norm_fwd")
+        return fn, None, rl * H * 2 * (world + 2 + world), (parts, gathered)
+    if which == "attn_merge":
+        B, T, Hq, D = 1, a.batch * 2048, 8, a.head_dim
+        acc = torch.randn(B, T, Hq, D, device=dev)
+        lse = torch.randn(B, Hq, T, device=dev)
+        part, lp = _bf(B, T, Hq, D, dev=dev), torch.randn(B, Hq, T, device=dev)
+        fn = lambda: nv.check(nv.cuda().cvb_attn_merge(acc.data_ptr(), lse.data_ptr(), part.data_ptr(), lp.data_ptr(),
+                                                       B, T, T, Hq, D, 0, 0, st()), "attn_merge")
+        return fn, None, B * T * Hq * D * (4 + 4 + 2), (acc, part)
+    raise SystemExit(f"unknown kernel {which}")
+
+
 def case_lmhead(a, dev, backward):
     from . import ops
     T, H, V = a.m, a.k, a.n
@@ -272,6 +335,9 @@ def main(argv=None) -> int:
         fn, flops, nbytes = case_adamw(a, dev)
     elif k == "ppo_loss":
         fn, flops, nbytes = case_ppo(a, dev)
+    elif k in ("rs_acc", "adamw_allgather", "bcast_store", "sp_norm_fwd", "attn_merge"):
+        fn, nbytes, keep = (lambda r: (r[0], r[2], r[3]))(case_peer_emulated(a, dev, k))
+        flops = None
     else:
         raise SystemExit(f"unknown kernel {k}")
     flush = _Flush(dev) if (nbytes is not None and nbytes < (512 << 20)) or (flops is not None and a.small) else None

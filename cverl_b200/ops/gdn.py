@@ -215,8 +215,14 @@ class _GdnChunked(torch.autograd.Function):
                 ctx.cfg = (scale, chunk, 0, T // chunk, S0 is not None)
                 ctx.native = True
                 ctx.keep = keep
+                ctx.states_kept = True
                 if keep:   # the backward kernels reuse the chunk-local operands instead of recomputing them
-                    ctx.save_for_backward(q, k, v, beta, g, Vn, SsT.transpose(-1, -2), Sf, pre["W"], pre["Kd"],
+                    ctx.states_kept = gdn_native.keep_states(B, H, T // chunk)
+                    if ctx.states_kept:
+                        a, b = Vn, SsT.transpose(-1, -2)
+                    else:  # regenerated in the backward pass from U and the initial state
+                        a, b = pre["U"], (S0 if S0 is not None else q.new_empty(0))
+                    ctx.save_for_backward(q, k, v, beta, g, a, b, Sf, pre["W"], pre["Kd"],
                                           pre["Qd"], pre["P"], pre["egam"], pre["Tm"], pre["aux"])
                 else:
                     ctx.save_for_backward(q, k, v, beta, g, Vn, SsT.transpose(-1, -2), Sf)
@@ -253,8 +259,11 @@ class _GdnChunked(torch.autograd.Function):
             q, k, v, beta, g, Vn, Ss, Sf, W_, Kd_, Qd_, P_, eg_, Tm_, aux_ = ctx.saved_tensors
             from . import gdn_native
             pre = dict(W=W_, Kd=Kd_, Qd=Qd_, P=P_, egam=eg_, Tm=Tm_, aux=aux_)
-            dq, dk, dv, dbeta, dg, dS0 = gdn_native.chunk_backward(q, k, v, beta, scale, pre, Vn,
-                                                                   Ss.transpose(-1, -2), Sf, do, dSf)
+            if ctx.states_kept:
+                SsT = Ss.transpose(-1, -2)
+            else:
+                Vn, SsT = gdn_native.regenerate_states(W_, Vn, Kd_, eg_, Ss if has_s0 else None)
+            dq, dk, dv, dbeta, dg, dS0 = gdn_native.chunk_backward(q, k, v, beta, scale, pre, Vn, SsT, Sf, do, dSf)
             return (dq, dk, dv, dbeta.to(beta.dtype), dg.to(g.dtype), (dS0 if has_s0 else None), None, None)
         if ctx.native:
             q, k, v, beta, g, Vn, Ss, Sf = ctx.saved_tensors
@@ -418,16 +427,24 @@ class _GdnPacked(torch.autograd.Function):
         from . import gdn_native
         q, k, v = _GdnPacked._views(mixed, H)
         o, Sf, Vn, SsT, pre = gdn_native.chunk_forward(q, k, v, beta, g, S0, scale, keep_prep=True)
-        ctx.cfg = (scale, H, S0 is not None)
-        ctx.save_for_backward(mixed, beta, g, Vn, SsT, Sf, pre["W"], pre["Kd"], pre["Qd"], pre["P"], pre["egam"],
+        B, T = mixed.shape[:2]
+        kept = gdn_native.keep_states(B, H, T // 64)
+        ctx.cfg = (scale, H, S0 is not None, kept)
+        if kept:
+            a, b = Vn, SsT
+        else:   # the backward pass regenerates V' and the states from U and the initial state
+            a, b = pre["U"], (S0 if S0 is not None else mixed.new_empty(0))
+        ctx.save_for_backward(mixed, beta, g, a, b, Sf, pre["W"], pre["Kd"], pre["Qd"], pre["P"], pre["egam"],
                               pre["Tm"], pre["aux"])
         return o, Sf
 
     @staticmethod
     def backward(ctx, do, dSf):
         from . import gdn_native
-        scale, H, has_s0 = ctx.cfg
+        scale, H, has_s0, kept = ctx.cfg
         mixed, beta, g, Vn, SsT, Sf, W_, Kd_, Qd_, P_, eg_, Tm_, aux_ = ctx.saved_tensors
+        if not kept:
+            Vn, SsT = gdn_native.regenerate_states(W_, Vn, Kd_, eg_, SsT if has_s0 else None)
         q, k, v = _GdnPacked._views(mixed, H)
         d_mixed = torch.empty(mixed.shape, dtype=mixed.dtype, device=mixed.device)
         pre = dict(W=W_, Kd=Kd_, Qd=Qd_, P=P_, egam=eg_, Tm=Tm_, aux=aux_)

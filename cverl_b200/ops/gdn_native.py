@@ -104,6 +104,65 @@ def chunk_prep(q, k, v, beta, g, scale: float, eps: float = 1e-6, want_aux: bool
     return out
 
 
+def state_mode() -> str:
+    """What the backward pass gets of the per-chunk recurrent states: ``full`` (kept from the forward pass),
+    ``recompute`` (regenerated by one more launch of the forward scan) or ``budget`` (kept while they fit a byte
+    budget).  Same environment switches as the reference (src/model/qwen3_5_text.cc:288-339):
+    ``CVERL_LINEAR_ATTN_STATE_MODE`` = none | recompute | full | chunk | checkpoint, ``CVERL_LINEAR_ATTN_SAVE_STATES=1``
+    (= full), ``CVERL_LINEAR_ATTN_CHECKPOINT_MAX_BYTES_MB`` and ``CVERL_LINEAR_ATTN_CHECKPOINT_INTERVAL``.
+
+    The reference's chunk mode keeps every k-th state and replays k chunks at a time; the scan kernel here replays
+    a whole sequence from its initial state in one launch (0.26 ms for 32 x 1280 tokens), so intermediate
+    checkpoints would shorten nothing: chunk mode keeps ALL states of a call while they fit the budget and none
+    otherwise.  The interval is validated and otherwise unused."""
+    import os
+    mode = os.environ.get("CVERL_LINEAR_ATTN_STATE_MODE", "")
+    interval = os.environ.get("CVERL_LINEAR_ATTN_CHECKPOINT_INTERVAL", "")
+    if interval and int(interval) <= 0:
+        raise ValueError("CVERL_LINEAR_ATTN_CHECKPOINT_INTERVAL must be positive")
+    if mode:
+        if mode in ("none", "recompute"):
+            return "recompute"
+        if mode == "full":
+            return "full"
+        if mode in ("chunk", "checkpoint"):
+            return "budget"
+        raise ValueError("CVERL_LINEAR_ATTN_STATE_MODE must be none|recompute|full|chunk|checkpoint")
+    if os.environ.get("CVERL_LINEAR_ATTN_SAVE_STATES", "") == "1":
+        return "full"
+    return "budget"
+
+
+def keep_states(B: int, H: int, n: int) -> bool:
+    """Whether a call with ``n`` chunks per (batch, head) keeps its states (bf16 S_c 128 x 128 and V' 64 x 128)."""
+    import os
+    mode = state_mode()
+    if mode != "budget":
+        return mode == "full"
+    budget = os.environ.get("CVERL_LINEAR_ATTN_CHECKPOINT_MAX_BYTES_MB", "")
+    if not budget:
+        return True
+    if int(budget) <= 0:
+        raise ValueError("CVERL_LINEAR_ATTN_CHECKPOINT_MAX_BYTES_MB must be positive")
+    return B * H * n * (128 * 128 + 64 * 128) * 2 <= int(budget) * 1024 * 1024
+
+
+def regenerate_states(W, U, Kd, egam, S0):
+    """(V', S^T per chunk) again from the scan's inputs: the forward scan kernel, final state discarded."""
+    B, H, n = W.shape[:3]
+    dev = W.device
+    s0 = S0.float().contiguous() if S0 is not None else None
+    Vn = torch.empty((B, H, n, 64, 128), dtype=torch.bfloat16, device=dev)
+    SsT = torch.empty((B, H, n, 128, 128), dtype=torch.bfloat16, device=dev)
+    Sf = torch.empty((B, H, 128, 128), dtype=torch.float32, device=dev)
+    rc = nv.cuda().cvb_gdn_scan_fwd(W.data_ptr(), U.data_ptr(), Kd.data_ptr(), egam.data_ptr(), nv.ptr(s0),
+                                    Sf.data_ptr(), Vn.data_ptr(), SsT.data_ptr(), B * H, n,
+                                    nv.status_word(dev).data_ptr(), nv.stream())
+    nv.check(rc, "cvb_gdn_scan_fwd")
+    count_launch()
+    return Vn, SsT
+
+
 def chunk_forward(q, k, v, beta, g, S0, scale: float, keep_prep: bool = False):
     """Full chunked forward on the three kernels. Returns (o [B,T,H,128] bf16, Sf fp32, Vn, SsT, prep) where
     ``prep`` is the prep kernel's output dict (with T and the per-token scalars when ``keep_prep``)."""

@@ -311,3 +311,45 @@ def test_gdn_packed_entry_matches_split_entry():
         res.append((o.detach(), Sf, mixed.grad, beta.grad, g.grad))
     for a, b in zip(*res):
         assert torch.equal(a, b)
+
+
+def test_gdn_state_modes_give_identical_gradients(monkeypatch):
+    """Keeping the per-chunk states for the backward pass, regenerating them with one more forward-scan launch, and
+    letting a byte budget decide are the same computation: outputs and gradients agree bit for bit, with and
+    without an initial state, and the regenerating mode saves less."""
+    from cverl_b200.ops import gdn, gdn_native
+    from cverl_b200 import _native as nv
+    torch.manual_seed(11)
+    B, T, H = 2, 512, 2
+    base = torch.randn(B, T, 3 * H * 128, device=_dev(), dtype=torch.bfloat16)
+    beta0 = torch.sigmoid(torch.randn(B, T, H, device=_dev()))
+    g0 = -0.5 * torch.rand(B, T, H, device=_dev())
+    S0 = 0.1 * torch.randn(B, H, 128, 128, device=_dev())
+    scale = 128 ** -0.5
+    for init in (None, S0):
+        res, saved = [], []
+        for env in ({"CVERL_LINEAR_ATTN_STATE_MODE": "full"}, {"CVERL_LINEAR_ATTN_STATE_MODE": "none"},
+                    {"CVERL_LINEAR_ATTN_STATE_MODE": "chunk", "CVERL_LINEAR_ATTN_CHECKPOINT_MAX_BYTES_MB": "1"},
+                    {"CVERL_LINEAR_ATTN_SAVE_STATES": "1"}):
+            for key in ("CVERL_LINEAR_ATTN_STATE_MODE", "CVERL_LINEAR_ATTN_CHECKPOINT_MAX_BYTES_MB",
+                        "CVERL_LINEAR_ATTN_SAVE_STATES"):
+                monkeypatch.delenv(key, raising=False)
+            for key, val in env.items():
+                monkeypatch.setenv(key, val)
+            mixed = base.clone().requires_grad_(True)
+            beta, g = beta0.clone().requires_grad_(True), g0.clone().requires_grad_(True)
+            s0 = init.clone().requires_grad_(True) if init is not None else None
+            o, Sf = gdn.gated_delta_rule_packed(mixed, beta, g, s0, scale=scale, heads=H)
+            saved.append(sum(t.numel() * t.element_size() for t in o.grad_fn.saved_tensors))
+            torch.manual_seed(12)
+            (o.float() * torch.randn_like(o, dtype=torch.float32)).sum().backward()
+            nv.check_status()
+            res.append((o.detach(), Sf.detach(), mixed.grad, beta.grad, g.grad) + ((s0.grad,) if s0 is not None else ()))
+        for other in res[1:]:
+            for a, b in zip(res[0], other):
+                assert torch.equal(a, b)
+        # 2 x 2 x 8 chunk states of 48 KB (S and V') are 1.5 MB: over the 1 MB budget, so that mode regenerates too
+        assert saved[1] < saved[0] and saved[3] == saved[0] and saved[2] == saved[1]
+    monkeypatch.setenv("CVERL_LINEAR_ATTN_STATE_MODE", "sometimes")
+    with pytest.raises(ValueError):
+        gdn_native.state_mode()
