@@ -125,6 +125,48 @@ def build_host(force: bool = False, verbose: bool = False) -> Path:
     return HOST_LIB
 
 
+def _sanitizer_cxx(flags) -> str:
+    """The first C++ compiler whose installation has the sanitizer runtime (a toolchain may ship without it)."""
+    import shutil
+    import tempfile
+    seen = []
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), "/usr/bin/g++", shutil.which("clang++")):
+        if not cand or cand in seen or not Path(cand).exists():
+            continue
+        seen.append(cand)
+        with tempfile.TemporaryDirectory() as d:
+            src = Path(d) / "probe.cc"
+            src.write_text("int main() { return 0; }\n")
+            r = subprocess.run([cand, *flags, str(src), "-o", str(Path(d) / "probe")], capture_output=True)
+            if r.returncode == 0:
+                return cand
+    raise RuntimeError("no C++ compiler with the runtime for " + " ".join(flags) + " (tried " + ", ".join(seen) + ")")
+
+
+def build_sanitized(kind: str, verbose: bool = False) -> Path:
+    """The host runtime and its self-test driver (``csrc/host_selftest_main.cc``) as ONE executable built with a
+    sanitizer: ``kind`` = "address" (AddressSanitizer + UBSan) or "thread" (ThreadSanitizer).  Returns the path;
+    run it on a CPU box - exit code 0 and no sanitizer report is the pass criterion.  The executable links the
+    sources directly (a sanitized shared library cannot be loaded into an unsanitized Python)."""
+    flags = {"address": ["-fsanitize=address,undefined", "-fno-omit-frame-pointer"],
+             "thread": ["-fsanitize=thread"]}[kind]
+    srcs = sorted(p for p in (PKG / "csrc").glob("*.cc") if not p.name.endswith("_main.cc")
+                  and not p.name.endswith("_fixture.cc"))
+    LIB_DIR.mkdir(parents=True, exist_ok=True)
+    exe = LIB_DIR / f"host_selftest_{kind}"
+    newest = max(_newest(srcs), _newest(list((PKG / "csrc" / "include").rglob("*.h"))),
+                 (PKG / "csrc" / "host_selftest_main.cc").stat().st_mtime)
+    if exe.exists() and exe.stat().st_mtime >= newest:
+        return exe
+    if verbose:
+        print(f"[g++ -fsanitize={kind}] host runtime + self-test", flush=True)
+    cxx = _sanitizer_cxx(flags)
+    base = [f for f in CXX_FLAGS if f not in ("-O2", "-O3", "-fPIC")]
+    _run([cxx, *base, "-O1", "-g", *flags, "-I", str(PKG / "csrc" / "include"), *map(str, srcs),
+          str(PKG / "csrc" / "host_selftest_main.cc"), "-o", str(exe), "-ldl", "-lrt", "-pthread"])
+    return exe
+
+
 def _nccl_paths():
     """(include dir, library file) of the NCCL that ``torch`` uses, or (None, None)."""
     import site
@@ -164,5 +206,8 @@ def build_all(force: bool = False, verbose: bool = False) -> None:
 
 
 if __name__ == "__main__":
+    if "--sanitize" in sys.argv:
+        print("built:", build_sanitized(sys.argv[sys.argv.index("--sanitize") + 1], verbose=True))
+        sys.exit(0)
     build_all(force="--force" in sys.argv, verbose=True)
     print("built:", CUDA_LIB, HOST_LIB)

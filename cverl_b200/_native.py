@@ -112,6 +112,7 @@ _CUDA_PROTOS = {
     "cvb_gdn_decode_step": "p l ii pp i p pp l pp pp i p",
     "cvb_router_topk_fwd": "p l iii pp p",
     "cvb_router_topk_bwd": "pppp l iii p p",
+    "cvb_expert_layout": "p l ii ppp i pp p",
 }
 
 

@@ -59,6 +59,9 @@ def main(argv=None) -> int:
     ap.add_argument("--model-dir", default="")
     ap.add_argument("--backend", default="nccl", choices=["nccl", "gloo"])
     ap.add_argument("--seed", type=int, default=17)
+    ap.add_argument("--weight-push", default="nccl", choices=["nccl", "symm", "nvls"],
+                    help="trainer -> rollout weights: library send / recv per bucket, stores into peer-mapped receive "
+                         "buffers by this package's kernel, or one multicast store through the NVSwitch (CUDA only)")
     a = ap.parse_args(argv)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -86,6 +89,12 @@ def main(argv=None) -> int:
         kind="tiny" if a.policy == "tiny" else "qwen3_5", vocab_size=tok.vocab_size, hidden_size=a.hidden_dim,
         pad_id=max(tok.pad_id, 0), model_dir=a.model_dir)).to_device(device)
     params = module_parameter_views(policy)
+    pusher = None
+    if a.weight_push != "nccl":
+        if a.backend != "nccl":
+            raise SystemExit("--weight-push symm / nvls needs --backend nccl (CUDA peer memory)")
+        from ..parallel.weight_sync import PeerMemoryWeightPush
+        pusher = PeerMemoryWeightPush(params, device, T, world, a.weight_push)
     version = 0
     if is_trainer:
         opt = torch.optim.AdamW(policy.parameters(), lr=a.lr)
@@ -141,7 +150,11 @@ def main(argv=None) -> int:
                     f"mean_reward={float(stats[1] / stats[2].clamp_min(1)):.4f} sequences={int(stats[2])} "
                     f"max_staleness={stale} weight_version={version}")
         # ---- weight push: each trainer to the rollout ranks it serves ------------------------------------
-        if is_trainer:
+        if pusher is not None:
+            pusher.push(rank, my_rollouts)
+            if not is_trainer:
+                version += 1
+        elif is_trainer:
             for dst in my_rollouts:
                 send_parameter_shards(params, comm, dst)
         else:

@@ -135,3 +135,148 @@ extern "C" int cvb_router_topk_bwd(const float* logits, const long long* idx, co
       logits, idx, w, dw, T, E, k, norm_topk, dlogits);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Expert-layout bookkeeping for the grouped expert GEMM, in four small launches and no host read.
+//
+// Given one expert id per (token, k) entry, the grouped GEMM wants the entries grouped by expert, every expert's
+// segment padded to a multiple of 128 rows, and a table naming the expert of each 128-row tile.  The layout keeps
+// the entries of an expert in their original order (a stable counting sort), so that results do not depend on
+// the block schedule:
+//   1. expert_rank_kernel    per 256 entries: each entry's rank among the same-expert entries of its block
+//                            (warp match + per-warp counts), and the block's per-expert counts
+//   2. expert_prefix_kernel  a warp per expert: exclusive prefix of the block counts over the blocks;
+//      expert_offsets_kernel one block: the padded segment bounds and the tile table
+//   3. expert_place_kernel   row of every entry = padded segment start + prefix of its block + rank in block
+// The reference (and the tensor-op fallback of this package) builds the same layout from bincount, sort, cumsum,
+// index_put_, nonzero and index_select calls with host reads of the capacities
+// (src/distributed/expert_parallel.cc:116-136, src/model/qwen3_5_text.cc:882-923).
+// ---------------------------------------------------------------------------------------------------
+namespace cvb {
+
+constexpr int EL_THREADS = 256;
+constexpr int EL_MAX_E = 257;     // 256 experts + the bucket of unused entries (id == E)
+
+__global__ void __launch_bounds__(EL_THREADS)
+expert_rank_kernel(const long long* __restrict__ ids, long long n, int E, int* __restrict__ rank_in_block,
+                   int* __restrict__ block_counts, int* __restrict__ bad) {
+  __shared__ int warp_cnt[EL_THREADS / 32][EL_MAX_E];
+  const int t = threadIdx.x, w = t >> 5, lane = t & 31;
+  for (int i = t; i < (EL_THREADS / 32) * EL_MAX_E; i += EL_THREADS) (&warp_cnt[0][0])[i] = 0;
+  __syncthreads();
+  const long long i = static_cast<long long>(blockIdx.x) * EL_THREADS + t;
+  long long e64 = i < n ? ids[i] : -1;
+  if (i < n && (e64 < 0 || e64 >= E)) {       // an id outside the table: reported, entry parked on the last row
+    atomicCAS(bad, 0, ERR_BAD_ARG);
+    e64 = -1;
+  }
+  const int e = static_cast<int>(e64);
+  const unsigned peers = __match_any_sync(0xffffffffu, e);
+  const int r_warp = __popc(peers & ((1u << lane) - 1u));
+  if (e >= 0 && r_warp == 0) warp_cnt[w][e] = __popc(peers);
+  __syncthreads();
+  int base = 0;
+  if (e >= 0) {
+    for (int ww = 0; ww < w; ++ww) base += warp_cnt[ww][e];
+    rank_in_block[i] = base + r_warp;
+  }
+  for (int ee = t; ee < E; ee += EL_THREADS) {
+    int s = 0;
+#pragma unroll
+    for (int ww = 0; ww < EL_THREADS / 32; ++ww) s += warp_cnt[ww][ee];
+    block_counts[static_cast<long long>(blockIdx.x) * E + ee] = s;
+  }
+}
+
+// block_counts [nblocks, E] -> exclusive prefix over blocks in place, totals [E]: one warp per expert walks the
+// blocks 32 at a time with a shuffle scan
+__global__ void __launch_bounds__(EL_THREADS)
+expert_prefix_kernel(int* __restrict__ block_counts, int nblocks, int E, int* __restrict__ totals) {
+  const int e = blockIdx.x * (EL_THREADS / 32) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (e >= E) return;
+  int carry = 0;
+  for (int b0 = 0; b0 < nblocks; b0 += 32) {
+    const int b = b0 + lane;
+    const int c = b < nblocks ? block_counts[static_cast<long long>(b) * E + e] : 0;
+    int incl = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (b < nblocks) block_counts[static_cast<long long>(b) * E + e] = carry + incl - c;
+    carry += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0) totals[e] = carry;
+}
+
+// totals [E] -> offsets [E + 1] (padded segment bounds, int32) and tile_group [n_tiles] (expert of each tile_m-row
+// tile, -1 past the end)
+__global__ void __launch_bounds__(EL_THREADS)
+expert_offsets_kernel(const int* __restrict__ totals, int E, int tile_m, int* __restrict__ offsets,
+                      int* __restrict__ tile_group, int n_tiles) {
+  __shared__ int padded[EL_MAX_E + 1];
+  const int t = threadIdx.x;
+  for (int e = t; e < E; e += EL_THREADS) padded[e + 1] = (totals[e] + tile_m - 1) / tile_m * tile_m;
+  __syncthreads();
+  if (t == 0) {
+    padded[0] = 0;
+    for (int e = 0; e < E; ++e) padded[e + 1] += padded[e];
+  }
+  __syncthreads();
+  for (int e = t; e <= E; e += EL_THREADS) offsets[e] = padded[e];
+  for (int tile = t; tile < n_tiles; tile += EL_THREADS) {
+    const int row = tile * tile_m;
+    int g = -1;
+    if (row < padded[E]) {
+      int lo = 0, hi = E;                      // first e with padded[e + 1] > row
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (padded[mid + 1] > row) hi = mid; else lo = mid + 1;
+      }
+      g = lo;
+    }
+    tile_group[tile] = g;
+  }
+}
+
+__global__ void __launch_bounds__(EL_THREADS)
+expert_place_kernel(const long long* __restrict__ ids, long long n, int E, const int* __restrict__ rank_in_block,
+                    const int* __restrict__ block_prefix, const int* __restrict__ offsets,
+                    long long* __restrict__ row_of_entry, long long last_row) {
+  const long long i = static_cast<long long>(blockIdx.x) * EL_THREADS + threadIdx.x;
+  if (i >= n) return;
+  const long long e = ids[i];
+  if (e < 0 || e >= E) {                      // already reported by expert_rank_kernel; any valid row will do
+    row_of_entry[i] = last_row;
+    return;
+  }
+  // bucket E - 1 is the "unused" bucket: offsets[E - 1] is the end of the last real segment
+  long long r = offsets[e] + block_prefix[static_cast<long long>(blockIdx.x) * E + e] + rank_in_block[i];
+  row_of_entry[i] = r <= last_row ? r : last_row;
+}
+
+}  // namespace cvb
+
+// ids in [0, E) name an expert; id == E marks an unused entry (placed after the last segment, as the tensor-op
+// version does); anything else sets *bad = ERR_BAD_ARG.  scratch: int32 [n + (nblocks + 1) * (E + 1)] with
+// nblocks = ceil(n / 256).  Every row written is inside [0, n_tiles * tile_m).
+extern "C" int cvb_expert_layout(const long long* ids, long long n, int E, int tile_m, int* scratch, int* offsets,
+                                 int* tile_group, int n_tiles, long long* row_of_entry, int* bad, void* stream) {
+  using namespace cvb;
+  if (E <= 0 || E + 1 > EL_MAX_E || tile_m <= 0 || n < 0 || n >= (1ll << 31) - EL_THREADS || n_tiles <= 0) return -1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int nblocks = static_cast<int>((n + EL_THREADS - 1) / EL_THREADS);
+  const int Eb = E + 1;
+  int* rank = scratch;
+  int* counts = scratch + n;
+  int* totals = counts + static_cast<long long>(nblocks) * Eb;
+  if (nblocks > 0)
+    expert_rank_kernel<<<nblocks, EL_THREADS, 0, st>>>(ids, n, Eb, rank, counts, bad);
+  expert_prefix_kernel<<<(Eb + EL_THREADS / 32 - 1) / (EL_THREADS / 32), EL_THREADS, 0, st>>>(counts, nblocks, Eb, totals);
+  expert_offsets_kernel<<<1, EL_THREADS, 0, st>>>(totals, E, tile_m, offsets, tile_group, n_tiles);
+  if (nblocks > 0)
+    expert_place_kernel<<<nblocks, EL_THREADS, 0, st>>>(ids, n, Eb, rank, counts, offsets, row_of_entry,
+                                                        static_cast<long long>(n_tiles) * tile_m - 1);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -72,16 +72,43 @@ def sort_by_expert(expert_ids: torch.Tensor, num_experts: int):
     return order, dest, tile_group.to(torch.int32), offsets.to(torch.int32), m_pad
 
 
+def expert_layout(expert_ids: torch.Tensor, num_experts: int):
+    """``(row, tile_group, offsets, m_pad)``: ``row[i]`` is the row of entry ``i`` in the expert-grouped, 128-row
+    padded matrix the grouped GEMM reads (entries of one expert keep their order), ``tile_group`` the expert of
+    each 128-row tile (-1 = unused), ``offsets`` int32 [E+1] the padded segment bounds, ``m_pad`` a static upper
+    bound of the padded row count.  On CUDA the table comes from ``cvb_expert_layout`` (four small launches, no
+    sort, no host read); elsewhere from ``sort_by_expert``."""
+    n = expert_ids.numel()
+    dev = expert_ids.device
+    m_pad = (n + num_experts * (TILE_M - 1) + TILE_M - 1) // TILE_M * TILE_M
+    if expert_ids.is_cuda and expert_ids.dtype == torch.int64 and num_experts <= 256 and n > 0:
+        from .. import _native as nv
+        ids = expert_ids.contiguous()
+        nblocks = (n + 255) // 256
+        scratch = torch.empty(n + (nblocks + 1) * (num_experts + 1), dtype=torch.int32, device=dev)
+        offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+        tile_group = torch.empty(m_pad // TILE_M, dtype=torch.int32, device=dev)
+        row = torch.empty(n, dtype=torch.int64, device=dev)
+        nv.check(nv.cuda().cvb_expert_layout(ids.data_ptr(), n, num_experts, TILE_M, scratch.data_ptr(),
+                                             offsets.data_ptr(), tile_group.data_ptr(), m_pad // TILE_M,
+                                             row.data_ptr(), nv.status_word(dev).data_ptr(), nv.stream()),
+                 "cvb_expert_layout")
+        ops.launch_counter["n"] += 4
+        return row, tile_group, offsets, m_pad
+    order, dest, tile_group, offsets, m_pad = sort_by_expert(expert_ids, num_experts)
+    row = torch.empty_like(order)
+    row[order] = dest
+    return row, tile_group, offsets, m_pad
+
+
 def _local_experts(rows: torch.Tensor, local_ids: torch.Tensor, gate_up, down, num_local: int) -> torch.Tensor:
     """Runs ``rows[j]`` through local expert ``local_ids[j]``; returns outputs in the input order."""
-    order, dest, tile_group, offsets, m_pad = sort_by_expert(local_ids, num_local)
-    xp = rows.new_zeros((m_pad, rows.shape[1])).index_copy(0, dest, rows[order])
+    row, tile_group, offsets, m_pad = expert_layout(local_ids, num_local)
+    xp = rows.new_zeros((m_pad, rows.shape[1])).index_copy(0, row, rows)
     gu = grouped_linear(xp, gate_up, tile_group, offsets)
     act = ops.swiglu(gu)
     yp = grouped_linear(act, down, tile_group, offsets)
-    inv = torch.empty_like(order)
-    inv[order] = torch.arange(order.numel(), device=order.device)
-    return yp[dest][inv]
+    return yp[row]
 
 
 def moe_mlp(model, x: torch.Tensor, layer: int) -> torch.Tensor:

@@ -123,3 +123,57 @@ def recv_parameter_shards(params: Sequence[ParameterView], comm: Collectives, sr
         stats.tensors += len(bucket)
         stats.bytes += like.numel() * like.element_size()
     return stats
+
+
+class PeerMemoryWeightPush:
+    """Trainer -> rollout weight push by this package's own kernels instead of library send / recv.
+
+    ``mode="symm"``: every trainer stores the flattened parameters into the peer-mapped receive buffer of each
+    rollout rank it serves (``cvb_broadcast_store``: one read, one store per destination, plain NVLink stores).
+    ``mode="nvls"``: the trainers hold identical weights after their gradient all-reduce, so trainer t multicasts
+    slice t of the flat buffer through the NVSwitch multicast address (``multimem.st``) and every rank's buffer
+    ends up with all of it, each sender's links carrying 1 / T of the weights once.
+    Both end with a flag barrier over all ranks; the rollout ranks then copy the buffer into their parameters.
+    All parameters must share one dtype.  Collective constructor over the default group.
+    (Reference: ncclBroadcast / send-recv per bucket, src/distributed/weight_sync.cc:86-189.)"""
+
+    def __init__(self, params: Sequence[ParameterView], device, trainers: int, world: int, mode: str = "symm"):
+        import torch.distributed as dist
+        self.params = list(params)
+        dt = {pv.tensor.dtype for pv in self.params}
+        if len(dt) != 1:
+            raise ValueError("PeerMemoryWeightPush needs parameters of one dtype")
+        self.dtype = dt.pop()
+        self.numel = sum(pv.tensor.numel() for pv in self.params)
+        esz = torch.empty((), dtype=self.dtype).element_size()
+        self.nbytes = (self.numel * esz + 255) // 256 * 256
+        self.trainers, self.world, self.mode = trainers, world, mode
+        if mode == "symm":
+            from .symm import P2pBroadcaster, SymmetricHeap
+            self.bc = P2pBroadcaster(SymmetricHeap(dist.group.WORLD, device), self.nbytes)
+        elif mode == "nvls":
+            from .nvls import NvlsBroadcaster
+            self.bc = NvlsBroadcaster(dist.group.WORLD, device, self.nbytes)
+        else:
+            raise ValueError("mode must be symm or nvls")
+        self.recv = self.bc.tensor(self.numel, self.dtype)
+
+    def push(self, rank: int, my_rollouts: Sequence[int]) -> None:
+        """Called by every rank once per weight version (trainers send, everyone synchronises, rollout ranks load)."""
+        if rank < self.trainers:
+            flat = _flatten(self.params)
+            padded = (self.numel + 7) // 8 * 8               # whole 16-byte pieces for every dtype of 2+ bytes
+            if padded != self.numel:
+                flat = torch.nn.functional.pad(flat, (0, padded - self.numel))
+            if self.mode == "symm":
+                if my_rollouts:
+                    self.bc.push(flat, list(my_rollouts))
+            else:
+                per = (padded // self.trainers + 7) // 8 * 8
+                lo = min(rank * per, padded)
+                hi = padded if rank == self.trainers - 1 else min(lo + per, padded)
+                if hi > lo:
+                    self.bc.push(flat[lo:hi], lo * flat.element_size())
+        self.bc.sync()
+        if rank >= self.trainers:
+            _scatter_back(self.params, self.recv)

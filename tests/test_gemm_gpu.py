@@ -197,6 +197,33 @@ def test_grouped_linear_fwd_bwd():
     assert _rel_err(w.grad, wr.grad) < 8e-3
 
 
+def test_expert_layout_kernel_matches_tensor_ops():
+    """The bookkeeping kernels (stable counting sort into 128-row padded expert segments) give the same rows, segment
+    bounds and tile table as the argsort / bincount / cumsum / searchsorted version, for experts without tokens,
+    unused entries (id == E), one block and many blocks; an id outside the table is reported, not followed."""
+    from cverl_b200 import _native as nv
+    from cverl_b200.models.moe import expert_layout, sort_by_expert
+    g = torch.Generator(device=_dev()).manual_seed(31)
+    for E, n, unused in ((6, 700, False), (128, 40000, False), (16, 5000, True), (256, 300, True), (3, 1, False)):
+        ids = torch.randint(0, E + (1 if unused else 0), (n,), device=_dev(), generator=g)
+        if E > 4:
+            ids[ids == 4] = 3                                   # an expert without tokens
+        row, tile_group, offsets, m_pad = expert_layout(ids, E)
+        order, dest, tg_ref, off_ref, m_ref = sort_by_expert(ids, E)
+        want = torch.empty_like(order)
+        want[order] = dest
+        nv.check_status()
+        assert m_pad == m_ref and torch.equal(offsets, off_ref) and torch.equal(tile_group, tg_ref)
+        assert torch.equal(row, want)
+        assert int(row.max()) < m_pad and row.unique().numel() == n
+    bad = torch.tensor([0, 1, 99, -5, 2], device=_dev())
+    row, _, _, m_pad = expert_layout(bad, 4)
+    torch.cuda.synchronize()
+    assert int(row.min()) >= 0 and int(row.max()) < m_pad          # every row stays inside the buffer
+    with pytest.raises(RuntimeError):
+        nv.check_status()                                          # ... and the bad ids are reported
+
+
 def test_moe_model_gpu_matches_cpu():
     from cverl_b200.models.config import Qwen35TextConfig
     from cverl_b200.models.qwen3_5 import Qwen35Model
