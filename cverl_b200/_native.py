@@ -41,6 +41,7 @@ class GemmArgs(C.Structure):
         ("lse", c_void_p), ("gscale", c_void_p), ("status", c_void_p),
         ("mirror", c_void_p * 7), ("n_mirror", C.c_int32),
         ("scatter_base", c_void_p * 8), ("scatter_rows", C.c_int32),
+        ("row_addr", c_void_p),
     ]
 
 

@@ -160,7 +160,11 @@ __device__ __forceinline__ void epilogue_slab(const GemmParams& p, int m0, int n
             if (grow < p.M) {
               const uint4 o = *reinterpret_cast<const uint4*>(stg + rr * Cfg::STG_ROW + ch * 16);
               const long long off = c_off + static_cast<long long>(grow) * p.ldc + cbase + ch * 8;
-              if (p.scatter_rows > 0) {
+              if (p.row_addr != nullptr) {
+                // per-row destination (MoE combine): the row's home buffer gets it, address 0 drops the row
+                const long long dst = p.row_addr[grow];
+                if (dst != 0) *reinterpret_cast<uint4*>(dst + static_cast<long long>(cbase + ch * 8) * 2) = o;
+              } else if (p.scatter_rows > 0) {
                 // reduce-scatter epilogue: the row block's owner gets the tile, nobody else
                 *reinterpret_cast<uint4*>(
                     reinterpret_cast<__nv_bfloat16*>(p.scatter_base[grow / p.scatter_rows]) + off) = o;
@@ -919,7 +923,14 @@ extern "C" int cvb_gemm_bf16(const CvbGemmArgs* a, void* stream_v) {
     // register -> global path for comparison.
     static const bool direct = [] { const char* e = getenv("CVERL_B200_GEMM_DIRECT_STORE"); return e && e[0] == '1'; }();
     p.staged_store = (a->epi == EPI_STORE_BF16 && a->N % 64 == 0 &&
-                      (a->n_mirror > 0 || a->scatter_rows > 0 || !direct)) ? 1 : 0;
+                      (a->n_mirror > 0 || a->scatter_rows > 0 || a->row_addr != nullptr || !direct)) ? 1 : 0;
+  }
+  p.row_addr = nullptr;
+  if (a->row_addr != nullptr) {
+    if (a->epi != EPI_STORE_BF16 || a->N % 64 != 0 || a->n_mirror != 0 || a->scatter_rows != 0 ||
+        a->k_group_offsets != nullptr)
+      return -6;
+    p.row_addr = a->row_addr;
   }
   p.scatter_rows = 0;
   if (a->scatter_rows != 0) {

@@ -57,6 +57,11 @@ typedef struct CvbGemmArgs {
   // over NVLink).  The caller folds the owner's row origin into each base pointer.
   void* scatter_base[8];
   int32_t scatter_rows;
+  // EPI_STORE_BF16 with row_addr != nullptr: output row r is stored ONLY at byte address row_addr[r] (+ 2 * col),
+  // rows with address 0 are dropped, C is not written.  The combine of expert-parallel MoE rides on the down
+  // projection's epilogue this way: every expert output row goes straight back into the buffer of the rank its
+  // token came from (own memory or a peer's, over NVLink).  Addresses must be 16-byte aligned; N % 64 == 0.
+  const long long* row_addr;
 } CvbGemmArgs;
 
 // Launches on `stream` (a cudaStream_t).  Returns 0 or a negative/CUDA error.
@@ -91,6 +96,7 @@ struct GemmParams {
   int n_mirror;
   void* scatter_base[8];
   int scatter_rows;
+  const long long* row_addr;
   int staged_store;  // bf16 epilogue through shared memory (coalesced 128-byte segments)
 };
 int make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,

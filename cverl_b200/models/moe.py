@@ -132,8 +132,16 @@ def moe_mlp(model, x: torch.Tensor, layer: int) -> torch.Tensor:
         eps = ctx.ep_symm
         peer_rank, peer_row, recv_expert = eps.plan(flat_e // e_local, flat_e % e_local, e_local)
         got_rows = ep_symm.dispatch(rows, peer_rank, peer_row, eps)
-        got_y = _local_experts(got_rows, recv_expert, gate_up, down, e_local)
-        y = ep_symm.combine(got_y, peer_rank, peer_row, eps)
+        if eps.fuse_combine and down.shape[1] % 64 == 0 and rows.shape[0] <= eps.cap:
+            # the down projection's epilogue stores every output row into its token's home rank: no separate
+            # combine, the expert outputs are never materialised on the expert rank
+            row, tile_group, offsets, m_pad = expert_layout(recv_expert, e_local)
+            xp = got_rows.new_zeros((m_pad, got_rows.shape[1])).index_copy(0, row, got_rows)
+            act = ops.swiglu(grouped_linear(xp, gate_up, tile_group, offsets))
+            y = ep_symm.fused_down_combine(act, down, tile_group, offsets, row, peer_rank, peer_row, eps)
+        else:
+            got_y = _local_experts(got_rows, recv_expert, gate_up, down, e_local)
+            y = ep_symm.combine(got_y, peer_rank, peer_row, eps)
     else:
         import torch.distributed as dist
         dst_rank = flat_e // e_local

@@ -77,12 +77,13 @@ def gemm_raw(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, M: int, N: int
              tile_group=None, b_group_rows: int = 0, b_total_rows: int = 0, k_group_offsets=None,
              num_groups: int = 0, c_group_stride: int = 0, targets=None, part_max=None, part_sum=None,
              tgt_logit=None, lse=None, gscale=None, max_ctas: int = 0, mirrors=(), scatter=None,
-             ldc: int = 0) -> None:
+             ldc: int = 0, row_addr=None) -> None:
     """One launch of the tcgen05 GEMM. Operands are 2-D bf16 tensors with unit inner stride.
 
     ``scatter=(bases, rows_per_owner)``: reduce-scatter epilogue - row block ``row // rows_per_owner`` of the
     bf16 result is stored only at raw address ``bases[block] + (row * ldc + col) * 2`` (``out`` is None and ``ldc``
-    is given)."""
+    is given).  ``row_addr`` (int64 [M], device): output row r is stored only at byte address ``row_addr[r]``
+    (0 drops it); ``out`` is None."""
     lib = nv.cuda()
     args = nv.GemmArgs()
     args.A, args.B, args.C = a.data_ptr(), b.data_ptr(), out.data_ptr() if out is not None else None
@@ -107,6 +108,7 @@ def gemm_raw(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, M: int, N: int
         args.scatter_rows = rows_per_owner
         for i, base in enumerate(bases):
             args.scatter_base[i] = base
+    args.row_addr = nv.ptr(row_addr)
     rc = lib.cvb_gemm_bf16(C.byref(args), nv.stream())
     nv.check(rc, "cvb_gemm_bf16")
     count_launch()

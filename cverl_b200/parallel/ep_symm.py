@@ -7,6 +7,10 @@ table of per-(source, destination) counts that the ranks push to each other firs
 synchronises with the host (the all-to-all path reads the split sizes on the host).  The backward of a
 dispatch is a gather, the backward of a combine is a scatter.
 
+The combine can also ride on the experts' down projection (``fused_down_combine``, the default): the grouped GEMM's
+epilogue stores every output row straight into the return buffer of the rank the token came from, addressed
+through a per-row table that ``plan`` builds from the (source rank, source entry) pair each dispatched row carries.
+
 Buffers have a fixed capacity (``capacity_rows`` per rank); rows beyond the received count are marked with
 the expert id ``num_local_experts`` and skipped by the grouped GEMM.  Overflow sets a device flag that
 ``check()`` turns into an exception.
@@ -62,16 +66,24 @@ class EpSymm:
         self.b_out = self.heap.alloc(capacity_rows * row)       # expert outputs to be pulled (forward)
         self.b_gout = self.heap.alloc(capacity_rows * row)      # gradient of the expert outputs (backward)
         self.b_grow = self.heap.alloc(capacity_rows * row)      # gradient of the dispatched rows (backward)
-        self.b_ids = self.heap.alloc(capacity_rows * 16)        # local expert id of each received row (int32 x4)
+        self.b_ids = self.heap.alloc(capacity_rows * 16)        # per received row: local expert, source entry, source rank
+        self.b_ret = self.heap.alloc(capacity_rows * row)       # expert outputs stored back by the down-projection GEMM
         self.b_cnt = self.heap.alloc(self.world * 32)           # count table [src][8] int32
         self.rows = self.b_rows.tensor(capacity_rows * hidden, torch.bfloat16).view(capacity_rows, hidden)
         self.out = self.b_out.tensor(capacity_rows * hidden, torch.bfloat16).view(capacity_rows, hidden)
         self.gout = self.b_gout.tensor(capacity_rows * hidden, torch.bfloat16).view(capacity_rows, hidden)
         self.grow = self.b_grow.tensor(capacity_rows * hidden, torch.bfloat16).view(capacity_rows, hidden)
         self.ids = self.b_ids.tensor(capacity_rows * 4, torch.int32).view(capacity_rows, 4)
+        self.ret = self.b_ret.tensor(capacity_rows * hidden, torch.bfloat16).view(capacity_rows, hidden)
+        self.ret_bases = torch.tensor(self.b_ret.peer_ptrs, dtype=torch.int64, device=self.device)
+        self.return_addr: Optional[torch.Tensor] = None         # set by ``plan``: see ``fused_down_combine``
         self.cnt = self.b_cnt.tensor(self.world * 8, torch.int32).view(self.world, 8)
         self.barrier = SymmBarrier(self.heap)
         self.overflow = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # down projection + combine in one GEMM (``fused_down_combine``); CVERL_B200_EP_FUSE_COMBINE=0 keeps them apart
+        import os
+        self.fuse_combine = os.environ.get("CVERL_B200_EP_FUSE_COMBINE", "1") != "0"
+        self.fused_combines = 0                                  # layers that took the fused path (for tests)
         if self.world > 8:
             raise ValueError("EpSymm supports up to 8 ranks per expert-parallel group")
 
@@ -108,10 +120,19 @@ class EpSymm:
         # expert ids travel as 16-byte rows
         idrow = torch.zeros((n, 4), dtype=torch.int32, device=dev)
         idrow[:, 0] = local_expert.to(torch.int32)
+        idrow[:, 1] = torch.arange(n, dtype=torch.int32, device=dev)     # where the expert's output goes back to
+        idrow[:, 2] = self.rank
         self._move(False, idrow, self.b_ids, peer_rank, peer_row, 16)
         self.barrier()
-        recv_expert = torch.where(torch.arange(self.cap, device=dev) < received, self.ids[:, 0].to(torch.int64),
+        valid = torch.arange(self.cap, device=dev) < received
+        recv_expert = torch.where(valid, self.ids[:, 0].to(torch.int64),
                                   torch.full((self.cap,), num_local, dtype=torch.int64, device=dev))
+        # byte address, in the SOURCE rank's return buffer, of the row each received entry's output belongs to
+        # (0 for unused capacity, and for a source rank / entry outside the tables: such a row is dropped)
+        src_rank, src_row = self.ids[:, 2].to(torch.int64), self.ids[:, 1].to(torch.int64)
+        ok = valid & (src_rank >= 0) & (src_rank < self.world) & (src_row >= 0) & (src_row < self.cap)
+        addr = self.ret_bases[src_rank.clamp(0, self.world - 1)] + src_row.clamp(0, self.cap - 1) * self.row_bytes
+        self.return_addr = torch.where(ok, addr, torch.zeros_like(addr))
         return peer_rank, peer_row, recv_expert
 
     def check(self) -> None:
@@ -176,3 +197,68 @@ def dispatch(rows: torch.Tensor, peer_rank, peer_row, eps: EpSymm) -> torch.Tens
 
 def combine(y: torch.Tensor, peer_rank, peer_row, eps: EpSymm) -> torch.Tensor:
     return _Combine.apply(y, peer_rank, peer_row, eps)
+
+
+class _DownCombine(torch.autograd.Function):
+    """The experts' down projection with the combine in its epilogue: every output row of the grouped GEMM is
+    stored straight into the return buffer of the rank its token came from (``row_addr``), so the expert ranks
+    neither materialise their outputs nor have them gathered.  ``act`` [m_pad, I] is expert-sorted and padded,
+    ``row`` [cap] the padded row of every received entry; returns the ``n`` rows this rank routed, in entry order.
+    Backward: the gradient rows travel to the expert ranks like any combine's (peer stores), then the grouped
+    input- and weight-gradient GEMMs run on them."""
+
+    @staticmethod
+    def forward(ctx, act, w, tile_group, group_offsets, row_addr, row, peer_rank, peer_row, eps: EpSymm):
+        from ..ops.gemm import gemm_raw
+        M, K = act.shape
+        E, N, _ = w.shape
+        n = peer_rank.numel()
+        eps.barrier()                                            # everyone has taken the previous layer's rows
+        gemm_raw(act, w.view(E * N, K), None, M, N, K, a_mn=False, b_mn=False, epi=nv.EPI_STORE_BF16,
+                 block_n=256 if N >= 256 else 128, tile_group=tile_group, b_group_rows=N, b_total_rows=E * N,
+                 row_addr=row_addr, ldc=N)
+        eps.barrier()                                            # every expert rank's stores have landed
+        out = eps.ret[:n].clone()
+        out.masked_fill_((peer_rank < 0).unsqueeze(-1), 0)       # entries that did not fit a receive buffer
+        ctx.eps = eps
+        ctx.save_for_backward(act, w, tile_group, group_offsets, row, peer_rank, peer_row)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        from ..ops.gemm import gemm_raw
+        eps = ctx.eps
+        act, w, tile_group, group_offsets, row, peer_rank, peer_row = ctx.saved_tensors
+        M, K = act.shape
+        E, N, _ = w.shape
+        eps.barrier()
+        eps.gout.zero_()
+        eps.barrier()                                            # cleared everywhere before anyone writes
+        eps._move(False, g.contiguous(), eps.b_gout, peer_rank, peer_row, eps.row_bytes)
+        eps.barrier()
+        dy = torch.zeros((M, N), dtype=torch.bfloat16, device=g.device).index_copy(0, row, eps.gout)
+        dact = None
+        if ctx.needs_input_grad[0]:
+            dact = torch.zeros((M, K), dtype=act.dtype, device=act.device)
+            gemm_raw(dy, w.view(E * N, K), dact, M, K, N, a_mn=False, b_mn=True, epi=nv.EPI_STORE_BF16,
+                     block_n=256 if K >= 256 else 128, tile_group=tile_group, b_group_rows=N, b_total_rows=E * N)
+        dw = None
+        if ctx.needs_input_grad[1]:
+            main_grad = getattr(w, "main_grad", None)
+            acc = main_grad if main_grad is not None else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+            gemm_raw(dy, act, acc.view(E * N, K), N, K, M, a_mn=True, b_mn=True, epi=nv.EPI_ATOMIC_F32,
+                     block_n=256 if K >= 256 else 128, k_group_offsets=group_offsets, num_groups=E,
+                     c_group_stride=N * K)
+            if main_grad is None:
+                dw = acc.to(w.dtype)
+        return dact, dw, None, None, None, None, None, None, None
+
+
+def fused_down_combine(act, w, tile_group, group_offsets, row, peer_rank, peer_row, eps: EpSymm) -> torch.Tensor:
+    """Down projection of the local experts whose epilogue IS the combine (see ``_DownCombine``).  ``row`` maps the
+    ``cap`` received entries to padded rows; ``eps.return_addr`` (from ``plan``) names each entry's home."""
+    m_pad = act.shape[0]
+    eps.fused_combines += 1
+    row_addr = torch.zeros(m_pad, dtype=torch.int64, device=act.device).index_copy(0, row, eps.return_addr)
+    return _DownCombine.apply(act.contiguous(), w, tile_group.to(torch.int32), group_offsets.to(torch.int32), row_addr,
+                              row, peer_rank, peer_row, eps)

@@ -615,28 +615,33 @@ def _ep_symm_rank(rank, world):
     dev = torch.device("cuda", rank)
     cfg = Qwen35TextConfig.tiny(moe=True, layers=2)
     outs = []
-    for use_symm in (False, True):
+    for mode in ("all_to_all", "symm", "symm_fused"):       # fused: the combine rides on the down projection's epilogue
         ctx = build_context(world, rank, tp=1, dp=1, ep=world)
-        if use_symm:
+        if mode != "all_to_all":
             ctx.ep_symm = EpSymm(ctx.ep_group, dev, capacity_rows=2 * 24 * cfg.num_experts_per_tok * world,
                                  hidden=cfg.hidden_size)
+            ctx.ep_symm.fuse_combine = mode == "symm_fused"
         model = Qwen35Model(cfg, dtype=torch.bfloat16, device=dev, ctx=ctx)
         model.init_weights(seed=5)
         ids = torch.randint(0, cfg.vocab_size, (2, 24), generator=torch.Generator().manual_seed(100 + rank)).to(dev)
-        lp = model.response_logprobs(ids, 8)
-        lp.sum().backward()
+        for _ in range(2):                                   # twice: the return buffer is reused layer after layer
+            model.flat.main_grad.zero_()
+            lp = model.response_logprobs(ids, 8)
+            lp.sum().backward()
         for p in list(model.flat.params.values()) + list(model.fused.values()):
             if p.grad is not None:
                 p.main_grad.add_(p.grad.float())
                 p.grad = None
         torch.cuda.synchronize()
         nv.check_status()
-        if use_symm:
+        if mode != "all_to_all":
             ctx.ep_symm.check()
+            assert ctx.ep_symm.fused_combines == (2 * cfg.num_hidden_layers if mode == "symm_fused" else 0)
         outs.append((lp.detach().float().clone(), model.flat.main_grad.clone()))
-    (lp_a, g_a), (lp_b, g_b) = outs
-    torch.testing.assert_close(lp_b, lp_a, rtol=2e-2, atol=2e-2)
-    assert ((g_b - g_a).norm() / g_a.norm()).item() < 2e-2
+    (lp_a, g_a) = outs[0]
+    for lp_b, g_b in outs[1:]:
+        torch.testing.assert_close(lp_b, lp_a, rtol=2e-2, atol=2e-2)
+        assert ((g_b - g_a).norm() / g_a.norm()).item() < 2e-2
     dist.barrier()
 
 
