@@ -80,6 +80,7 @@ def main(argv=None) -> int:
         raise SystemExit("need at least one trainer and a rollout count that is a multiple of the trainer count")
     is_trainer = rank < T
     trainer_group = list(range(T))
+    comm.pg(trainer_group)       # sub-groups are created collectively: the rollout ranks take part, then never use it
     my_trainer = (rank - T) % T if not is_trainer else rank
     my_rollouts = [T + j for j in range(R) if j % T == rank] if is_trainer else []
 

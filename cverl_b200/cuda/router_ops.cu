@@ -36,7 +36,11 @@ router_topk_fwd_kernel(const float* __restrict__ logits, long long T, int E, int
 #pragma unroll
   for (int j = 0; j < RT_MAX_PER_LANE; ++j) {
     const int e = j * 32 + lane;
-    v[j] = (j < per && e < E) ? logits[tok * E + e] : -INFINITY;
+    float x = (j < per && e < E) ? logits[tok * E + e] : -INFINITY;
+    // -inf marks "not a candidate"; a NaN or infinite logit becomes a finite extreme, so that k experts are always
+    // found and every id written is inside [0, E) (ids index tables further down the layer)
+    if (j < per && e < E) x = (x != x) ? -3.0e38f : fminf(fmaxf(x, -3.0e38f), 3.0e38f);
+    v[j] = x;
     mx = fmaxf(mx, v[j]);
   }
   mx = warp_max(mx);
@@ -61,6 +65,7 @@ router_topk_fwd_kernel(const float* __restrict__ logits, long long T, int E, int
       for (int j = 0; j < RT_MAX_PER_LANE; ++j)
         if (j == (bi >> 5)) v[j] = -INFINITY;
     }
+    if (bi >= E) bi = r < E ? r : 0;                   // cannot happen for k <= E; keeps the id inside the table
     if (lane == r) sel_val = bv, sel_idx = bi;
     denom_k += __expf(bv - mx);                       // first winner is the global max: exponents <= 0
   }

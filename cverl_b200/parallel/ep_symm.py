@@ -104,6 +104,12 @@ class EpSymm:
         marks unused capacity)."""
         n = dst_rank.numel()
         dev = self.device
+        # Expert ids come from data (a router fed non-finite activations yields ids outside the table): such an
+        # entry is routed nowhere and reported through the overflow flag (bit 1) - no index below may leave its table
+        bad = (dst_rank < 0) | (dst_rank >= self.world) | (local_expert < 0) | (local_expert >= num_local)
+        self.overflow.copy_(self.overflow | (bad.any().to(torch.int32) * 2))
+        dst_rank = torch.where(bad, torch.zeros_like(dst_rank), dst_rank)
+        local_expert = torch.where(bad, torch.zeros_like(local_expert), local_expert)
         counts = torch.bincount(dst_rank, minlength=self.world)[:self.world].to(torch.int32)
         mine = torch.zeros(8, dtype=torch.int32, device=dev)
         mine[:self.world] = counts
@@ -116,7 +122,8 @@ class EpSymm:
         table = self.cnt[:, :self.world].to(torch.int64)         # [src, dst]
         received = table[:, self.rank].sum().clamp(max=self.cap)
         peer_rank, peer_row, over = plan_rows(table, self.rank, dst_rank, self.cap)
-        self.overflow.copy_(torch.maximum(self.overflow, over))
+        peer_rank = torch.where(bad, torch.full_like(peer_rank, -1), peer_rank)     # the row kernels skip rank -1
+        self.overflow.copy_(self.overflow | over)
         # expert ids travel as 16-byte rows
         idrow = torch.zeros((n, 4), dtype=torch.int32, device=dev)
         idrow[:, 0] = local_expert.to(torch.int32)
@@ -136,9 +143,15 @@ class EpSymm:
         return peer_rank, peer_row, recv_expert
 
     def check(self) -> None:
-        if int(self.overflow.item()) != 0:
+        code = int(self.overflow.item())
+        if code != 0:
             self.overflow.zero_()
-            raise RuntimeError("EpSymm: a rank received more rows than its buffer capacity")
+            what = []
+            if code & 1:
+                what.append("a rank received more rows than its buffer capacity")
+            if code & 2:
+                what.append("the router produced expert ids outside the table (non-finite activations?)")
+            raise RuntimeError("EpSymm: " + "; ".join(what))
 
 
 class _Dispatch(torch.autograd.Function):

@@ -224,6 +224,26 @@ def test_expert_layout_kernel_matches_tensor_ops():
         nv.check_status()                                          # ... and the bad ids are reported
 
 
+def test_router_ids_stay_in_table_for_non_finite_logits():
+    """Rows of NaN / infinite activations still give k distinct expert ids inside [0, E): the ids index tables
+    further down the layer, so they must never leave them whatever the data."""
+    from cverl_b200.ops.router import route
+    torch.manual_seed(3)
+    T, H, E, k = 64, 128, 32, 8
+    x = torch.randn(T, H, device=_dev(), dtype=torch.bfloat16)
+    x[5] = float("nan")
+    x[9, :7] = float("inf")
+    x[17] = float("-inf")
+    gate = (0.1 * torch.randn(E, H, device=_dev())).to(torch.bfloat16)
+    idx, w = route(x, gate, k, True)
+    torch.cuda.synchronize()
+    assert int(idx.min()) >= 0 and int(idx.max()) < E
+    assert all(len(set(row.tolist())) == k for row in idx.cpu())
+    good = torch.ones(T, dtype=torch.bool)
+    good[[5, 9, 17]] = False
+    assert torch.isfinite(w.cpu()[good]).all()
+
+
 def test_moe_model_gpu_matches_cpu():
     from cverl_b200.models.config import Qwen35TextConfig
     from cverl_b200.models.qwen3_5 import Qwen35Model
