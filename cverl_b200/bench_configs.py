@@ -359,14 +359,22 @@ def zero2_dp8_push(args, ClockSampler) -> int:
         want = torch.stack([src[:1 << 24].float().sum(), src[-(1 << 24):].float().sum()])
         if rank >= half:
             own.zero_()
-        lo = rank * part
-        hi = min(lo + part, nbytes) // 16 * 16
-        arr = (C.c_void_p * half)(*[dst_ptrs[d] + lo for d in range(half, world)])
+        # every trainer holds the full weights: trainer t pushes the whole buffer to rollout rank half + t (one
+        # stream per link pair).  --push-pattern slices: trainer t stores slice t into EVERY rollout rank instead
+        # (each sender then feeds every rollout rank at once: measured 14x slower on 8 GPUs with 61 GB)
+        if args.push_pattern == "pairs":
+            lo, hi = 0, nbytes // 16 * 16
+            dsts = [dst_ptrs[half + rank]] if rank < half else []
+        else:
+            lo = rank * part
+            hi = min(lo + part, nbytes) // 16 * 16
+            dsts = [dst_ptrs[d] + lo for d in range(half, world)]
+        arr = (C.c_void_p * max(len(dsts), 1))(*dsts)
 
         def push_fn():
             barrier()                                  # receivers are ready (nobody still reads the old weights)
             if rank < half and hi > lo:
-                nv.check(nv.cuda().cvb_broadcast_store(src[lo:hi].data_ptr(), arr, half, hi - lo, nv.stream()),
+                nv.check(nv.cuda().cvb_broadcast_store(src[lo:hi].data_ptr(), arr, len(dsts), hi - lo, nv.stream()),
                          "cvb_broadcast_store")
                 ops.launch_counter["n"] += 1
             barrier()                                  # every piece has landed
@@ -381,7 +389,8 @@ def zero2_dp8_push(args, ClockSampler) -> int:
         ok = all(torch.equal(sums[r], wants[0]) for r in range(half, world))
         push = {"weight_push_ms": ms_push, "weight_bytes": nbytes, "trainers": half, "rollout_ranks": half,
                 "per_receiver_gbs": nbytes / (ms_push / 1e3) / 1e9,
-                "per_sender_gbs": (hi - lo) * half / (ms_push / 1e3) / 1e9, "push_verified": ok,
+                "per_sender_gbs": (hi - lo) * len(dsts) / (ms_push / 1e3) / 1e9 if rank < half else None,
+                "push_pattern": args.push_pattern, "push_verified": ok,
                 "push_target": "parameter buffers" if comm is not None else "receive buffers"}
     tokens = seqs * S * world
     out = {"metric": "ZeRO-2 supervised-step tokens/s (device, max over ranks); weight-sync seconds",

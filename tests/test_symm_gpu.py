@@ -648,3 +648,26 @@ def _ep_symm_rank(rank, world):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_expert_parallel_symm_matches_all_to_all_two_gpus():
     run_ranks(_ep_symm_rank, 2, backend="nccl", timeout=300)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("push", ["nccl", "symm", "nvls"])
+def test_static_split_on_gpus_with_each_weight_push(push):
+    """The static trainer / rollout split on two GPUs with the weight push by library send / recv, by the peer-store
+    kernel and by one multicast store through the NVSwitch: weights agree on both ranks afterwards and the rollout
+    rank generates with the pushed version."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    port = {"nccl": "29780", "symm": "29781", "nvls": "29782"}[push]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", port, "-m", "cverl_b200.cli.static_split", "--backend", "nccl", "--trainers",
+           "1", "--steps", "2", "--weight-push", push]
+    p = subprocess.run(cmd, cwd=root, env=dict(os.environ, PYTHONPATH=str(root)), capture_output=True, text=True,
+                       timeout=120)
+    if push == "nvls" and "NVLS unavailable" in (p.stdout + p.stderr):
+        pytest.skip("no NVSwitch multicast on this machine")
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-3000:]
+    assert "weights_in_sync=True" in p.stdout and "weight_version=1" in p.stdout
