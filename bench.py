@@ -261,6 +261,7 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return ms.item()
 
+    barrier()        # model construction takes different times per rank; the kernels' flag barriers are bounded waits
     check = None
     if world > 1 and not args.no_check:
         check = consistency_check(model, ctx, opt, fused_comm, dev_batch, args.micro_batch, world, dev)

@@ -160,6 +160,8 @@ def moe30b_ep8_sft(args, ClockSampler) -> int:
     ids_dev = host_ids.to(dev)
     extra = (lambda: _average_non_expert_grads(model, ctx)) if world > 1 else None
     step = _sft_step_fn(model, opt, ids_dev, mb, extra)
+    _barrier(world)      # ranks finish building and initialising the model at different times; the flag barriers
+    #                      inside the step are bounded waits of about a second, so line the ranks up first
     for _ in range(max(args.warmup, 0)):
         step()
     sampler = ClockSampler(local_rank)
@@ -235,6 +237,7 @@ def cp8_attention(args, ClockSampler) -> int:
     def fwd_bwd():
         q4.grad = k4.grad = v4.grad = None
         fwd().backward(do4)
+    _barrier(world)
     for _ in range(max(args.warmup, 1)):
         fwd_bwd()
         ring_fwd_bwd()
@@ -318,6 +321,7 @@ def zero2_dp8_push(args, ClockSampler) -> int:
     host_ids = torch.randint(0, cfg.vocab_size, (seqs, S), generator=g).pin_memory()
     ids_dev = host_ids.to(dev)
     step = _sft_step_fn(model, opt, ids_dev, mb)
+    _barrier(world)      # line the ranks up before the first bounded flag barrier (see moe30b_ep8_sft)
     for _ in range(max(args.warmup, 0)):
         step()
     sampler = ClockSampler(local_rank)

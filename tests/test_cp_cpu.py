@@ -130,7 +130,7 @@ def _zigzag_worker(rank, world):
         torch.testing.assert_close(got.grad, full.grad[:, cont], rtol=1e-4, atol=1e-5)
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 3, 4])
 def test_zigzag_ring_attention_matches_dense(world):
     run_ranks(_zigzag_worker, world)
 
