@@ -92,3 +92,60 @@ def test_demo_programs(tmp_path, tiny_dir):
     assert kv["backend"] == "cverl_b200" and float(kv["train_tokens_per_second"]) > 0 and kv["dataset_rows"] == "9"
     assert float(kv["train_tokens_per_second"]) == pytest.approx(
         6 * 8 * 4 * 16 * 2 / float(kv["seconds"]), rel=1e-3)
+
+
+def test_mnist_demo_reads_idx_files_and_learns(tmp_path, capsys):
+    """The small supervised demo: raw IDX files (big-endian headers) in, falling loss and the reference's CSV columns
+    out; a damaged header is refused."""
+    import struct
+    from cverl_b200.cli import mnist_demo
+    x, y = mnist_demo.synthetic_split(2048, 3)
+    xt, yt = mnist_demo.synthetic_split(128, 4)
+    for stem, (xs, ys) in {"train": (x, y), "t10k": (xt, yt)}.items():
+        (tmp_path / f"{stem}-images-idx3-ubyte").write_bytes(
+            struct.pack(">iiii", 2051, xs.shape[0], 28, 28) + (xs * 255).to(torch.uint8).numpy().tobytes())
+        (tmp_path / f"{stem}-labels-idx1-ubyte").write_bytes(
+            struct.pack(">ii", 2049, ys.shape[0]) + ys.to(torch.uint8).numpy().tobytes())
+    xr, yr = mnist_demo.load_split(tmp_path, True)
+    assert xr.shape == (2048, 1, 28, 28) and torch.equal(yr, y) and float((xr - (x * 255).to(torch.uint8) / 255).abs().max()) < 1e-6
+    csv = tmp_path / "m.csv"
+    rc = mnist_demo.main(["--data-dir", str(tmp_path), "--device", "cpu", "--batch-size", "64", "--epochs", "2",
+                          "--lr", "3e-3", "--metrics-csv", str(csv)])
+    out = capsys.readouterr().out
+    assert rc == 0 and "mnist_demo finished" in out
+    rows = csv.read_text().splitlines()
+    assert rows[0] == mnist_demo.COLUMNS and len(rows) == 1 + 2 * 32 + 2
+    assert float(rows[-1].split(",")[-1]) > 0.5                      # test accuracy after two epochs
+    (tmp_path / "train-labels-idx1-ubyte").write_bytes(struct.pack(">ii", 1234, 2048) + bytes(2048))
+    with pytest.raises(ValueError):
+        mnist_demo.load_split(tmp_path, True)
+
+
+def test_cifar10_export_and_resnet_bench(tmp_path, capsys):
+    """Parquet of PNG records -> normalised flat tensors + metadata; the ResNet training-step benchmark maps them."""
+    import io
+    import numpy as np
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+    from PIL import Image
+    from cverl_b200.cli import export_cifar10_tensors as ex, resnet_cifar10_bench as rb
+    rng = np.random.default_rng(0)
+    raw = rng.integers(0, 256, (24, 32, 32, 3), dtype=np.uint8)
+    recs = []
+    for img in raw:
+        buf = io.BytesIO()
+        Image.fromarray(img).save(buf, format="PNG")
+        recs.append({"bytes": buf.getvalue(), "path": None})
+    labels = [int(i % 10) for i in range(24)]
+    pq.write_table(pa.table({"img": recs, "label": labels}), tmp_path / "train.parquet")
+    meta = ex.export(str(tmp_path / "train.parquet"), str(tmp_path / "out"))
+    assert meta["shape"] == [24, 3, 32, 32] and meta["normalized"]
+    x, y = rb.load_tensors(tmp_path / "out")
+    want = (raw[5].astype(np.float32).transpose(2, 0, 1) / 255.0 - np.asarray(ex.MEAN, np.float32).reshape(3, 1, 1)) \
+        / np.asarray(ex.STD, np.float32).reshape(3, 1, 1)
+    assert np.allclose(x[5].numpy(), want, atol=1e-6) and y.tolist() == labels
+    rc = rb.main(["--data-dir", str(tmp_path / "out"), "--device", "cpu", "--depth", "14", "--width", "8",
+                  "--batch-size", "8", "--steps", "2", "--warmup", "1", "--dtype", "float32"])
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rc == 0 and line["images_per_s"] > 0 and line["benchmark"] == "resnet14_cifar10_train_step"
+    assert len(rb.BLOCKS[152]) == 4 and sum(rb.BLOCKS[152]) == 50      # 3 * 50 + 2 = 152 layers
