@@ -1,4 +1,4 @@
-"""Cached autoregressive decode for ``Qwen35Model`` (single rank).
+"""Cached autoregressive decode for ``Qwen35Model`` (one rank, or the ranks of a tensor-parallel group).
 
 The reference generates by re-running the whole forward over prompt + prefix for every new
 token (src/rollout/policy_worker.cc:99-102, O(N^2)).  Here ``prefill`` runs the prompt once
@@ -11,7 +11,10 @@ every projection and the LM head, the fused norm / RoPE / gate kernels of traini
 (appends the token's key / value to the cache and attends over it, reading the length from device memory) and
 ``cvb_gdn_decode_step`` (one read and one write of the recurrent state).  Nothing in that step depends on a
 host-side shape or scalar, so ``GraphedDecoder`` captures it once in a CUDA graph and replays it per token.
-The fp32 PyTorch statement below stays as the CPU path and the test oracle.
+The fp32 PyTorch statement below stays as the CPU path and the test oracle.  It also serves tensor parallelism:
+every rank keeps the caches of its own heads, the row-parallel projections are summed over the group, the
+embedding lookup is vocabulary-parallel and the LM head's logits are gathered; the native step and the CUDA graph
+are single-rank (``native_decode_supported``), so a tensor-parallel decode on GPUs runs this statement.
 """
 from __future__ import annotations
 
@@ -66,6 +69,26 @@ def _lin(x, w):
     return (x.to(w.dtype) @ w.t())
 
 
+def _tp_sum(model, t: torch.Tensor) -> torch.Tensor:
+    """Sum of the tensor-parallel ranks' partial results (the output of a row-parallel projection)."""
+    if model.ctx.tp_size > 1:
+        import torch.distributed as dist
+        t = t.contiguous()
+        dist.all_reduce(t, group=model.ctx.tp_group)
+    return t
+
+
+def _full_logits(model, hidden: torch.Tensor) -> torch.Tensor:
+    """hidden [B, H] -> fp32 logits [B, V]; the LM head is sharded over vocabulary rows under tensor parallelism."""
+    logits = hidden.float() @ model.lm_head_weight().float().t()
+    if model.ctx.tp_size > 1:
+        import torch.distributed as dist
+        parts = [torch.empty_like(logits) for _ in range(model.ctx.tp_size)]
+        dist.all_gather(parts, logits.contiguous(), group=model.ctx.tp_group)
+        logits = torch.cat(parts, dim=-1)
+    return logits
+
+
 @torch.no_grad()
 def prefill(model, prompt_ids: torch.Tensor, max_len: int):
     """Runs the prompt; returns ``(state, logits [B, V] of the next token)``."""
@@ -80,8 +103,7 @@ def prefill(model, prompt_ids: torch.Tensor, max_len: int):
             v = torch.zeros_like(k)
             k[:, :S], v[:, :S] = c["k"], c["v"]
             c["k"], c["v"] = k, v
-    logits = hidden[:, -1].float() @ model.lm_head_weight().float().t()
-    return DecodeState(S, caches), logits
+    return DecodeState(S, caches), _full_logits(model, hidden[:, -1])
 
 
 def native_decode_supported(model) -> bool:
@@ -104,7 +126,7 @@ def decode_step(model, state: DecodeState, tokens: torch.Tensor) -> torch.Tensor
     B = tokens.shape[0]
     pos = state.length
     eps, off = cfg.rms_norm_eps, cfg.norm_weight_offset
-    h = ops.embedding(tokens.view(B), model.param(cfg.embed_name)).float()
+    h = model.embed(tokens.view(B, 1)).float()          # vocabulary-parallel lookup + sum under tensor parallelism
     for li, i in enumerate(range(model.layer_begin, model.layer_end)):
         p = f"{cfg.layer_root}{i}."
         c = state.layers[li]
@@ -118,13 +140,14 @@ def decode_step(model, state: DecodeState, tokens: torch.Tensor) -> torch.Tensor
         h = h + model.mlp(n2.to(model.dtype), i).float()
     state.length += 1
     out = rmsnorm_ref(h, model.param(cfg.final_norm_name), eps, off)
-    return out.float() @ model.lm_head_weight().float().t()
+    return _full_logits(model, out)
 
 
 def _full_attention_step(model, x, i, c, pos):
     cfg = model.cfg
     p = f"{cfg.layer_root}{i}.self_attn."
-    d, h, kvh = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+    tp = model.ctx.tp_size                                # heads are sharded over the tensor-parallel ranks
+    d, h, kvh = cfg.head_dim, cfg.num_attention_heads // tp, cfg.num_key_value_heads // tp
     B = x.shape[0]
     qkv = _lin(x, model.fused[f"{i}.qkv"]).float()
     qmul = 1 if cfg.is_qwen3_moe else 2
@@ -149,13 +172,14 @@ def _full_attention_step(model, x, i, c, pos):
     o = torch.einsum("bhl,blhd->bhd", torch.softmax(scores, dim=-1), vals)
     if gate is not None:
         o = o * torch.sigmoid(gate)
-    return _lin(o.reshape(B, h * d), model.param(p + "o_proj.weight"))
+    return _tp_sum(model, _lin(o.reshape(B, h * d), model.param(p + "o_proj.weight")))
 
 
 def _linear_attention_step(model, x, i, c):
     cfg = model.cfg
     p = f"{cfg.layer_root}{i}.linear_attn."
-    kh, vh = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+    tp = model.ctx.tp_size
+    kh, vh = cfg.linear_num_key_heads // tp, cfg.linear_num_value_heads // tp
     kd, vd = cfg.linear_key_head_dim, cfg.linear_value_head_dim
     key_dim, value_dim = kh * kd, vh * vd
     conv_dim = 2 * key_dim + value_dim
@@ -181,7 +205,7 @@ def _linear_attention_step(model, x, i, c):
     c["state"] = S
     o = (S * q.unsqueeze(-1)).sum(-2)
     y = rmsnorm_ref(o, model.param(p + "norm.weight"), cfg.rms_norm_eps, 0.0, gate=z.view(B, vh, vd))
-    return _lin(y.reshape(B, value_dim), model.param(p + "out_proj.weight"))
+    return _tp_sum(model, _lin(y.reshape(B, value_dim), model.param(p + "out_proj.weight")))
 
 
 # ---------------------------------------------------------------------------------------------------------

@@ -377,3 +377,31 @@ def test_flat_params_gradient_buckets_layout():
         fp.fused_view(["l0.b", "l1.a"], (32,))                  # crosses a bucket boundary
     with pytest.raises(ValueError):
         FlatParams(entries, grad_buckets=[0, 1, 0, 2, 2, 3])    # bucket ids must not decrease
+
+
+def _tp_decode_worker(rank, world):
+    """Cached decode (prefill + one-token steps: KV cache, convolution tail, recurrent state) under tensor
+    parallelism against the same model on one rank: the logits of every step agree."""
+    from cverl_b200.models import decode
+    from cverl_b200.parallel.mesh import build_context
+    cfg = Qwen35TextConfig.tiny(layers=4)
+    ctx = build_context(world, rank, tp=world, dp=1)
+    tp_model = Qwen35Model(cfg, dtype=torch.float32, ctx=ctx)
+    tp_model.init_weights(seed=9)
+    dense = Qwen35Model(cfg, dtype=torch.float32)
+    dense.init_weights(seed=9)
+    prompt = torch.randint(0, cfg.vocab_size, (2, 7), generator=torch.Generator().manual_seed(4))
+    st_tp, lg_tp = decode.prefill(tp_model, prompt, 12)
+    st_d, lg_d = decode.prefill(dense, prompt, 12)
+    torch.testing.assert_close(lg_tp, lg_d, rtol=2e-4, atol=2e-4)
+    assert lg_tp.shape == (2, cfg.vocab_size)
+    for _ in range(4):
+        tok = lg_d.argmax(-1)
+        lg_tp = decode.decode_step(tp_model, st_tp, tok)
+        lg_d = decode.decode_step(dense, st_d, tok)
+        torch.testing.assert_close(lg_tp, lg_d, rtol=2e-4, atol=2e-4)
+    assert st_tp.length == st_d.length == 11
+
+
+def test_cached_decode_under_tensor_parallelism():
+    run_ranks(_tp_decode_worker, 2)
