@@ -163,3 +163,35 @@ def _model_zigzag_worker(rank, world):
 
 def test_hybrid_model_zigzag_context_parallel_matches_dense():
     run_ranks(_model_zigzag_worker, 2)
+
+
+@pytest.mark.parametrize("cp", [2, 3, 4, 8])
+def test_zigzag_hop_plans_cover_the_causal_mask_once_and_balance_the_work(cp):
+    """Over all ranks and owners, the one-launch-per-hop plans visit every (query half-chunk, key half-chunk) pair
+    below the diagonal exactly once, the diagonal pairs causally, nothing above it - and every rank does the same
+    amount of work per hop."""
+    from cverl_b200.parallel.cp_zigzag import _hop_plan, zigzag_chunks
+    from cverl_b200.parallel.context_parallel import ring_schedule
+    h = 1
+    seen = torch.zeros(2 * cp, 2 * cp, dtype=torch.int64)          # [query half-chunk, key half-chunk]
+    causal_pairs = set()
+    for rank in range(cp):
+        mine = zigzag_chunks(rank, cp)
+        work = []
+        for owner, _, _ in ring_schedule(rank, cp):
+            theirs = zigzag_chunks(owner, cp)
+            (q0, q1), (k0, k1), causal = _hop_plan(owner, rank, h)
+            qs = [mine[i] for i in range(2) if q0 <= i * h < q1]
+            ks = [theirs[i] for i in range(2) if k0 <= i * h < k1]
+            for qi, qc in enumerate(qs):
+                for ki, kc in enumerate(ks):
+                    if causal and ki > qi:
+                        continue                                   # masked by the local causal rule
+                    seen[qc, kc] += 1
+                    if causal and ki == qi:
+                        causal_pairs.add((qc, kc))
+            work.append(len(qs) * len(ks))
+        assert len(set(work)) <= 2 and set(work) <= {2, 4}          # 2 h^2 scores per hop (4 half-masked on the diagonal)
+    want = torch.tril(torch.ones(2 * cp, 2 * cp, dtype=torch.int64))
+    assert torch.equal(seen, want)
+    assert causal_pairs == {(c, c) for c in range(2 * cp)}
