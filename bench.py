@@ -47,6 +47,8 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=0, help="other configurations: 0 = the named sequence length")
     ap.add_argument("--ep-comm", default="symm", choices=["symm", "nccl"])
     ap.add_argument("--cp-comm", default="nccl", choices=["symm", "nccl"])
+    ap.add_argument("--ep-capacity-factor", type=float, default=3.0,
+                    help="moe30b_ep8_sft: receive-buffer rows per rank as a multiple of the balanced load")
     ap.add_argument("--grad-slots", type=int, default=2, help="zero2_dp8_push: gradient bucket buffers in flight")
     ap.add_argument("--rs-blocks", type=int, default=0,
                     help="zero2_dp8_push: CTAs of a bucket's reduce-scatter kernel while it overlaps the backward pass")

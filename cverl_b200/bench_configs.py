@@ -148,7 +148,11 @@ def moe30b_ep8_sft(args, ClockSampler) -> int:
     ctx = build_context(world, rank, ep=world)
     if world > 1 and args.ep_comm == "symm":
         from .parallel.ep_symm import EpSymm
-        cap = int(mb * S * cfg.num_experts_per_tok * 2.0) + 128
+        # A randomly initialised router may send many tokens of a deep layer to the same few experts; an entry that
+        # does not fit its receive buffer is dropped (its rows read as zeros) and the run reports it.  Every buffer
+        # and every saved activation of the expert path has the capacity's static size, so the factor is a trade
+        # against memory: 3 x the balanced load keeps the 48-layer model inside 180 GB.
+        cap = int(mb * S * cfg.num_experts_per_tok * args.ep_capacity_factor) + 128
         ctx.ep_symm = EpSymm(ctx.ep_group, dev, cap, cfg.hidden_size)
     model = Qwen35Model(cfg, dtype=torch.bfloat16, device=dev, ctx=ctx, pad_multiple=8)
     model.init_weights_on_device(seed=1234)

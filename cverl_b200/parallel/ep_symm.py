@@ -173,7 +173,9 @@ class _Dispatch(torch.autograd.Function):
         eps.barrier()
         eps.grow.copy_(g)
         eps.barrier()                                            # every rank's gradient rows are in place
-        out = torch.empty((ctx.n, eps.hidden), dtype=torch.bfloat16, device=g.device)
+        # zeros, not empty: the gather leaves out the entries that did not fit a receive buffer (rank -1), and
+        # their rows must be a defined value (an uninitialised row here becomes a non-finite weight gradient)
+        out = torch.zeros((ctx.n, eps.hidden), dtype=torch.bfloat16, device=g.device)
         eps._move(True, out, eps.b_grow, peer_rank, peer_row, eps.row_bytes)
         return out, None, None, None
 
@@ -188,7 +190,7 @@ class _Combine(torch.autograd.Function):
         eps.barrier()
         eps.out.copy_(y)
         eps.barrier()
-        out = torch.empty((peer_rank.numel(), eps.hidden), dtype=torch.bfloat16, device=y.device)
+        out = torch.zeros((peer_rank.numel(), eps.hidden), dtype=torch.bfloat16, device=y.device)   # see _Dispatch
         eps._move(True, out, eps.b_out, peer_rank, peer_row, eps.row_bytes)
         return out
 
