@@ -645,6 +645,54 @@ def _ep_symm_rank(rank, world):
     dist.barrier()
 
 
+def _ep_overflow_rank(rank, world):
+    """A receive buffer too small for the routed rows: the entries that do not fit are dropped (their outputs and
+    gradients read as zeros, never as uninitialised memory), nothing is written past a buffer, and the overflow
+    is reported when the trainer would read its metrics."""
+    import torch.distributed as dist
+    from cverl_b200 import _native as nv
+    from cverl_b200.models.config import Qwen35TextConfig
+    from cverl_b200.models.qwen3_5 import Qwen35Model
+    from cverl_b200.parallel.ep_symm import EpSymm
+    from cverl_b200.parallel.mesh import build_context
+    dev = torch.device("cuda", rank)
+    cfg = Qwen35TextConfig.tiny(moe=True, layers=2)
+    ctx = build_context(world, rank, tp=1, dp=1, ep=world)
+    ctx.ep_symm = EpSymm(ctx.ep_group, dev, capacity_rows=32, hidden=cfg.hidden_size)     # 96 entries are routed
+    model = Qwen35Model(cfg, dtype=torch.bfloat16, device=dev, ctx=ctx)
+    model.init_weights(seed=5)
+    # poison the allocator's free memory, so that an uninitialised output row would show up as NaN
+    junk = torch.full((1 << 22,), float("nan"), device=dev, dtype=torch.bfloat16)
+    del junk
+    ids = torch.randint(0, cfg.vocab_size, (2, 24), generator=torch.Generator().manual_seed(100 + rank)).to(dev)
+    failures = []
+    for _ in range(2):
+        lp = model.response_logprobs(ids, 8)
+        lp.sum().backward()
+        torch.cuda.synchronize()
+        if not bool(torch.isfinite(lp).all()):
+            failures.append("non-finite log-probs")
+        if not bool(torch.isfinite(model.flat.main_grad).all()):
+            failures.append("non-finite gradients")
+    try:
+        nv.check_status()
+    except RuntimeError as exc:
+        failures.append(f"status word: {exc}")
+    try:
+        ctx.ep_symm.check()
+        failures.append("overflow not reported")
+    except RuntimeError as exc:
+        if "capacity" not in str(exc):
+            failures.append(str(exc))
+    dist.barrier()
+    assert not failures, failures
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_receive_overflow_is_dropped_and_reported_two_gpus():
+    run_ranks(_ep_overflow_rank, 2, backend="nccl", timeout=300)
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_expert_parallel_symm_matches_all_to_all_two_gpus():
     run_ranks(_ep_symm_rank, 2, backend="nccl", timeout=300)
