@@ -72,29 +72,33 @@ def sort_by_expert(expert_ids: torch.Tensor, num_experts: int):
     return order, dest, tile_group.to(torch.int32), offsets.to(torch.int32), m_pad
 
 
-def expert_layout(expert_ids: torch.Tensor, num_experts: int):
-    """``(row, tile_group, offsets, m_pad)``: ``row[i]`` is the row of entry ``i`` in the expert-grouped, 128-row
-    padded matrix the grouped GEMM reads (entries of one expert keep their order), ``tile_group`` the expert of
-    each 128-row tile (-1 = unused), ``offsets`` int32 [E+1] the padded segment bounds, ``m_pad`` a static upper
-    bound of the padded row count.  On CUDA the table comes from ``cvb_expert_layout`` (four small launches, no
-    sort, no host read); elsewhere from ``sort_by_expert``."""
+def expert_layout(expert_ids: torch.Tensor, num_experts: int, tile_m: int = TILE_M):
+    """``(row, tile_group, offsets, m_pad)``: ``row[i]`` is the row of entry ``i`` in the expert-grouped matrix the
+    grouped GEMM reads, every expert's segment padded to a multiple of ``tile_m`` (128) rows and the entries of one
+    expert in their original order; ``tile_group`` is the expert of each ``tile_m``-row tile (-1 = unused),
+    ``offsets`` int32 [E+1] the padded segment bounds, ``m_pad`` a static upper bound of the padded row count.
+    On CUDA the table comes from ``cvb_expert_layout`` (four small launches, no sort, no host read); elsewhere
+    from ``sort_by_expert``.  With ``tile_m=1`` it is a plain stable grouping (used for the expert-parallel
+    destination rows)."""
     n = expert_ids.numel()
     dev = expert_ids.device
-    m_pad = (n + num_experts * (TILE_M - 1) + TILE_M - 1) // TILE_M * TILE_M
+    m_pad = (n + num_experts * (tile_m - 1) + tile_m - 1) // tile_m * tile_m
     if expert_ids.is_cuda and expert_ids.dtype == torch.int64 and num_experts <= 256 and n > 0:
         from .. import _native as nv
         ids = expert_ids.contiguous()
         nblocks = (n + 255) // 256
         scratch = torch.empty(n + (nblocks + 1) * (num_experts + 1), dtype=torch.int32, device=dev)
         offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
-        tile_group = torch.empty(m_pad // TILE_M, dtype=torch.int32, device=dev)
+        tile_group = torch.empty(m_pad // tile_m, dtype=torch.int32, device=dev)
         row = torch.empty(n, dtype=torch.int64, device=dev)
-        nv.check(nv.cuda().cvb_expert_layout(ids.data_ptr(), n, num_experts, TILE_M, scratch.data_ptr(),
-                                             offsets.data_ptr(), tile_group.data_ptr(), m_pad // TILE_M,
+        nv.check(nv.cuda().cvb_expert_layout(ids.data_ptr(), n, num_experts, tile_m, scratch.data_ptr(),
+                                             offsets.data_ptr(), tile_group.data_ptr(), m_pad // tile_m,
                                              row.data_ptr(), nv.status_word(dev).data_ptr(), nv.stream()),
                  "cvb_expert_layout")
         ops.launch_counter["n"] += 4
         return row, tile_group, offsets, m_pad
+    if tile_m != TILE_M:
+        raise ValueError("the tensor-op layout pads to 128 rows only")
     order, dest, tile_group, offsets, m_pad = sort_by_expert(expert_ids, num_experts)
     row = torch.empty_like(order)
     row[order] = dest

@@ -38,15 +38,21 @@ def plan_rows(table: torch.Tensor, rank: int, dst_rank: torch.Tensor, capacity_r
     world = table.shape[0]
     n = dst_rank.numel()
     dev = dst_rank.device
-    counts = torch.bincount(dst_rank, minlength=world)[:world].to(torch.int64)
     base = table[:rank].sum(0)
-    order = torch.argsort(dst_rank, stable=True)
-    starts = torch.zeros(world + 1, dtype=torch.int64, device=dev)
-    starts[1:] = counts.cumsum(0)
-    sorted_dst = dst_rank[order]
-    idx_in_seg = torch.arange(n, device=dev) - starts[sorted_dst]
-    peer_row = torch.empty(n, dtype=torch.int64, device=dev)
-    peer_row[order] = base[sorted_dst] + idx_in_seg
+    if dst_rank.is_cuda and n > 0:
+        # stable position of every entry inside its destination's group from the layout kernels (no sort)
+        from ..models.moe import expert_layout
+        pos, _, starts32, _ = expert_layout(dst_rank, world, tile_m=1)
+        peer_row = pos - starts32.to(torch.int64)[dst_rank] + base[dst_rank]
+    else:
+        counts = torch.bincount(dst_rank, minlength=world)[:world].to(torch.int64)
+        order = torch.argsort(dst_rank, stable=True)
+        starts = torch.zeros(world + 1, dtype=torch.int64, device=dev)
+        starts[1:] = counts.cumsum(0)
+        sorted_dst = dst_rank[order]
+        idx_in_seg = torch.arange(n, device=dev) - starts[sorted_dst]
+        peer_row = torch.empty(n, dtype=torch.int64, device=dev)
+        peer_row[order] = base[sorted_dst] + idx_in_seg
     fits = peer_row < capacity_rows
     peer_rank = torch.where(fits, dst_rank.to(torch.int32), torch.full_like(dst_rank, -1, dtype=torch.int32))
     peer_row = torch.where(fits, peer_row, torch.zeros_like(peer_row))

@@ -224,6 +224,22 @@ def test_expert_layout_kernel_matches_tensor_ops():
         nv.check_status()                                          # ... and the bad ids are reported
 
 
+def test_expert_parallel_row_plan_on_the_layout_kernels_matches_tensor_ops():
+    """Destination rows of routed entries: the CUDA path (stable grouping by the layout kernels) equals the
+    sort-based tensor-op statement, including the entries that do not fit the receive buffer."""
+    from cverl_b200.parallel.ep_symm import plan_rows
+    g = torch.Generator().manual_seed(4)
+    for world, n, cap in ((2, 96, 1000), (8, 5000, 700), (4, 1, 10)):
+        dst = torch.randint(0, world, (n,), generator=g)
+        table = torch.randint(0, 300, (world, world), generator=g)
+        for rank in (0, world - 1):
+            table[rank] = torch.bincount(dst, minlength=world)
+            want = plan_rows(table, rank, dst, cap)
+            got = plan_rows(table.to(_dev()), rank, dst.to(_dev()), cap)
+            for a, b in zip(got, want):
+                assert torch.equal(a.cpu(), b)
+
+
 def test_router_ids_stay_in_table_for_non_finite_logits():
     """Rows of NaN / infinite activations still give k distinct expert ids inside [0, E): the ids index tables
     further down the layer, so they must never leave them whatever the data."""
