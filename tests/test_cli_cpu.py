@@ -163,3 +163,15 @@ def test_benchmark_modules_parse_their_flags():
                            capture_output=True, text=True, timeout=120)
         assert p.returncode == 0, p.stderr[-2000:]
         assert "--iters" in p.stdout
+
+
+def test_env_driven_trainer_launcher_script():
+    """examples/run_pp_tp_ppo_trainer.sh maps the reference launcher's environment variables onto the trainer's flags."""
+    env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1", DP_SIZE="1", PP_SIZE="1", TP_SIZE="2", LAYERS="2",
+               CONFIG="tiny", PROMPT_LEN="8", RESPONSE_LEN="8", DTYPE="float32", ZERO_COMM="nccl", TP_COMM="nccl",
+               EP_COMM="nccl", MASTER_PORT="29578", STEPS="2", CLIP_RATIO="0.25", MAX_GRAD_NORM="0.5")
+    p = subprocess.run(["bash", str(ROOT / "examples" / "run_pp_tp_ppo_trainer.sh"), "", "--backend", "gloo"], cwd=ROOT,
+                       env=env, capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-2500:]
+    steps = [ln for ln in p.stdout.splitlines() if ln.startswith("step=")]
+    assert len(steps) == 2 and " tp=2 " in steps[0] and " pp=1 " in steps[0] and "dtype=float32" in steps[0]
