@@ -176,13 +176,13 @@ def consistency_check(model, ctx, opt, fused_comm, dev_batch, micro_batch, world
 
 def main():
     args = parse_args()
-    if args.impl == "reference":
-        return reference_arm(args)
-    if args.config != "grpo_0_8b":
+    if args.config != "grpo_0_8b" and args.impl != "reference":
         from cverl_b200 import bench_configs
         return bench_configs.run(args, ClockSampler)
     if args.seqs_per_gpu <= 0:
         args.seqs_per_gpu = SEQS_PER_GPU
+    if args.impl == "reference":
+        return reference_arm(args)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

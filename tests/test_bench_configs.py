@@ -49,3 +49,19 @@ def test_gpu_configs_reduced(config, flags):
             assert out["push_verified"] is True
     if config != "cp8_attention":
         assert out["invalid"] and 0 < out["loss"] < 20
+
+
+def test_reference_arm_gets_the_headline_batch_by_default(monkeypatch):
+    """`bench.py --impl reference` hands the reference arm the headline configuration (128 sequences per GPU) when
+    no size is given, and the caller's value when one is."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench_under_test", ROOT / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    seen = []
+    monkeypatch.setattr(bench, "reference_arm", lambda args: seen.append(args.seqs_per_gpu) or 0)
+    monkeypatch.setattr(sys, "argv", ["bench.py", "--impl", "reference", "--gpus", "1"])
+    assert bench.main() == 0
+    monkeypatch.setattr(sys, "argv", ["bench.py", "--impl", "reference", "--seqs-per-gpu", "4"])
+    assert bench.main() == 0
+    assert seen == [bench.SEQS_PER_GPU, 4] and bench.SEQS_PER_GPU == 128
