@@ -16,7 +16,6 @@ from __future__ import annotations
 from typing import Tuple
 
 import torch
-import torch.nn.functional as F
 
 from .. import ops
 from ..ops.grouped_gemm import TILE_M, grouped_linear

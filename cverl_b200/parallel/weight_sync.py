@@ -13,7 +13,7 @@ peer-mapped copy, one pass over the weights); this module is the portable path o
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Iterable, List, Optional, Sequence
+from typing import List, Optional, Sequence
 
 import torch
 

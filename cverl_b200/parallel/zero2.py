@@ -26,7 +26,6 @@ full gradients; its ``--dp-grad-comm-dtype model`` halves them.
 """
 from __future__ import annotations
 
-import ctypes as C
 from typing import Dict, List, Optional
 
 import torch
@@ -273,7 +272,6 @@ class BucketedZero2Optimizer:
                 done.record(self.side)
                 if slot is not None:
                     self._slot_free[slot] = done
-                self._last_done = done
 
     def finish_backward(self) -> None:
         """Reduce whatever the boundaries have not (the first layer when its input needs no gradient, the pinned
