@@ -52,6 +52,8 @@ def parse_args():
     ap.add_argument("--grad-slots", type=int, default=2, help="zero2_dp8_push: gradient bucket buffers in flight")
     ap.add_argument("--rs-blocks", type=int, default=0,
                     help="zero2_dp8_push: CTAs of a bucket's reduce-scatter kernel while it overlaps the backward pass")
+    ap.add_argument("--grad-comm-dtype", default="float32", choices=["float32", "bfloat16"],
+                    help="zero2_dp8_push with --zero-comm nccl: dtype in which the gradient buckets are reduced")
     ap.add_argument("--push-pattern", default="pairs", choices=["pairs", "slices"],
                     help="zero2_dp8_push: trainer t -> rollout t (whole buffer), or slice t -> every rollout rank")
     ap.add_argument("--no-overlap", action="store_true", help="zero2_dp8_push: reduce buckets on the main stream")

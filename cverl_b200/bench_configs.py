@@ -320,7 +320,9 @@ def zero2_dp8_push(args, ClockSampler) -> int:
     opt = BucketedZero2Optimizer(model, AdamWOptions(lr=1e-6, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.01,
                                                      use_master_weights=False),
                                  dp_group=ctx.dp_group, dp_rank=rank, dp_size=world, norm_group=None,
-                                 norm_world=world, max_grad_norm=1.0, fused_comm=comm, overlap=not args.no_overlap)
+                                 norm_world=world, max_grad_norm=1.0, fused_comm=comm, overlap=not args.no_overlap,
+                                 comm_dtype=torch.bfloat16 if (comm is None and args.grad_comm_dtype == "bfloat16")
+                                 else None)
     g = torch.Generator().manual_seed(1000 + rank)
     host_ids = torch.randint(0, cfg.vocab_size, (seqs, S), generator=g).pin_memory()
     ids_dev = host_ids.to(dev)
@@ -408,7 +410,7 @@ def zero2_dp8_push(args, ClockSampler) -> int:
                       "seq_len": S, "seqs_per_gpu": seqs, "micro_batch_seqs": mb, "parallelism": f"dp{world}",
                       "zero": "stage 2, per-layer buckets reduced during backward on a side stream",
                       "zero_comm": args.zero_comm if world > 1 else "none", "overlap": not args.no_overlap,
-                      "grad_slots": args.grad_slots, "rs_blocks": args.rs_blocks if comm else None, "params": int(model.flat.numel),
+                      "grad_comm_dtype": args.grad_comm_dtype if comm is None else "float32", "grad_slots": args.grad_slots, "rs_blocks": args.rs_blocks if comm else None, "params": int(model.flat.numel),
                       "buckets_reduced_inside_each_backward_pass": in_backward,
                       "l2": "working set far above the 126 MB L2"},
            "optimizer_tail_ms": ms_tail,

@@ -139,8 +139,14 @@ class BucketedZero2Optimizer:
 
     def __init__(self, model, options: AdamWOptions, *, dp_group=None, dp_rank: int = 0, dp_size: int = 1,
                  norm_group=None, norm_world: int = 1, max_grad_norm: float = 1.0, fused_comm=None,
-                 overlap: bool = True):
+                 overlap: bool = True, comm_dtype: Optional[torch.dtype] = None):
+        """``comm_dtype`` (library transports only): reduce the buckets in this dtype instead of fp32 - bf16 halves the
+        gradient traffic, the sum still lands in the fp32 shard gradient (the reference's ``--dp-grad-comm-dtype``,
+        src/distributed/optimizer_sharding.cc:463-585)."""
         options.validate("BucketedZero2Optimizer")
+        self.comm_dtype = comm_dtype if comm_dtype not in (None, torch.float32) else None
+        if self.comm_dtype is not None and fused_comm is not None:
+            raise ValueError("the peer-memory kernels reduce in fp32; use comm_dtype with the library transports")
         fp = model.flat
         if not fp.bucketed:
             raise ValueError("BucketedZero2Optimizer needs a model built with grad_buckets=True")
@@ -256,16 +262,22 @@ class BucketedZero2Optimizer:
             if self.fused is not None:
                 self.fused.reduce_scatter_acc(g, self.dp_rank * c, c, 1.0 / self.dp_size, out)
             elif self._cuda:
-                if self._tmp is None or self._tmp.numel() < c:
-                    self._tmp = torch.empty(max(self.chunk.values()), dtype=torch.float32, device=self.device)
+                cd = self.comm_dtype or torch.float32
+                if self._tmp is None or self._tmp.numel() < c or self._tmp.dtype != cd:
+                    self._tmp = torch.empty(max(self.chunk.values()), dtype=cd, device=self.device)
                 tmp = self._tmp[:c]
-                dist.reduce_scatter_tensor(tmp, g, op=dist.ReduceOp.AVG, group=self.dp_group)
-                out.add_(tmp)
+                src = g if self.comm_dtype is None else g.to(cd)
+                if self.comm_dtype is None:
+                    dist.reduce_scatter_tensor(tmp, src, op=dist.ReduceOp.AVG, group=self.dp_group)
+                    out.add_(tmp)
+                else:       # low-precision sum, mean taken in fp32
+                    dist.reduce_scatter_tensor(tmp, src, op=dist.ReduceOp.SUM, group=self.dp_group)
+                    out.add_(tmp.float(), alpha=1.0 / self.dp_size)
                 g.zero_()
             else:   # gloo has no reduce-scatter: all-reduce the bucket and keep this rank's piece
-                full = g.clone()
+                full = g.clone() if self.comm_dtype is None else g.to(self.comm_dtype)
                 dist.all_reduce(full, group=self.dp_group)
-                out.add_(full[self.dp_rank * c:(self.dp_rank + 1) * c] / self.dp_size)
+                out.add_(full[self.dp_rank * c:(self.dp_rank + 1) * c].float() / self.dp_size)
                 g.zero_()
             if self.overlap:
                 done = torch.cuda.Event()

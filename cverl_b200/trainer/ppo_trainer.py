@@ -566,7 +566,7 @@ def run(argv=None) -> int:
         from ..parallel.zero2 import BucketedZero2Optimizer
         opt = BucketedZero2Optimizer(model, adam_opts, dp_group=ctx.dp_group, dp_rank=ctx.dp_rank, dp_size=args.dp,
                                      norm_group=None, norm_world=world, max_grad_norm=args.max_grad_norm,
-                                     fused_comm=fused_comm)
+                                     fused_comm=fused_comm, comm_dtype=None if fused_comm is not None else comm_dtype)
     elif opt_mode == "flat":
         opt = FlatZeroOptimizer(model.flat, adam_opts, dp_group=ctx.dp_group, dp_rank=ctx.dp_rank, dp_size=args.dp,
                                 norm_group=None, norm_world=world, max_grad_norm=args.max_grad_norm,

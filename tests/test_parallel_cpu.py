@@ -405,3 +405,30 @@ def _tp_decode_worker(rank, world):
 
 def test_cached_decode_under_tensor_parallelism():
     run_ranks(_tp_decode_worker, 2)
+
+
+def _zero2_bf16_comm_worker(rank, world):
+    """Buckets reduced in bf16: the shard gradient equals the fp32 reduction up to bf16 rounding of each addend."""
+    from cverl_b200.parallel.mesh import build_context
+    from cverl_b200.parallel.zero2 import BucketedZero2Optimizer
+    cfg = Qwen35TextConfig.tiny(layers=2)
+    ctx = build_context(world, rank, tp=1, dp=2)
+    opts = AdamWOptions(lr=1e-2, beta2=0.95, use_master_weights=False)
+    shards = []
+    for cd in (None, torch.bfloat16):
+        model = Qwen35Model(cfg, dtype=torch.float32, ctx=ctx, pad_multiple=16, grad_buckets=True, bucket_align=16)
+        model.init_weights(seed=5)
+        opt = BucketedZero2Optimizer(model, opts, dp_group=ctx.dp_group, dp_rank=rank, dp_size=2, norm_world=2,
+                                     max_grad_norm=0.0, comm_dtype=cd)
+        ids = torch.randint(0, cfg.vocab_size, (2, 12), generator=torch.Generator().manual_seed(20 + rank))
+        model.response_logprobs(ids, 4).sum().backward()
+        opt.finish_backward()
+        shards.append(opt.grad_shard.clone())
+    rel = ((shards[1] - shards[0]).norm() / shards[0].norm()).item()
+    assert 0 < rel < 1e-2, rel
+    with pytest.raises(ValueError):
+        BucketedZero2Optimizer(model, opts, dp_size=2, fused_comm=object(), comm_dtype=torch.bfloat16)
+
+
+def test_bucketed_zero2_low_precision_gradient_communication():
+    run_ranks(_zero2_bf16_comm_worker, 2)
