@@ -1,4 +1,6 @@
 """A Hugging Face dataset split on disk as prompt / answer JSONL."""
+import sys
+
 import pytest
 
 
@@ -30,3 +32,30 @@ def test_hf_dataset_split_to_prompt_answer_jsonl(tmp_path, capsys):
         download_hf_dataset(str(tmp_path / "snap"), tmp_path / "x.jsonl", name="main", prompt_field="prompt")
     with pytest.raises(FileNotFoundError):
         download_hf_dataset(str(tmp_path / "snap"), tmp_path / "x.jsonl", name="main", split="validation")
+
+
+def test_hf_download_cli_options_and_offline_behaviour(tmp_path, capsys, monkeypatch):
+    """The snapshot CLI: a directory that already holds a model is returned without touching the hub; the options
+    of the reference's wrapper reach ``snapshot_download``; a dry run prints the repository's commit and file count."""
+    import types
+    from cverl_b200.cli import hf_download
+    local = tmp_path / "m"
+    local.mkdir()
+    (local / "config.json").write_text("{}")
+    (local / "model.safetensors").write_bytes(b"")
+    assert hf_download.main(["model", "org/name", "--local-dir", str(local)]) == 0
+    assert f"CVERL_HF_LOCAL_DIR={local}" in capsys.readouterr().out
+    calls = {}
+    fake = types.ModuleType("huggingface_hub")
+    fake.snapshot_download = lambda **kw: calls.update(kw) or str(tmp_path / "snap")
+    fake.model_info = lambda repo, revision=None, token=None: types.SimpleNamespace(sha="abc123", siblings=[1, 2, 3])
+    monkeypatch.setitem(sys.modules, "huggingface_hub", fake)
+    assert hf_download.main(["model", "org/name", "--local-dir", str(tmp_path / "new"), "--revision", "v1",
+                             "--allow-pattern", "*.json", "--allow-pattern", "*.safetensors", "--ignore-pattern", "*.bin",
+                             "--local-files-only", "--token", "t"]) == 0
+    assert calls["revision"] == "v1" and calls["allow_patterns"] == ["*.json", "*.safetensors"]
+    assert calls["ignore_patterns"] == ["*.bin"] and calls["local_files_only"] is True and calls["token"] == "t"
+    capsys.readouterr()
+    assert hf_download.main(["model", "org/name", "--dry-run"]) == 0
+    out = capsys.readouterr().out
+    assert "CVERL_HF_SHA=abc123" in out and "CVERL_HF_FILE_COUNT=3" in out
