@@ -432,3 +432,44 @@ def _zero2_bf16_comm_worker(rank, world):
 
 def test_bucketed_zero2_low_precision_gradient_communication():
     run_ranks(_zero2_bf16_comm_worker, 2)
+
+
+def test_peer_memory_weight_push_slices_cover_the_buffer_once():
+    """The multicast weight push: trainer t sends slice t; over all trainers the slices tile the padded flat buffer
+    exactly once, each starting on a 16-byte boundary; the peer-store mode sends the whole buffer to the served ranks."""
+    from cverl_b200.parallel.weight_sync import ParameterView, PeerMemoryWeightPush
+
+    class FakeBroadcaster:
+        def __init__(self):
+            self.pushed, self.syncs = [], 0
+
+        def push(self, src, second=0):
+            self.pushed.append((src.clone(), second))
+
+        def sync(self):
+            self.syncs += 1
+
+    params = [ParameterView(f"p{i}", torch.arange(n, dtype=torch.float32) + 100 * i) for i, n in enumerate((5, 13, 7))]
+    for trainers in (1, 2, 3):
+        got = torch.full((32,), -1.0)
+        for rank in range(trainers):
+            push = object.__new__(PeerMemoryWeightPush)
+            push.params, push.dtype, push.numel, push.trainers, push.world, push.mode = params, torch.float32, 25, trainers, 6, "nvls"
+            push.bc, push.recv = FakeBroadcaster(), torch.zeros(25)
+            push.push(rank, [])
+            assert push.bc.syncs == 1
+            for src, off in push.bc.pushed:
+                assert off % 16 == 0 and src.numel() % 4 == 0
+                assert (got[off // 4: off // 4 + src.numel()] == -1).all()        # nobody wrote here before
+                got[off // 4: off // 4 + src.numel()] = src
+        flat = torch.cat([p.tensor for p in params])
+        assert torch.equal(got[:25], flat) and (got[25:32] == 0).all()
+    push = object.__new__(PeerMemoryWeightPush)
+    push.params, push.dtype, push.numel, push.trainers, push.world, push.mode = params, torch.float32, 25, 2, 4, "symm"
+    push.bc, push.recv = FakeBroadcaster(), torch.zeros(25)
+    push.push(1, [3])
+    (src, dsts), = push.bc.pushed
+    assert dsts == [3] and src.numel() == 32 and torch.equal(src[:25], torch.cat([p.tensor for p in params]))
+    push.bc = FakeBroadcaster()
+    push.push(2, [])                                  # a rollout rank: no send, one barrier, parameters loaded
+    assert push.bc.pushed == [] and push.bc.syncs == 1
