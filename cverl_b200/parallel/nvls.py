@@ -116,6 +116,15 @@ class NvlsReduceScatter(_WithBarrier):
         return self.sq
 
 
+def allreduce_slice(n: int, world: int, rank: int):
+    """``(begin, length)`` of the slice of an ``n``-element bf16 buffer that ``rank`` reduces and re-broadcasts: equal
+    parts rounded up to 8 elements (16 bytes), the last rank taking what is left; the slices tile ``[0, n)``."""
+    per = (n // world + 7) // 8 * 8
+    lo = min(rank * per, n)
+    hi = min(lo + per, n) if rank < world - 1 else n
+    return lo, max(hi - lo, 0)
+
+
 class NvlsAllReduce(_WithBarrier):
     """bf16 buffer in multicast memory; ``all_reduce`` sums it over the ranks in place on every rank."""
 
@@ -127,11 +136,9 @@ class NvlsAllReduce(_WithBarrier):
 
     def all_reduce(self, numel: Optional[int] = None, max_blocks: int = 0) -> torch.Tensor:
         n = self.numel if numel is None else numel
-        w, r = self.buf.world, self.buf.rank
-        per = (n // w + 7) // 8 * 8
-        lo = min(r * per, n)
-        hi = min(lo + per, n) if r < w - 1 else n
-        if (hi - lo) % 8:
+        lo, length = allreduce_slice(n, self.buf.world, self.buf.rank)
+        hi = lo + length
+        if length % 8:
             raise ValueError("NvlsAllReduce: element count must be a multiple of 8")
         self.barrier()                   # every rank's partial result is in its buffer
         nv.check(nv.cuda().cvb_multimem_allreduce_bf16(self.buf.multicast_ptr, lo, hi - lo, max_blocks, nv.stream()),

@@ -473,3 +473,15 @@ def test_peer_memory_weight_push_slices_cover_the_buffer_once():
     push.bc = FakeBroadcaster()
     push.push(2, [])                                  # a rollout rank: no send, one barrier, parameters loaded
     assert push.bc.pushed == [] and push.bc.syncs == 1
+
+
+def test_multicast_allreduce_slices_tile_the_buffer():
+    from cverl_b200.parallel.nvls import allreduce_slice
+    for n in (8, 40, 40968, 83886080):
+        for world in (2, 3, 4, 8):
+            pos = 0
+            for r in range(world):
+                lo, length = allreduce_slice(n, world, r)
+                assert lo == pos and lo % 8 == 0 and length >= 0
+                pos += length
+            assert pos == n
