@@ -377,3 +377,15 @@ def test_zero_stage2_matches_stage1_and_resumes(tmp_path):
         assert float(ra["loss_sum"]) == pytest.approx(float(rb["loss_sum"]), rel=1e-5, abs=1e-7)
     bad = _run(2, "--tp", "2", "--zero-stage", "2", port=29715, check=False)
     assert bad.returncode != 0 and "--zero-stage 2 needs" in (bad.stdout + bad.stderr)
+
+
+def test_context_parallel_attention_layouts_agree_in_the_trainer():
+    """--cp-attn zigzag (resharded, load-balanced ring) and --cp-attn ring (contiguous shards) are the same attention:
+    two context-parallel ranks reach the same losses and gradient norms."""
+    base = ["--cp", "2", "--steps", "3", "--prompt-len", "8", "--response-len", "8"]
+    zig = _lines(_run(2, *base, "--cp-attn", "zigzag", port=29721))
+    ring = _lines(_run(2, *base, "--cp-attn", "ring", port=29722))
+    assert len(zig) == len(ring) == 3
+    for a, b in zip(zig, ring):
+        assert float(a["loss_sum"]) == pytest.approx(float(b["loss_sum"]), rel=2e-4, abs=1e-6)
+        assert float(a["global_grad_norm"]) == pytest.approx(float(b["global_grad_norm"]), rel=1e-3)
