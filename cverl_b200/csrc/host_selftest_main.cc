@@ -3,6 +3,7 @@
 //   * the RL math entry points on ragged masks, from several threads at once (they share no state);
 //   * argument validation paths (null data, shape mismatch) that must return an error, not touch memory;
 //   * the topology planner, 1F1B schedule and greedy owner assignment;
+//   * the safetensors writer / reader round trip, the byte tokenizer, the GSM8K answer extraction and the JSONL reader;
 //   * the shared-memory request / response transport with a server thread and a client thread.
 // Exit code 0 and a silent sanitizer are the pass criterion.  The reference ships no sanitizer target.
 #include <cmath>
@@ -25,6 +26,25 @@ int64_t cverl_shm_client_call(void* h, const void* request, int64_t request_size
                               int64_t response_capacity, int64_t timeout_ms);
 int64_t cverl_shm_server_wait(void* h, void* request, int64_t capacity, int64_t timeout_ms);
 int cverl_shm_server_reply(void* h, const void* response, int64_t size, int status);
+void* cverl_st_open(const char* path, char* err, int err_len);
+void cverl_st_close(void* h);
+int64_t cverl_st_count(void* h);
+const char* cverl_st_name(void* h, int64_t i);
+int cverl_st_info(void* h, const char* name, int* dtype, int* ndim, int64_t* shape8, int64_t* nbytes);
+int cverl_st_read(void* h, const char* name, void* dst, int64_t nbytes);
+int cverl_st_write(const char* path, int64_t n, const char* const* names, const int* dtypes, const int* ndims,
+                   const int64_t* shapes, const void* const* data);
+int64_t cverl_byte_encode(const char* text, int64_t len, int add_bos, int add_eos, int64_t max_tokens, int64_t* out,
+                          int64_t capacity);
+int64_t cverl_byte_decode(const int64_t* ids, int64_t n, int skip_special, char* out, int64_t capacity);
+int cverl_gsm8k_extract(const char* solution, int flexible, int64_t clip_chars, char* out, int64_t capacity);
+double cverl_gsm8k_reward(const char* solution, const char* ground_truth, int flexible, int64_t clip_chars,
+                          double correct_score, double format_score, double no_answer_score);
+void* cverl_jsonl_open(const char* path, const char* field_a, const char* field_b, int64_t max_rows);
+const char* cverl_jsonl_error(void* h);
+int64_t cverl_jsonl_rows(void* h);
+const char* cverl_jsonl_get(void* h, int64_t row, int which);
+void cverl_jsonl_close(void* h);
 }
 
 namespace {
@@ -151,6 +171,70 @@ void transport() {
   cverl_shm_transport_close(server);
 }
 
+void safetensors_round_trip() {
+  const std::string path = "/tmp/cverl_selftest_" + std::to_string(static_cast<long long>(getpid())) + ".safetensors";
+  std::vector<float> a(6);
+  std::vector<int64_t> b(3);
+  for (size_t i = 0; i < a.size(); ++i) a[i] = 0.5f * static_cast<float>(i);
+  for (size_t i = 0; i < b.size(); ++i) b[i] = 7 - static_cast<int64_t>(i);
+  const char* names[2] = {"layer.weight", "step \"q\""};
+  const int dtypes[2] = {0, 3};       // F32, I64
+  const int ndims[2] = {2, 1};
+  const int64_t shapes[3] = {2, 3, 3};
+  const void* data[2] = {a.data(), b.data()};
+  EXPECT(cverl_st_write(path.c_str(), 2, names, dtypes, ndims, shapes, data) == 0);
+  char err[256] = {0};
+  void* h = cverl_st_open(path.c_str(), err, sizeof(err));
+  EXPECT(h != nullptr);
+  if (h) {
+    EXPECT(cverl_st_count(h) == 2);
+    EXPECT(cverl_st_name(h, 5) == nullptr);
+    int dt = -1, nd = -1;
+    int64_t shape8[8] = {0}, nbytes = 0;
+    EXPECT(cverl_st_info(h, "layer.weight", &dt, &nd, shape8, &nbytes) == 0 && dt == 0 && nd == 2 && shape8[1] == 3 &&
+           nbytes == 24);
+    std::vector<float> back(6);
+    EXPECT(cverl_st_read(h, "layer.weight", back.data(), 24) == 0 && back[5] == 2.5f);
+    EXPECT(cverl_st_read(h, "layer.weight", back.data(), 20) != 0);       // wrong size: refused, nothing read
+    EXPECT(cverl_st_info(h, "missing", &dt, &nd, shape8, &nbytes) != 0);
+    cverl_st_close(h);
+  }
+  EXPECT(cverl_st_open("/tmp/cverl_selftest_no_such_file", err, sizeof(err)) == nullptr && err[0] != 0);
+  std::remove(path.c_str());
+}
+
+void text_and_reward() {
+  const char* text = "12 + 30 = 42";
+  int64_t ids[8];
+  const int64_t full = cverl_byte_encode(text, 12, 1, 1, 0, ids, 8);      // capacity smaller than the encoding
+  EXPECT(full == 14 && ids[0] == 1 && ids[1] == 4 + '1');
+  std::vector<int64_t> all(static_cast<size_t>(full));
+  EXPECT(cverl_byte_encode(text, 12, 1, 1, 0, all.data(), full) == full);
+  char out[32];
+  const int64_t n = cverl_byte_decode(all.data(), full, 1, out, sizeof(out));
+  EXPECT(n == 12 && std::memcmp(out, text, 12) == 0);
+  EXPECT(cverl_byte_decode(all.data(), full, 0, out, 4) > 4);             // truncated write, full length returned
+  char ans[64];
+  EXPECT(cverl_gsm8k_extract("so the total is\n#### 1,234", 0, 0, ans, sizeof(ans)) == 1 && std::string(ans) == "1234");
+  EXPECT(cverl_gsm8k_extract("no marker here", 0, 0, ans, sizeof(ans)) == 0);
+  EXPECT(cverl_gsm8k_reward("#### 42", "#### 42", 0, 0, 1.0, 0.1, 0.0) == 1.0);
+  EXPECT(cverl_gsm8k_reward("#### 41", "#### 42", 0, 0, 1.0, 0.1, 0.0) == 0.1);
+  const std::string path = "/tmp/cverl_selftest_" + std::to_string(static_cast<long long>(getpid())) + ".jsonl";
+  if (FILE* f = std::fopen(path.c_str(), "w")) {
+    std::fputs("{\"prompt\": \"2+2?\", \"answer\": \"#### 4\"}\n{\"prompt\": \"a \\\"q\\\"\", \"answer\": \"x\"}\n", f);
+    std::fclose(f);
+    void* rows = cverl_jsonl_open(path.c_str(), "prompt", "answer", 0);
+    EXPECT(rows != nullptr);
+    if (rows) {
+      EXPECT(cverl_jsonl_rows(rows) == 2);
+      EXPECT(std::string(cverl_jsonl_get(rows, 0, 1)) == "#### 4");
+      EXPECT(std::string(cverl_jsonl_get(rows, 1, 0)) == "a \"q\"");
+      cverl_jsonl_close(rows);
+    }
+    std::remove(path.c_str());
+  }
+}
+
 }  // namespace
 
 int main() {
@@ -158,6 +242,8 @@ int main() {
   for (unsigned t = 0; t < 4; ++t) pool.emplace_back(rl_math, t);
   planner();
   for (auto& th : pool) th.join();
+  safetensors_round_trip();
+  text_and_reward();
   transport();
   if (g_failures) {
     std::fprintf(stderr, "%d checks failed\n", g_failures);
