@@ -19,6 +19,7 @@
 #include <fstream>
 #include <map>
 #include <memory>
+#include <mutex>
 #include <sstream>
 #include <stdexcept>
 #include <string>
@@ -484,7 +485,12 @@ struct Tokenizer {
     }
   }
 
+  // One handle may be shared by several threads (a data loader's workers): the regex match data and the merge
+  // cache are per handle, so encoding takes the handle's lock.  Decoding only reads the vocabulary.
+  std::mutex encode_mutex;
+
   std::vector<int64_t> encode(const std::string& text) {
+    std::lock_guard<std::mutex> lock(encode_mutex);
     std::vector<int64_t> out;
     size_t pos = 0, span_begin = 0;
     while (pos < text.size()) {

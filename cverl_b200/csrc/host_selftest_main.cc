@@ -4,7 +4,8 @@
 //   * argument validation paths (null data, shape mismatch) that must return an error, not touch memory;
 //   * the topology planner, 1F1B schedule and greedy owner assignment;
 //   * the safetensors writer / reader round trip, the byte tokenizer, the GSM8K answer extraction and the JSONL reader;
-//   * the shared-memory request / response transport with a server thread and a client thread.
+//   * the shared-memory request / response transport with a server thread and a client thread;
+//   * with a tokenizer.json as the first argument, the BPE tokenizer from two threads on one handle.
 // Exit code 0 and a silent sanitizer are the pass criterion.  The reference ships no sanitizer target.
 #include <cmath>
 #include <cstdint>
@@ -45,6 +46,11 @@ const char* cverl_jsonl_error(void* h);
 int64_t cverl_jsonl_rows(void* h);
 const char* cverl_jsonl_get(void* h, int64_t row, int which);
 void cverl_jsonl_close(void* h);
+void* cverl_bpe_open(const char* tokenizer_json, char* err, int err_len);
+void cverl_bpe_close(void* h);
+int64_t cverl_bpe_vocab_size(void* h);
+int64_t cverl_bpe_encode(void* h, const char* text, int64_t len, int64_t* out, int64_t capacity);
+int64_t cverl_bpe_decode(void* h, const int64_t* ids, int64_t n, int skip_special, char* out, int64_t capacity);
 }
 
 namespace {
@@ -235,9 +241,38 @@ void text_and_reward() {
   }
 }
 
+// argv[1] (optional): a Hugging Face tokenizer.json; encode / decode round trips from two threads sharing one handle
+void bpe(const char* tokenizer_json) {
+  char err[256] = {0};
+  void* h = cverl_bpe_open(tokenizer_json, err, sizeof(err));
+  EXPECT(h != nullptr);
+  if (!h) {
+    std::fprintf(stderr, "bpe: %s\n", err);
+    return;
+  }
+  EXPECT(cverl_bpe_vocab_size(h) > 0);
+  auto work = [&](const char* text) {
+    const int64_t len = static_cast<int64_t>(std::strlen(text));
+    std::vector<int64_t> ids(256);
+    const int64_t n = cverl_bpe_encode(h, text, len, ids.data(), 256);
+    EXPECT(n > 0 && n <= 256);
+    std::vector<char> out(512);
+    const int64_t m = cverl_bpe_decode(h, ids.data(), n, 1, out.data(), 512);
+    EXPECT(m == len && std::memcmp(out.data(), text, static_cast<size_t>(len)) == 0);
+    int64_t two[2];
+    EXPECT(cverl_bpe_encode(h, text, len, two, 2) == n);            // capacity smaller than the encoding
+  };
+  std::thread t1(work, "hello world, 123 + 456 = 579"), t2(work, "the quick brown fox\n  jumps");
+  t1.join();
+  t2.join();
+  cverl_bpe_close(h);
+  EXPECT(cverl_bpe_open("/tmp/cverl_selftest_no_such_tokenizer.json", err, sizeof(err)) == nullptr);
+}
+
 }  // namespace
 
-int main() {
+int main(int argc, char** argv) {
+  if (argc > 1) bpe(argv[1]);
   std::vector<std::thread> pool;
   for (unsigned t = 0; t < 4; ++t) pool.emplace_back(rl_math, t);
   planner();

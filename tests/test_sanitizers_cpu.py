@@ -1,7 +1,9 @@
 """The host runtime under AddressSanitizer + UBSan and under ThreadSanitizer: the C ABI self-test driver
-(``csrc/host_selftest_main.cc``: RL math from four threads, argument validation, planner, shared-memory transport
-with a server and a client thread) must exit 0 without a sanitizer report."""
+(``csrc/host_selftest_main.cc``: RL math from four threads, argument validation, planner, safetensors round trip,
+byte tokenizer, reward extraction, JSONL reader, the BPE tokenizer from two threads on one handle, shared-memory
+transport with a server and a client thread) must exit 0 without a sanitizer report."""
 import subprocess
+from pathlib import Path
 
 import pytest
 
@@ -16,7 +18,8 @@ def test_host_runtime_under_sanitizer(kind):
         if "no C++ compiler with the runtime" in str(exc):
             pytest.skip(str(exc))
         raise
-    p = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
+    tokenizer = Path(__file__).resolve().parent / "fixtures" / "synthetic_tokenizer.json"
+    p = subprocess.run([str(exe), str(tokenizer)], capture_output=True, text=True, timeout=300)   # BPE from two threads
     assert p.returncode == 0, p.stdout + p.stderr
     assert "host self-test passed" in p.stdout
     for word in ("AddressSanitizer", "ThreadSanitizer", "runtime error:", "LeakSanitizer"):
