@@ -5,7 +5,8 @@
 //   * the topology planner, 1F1B schedule and greedy owner assignment;
 //   * the safetensors writer / reader round trip, the byte tokenizer, the GSM8K answer extraction and the JSONL reader;
 //   * the shared-memory request / response transport with a server thread and a client thread;
-//   * with a tokenizer.json as the first argument, the BPE tokenizer from two threads on one handle.
+//   * with a tokenizer.json as the first argument, the BPE tokenizer from two threads on one handle;
+//   * with a plugin .so as the second argument, the rollout-worker plugin loader.
 // Exit code 0 and a silent sanitizer are the pass criterion.  The reference ships no sanitizer target.
 #include <cmath>
 #include <cstdint>
@@ -18,6 +19,7 @@
 #include <unistd.h>
 
 #include "cverl/core_algos.h"
+#include "cverl/rollout_plugin.h"
 #include "cverl/topology.h"
 
 extern "C" {
@@ -269,10 +271,48 @@ void bpe(const char* tokenizer_json) {
   EXPECT(cverl_bpe_open("/tmp/cverl_selftest_no_such_tokenizer.json", err, sizeof(err)) == nullptr);
 }
 
+// argv[2] (optional): a rollout-worker plugin (.so): load, generate into caller buffers, walk the parameters, unload
+void plugin(const char* so_path) {
+  char err[256] = {0};
+  void* h = cverl_plugin_load(so_path, "{\"vocab_size\": 32}", err, sizeof(err));
+  EXPECT(h != nullptr);
+  if (!h) {
+    std::fprintf(stderr, "plugin: %s\n", err);
+    return;
+  }
+  const int64_t B = 2, P = 4, N = 3;
+  std::vector<int64_t> ids(B * P, 5), mask(B * P, 1), lens(B, P), out_ids(B * N, -1), out_len(B, -1);
+  std::vector<float> out_lp(B * N, 1.f);
+  cverl_generate_args_t a{};
+  a.token_ids = ids.data();
+  a.attention_mask = mask.data();
+  a.lengths = lens.data();
+  a.batch = B;
+  a.prompt_len = P;
+  a.config.max_new_tokens = N;
+  a.config.temperature = 1.0;
+  a.config.top_p = 1.0;
+  a.config.eos_token_id = -1;
+  a.config.seed = 7;
+  a.out_token_ids = out_ids.data();
+  a.out_logprobs = out_lp.data();
+  a.out_lengths = out_len.data();
+  EXPECT(cverl_plugin_generate(h, &a) == 0);
+  for (int64_t b = 0; b < B; ++b) EXPECT(out_len[b] >= 0 && out_len[b] <= N);
+  const int64_t np = cverl_plugin_num_parameters(h);
+  EXPECT(np >= 0);
+  cverl_parameter_view_t view{};
+  for (int64_t i = 0; i < np; ++i) EXPECT(cverl_plugin_parameter(h, i, &view) == 0 && view.name != nullptr);
+  EXPECT(cverl_plugin_parameter(h, np, &view) != 0);                       // one past the end
+  cverl_plugin_unload(h);
+  EXPECT(cverl_plugin_load("/tmp/cverl_selftest_no_such_plugin.so", "{}", err, sizeof(err)) == nullptr && err[0] != 0);
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
   if (argc > 1) bpe(argv[1]);
+  if (argc > 2) plugin(argv[2]);
   std::vector<std::thread> pool;
   for (unsigned t = 0; t < 4; ++t) pool.emplace_back(rl_math, t);
   planner();
