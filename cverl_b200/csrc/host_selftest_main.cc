@@ -128,6 +128,36 @@ void rl_math(unsigned seed) {
                                         -1.f, -1.f, 0.5f, CVERL_LOSS_AGG_TOKEN_MEAN, &res) != CVERL_OK);
 }
 
+// degenerate shapes and values: empty tensors, an all-zero mask, infinities - a status code, never a bad access
+void rl_math_edges() {
+  std::vector<float> one(1, 0.f), big(12);
+  for (size_t i = 0; i < big.size(); ++i) big[i] = (i % 3 == 0) ? INFINITY : (i % 3 == 1 ? -1e30f : 1e30f);
+  std::vector<float> zeros(12, 0.f), out(12), out2(12);
+  std::vector<int64_t> groups(3, 0);
+  float v = 0.f;
+  for (int64_t r : {int64_t(0), int64_t(3)}) {
+    for (int64_t c : {int64_t(0), int64_t(4)}) {
+      const cverl_const_tensor2d_t x{big.data(), CVERL_DTYPE_F32, CVERL_DEVICE_CPU, r, c};
+      const cverl_const_tensor2d_t m{zeros.data(), CVERL_DTYPE_F32, CVERL_DEVICE_CPU, r, c};
+      const cverl_tensor2d_t o{out.data(), CVERL_DTYPE_F32, CVERL_DEVICE_CPU, r, c};
+      const cverl_tensor2d_t o2{out2.data(), CVERL_DTYPE_F32, CVERL_DEVICE_CPU, r, c};
+      (void)cverl_masked_sum_f32_cpu(x, m, &v);
+      (void)cverl_masked_mean_f32_cpu(x, m, &v);
+      (void)cverl_masked_whiten_f32_cpu(x, m, 1, o);
+      (void)cverl_kl_penalty_f32_cpu(x, x, CVERL_KL_K3, o);
+      (void)cverl_gae_advantage_return_f32_cpu(x, x, m, 1.0f, 0.95f, o, o2);
+      (void)cverl_grpo_outcome_advantage_f32_cpu(x, m, groups.data(), 1e-6f, 1, o, o2);
+      cverl_ppo_loss_result_t res{};
+      (void)cverl_ppo_clipped_loss_f32_cpu(x, x, x, m, 0.2f, -1.f, -1.f, 3.0f, CVERL_LOSS_AGG_SEQ_MEAN_TOKEN_MEAN, &res);
+      (void)cverl_ppo_clipped_loss_backward_f32_cpu(x, x, x, m, 0.2f, -1.f, -1.f, 3.0f, CVERL_LOSS_AGG_SEQ_MEAN_TOKEN_SUM, o);
+    }
+  }
+  const cverl_const_tensor2d_t neg{one.data(), CVERL_DTYPE_F32, CVERL_DEVICE_CPU, -1, 1};
+  EXPECT(cverl_masked_sum_f32_cpu(neg, neg, &v) != CVERL_OK);
+  const cverl_const_tensor2d_t cuda_view{one.data(), CVERL_DTYPE_F32, CVERL_DEVICE_CUDA, 1, 1};
+  EXPECT(cverl_masked_sum_f32_cpu(cuda_view, cuda_view, &v) != CVERL_OK);   // a device view on the CPU entry point
+}
+
 void planner() {
   const int64_t dims[7] = {2, 2, 1, 2, 1, 1, 4};   // dp, pp, cp, tp, ep, sp, micro-batches
   int64_t coords[5];
@@ -141,6 +171,24 @@ void planner() {
   int64_t micro[64], n = 0, live = 0;
   EXPECT(cverl_pipeline_1f1b(1, 4, 8, types, micro, 64, &n, &live) == 0 && n == 16);
   EXPECT(cverl_pipeline_1f1b(1, 4, 8, types, micro, 3, &n, &live) != 0);          // capacity too small
+  // many layouts, valid and not: every call must return (0 or an error), never touch memory past its capacities
+  uint32_t s = 12345u;
+  auto rnd = [&](int lo, int hi) { s = s * 1664525u + 1013904223u; return lo + static_cast<int>((s >> 10) % static_cast<uint32_t>(hi - lo + 1)); };
+  for (int iter = 0; iter < 400; ++iter) {
+    int64_t d[7] = {rnd(0, 3), rnd(0, 3), rnd(1, 2), rnd(1, 4), rnd(1, 2), 1, rnd(0, 6)};
+    const int64_t prod = d[0] * d[1] * d[2] * d[3] * d[4];
+    const int64_t w = rnd(0, 4) == 0 ? prod + rnd(-1, 1) : prod;
+    const int64_t rank = rnd(-1, static_cast<int>(w > 0 ? w : 1));
+    int64_t c5[5], out[4], cnt = 0;
+    const int rc = cverl_topology_coords(d, w, rnd(1, 8), rank, c5);
+    if (rc == 0) EXPECT(rank >= 0 && rank < w && w == prod);
+    for (int axis = 0; axis < 5; ++axis) (void)cverl_topology_group(d, w, 8, rank, axis, out, rnd(0, 4), &cnt);
+    int64_t lb = 0, le = 0;
+    (void)cverl_pipeline_layer_range(rnd(0, 48), d[1], rnd(-1, 4), &lb, &le);
+    int32_t t4[4];
+    int64_t m4[4], n4 = 0, live4 = 0;
+    (void)cverl_pipeline_1f1b(rnd(-1, 4), d[1], d[6], t4, m4, rnd(0, 4), &n4, &live4);
+  }
   const int64_t numels[6] = {50, 10, 40, 30, 20, 60};
   int64_t owners[6];
   EXPECT(cverl_greedy_owners(numels, 6, 3, owners) == 0);
@@ -316,6 +364,7 @@ int main(int argc, char** argv) {
   std::vector<std::thread> pool;
   for (unsigned t = 0; t < 4; ++t) pool.emplace_back(rl_math, t);
   planner();
+  rl_math_edges();
   for (auto& th : pool) th.join();
   safetensors_round_trip();
   text_and_reward();
