@@ -49,6 +49,7 @@ from ..utils import checkpoint as ckpt
 from ..utils import fallbacks as _fallbacks
 from ..utils.metrics import MetricsCsv, format_line
 from ..utils.watchdog import Heartbeat, PeerFailure, Watchdog
+from ..utils.fault_injection import HostFault
 from .actor import ActorConfig, ActorEngine
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -622,7 +623,10 @@ def run(argv=None) -> int:
     engine = ActorEngine(model, opt, ecfg)
     exit_ok = True
     log_lines = []
+    fault = HostFault.from_env()
     for step in range(start_step, args.steps):
+        if fault is not None:           # tests only: a host-side failure between steps, nothing in flight
+            fault.fire(rank, step, sync=torch.cuda.synchronize if use_cuda else None)
         if watchdog is not None:
             watchdog.hb.beat(step)
             watchdog.check()            # host-side: raises before any kernel of this step is launched

@@ -35,5 +35,12 @@ fi
 [ -n "${RESUME_CHECKPOINT:-}" ] && ARGS+=(--resume-checkpoint "$RESUME_CHECKPOINT")
 [ -n "${METRICS_CSV:-}" ] && ARGS+=(--metrics-csv "$METRICS_CSV")
 [ -n "${NCCL_LIB_DIR:-}" ] && export LD_LIBRARY_PATH="$NCCL_LIB_DIR:${LD_LIBRARY_PATH:-}"
+if [ -n "${MAX_RESTARTS:-}" ] || [ -n "${LOG_DIR:-}" ]; then
+  # supervised: one log per rank under LOG_DIR, a failed or stalled rank ends the attempt, and the job is started
+  # again from the newest complete checkpoint of CHECKPOINT_DIR up to MAX_RESTARTS times
+  exec python -m cverl_b200.cli.launch --nproc "${LOCAL_WORLD_SIZE:-$WORLD_SIZE}" --master-addr 127.0.0.1 \
+    --master-port "${MASTER_PORT:-29500}" --max-restarts "${MAX_RESTARTS:-0}" --log-dir "${LOG_DIR:-}" \
+    --stall-timeout-s "${STALL_TIMEOUT_S:-0}" -- -m cverl_b200.trainer.ppo_trainer "${ARGS[@]}" "$@"
+fi
 exec python -m torch.distributed.run --nnodes=1 --nproc-per-node "${LOCAL_WORLD_SIZE:-$WORLD_SIZE}" \
   --master-addr 127.0.0.1 --master-port "${MASTER_PORT:-29500}" -m cverl_b200.trainer.ppo_trainer "${ARGS[@]}" "$@"

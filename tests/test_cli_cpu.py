@@ -175,3 +175,10 @@ def test_env_driven_trainer_launcher_script():
     assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-2500:]
     steps = [ln for ln in p.stdout.splitlines() if ln.startswith("step=")]
     assert len(steps) == 2 and " tp=2 " in steps[0] and " pp=1 " in steps[0] and "dtype=float32" in steps[0]
+    # MAX_RESTARTS / LOG_DIR select the supervising launcher: same flags, one log per rank, a JSON summary
+    env.update(MAX_RESTARTS="1", MASTER_PORT="29588")
+    p = subprocess.run(["bash", str(ROOT / "examples" / "run_pp_tp_ppo_trainer.sh"), "", "--backend", "gloo"], cwd=ROOT,
+                       env=env, capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-2500:]
+    assert len([ln for ln in p.stdout.splitlines() if ln.startswith("step=")]) == 2
+    assert json.loads(p.stdout.splitlines()[-1])["launch"]["ok"]
