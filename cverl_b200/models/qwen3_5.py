@@ -27,6 +27,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint as _checkpoint
 
 from .. import ops
 from ..ops import attention as attn_ops
@@ -48,12 +49,17 @@ class Qwen35Model(torch.nn.Module):
                  ctx: ParallelContext = SINGLE, layer_begin: int = 0, layer_end: Optional[int] = None,
                  first_stage: bool = True, last_stage: bool = True, pad_multiple: int = 1,
                  with_main_grad: bool = True, flat_allocator=None, grad_buckets: bool = False,
-                 bucket_align: int = 8, grad_slots: int = 2):
+                 bucket_align: int = 8, grad_slots: int = 2, activation_checkpointing: bool = False):
         """``grad_buckets``: per-layer gradient buckets on ``grad_slots`` rotating buffers instead of a full fp32
         gradient twin (for ``BucketedZero2Optimizer``, which reduces a layer's gradients while the backward pass
-        runs the next layer); the embedding and the head keep a buffer each."""
+        runs the next layer); the embedding and the head keep a buffer each.
+        ``activation_checkpointing``: a layer keeps only its input between the forward and the backward pass and is
+        run again when its backward starts (the reference declares the policy flag,
+        include/cverl/distributed/topology.h:29, and implements recomputation only inside its two custom autograd
+        functions)."""
         super().__init__()
         self.cfg = cfg
+        self.activation_checkpointing = activation_checkpointing
         self.ctx = ctx
         self.dtype = dtype
         self.layer_begin = layer_begin
@@ -491,28 +497,42 @@ class Qwen35Model(torch.nn.Module):
                                    grad_in_tensor=True)
         return out
 
+    def _layer(self, i: int, delta: torch.Tensor, resid: Optional[torch.Tensor], batch: int, seq: int,
+               cache: Optional[dict]):
+        """Layer ``i`` on the (delta, residual) pair: norm, attention of the layer's kind, norm, MLP."""
+        cfg = self.cfg
+        eps, off = cfg.rms_norm_eps, cfg.norm_weight_offset
+        p = f"{cfg.layer_root}{i}."
+        n1, resid = ops.add_rmsnorm(delta, resid, self.param(p + "input_layernorm.weight"), eps, off)
+        if cfg.layer_types[i] == "full_attention":
+            a = self.full_attention(n1, i, batch, seq, cache=cache)
+        else:
+            a = self.linear_attention(n1, i, batch, seq, cache=cache)
+        n2, resid = ops.add_rmsnorm(a, resid, self.param(p + "post_attention_layernorm.weight"), eps, off)
+        return self.mlp(n2, i), resid
+
     def forward_layers(self, x: torch.Tensor, batch: int, seq: int, final_norm: bool = True,
                        caches: Optional[list] = None) -> torch.Tensor:
         """Run this stage's layers on the packed residual stream ``x`` ``[B*S, H]``."""
         cfg = self.cfg
         eps, off = cfg.rms_norm_eps, cfg.norm_weight_offset
         delta, resid = x, None
-        boundary = self.backward_boundary if torch.is_grad_enabled() else None
+        boundary_ok = torch.is_grad_enabled()
+        boundary = self.backward_boundary if boundary_ok else None
         for i in range(self.layer_begin, self.layer_end):
-            p = f"{cfg.layer_root}{i}."
             if boundary is not None:       # backward: layer i (bucket 1 + i - begin) is complete when this fires
                 delta, resid = boundary(delta, resid, 1 + i - self.layer_begin)
-            n1, resid = ops.add_rmsnorm(delta, resid, self.param(p + "input_layernorm.weight"), eps, off)
             cache = None
             if caches is not None:
                 cache = {}
                 caches.append(cache)
-            if cfg.layer_types[i] == "full_attention":
-                a = self.full_attention(n1, i, batch, seq, cache=cache)
+            if self.activation_checkpointing and boundary_ok and cache is None:
+                # only (delta, resid) stay alive; the layer runs again when the backward pass reaches it.  No
+                # random numbers are drawn in a layer, so there is no generator state to carry
+                delta, resid = _checkpoint(self._layer, i, delta, resid, batch, seq, None, use_reentrant=False,
+                                           preserve_rng_state=False)
             else:
-                a = self.linear_attention(n1, i, batch, seq, cache=cache)
-            n2, resid = ops.add_rmsnorm(a, resid, self.param(p + "post_attention_layernorm.weight"), eps, off)
-            delta = self.mlp(n2, i)
+                delta, resid = self._layer(i, delta, resid, batch, seq, cache)
         if boundary is not None:           # fires before the last layer's backward starts
             delta, resid = boundary(delta, resid, self.layer_end - self.layer_begin + 1)
         if self.last_stage and final_norm:
@@ -525,6 +545,9 @@ class Qwen35Model(torch.nn.Module):
         batch, seq = input_ids.shape
         if self.sequence_parallel:
             sp = self.ctx.tp_sp
+            if self.activation_checkpointing:
+                raise RuntimeError("activation checkpointing is not combined with the sequence-parallel tensor-parallel "
+                                   "path (its peer-mapped buffers are handed from layer to layer in launch order)")
             if not (self.first_stage and self.last_stage) or self.cfg.is_qwen3_moe or self.ctx.cp_size > 1:
                 raise RuntimeError("the sequence-parallel tensor-parallel path needs a dense single-stage model")
             if not (sp.fits(batch * seq, self.cfg.hidden_size) and input_ids.is_cuda):

@@ -121,6 +121,8 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--zero-stage", type=int, default=1, choices=[1, 2],
                    help="2: per-layer gradient buckets on rotating buffers, reduce-scattered from inside the backward "
                         "pass on a side stream (no full fp32 gradient copy; flat mode, --tp 1 --pp 1 --cp 1 --ep 1)")
+    _add_flag(g, "--activation-checkpointing",
+              help="keep only each layer's input for the backward pass and run the layer again there")
     g.add_argument("--zero-grad-slots", type=int, default=2, help="gradient bucket buffers in flight for --zero-stage 2")
     g.add_argument("--zero-comm", default="nccl", choices=["nccl", "symm"],
                    help="ZeRO gradient reduce-scatter / parameter all-gather: library collectives, or this "
@@ -525,6 +527,14 @@ def run(argv=None) -> int:
     symm_ok = use_cuda and dtype == torch.bfloat16
     seq_local = (args.prompt_len + args.response_len) // max(args.cp, 1)
     rows = args.micro_batch_seqs * seq_local
+    if args.activation_checkpointing:
+        # the peer-memory paths hand per-layer buffers from the forward to the backward pass in launch order; a layer
+        # that runs a second time in the middle of the backward pass is only validated on the collective paths
+        for name in ("tp_comm", "ep_comm", "cp_comm"):
+            if getattr(args, name) in ("sp", "symm"):
+                if rank == 0 and getattr(args, name.split("_")[0]) > 1:
+                    print(f"note: --activation-checkpointing uses --{name.replace('_', '-')} nccl", flush=True)
+                setattr(args, name, "nccl")
     if args.tp_comm == "symm" and args.tp > 2 and symm_ok:
         # the mirror-store all-reduce sends every partial N-1 times: measured faster than NCCL at TP=2 only
         if rank == 0:
@@ -555,7 +565,8 @@ def run(argv=None) -> int:
     model = Qwen35Model(cfg, dtype=dtype, device=device, ctx=ctx, layer_begin=lb, layer_end=le, first_stage=first,
                         last_stage=last, pad_multiple=args.dp * 8,
                         flat_allocator=fused_comm.allocator if fused_comm else None, grad_buckets=zero2,
-                        bucket_align=args.dp * 8, grad_slots=args.zero_grad_slots)
+                        bucket_align=args.dp * 8, grad_slots=args.zero_grad_slots,
+                        activation_checkpointing=args.activation_checkpointing)
     if loader is not None:
         load_model_weights(model, loader)
     else:

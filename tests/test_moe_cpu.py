@@ -1,4 +1,5 @@
 """Qwen3-MoE: grouped path vs the dense expert loop; expert parallelism over gloo ranks."""
+import pytest
 import torch
 
 from cverl_b200.models.config import Qwen35TextConfig
@@ -75,3 +76,46 @@ def _ep_worker(rank, world):
 
 def test_expert_parallel_matches_single_rank():
     run_ranks(_ep_worker, 2)
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_activation_checkpointing_same_gradients_fewer_saved_bytes(moe):
+    """A checkpointed layer keeps only its input: the gradients are those of the plain model (the recomputation is
+    the same arithmetic), and the bytes autograd holds between the passes drop."""
+    cfg = Qwen35TextConfig.tiny(moe=moe, layers=4)
+    ids = torch.randint(0, cfg.vocab_size, (2, 24))
+    grads, held = [], []
+    for ckpt in (False, True):
+        m = Qwen35Model(cfg, dtype=torch.float32, activation_checkpointing=ckpt)
+        m.init_weights(seed=5)
+        seen = {}
+
+        def pack(t):
+            if t.untyped_storage().data_ptr() not in params:
+                seen[t.untyped_storage().data_ptr()] = t.untyped_storage().nbytes()
+            return t
+        params = {p.untyped_storage().data_ptr() for p in m.parameters()}
+        with torch.autograd.graph.saved_tensors_hooks(pack, lambda t: t):
+            lp = m.response_logprobs(ids, 8)
+        held.append(sum(seen.values()))
+        lp.sum().backward()
+        m_grads = {n: (p.main_grad.clone() if getattr(p, "main_grad", None) is not None else None)
+                   for n, p in m.flat.params.items()}
+        for n, p in m.flat.params.items():
+            if p.grad is not None:
+                m_grads[n] = p.grad.clone() if m_grads[n] is None else m_grads[n] + p.grad
+        grads.append(m_grads)
+    assert held[1] < 0.6 * held[0], held
+    assert set(grads[0]) == set(grads[1])
+    checked = 0
+    for n, g in grads[0].items():
+        if g is None:
+            assert grads[1][n] is None
+            continue
+        torch.testing.assert_close(grads[1][n], g, rtol=1e-6, atol=1e-7)
+        checked += int(g.abs().sum() > 0)
+    assert checked > 10
+    # no graph, no checkpointing: inference and cached decode go straight through
+    m.eval()
+    with torch.no_grad():
+        assert torch.isfinite(m.response_logprobs(ids, 8)).all()

@@ -389,3 +389,20 @@ def test_context_parallel_attention_layouts_agree_in_the_trainer():
     for a, b in zip(zig, ring):
         assert float(a["loss_sum"]) == pytest.approx(float(b["loss_sum"]), rel=2e-4, abs=1e-6)
         assert float(a["global_grad_norm"]) == pytest.approx(float(b["global_grad_norm"]), rel=1e-3)
+
+
+@pytest.mark.parametrize("nproc,flags,port", [
+    (2, ["--pp", "2", "--micro-batches", "2"], 29731),
+    (2, ["--cp", "2"], 29733),
+    (2, ["--dp", "2", "--zero-stage", "2"], 29735),
+])
+def test_activation_checkpointing_changes_no_number(nproc, flags, port):
+    """Layers run again inside the backward pass - under the 1F1B schedule, with the context-parallel exchanges and
+    state hand-offs repeated, and with the stage-2 bucket boundaries between the layers: same losses, same norms."""
+    plain = _lines(_run(nproc, *flags, "--steps", "2", port=port))
+    ckpt = _lines(_run(nproc, *flags, "--steps", "2", "--activation-checkpointing", port=port + 1))
+    assert len(plain) == len(ckpt) == 2
+    for ra, rb in zip(plain, ckpt):
+        assert float(ra["loss_sum"]) == pytest.approx(float(rb["loss_sum"]), rel=1e-6, abs=1e-7)
+        assert float(ra["global_grad_norm"]) == pytest.approx(float(rb["global_grad_norm"]), rel=1e-5)
+        assert float(ra["grad_norm_sum"]) == pytest.approx(float(rb["grad_norm_sum"]), rel=1e-5)
