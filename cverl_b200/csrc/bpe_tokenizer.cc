@@ -11,10 +11,12 @@
 // development header is needed; without the library a hand-written scanner implements the
 // default pattern (ASCII classes exact, other code points treated as letters).
 #include <algorithm>
+#include <atomic>
 #include <cctype>
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <deque>
 #include <dlfcn.h>
 #include <fstream>
 #include <map>
@@ -23,6 +25,8 @@
 #include <sstream>
 #include <stdexcept>
 #include <string>
+#include <string_view>
+#include <thread>
 #include <unordered_map>
 #include <vector>
 
@@ -163,7 +167,9 @@ struct Pcre2 {
   using ovec_t = size_t* (*)(void*);
   using free_code_t = void (*)(void*);
   using free_md_t = void (*)(void*);
+  using jit_t = int (*)(void*, uint32_t);
   void* lib = nullptr;
+  jit_t jit_compile = nullptr;   // optional: absent in a PCRE2 built without JIT support
   compile_t compile = nullptr;
   mdata_t mdata = nullptr;
   match_t match = nullptr;
@@ -183,6 +189,7 @@ struct Pcre2 {
     ovec = reinterpret_cast<ovec_t>(dlsym(lib, "pcre2_get_ovector_pointer_8"));
     free_code = reinterpret_cast<free_code_t>(dlsym(lib, "pcre2_code_free_8"));
     free_md = reinterpret_cast<free_md_t>(dlsym(lib, "pcre2_match_data_free_8"));
+    jit_compile = reinterpret_cast<jit_t>(dlsym(lib, "pcre2_jit_compile_8"));
     ok = compile && mdata && match && ovec && free_code && free_md;
   }
   static Pcre2& get() {
@@ -190,7 +197,8 @@ struct Pcre2 {
     return p;
   }
 };
-constexpr uint32_t kPcre2Utf = 0x00080000u, kPcre2Ucp = 0x00020000u;
+constexpr uint32_t kPcre2Utf = 0x00080000u, kPcre2Ucp = 0x00020000u, kPcre2JitComplete = 0x00000001u,
+                   kPcre2NoUtfCheck = 0x40000000u;
 
 const char* kDefaultPattern =
     "(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\\r\\n\\p{L}\\p{N}]?\\p{L}+|\\p{N}| ?[^\\s\\p{L}\\p{N}]+[\\r\\n]*|\\s*[\\r\\n]+|\\s+(?!\\S)|\\s+";
@@ -218,15 +226,51 @@ struct Tokenizer {
   std::unordered_map<std::string, int> uni_to_byte;
   std::string pattern;
   void* re = nullptr;
-  void* md = nullptr;
+  bool jit = false;
   int64_t pad_id = -1, bos_id = -1, eos_id = -1, unk_id = -1;
-  std::unordered_map<std::string, std::vector<int64_t>> cache;
   std::string error;
+
+  // One handle serves any number of threads at once (a data loader's workers, encode_batch): everything below
+  // load() is read-only except these two pools, which carry their own locks.
+  //  * match data: a PCRE2 match block belongs to one match at a time; blocks are handed out from a free list.
+  //  * merge cache: piece -> ids, in kShards maps with a lock each (the shard is picked by the piece's hash).
+  std::mutex md_mutex;
+  std::vector<void*> md_free;
+  static constexpr size_t kShards = 64;
+  struct Shard {
+    std::mutex m;
+    std::deque<std::string> keys;   // owns the bytes the map's keys view (a deque never moves its elements)
+    std::unordered_map<std::string_view, std::vector<int64_t>> map;
+  };
+  Shard shards[kShards];
+
+  // merges over symbol ids: (left id, right id) -> (rank, id of the merged token).  Built when every merge's two
+  // sides and result are vocabulary entries (true of trained BPE vocabularies); otherwise the string form is used.
+  std::unordered_map<uint64_t, std::pair<int64_t, int64_t>> pair_merge;
+  bool id_merges = false;
+  int64_t byte_sym[256];                       // id of the one-symbol token of each byte, -1 if absent
+  std::vector<uint32_t> added_by_first[256];   // indices into `added` (longest first) by first byte
 
   ~Tokenizer() {
     auto& p = Pcre2::get();
-    if (md) p.free_md(md);
+    for (void* md : md_free) p.free_md(md);
     if (re) p.free_code(re);
+  }
+
+  void* acquire_md() {
+    {
+      std::lock_guard<std::mutex> lock(md_mutex);
+      if (!md_free.empty()) {
+        void* md = md_free.back();
+        md_free.pop_back();
+        return md;
+      }
+    }
+    return Pcre2::get().mdata(re, nullptr);
+  }
+  void release_md(void* md) {
+    std::lock_guard<std::mutex> lock(md_mutex);
+    md_free.push_back(md);
   }
 
   void build_byte_table() {
@@ -318,9 +362,35 @@ struct Tokenizer {
       size_t off = 0;
       re = p.compile(reinterpret_cast<const unsigned char*>(pattern.c_str()), ~static_cast<size_t>(0),
                      kPcre2Utf | kPcre2Ucp, &err, &off, nullptr);
-      if (re) md = p.mdata(re, nullptr);
+      if (re && p.jit_compile) jit = p.jit_compile(re, kPcre2JitComplete) == 0;
     }
     discover_special();
+    build_indexes();
+  }
+
+  void build_indexes() {
+    for (size_t i = 0; i < added.size(); ++i)
+      if (!added[i].first.empty()) added_by_first[static_cast<unsigned char>(added[i].first[0])].push_back(static_cast<uint32_t>(i));
+    id_merges = true;
+    for (int b = 0; b < 256; ++b) {
+      auto it = vocab.find(byte_to_uni[b]);
+      byte_sym[b] = it != vocab.end() ? it->second : -1;
+    }
+    for (const auto& kv : merge_rank) {
+      const size_t sp = kv.first.find(' ');
+      if (sp == std::string::npos) { id_merges = false; break; }
+      const std::string a = kv.first.substr(0, sp), b = kv.first.substr(sp + 1);
+      auto ia = vocab.find(a), ib = vocab.find(b), iab = vocab.find(a + b);
+      if (ia == vocab.end() || ib == vocab.end() || iab == vocab.end() || ia->second > 0xffffffffLL ||
+          ib->second > 0xffffffffLL || ia->second < 0 || ib->second < 0) {
+        id_merges = false;
+        break;
+      }
+      const uint64_t key = (static_cast<uint64_t>(ia->second) << 32) | static_cast<uint64_t>(ib->second);
+      auto ins = pair_merge.emplace(key, std::make_pair(kv.second, iab->second));
+      if (!ins.second && kv.second < ins.first->second.first) ins.first->second = {kv.second, iab->second};
+    }
+    if (!id_merges) pair_merge.clear();
   }
 
   int64_t find_token(std::initializer_list<const char*> names) const {
@@ -354,8 +424,8 @@ struct Tokenizer {
   }
 
   // hand-written matcher of the default pattern (used only without PCRE2)
-  std::vector<std::string> scan_default(const std::string& s) const {
-    std::vector<std::string> out;
+  template <class Sink>
+  void scan_default(const std::string& s, Sink&& sink) const {
     std::vector<uint32_t> cps;
     std::vector<size_t> offs;
     for (size_t i = 0; i < s.size();) {
@@ -367,7 +437,7 @@ struct Tokenizer {
     offs.push_back(s.size());
     const size_t n = cps.size();
     size_t i = 0;
-    auto emit = [&](size_t b, size_t e) { out.push_back(s.substr(offs[b], offs[e] - offs[b])); };
+    auto emit = [&](size_t b, size_t e) { sink(offs[b], offs[e] - offs[b]); };
     while (i < n) {
       // contractions
       if (cps[i] == '\'' && i + 1 < n) {
@@ -419,33 +489,64 @@ struct Tokenizer {
       emit(i, i + 1);
       ++i;
     }
-    return out;
   }
 
-  std::vector<std::string> pretokenize(const std::string& s) const {
+  // calls sink(offset, length) for every piece of s, in order
+  template <class Sink>
+  void pretokenize(const std::string& s, Sink&& sink) {
     auto& p = Pcre2::get();
-    if (!re || !md) return scan_default(s);
-    std::vector<std::string> out;
+    void* md = re ? acquire_md() : nullptr;
+    if (!md) {
+      scan_default(s, sink);
+      return;
+    }
     size_t pos = 0;
     const auto* subj = reinterpret_cast<const unsigned char*>(s.data());
+    uint32_t opts = 0;
     while (pos < s.size()) {
-      int rc = p.match(re, subj, s.size(), pos, 0, md, nullptr);
+      int rc = p.match(re, subj, s.size(), pos, opts, md, nullptr);
+      opts = kPcre2NoUtfCheck;   // the first match validated the whole subject; checking it again on every
+                                 // match would make a text of n bytes cost n * n
       if (rc < 0) {
-        out.push_back(s.substr(pos));
+        sink(pos, s.size() - pos);
         break;
       }
       size_t* ov = p.ovec(md);
-      if (ov[0] > pos) out.push_back(s.substr(pos, ov[0] - pos));  // unmatched gap kept as its own piece
-      if (ov[1] > ov[0]) out.push_back(s.substr(ov[0], ov[1] - ov[0]));
+      if (ov[0] > pos) sink(pos, ov[0] - pos);  // unmatched gap kept as its own piece
+      if (ov[1] > ov[0]) sink(ov[0], ov[1] - ov[0]);
       pos = ov[1] > pos ? ov[1] : pos + 1;
     }
-    return out;
+    release_md(md);
   }
 
   // --- BPE -----------------------------------------------------------------------
-  const std::vector<int64_t>& bpe(const std::string& piece) {
-    auto hit = cache.find(piece);
-    if (hit != cache.end()) return hit->second;
+  // merges on symbol ids; false when a byte of the piece has no one-symbol token (the string form then decides)
+  bool bpe_ids(std::string_view piece, std::vector<int64_t>& ids) const {
+    ids.clear();
+    ids.reserve(piece.size());
+    for (unsigned char c : piece) {
+      if (byte_sym[c] < 0) return false;
+      ids.push_back(byte_sym[c]);
+    }
+    while (ids.size() > 1) {
+      int64_t best = INT64_MAX, merged = -1;
+      size_t at = 0;
+      for (size_t i = 0; i + 1 < ids.size(); ++i) {
+        auto it = pair_merge.find((static_cast<uint64_t>(ids[i]) << 32) | static_cast<uint64_t>(ids[i + 1]));
+        if (it != pair_merge.end() && it->second.first < best) {
+          best = it->second.first;
+          merged = it->second.second;
+          at = i;
+        }
+      }
+      if (best == INT64_MAX) break;
+      ids[at] = merged;
+      ids.erase(ids.begin() + static_cast<long>(at) + 1);
+    }
+    return true;
+  }
+
+  void bpe_strings(std::string_view piece, std::vector<int64_t>& ids) const {
     std::string mapped;
     for (unsigned char c : piece) mapped += byte_to_uni[c];
     std::vector<std::string> parts = split_utf8(mapped);
@@ -463,7 +564,7 @@ struct Tokenizer {
       parts[at] += parts[at + 1];
       parts.erase(parts.begin() + static_cast<long>(at) + 1);
     }
-    std::vector<int64_t> ids;
+    ids.clear();
     for (const auto& t : parts) {
       auto it = vocab.find(t);
       if (it != vocab.end()) {
@@ -475,28 +576,43 @@ struct Tokenizer {
         }
       }
     }
-    return cache.emplace(piece, std::move(ids)).first->second;
   }
 
-  void encode_span(const std::string& span, std::vector<int64_t>& out) {
-    for (const auto& piece : pretokenize(span)) {
-      const auto& ids = bpe(piece);
-      out.insert(out.end(), ids.begin(), ids.end());
+  void bpe(std::string_view piece, std::vector<int64_t>& out) {
+    Shard& sh = shards[std::hash<std::string_view>{}(piece) % kShards];
+    {
+      std::lock_guard<std::mutex> lock(sh.m);
+      auto hit = sh.map.find(piece);
+      if (hit != sh.map.end()) {
+        out.insert(out.end(), hit->second.begin(), hit->second.end());
+        return;
+      }
+    }
+    std::vector<int64_t> ids;
+    if (!(id_merges && bpe_ids(piece, ids))) bpe_strings(piece, ids);
+    out.insert(out.end(), ids.begin(), ids.end());
+    if (piece.size() <= 64) {                  // long one-off pieces (base64 blobs, ...) are not worth keeping
+      std::lock_guard<std::mutex> lock(sh.m);
+      if (sh.map.find(piece) == sh.map.end()) {
+        sh.keys.emplace_back(piece);
+        sh.map.emplace(std::string_view(sh.keys.back()), std::move(ids));
+      }
     }
   }
 
-  // One handle may be shared by several threads (a data loader's workers): the regex match data and the merge
-  // cache are per handle, so encoding takes the handle's lock.  Decoding only reads the vocabulary.
-  std::mutex encode_mutex;
+  void encode_span(const std::string& span, std::vector<int64_t>& out) {
+    pretokenize(span, [&](size_t off, size_t len) { bpe(std::string_view(span.data() + off, len), out); });
+  }
 
   std::vector<int64_t> encode(const std::string& text) {
-    std::lock_guard<std::mutex> lock(encode_mutex);
     std::vector<int64_t> out;
+    out.reserve(text.size() / 3 + 4);
     size_t pos = 0, span_begin = 0;
     while (pos < text.size()) {
       bool matched = false;
-      for (const auto& at : added) {
-        if (!at.first.empty() && text.compare(pos, at.first.size(), at.first) == 0) {
+      for (uint32_t k : added_by_first[static_cast<unsigned char>(text[pos])]) {
+        const auto& at = added[k];
+        if (text.compare(pos, at.first.size(), at.first) == 0) {
           if (pos > span_begin) encode_span(text.substr(span_begin, pos - span_begin), out);
           out.push_back(at.second);
           pos += at.first.size();
@@ -507,7 +623,26 @@ struct Tokenizer {
       }
       if (!matched) ++pos;
     }
-    if (span_begin < text.size()) encode_span(text.substr(span_begin), out);
+    if (span_begin < text.size()) encode_span(span_begin == 0 ? text : text.substr(span_begin), out);
+    return out;
+  }
+
+  // texts[i] -> ids, on up to `threads` worker threads pulling indices from one counter
+  std::vector<std::vector<int64_t>> encode_batch(const char* const* texts, const int64_t* lens, int64_t n, int threads) {
+    std::vector<std::vector<int64_t>> out(static_cast<size_t>(n));
+    std::atomic<int64_t> next{0};
+    auto work = [&]() {
+      for (int64_t i = next.fetch_add(1); i < n; i = next.fetch_add(1))
+        out[static_cast<size_t>(i)] = encode(std::string(texts[i], static_cast<size_t>(lens[i])));
+    };
+    const int64_t nt = std::max<int64_t>(1, std::min<int64_t>(threads, n));
+    if (nt == 1) {
+      work();
+    } else {
+      std::vector<std::thread> pool;
+      for (int64_t t = 0; t < nt; ++t) pool.emplace_back(work);
+      for (auto& th : pool) th.join();
+    }
     return out;
   }
 
@@ -565,6 +700,27 @@ int64_t cverl_bpe_special_id(void* h, int which) {
   }
 }
 int cverl_bpe_uses_pcre2(void* h) { return static_cast<Tokenizer*>(h)->re != nullptr; }
+// 1 when the pre-tokenizer pattern runs as JIT-compiled code, and whether merges run on symbol ids
+int cverl_bpe_uses_jit(void* h) { return static_cast<Tokenizer*>(h)->jit ? 1 : 0; }
+int cverl_bpe_uses_id_merges(void* h) { return static_cast<Tokenizer*>(h)->id_merges ? 1 : 0; }
+// Encodes n texts on up to `threads` threads.  offsets[0..n] receive the running token counts; ids of text i go to
+// out[offsets[i] .. offsets[i+1]) as far as `capacity` reaches.  Returns the total count (call again with a
+// larger buffer when it exceeds `capacity`).
+int64_t cverl_bpe_encode_batch(void* h, const char* const* texts, const int64_t* lens, int64_t n, int threads,
+                               int64_t* out, int64_t capacity, int64_t* offsets) {
+  if (n < 0) return -1;
+  auto all = static_cast<Tokenizer*>(h)->encode_batch(texts, lens, n, threads);
+  int64_t total = 0;
+  for (int64_t i = 0; i < n; ++i) {
+    offsets[i] = total;
+    for (int64_t id : all[static_cast<size_t>(i)]) {
+      if (total < capacity) out[total] = id;
+      ++total;
+    }
+  }
+  offsets[n] = total;
+  return total;
+}
 int64_t cverl_bpe_encode(void* h, const char* text, int64_t len, int64_t* out, int64_t capacity) {
   auto ids = static_cast<Tokenizer*>(h)->encode(std::string(text, static_cast<size_t>(len)));
   const int64_t n = static_cast<int64_t>(ids.size());

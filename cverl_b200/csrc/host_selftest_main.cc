@@ -53,6 +53,17 @@ void cverl_bpe_close(void* h);
 int64_t cverl_bpe_vocab_size(void* h);
 int64_t cverl_bpe_encode(void* h, const char* text, int64_t len, int64_t* out, int64_t capacity);
 int64_t cverl_bpe_decode(void* h, const int64_t* ids, int64_t n, int skip_special, char* out, int64_t capacity);
+int cverl_build_gsm8k_rollout_batch(int tokenizer_kind, void* tokenizer, int64_t pad_id, const char* const* prompts,
+                                    const int64_t* prompt_lens, const char* const* answers, int64_t n_prompts,
+                                    const int64_t* sample_prompt, const char* const* responses,
+                                    const int64_t* response_lens, const int64_t* given_ids,
+                                    const int64_t* given_offsets, const uint8_t* has_given, int64_t n_samples,
+                                    int64_t max_prompt_len, int64_t max_response_len, int flexible, int64_t clip_chars,
+                                    double correct_score, double format_score, double no_answer_score, int threads,
+                                    int64_t* prompt_ids, int64_t* response_ids, float* response_mask,
+                                    float* token_rewards, float* rewards, int64_t* group_ids);
+int64_t cverl_bpe_encode_batch(void* h, const char* const* texts, const int64_t* lens, int64_t n, int threads,
+                               int64_t* out, int64_t capacity, int64_t* offsets);
 }
 
 namespace {
@@ -291,6 +302,37 @@ void text_and_reward() {
   }
 }
 
+// the rollout-batch builder on four threads (byte tokenizer): padding sides, truncation, reward placement, bad index
+void rollout_batch() {
+  const char* prompts[] = {"What is 2+2?", "unused", "hi"};
+  const char* answers[] = {"#### 4", "0", "1"};
+  const int64_t plen[] = {12, 6, 2};
+  const char* responses[] = {"it is #### 4", "it is #### 5", "", "#### 1", "a much longer response than sixteen bytes #### 4"};
+  int64_t rlen[5], sp[] = {0, 0, 2, 2, 0};
+  for (int i = 0; i < 5; ++i) rlen[i] = static_cast<int64_t>(std::strlen(responses[i]));
+  const int64_t given[] = {9, 8, 7}, goff[] = {0, 0, 0, 0, 3, 3};
+  const uint8_t has[] = {0, 0, 0, 1, 0};
+  const int64_t B = 5, P = 8, R = 16;
+  std::vector<int64_t> pid(B * P), rid(B * R), gid(B);
+  std::vector<float> mask(B * R), trew(B * R), rew(B);
+  EXPECT(cverl_build_gsm8k_rollout_batch(0, nullptr, 0, prompts, plen, answers, 3, sp, responses, rlen, given, goff, has,
+                                         B, P, R, 0, 300, 1.0, 0.0, 0.0, 4, pid.data(), rid.data(), mask.data(),
+                                         trew.data(), rew.data(), gid.data()) == 0);
+  EXPECT(rew[0] == 1.0f && rew[1] == 0.0f && rew[2] == 0.0f && rew[3] == 1.0f && rew[4] == 1.0f);
+  EXPECT(pid[0] == 4 + ' ' && pid[7] == 4 + '?');                       // tail of the 12-byte prompt
+  EXPECT(pid[2 * P] == 0 && pid[2 * P + 6] == 4 + 'h');                 // left padded
+  EXPECT(rid[3 * R] == 9 && rid[3 * R + 2] == 7 && mask[3 * R + 2] == 1.0f && mask[3 * R + 3] == 0.0f);
+  EXPECT(trew[3 * R + 2] == 1.0f && trew[4 * R + R - 1] == 1.0f && mask[4 * R + R - 1] == 1.0f);
+  EXPECT(mask[2 * R] == 0.0f && gid[2] == 2 && gid[4] == 0);
+  sp[1] = 3;                                                            // prompt index out of range
+  EXPECT(cverl_build_gsm8k_rollout_batch(0, nullptr, 0, prompts, plen, answers, 3, sp, responses, rlen, nullptr, nullptr,
+                                         nullptr, B, P, R, 0, 300, 1.0, 0.0, 0.0, 4, pid.data(), rid.data(), mask.data(),
+                                         trew.data(), rew.data(), gid.data()) == 1);
+  EXPECT(cverl_build_gsm8k_rollout_batch(1, nullptr, 0, prompts, plen, answers, 3, sp, responses, rlen, nullptr, nullptr,
+                                         nullptr, B, P, R, 0, 300, 1.0, 0.0, 0.0, 4, pid.data(), rid.data(), mask.data(),
+                                         trew.data(), rew.data(), gid.data()) == 1);   // BPE without a handle
+}
+
 // argv[1] (optional): a Hugging Face tokenizer.json; encode / decode round trips from two threads sharing one handle
 void bpe(const char* tokenizer_json) {
   char err[256] = {0};
@@ -315,6 +357,26 @@ void bpe(const char* tokenizer_json) {
   std::thread t1(work, "hello world, 123 + 456 = 579"), t2(work, "the quick brown fox\n  jumps");
   t1.join();
   t2.join();
+  // batch encoding on four threads while a fifth thread encodes through the same handle: the batch must give
+  // what one-by-one encoding gives, also when the output buffer is too small (count only) or the batch is empty
+  const char* texts[] = {"hello world", "the quick brown fox", "", "123 + 456 = 579", "hello hello hello", "  \n\n x"};
+  const int64_t n_texts = 6;
+  int64_t lens[6], offsets[7], small_offsets[7];
+  for (int i = 0; i < n_texts; ++i) lens[i] = static_cast<int64_t>(std::strlen(texts[i]));
+  std::vector<int64_t> flat(512);
+  std::thread side(work, "side thread: while the batch runs");
+  const int64_t total = cverl_bpe_encode_batch(h, texts, lens, n_texts, 4, flat.data(), 512, offsets);
+  side.join();
+  EXPECT(total > 0 && total <= 512 && offsets[0] == 0 && offsets[n_texts] == total && offsets[2] == offsets[3]);
+  for (int i = 0; i < n_texts; ++i) {
+    std::vector<int64_t> one(256);
+    const int64_t n = cverl_bpe_encode(h, texts[i], lens[i], one.data(), 256);
+    EXPECT(n == offsets[i + 1] - offsets[i]);
+    EXPECT(std::memcmp(one.data(), flat.data() + offsets[i], static_cast<size_t>(n) * sizeof(int64_t)) == 0);
+  }
+  int64_t tiny[3];
+  EXPECT(cverl_bpe_encode_batch(h, texts, lens, n_texts, 2, tiny, 3, small_offsets) == total);
+  EXPECT(cverl_bpe_encode_batch(h, texts, lens, 0, 2, tiny, 3, small_offsets) == 0 && small_offsets[0] == 0);
   cverl_bpe_close(h);
   EXPECT(cverl_bpe_open("/tmp/cverl_selftest_no_such_tokenizer.json", err, sizeof(err)) == nullptr);
 }
@@ -365,6 +427,7 @@ int main(int argc, char** argv) {
   for (unsigned t = 0; t < 4; ++t) pool.emplace_back(rl_math, t);
   planner();
   rl_math_edges();
+  rollout_batch();
   for (auto& th : pool) th.join();
   safetensors_round_trip();
   text_and_reward();

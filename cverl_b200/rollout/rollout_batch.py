@@ -4,6 +4,11 @@ Prompts are tokenised once per prompt index, LEFT-padded and truncated keeping t
 responses are RIGHT-padded; ``response_mask`` marks real response tokens; ``group_ids`` is
 the prompt index; the scalar GSM8K rule reward sits on the last real response token.
 Reference: src/rollout/rollout_batch.cc:12-136.
+
+With one of the two native tokenizers the whole batch is built by ``cverl_build_gsm8k_rollout_batch``
+(csrc/rollout_batch.cc): distinct prompts and then samples are tokenised and scored on several threads, each
+writing its own rows of the output tensors.  Any other ``Tokenizer`` takes the Python loop below, which states
+the same rules.
 """
 from __future__ import annotations
 
@@ -13,7 +18,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from ..reward import Gsm8kRewardOptions, compute_gsm8k_reward
-from ..text import EncodeOptions, Tokenizer
+from ..text import ByteTokenizer, EncodeOptions, HfBpeTokenizer, Tokenizer
 
 
 @dataclass
@@ -36,14 +41,69 @@ class RolloutBatch:
         return RolloutBatch(*(getattr(self, f).to(device) for f in self.__dataclass_fields__))
 
 
+def _build_native(tokenizer, prompts, answers, samples, P: int, R: int, opts: Gsm8kRewardOptions, pad: int,
+                  threads: int) -> RolloutBatch:
+    import ctypes as C
+    import os
+
+    import numpy as np
+
+    from .. import _native as nv
+    lib = nv.host()
+    fn = lib.cverl_build_gsm8k_rollout_batch
+    i64, i64p, cpp = C.c_int64, C.POINTER(C.c_int64), C.POINTER(C.c_char_p)
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_int, C.c_void_p, i64, cpp, i64p, cpp, i64, i64p, cpp, i64p, i64p, i64p, C.POINTER(C.c_uint8),
+                   i64, i64, i64, C.c_int, i64, C.c_double, C.c_double, C.c_double, C.c_int, i64p, i64p,
+                   C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float), i64p]
+    B, NP = len(samples), len(prompts)
+    praw = [p.encode("utf-8") for p in prompts]
+    araw = [a.encode("utf-8") for a in answers]
+    rraw = [s.response_text.encode("utf-8") for s in samples]
+    idx = np.asarray([s.prompt_index for s in samples], dtype=np.int64)
+    has = np.asarray([s.response_token_ids is not None for s in samples], dtype=np.uint8)
+    offs = np.zeros(B + 1, dtype=np.int64)
+    np.cumsum([len(s.response_token_ids) if s.response_token_ids is not None else 0 for s in samples], out=offs[1:])
+    given = np.asarray([t for s in samples if s.response_token_ids is not None for t in s.response_token_ids] or [0],
+                       dtype=np.int64)
+    out = RolloutBatch(torch.empty((B, P), dtype=torch.int64), torch.empty((B, R), dtype=torch.int64),
+                       torch.empty((B, R), dtype=torch.float32), torch.empty((B, R), dtype=torch.float32),
+                       torch.empty(B, dtype=torch.float32), torch.empty(B, dtype=torch.int64))
+
+    def ptr(t, ty):
+        return C.cast(t.data_ptr(), C.POINTER(ty))
+
+    def nptr(a, ty):
+        return a.ctypes.data_as(C.POINTER(ty))
+    is_bpe = isinstance(tokenizer, HfBpeTokenizer)
+    if threads <= 0:
+        threads = min(os.cpu_count() or 1, 16)
+    rc = fn(int(is_bpe), tokenizer._h if is_bpe else None, pad,
+            (C.c_char_p * max(NP, 1))(*praw), (i64 * max(NP, 1))(*[len(b) for b in praw]),
+            (C.c_char_p * max(NP, 1))(*araw), NP, nptr(idx, i64), (C.c_char_p * B)(*rraw),
+            (i64 * B)(*[len(b) for b in rraw]), nptr(given, i64), nptr(offs, i64), nptr(has, C.c_uint8), B, P, R,
+            int(opts.method == "flexible"), opts.solution_clip_chars, opts.correct_score, opts.format_score,
+            opts.no_answer_score, threads, ptr(out.prompt_ids, i64), ptr(out.response_ids, i64),
+            ptr(out.response_mask, C.c_float), ptr(out.token_rewards, C.c_float), ptr(out.rewards, C.c_float),
+            ptr(out.group_ids, i64))
+    if rc != 0:
+        raise ValueError("sample prompt_index out of range")
+    return out
+
+
 def build_gsm8k_rollout_batch(tokenizer: Tokenizer, prompts: Sequence[str], answers: Sequence[str],
                               samples: Sequence[RolloutSample], max_prompt_len: int, max_response_len: int,
-                              reward_options: Gsm8kRewardOptions = Gsm8kRewardOptions()) -> RolloutBatch:
+                              reward_options: Gsm8kRewardOptions = Gsm8kRewardOptions(),
+                              threads: int = 0) -> RolloutBatch:
+    """``threads``: worker threads of the native builder (0: one per core, at most 16); -1 forces the Python loop."""
     if len(prompts) != len(answers):
         raise ValueError("prompts and answers must have the same length")
     if not samples:
         raise ValueError("no rollout samples")
     pad = tokenizer.pad_id if tokenizer.pad_id >= 0 else 0
+    if threads >= 0 and type(tokenizer) in (ByteTokenizer, HfBpeTokenizer):
+        return _build_native(tokenizer, prompts, answers, samples, max_prompt_len, max_response_len, reward_options,
+                             pad, threads)
     cache: Dict[int, List[int]] = {}
     B = len(samples)
     prompt_ids = torch.full((B, max_prompt_len), pad, dtype=torch.int64)

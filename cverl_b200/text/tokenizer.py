@@ -41,6 +41,11 @@ def _bind():
     lib.cverl_bpe_uses_pcre2.argtypes = [p]
     lib.cverl_bpe_encode.restype = i64
     lib.cverl_bpe_encode.argtypes = [p, C.c_char_p, i64, C.POINTER(i64), i64]
+    lib.cverl_bpe_uses_jit.argtypes = [p]
+    lib.cverl_bpe_uses_id_merges.argtypes = [p]
+    lib.cverl_bpe_encode_batch.restype = i64
+    lib.cverl_bpe_encode_batch.argtypes = [p, C.POINTER(C.c_char_p), C.POINTER(i64), i64, C.c_int, C.POINTER(i64), i64,
+                                           C.POINTER(i64)]
     lib.cverl_bpe_decode.restype = i64
     lib.cverl_bpe_decode.argtypes = [p, C.POINTER(i64), i64, C.c_int, C.c_char_p, i64]
     lib._text_bound = True
@@ -121,8 +126,52 @@ class HfBpeTokenizer(Tokenizer):
     def uses_pcre2(self) -> bool:
         return bool(self._lib.cverl_bpe_uses_pcre2(self._h))
 
+    @property
+    def uses_jit(self) -> bool:
+        """The pre-tokenizer pattern runs as JIT-compiled code (a PCRE2 built with JIT support)."""
+        return bool(self._lib.cverl_bpe_uses_jit(self._h))
+
+    @property
+    def uses_id_merges(self) -> bool:
+        """Merges run on symbol ids (every merge's sides and result are vocabulary entries)."""
+        return bool(self._lib.cverl_bpe_uses_id_merges(self._h))
+
     def name(self) -> str:
         return "hf_bpe"
+
+    def encode_batch_flat(self, texts: Sequence[str], threads: int = 0):
+        """Encodes ``texts`` on ``threads`` native threads (0: one per core, at most 16).  Returns
+        ``(ids, offsets)`` as int64 numpy arrays: the ids of text i are ``ids[offsets[i]:offsets[i + 1]]``."""
+        import numpy as np
+        n = len(texts)
+        raws = [t.encode("utf-8") for t in texts]
+        arr = (C.c_char_p * max(n, 1))(*raws)
+        lens = (C.c_int64 * max(n, 1))(*[len(r) for r in raws])
+        if threads <= 0:
+            import os
+            threads = min(os.cpu_count() or 1, 16)
+        offsets = np.zeros(n + 1, dtype=np.int64)
+        cap = sum(len(r) for r in raws) + 8        # a token covers at least one byte
+        ids = np.empty(cap, dtype=np.int64)
+        i64p = C.POINTER(C.c_int64)
+        total = self._lib.cverl_bpe_encode_batch(self._h, arr, lens, n, threads, ids.ctypes.data_as(i64p), cap,
+                                                 offsets.ctypes.data_as(i64p))
+        if total < 0 or total > cap:
+            raise RuntimeError("cverl_bpe_encode_batch: output does not fit")
+        return ids[:total], offsets
+
+    def encode_batch(self, texts: Sequence[str], options: EncodeOptions = EncodeOptions(),
+                     threads: int = 0) -> List[List[int]]:
+        ids, offsets = self.encode_batch_flat(texts, threads)
+        out = []
+        for i in range(len(texts)):
+            row = ids[offsets[i]:offsets[i + 1]].tolist()
+            if options.add_bos and self.bos_id >= 0:
+                row = [self.bos_id] + row
+            if options.add_eos and self.eos_id >= 0:
+                row = row + [self.eos_id]
+            out.append(row[:options.max_tokens] if options.max_tokens > 0 else row)
+        return out
 
     def encode(self, text: str, options: EncodeOptions = EncodeOptions()) -> List[int]:
         raw = text.encode("utf-8")

@@ -206,6 +206,35 @@ def test_build_gsm8k_rollout_batch():
     assert short.prompt_ids[0, :6].tolist() == [0] * 6            # left padded
 
 
+@pytest.mark.parametrize("kind", ["byte", "bpe"])
+def test_native_batch_builder_equals_the_python_loop(kind):
+    """The multi-threaded C++ builder and the Python statement of the rules give the same six tensors: shared and
+    unused prompts, responses with and without their own token ids, truncation on both sides, empty responses."""
+    from pathlib import Path
+
+    from cverl_b200.reward import Gsm8kRewardOptions
+    from cverl_b200.text import HfBpeTokenizer
+    tok = ByteTokenizer() if kind == "byte" else HfBpeTokenizer(
+        str(Path(__file__).parent / "fixtures" / "synthetic_tokenizer.json"))
+    prompts = ["What is 2+2?", "never sampled", "hello world " * 9, ""]
+    answers = ["#### 4", "0", "12", "7"]
+    samples = [RolloutSample(0, "it is #### 4"), RolloutSample(2, "hello hello #### 12 " * 6), RolloutSample(0, ""),
+               RolloutSample(3, "the answer is 7", [5, 6, 7]), RolloutSample(2, "#### 13", list(range(4, 40))),
+               RolloutSample(0, "4 #### 4", [])]
+    opts = Gsm8kRewardOptions(method="flexible", correct_score=2.0, format_score=0.5, no_answer_score=-1.0)
+    ref = build_gsm8k_rollout_batch(tok, prompts, answers, samples, 8, 16, opts, threads=-1)
+    for threads in (1, 3):
+        got = build_gsm8k_rollout_batch(tok, prompts, answers, samples, 8, 16, opts, threads=threads)
+        for f in ref.__dataclass_fields__:
+            assert torch.equal(getattr(ref, f), getattr(got, f)), f
+    assert ref.rewards.tolist() == [2.0, 2.0, -1.0, 2.0, 0.5, 2.0] and ref.response_mask[4].sum() == 16
+    assert ref.response_mask[2].sum() == 0 and ref.token_rewards[2].sum() == 0 and ref.response_mask[5].sum() == 0
+    with pytest.raises(ValueError):
+        build_gsm8k_rollout_batch(tok, prompts, answers, [RolloutSample(4, "x")], 8, 16)
+    with pytest.raises(ValueError):
+        build_gsm8k_rollout_batch(tok, prompts, answers, [RolloutSample(-1, "x")], 8, 16)
+
+
 class CountingCollectives(SingleProcessCollectives):
     def __init__(self, world=2, rank=1):
         self._w, self._r, self.broadcasts, self.barriers, self.sent = world, rank, 0, 0, []

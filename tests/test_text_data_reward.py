@@ -63,3 +63,28 @@ def test_jsonl_reader(tmp_path):
         load_prompt_answer_jsonl(p, "missing", "answer")
     with pytest.raises(ValueError):
         load_prompt_answer_jsonl(tmp_path / "nope.jsonl")
+
+
+def test_bpe_batch_encoding_on_threads_equals_single_calls():
+    from cverl_b200.text import EncodeOptions
+    tok = HfBpeTokenizer(str(FIX / "synthetic_tokenizer.json"))
+    texts = ["hello world", "", "abc abc abc", "<|endoftext|>tail", "naïve café 数学 🙂", "x" * 300] * 7
+    single = [tok.encode(t) for t in texts]
+    for threads in (1, 4):
+        ids, offsets = tok.encode_batch_flat(texts, threads)
+        assert offsets[0] == 0 and offsets[-1] == len(ids) == sum(map(len, single))
+        assert [ids[offsets[i]:offsets[i + 1]].tolist() for i in range(len(texts))] == single
+    opts = EncodeOptions(add_bos=True, add_eos=True, max_tokens=5)
+    assert tok.encode_batch(texts[:4], opts, threads=2) == [tok.encode(t, opts) for t in texts[:4]]
+    ids, offsets = tok.encode_batch_flat([], 3)
+    assert len(ids) == 0 and offsets.tolist() == [0]
+    assert isinstance(tok.uses_jit, bool) and isinstance(tok.uses_id_merges, bool)
+
+
+def test_tokenizer_benchmark_runs_and_all_arms_agree(capsys):
+    import json
+    from cverl_b200 import bench_tokenizer
+    assert bench_tokenizer.main(["--max-mb", "0.25", "--vocab-size", "1500", "--threads", "1", "2", "--repeats", "1"]) == 0
+    doc = json.loads(capsys.readouterr().out)
+    assert doc["all_arms_same_ids"] and doc["rollout_batch_builder"]["same_tensors"]
+    assert doc["encode_mb_per_s"]["ours_batch_1_threads"] > 0 and doc["tokens"] > 1000
