@@ -8,16 +8,21 @@
 // Behaviour follows the reference (src/model/hf_model_loader.cc:55-373,
 // src/model/safetensors_writer.cc:92-159); dtypes F32/F16/BF16/I64/I32/U8.
 #include <algorithm>
+#include <atomic>
+#include <cerrno>
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
 #include <dirent.h>
+#include <fcntl.h>
 #include <fstream>
 #include <map>
 #include <memory>
 #include <stdexcept>
 #include <string>
 #include <sys/stat.h>
+#include <thread>
+#include <unistd.h>
 #include <vector>
 
 namespace {
@@ -245,17 +250,54 @@ int cverl_st_info(void* h, const char* name, int* dtype, int* ndim, int64_t* sha
   return 0;
 }
 
-int cverl_st_read(void* h, const char* name, void* dst, int64_t nbytes) {
+// Reads bytes [offset, offset + nbytes) of a tensor's data into dst with pread, split over up to `threads`
+// threads in pieces of at least 4 MiB (threads <= 0: one per 32 MiB, at most 8).  A contiguous range of rows of a
+// row-major tensor is such a byte range, so a tensor-parallel rank reads only its rows.
+int cverl_st_read_range(void* h, const char* name, int64_t offset, int64_t nbytes, void* dst, int threads) {
   auto* idx = static_cast<Index*>(h);
   auto it = idx->tensors.find(name);
   if (it == idx->tensors.end()) return 1;
   const TensorInfo& t = it->second;
-  if (nbytes != static_cast<int64_t>(t.end - t.begin)) return 2;
-  std::ifstream f(t.file, std::ios::binary);
-  if (!f) return 3;
-  f.seekg(static_cast<std::streamoff>(t.data_start + t.begin));
-  f.read(static_cast<char*>(dst), static_cast<std::streamsize>(nbytes));
-  return f ? 0 : 4;
+  const int64_t size = static_cast<int64_t>(t.end - t.begin);
+  if (offset < 0 || nbytes < 0 || offset + nbytes > size) return 2;
+  if (nbytes == 0) return 0;
+  const int fd = open(t.file.c_str(), O_RDONLY | O_CLOEXEC);
+  if (fd < 0) return 3;
+  const int64_t base = static_cast<int64_t>(t.data_start + t.begin) + offset;
+  constexpr int64_t kMinPiece = 4ll << 20;
+  int64_t nt = threads > 0 ? threads : std::min<int64_t>(8, nbytes / (32ll << 20) + 1);
+  nt = std::max<int64_t>(1, std::min<int64_t>(nt, (nbytes + kMinPiece - 1) / kMinPiece));
+  const int64_t piece = ((nbytes + nt - 1) / nt + 4095) / 4096 * 4096;
+  std::atomic<int> bad{0};
+  auto work = [&](int64_t k) {
+    int64_t lo = k * piece, hi = std::min(nbytes, lo + piece);
+    while (lo < hi) {
+      const ssize_t got = pread(fd, static_cast<char*>(dst) + lo, static_cast<size_t>(hi - lo), base + lo);
+      if (got <= 0) {
+        if (got < 0 && errno == EINTR) continue;
+        bad.store(1);
+        return;
+      }
+      lo += got;
+    }
+  };
+  if (nt == 1) {
+    work(0);
+  } else {
+    std::vector<std::thread> pool;
+    for (int64_t k = 0; k < nt; ++k) pool.emplace_back(work, k);
+    for (auto& th : pool) th.join();
+  }
+  close(fd);
+  return bad.load() ? 4 : 0;
+}
+
+int cverl_st_read(void* h, const char* name, void* dst, int64_t nbytes) {
+  auto* idx = static_cast<Index*>(h);
+  auto it = idx->tensors.find(name);
+  if (it == idx->tensors.end()) return 1;
+  if (nbytes != static_cast<int64_t>(it->second.end - it->second.begin)) return 2;
+  return cverl_st_read_range(h, name, 0, nbytes, dst, 0);
 }
 
 // Writes one file (tmp + rename).  shapes is a flat array of sum(ndims) extents.

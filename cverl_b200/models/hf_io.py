@@ -39,6 +39,7 @@ def _lib():
         lib.cverl_st_info.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_int), C.POINTER(C.c_int),
                                       C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
         lib.cverl_st_read.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_int64]
+        lib.cverl_st_read_range.argtypes = [C.c_void_p, C.c_char_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int]
         lib.cverl_st_write.argtypes = [C.c_char_p, C.c_int64, C.POINTER(C.c_char_p), C.POINTER(C.c_int),
                                        C.POINTER(C.c_int), C.POINTER(C.c_int64), C.POINTER(C.c_void_p)]
         lib._st_bound = True
@@ -60,6 +61,7 @@ class HfModelLoader:
         self.model_dir = str(model_dir)
         self._h = None
         self._infos: Dict[str, SafetensorInfo] = {}
+        self.bytes_read = 0            # tensor bytes read through this loader
 
     def load_metadata(self) -> "HfModelLoader":
         if self._h is not None:
@@ -103,6 +105,26 @@ class HfModelLoader:
             rc = _lib().cverl_st_read(self._h, name.encode(), out.data_ptr(), inf.nbytes)
             if rc != 0:
                 raise RuntimeError(f"HfModelLoader: read of {name} failed (code {rc})")
+            self.bytes_read += inf.nbytes
+        return out
+
+    def load_rows(self, name: str, begin: int, end: int, threads: int = 0) -> torch.Tensor:
+        """Rows ``[begin, end)`` of a tensor along its first dimension, reading only their bytes (rows of a
+        row-major tensor are one contiguous range of the file)."""
+        self.load_metadata()
+        inf = self._infos.get(name)
+        if inf is None:
+            raise KeyError(f"tensor {name} not found in {self.model_dir}")
+        if not inf.shape or not (0 <= begin <= end <= inf.shape[0]):
+            raise ValueError(f"load_rows: rows [{begin}, {end}) out of range for {name} of shape {inf.shape}")
+        row_bytes = inf.nbytes // inf.shape[0] if inf.shape[0] else 0
+        out = torch.empty((end - begin, *inf.shape[1:]), dtype=inf.dtype)
+        nbytes = (end - begin) * row_bytes
+        if nbytes:
+            rc = _lib().cverl_st_read_range(self._h, name.encode(), begin * row_bytes, nbytes, out.data_ptr(), threads)
+            if rc != 0:
+                raise RuntimeError(f"HfModelLoader: read of rows of {name} failed (code {rc})")
+            self.bytes_read += nbytes
         return out
 
     def config(self) -> Qwen35TextConfig:
@@ -144,10 +166,24 @@ def write_safetensors(path, tensors: Dict[str, torch.Tensor], dtype: Optional[to
 def load_model_weights(model, loader: HfModelLoader) -> None:
     """Fills a ``Qwen35Model`` (this rank's shards) from a model directory."""
     loader.load_metadata()
+    ctx = model.ctx
     for spec in model.specs:
         if not loader.has(spec.name):
             raise KeyError(f"model directory lacks required weight {spec.name}")
-        model.load_full_tensor(spec.name, loader.load_tensor(spec.name))
+        if not model.holds(spec):
+            continue                   # another expert-parallel rank's expert: not read at all
+        if spec.tp is not None and ctx.tp_size > 1 and spec.tp[0] == "rows":
+            # row-sharded: read this rank's rows of every section only (1 / tp of the tensor's bytes)
+            pieces, begin = [], 0
+            for section in spec.tp[1]:
+                if section % ctx.tp_size:
+                    raise ValueError(f"{spec.name}={section} is not divisible by tensor-parallel size {ctx.tp_size}")
+                step = section // ctx.tp_size
+                pieces.append(loader.load_rows(spec.name, begin + ctx.tp_rank * step, begin + (ctx.tp_rank + 1) * step))
+                begin += section
+            model.load_local_tensor(spec.name, pieces[0] if len(pieces) == 1 else torch.cat(pieces, dim=0))
+        else:
+            model.load_full_tensor(spec.name, loader.load_tensor(spec.name))
 
 
 def save_hf_checkpoint(model, out_dir, source_dir=None, dtype: Optional[torch.dtype] = None) -> None:

@@ -210,11 +210,23 @@ class Qwen35Model(torch.nn.Module):
                 t.normal_(0.0, std, generator=gen)
 
     @torch.no_grad()
+    def holds(self, spec: ParamSpec) -> bool:
+        """False for an expert weight that lives on another expert-parallel rank."""
+        if spec.expert < 0:
+            return True
+        e_local = self.cfg.num_experts // self.ctx.ep_size
+        lo = self.ctx.ep_rank * e_local
+        return lo <= spec.expert < lo + e_local
+
     def load_full_tensor(self, name: str, full: torch.Tensor) -> None:
         """Shard a full Hugging Face tensor for this rank and copy it into the flat buffer."""
         spec = self.spec_by_name[name]
+        self.load_local_tensor(name, shard_tensor(spec, full, self.ctx.tp_rank, self.ctx.tp_size))
+
+    def load_local_tensor(self, name: str, local: torch.Tensor) -> None:
+        """Copy this rank's (already sharded) piece of a Hugging Face tensor into the flat buffer."""
+        spec = self.spec_by_name[name]
         cfg, ctx = self.cfg, self.ctx
-        local = shard_tensor(spec, full, ctx.tp_rank, ctx.tp_size)
         if spec.expert >= 0:
             e_local = cfg.num_experts // ctx.ep_size
             lo = ctx.ep_rank * e_local

@@ -1,0 +1,82 @@
+"""The native safetensors reader / writer (csrc/safetensors.cc) behind ``models/hf_io.py``: every stored dtype,
+several files in one directory, the header layout, threaded and ranged reads, and interchange with the
+``safetensors`` package."""
+import json
+import struct
+
+import pytest
+import torch
+
+from cverl_b200.models.hf_io import HfModelLoader, write_safetensors
+
+
+def _tensors():
+    g = torch.Generator().manual_seed(3)
+    return {
+        "a.f32": torch.randn(5, 7, generator=g), "b.f16": torch.randn(4, 3, generator=g).half(),
+        "c.bf16": torch.randn(2, 3, 4, generator=g).bfloat16(), "d.i64": torch.arange(9).reshape(3, 3),
+        "e.i32": torch.arange(6, dtype=torch.int32), "f.u8": torch.arange(11, dtype=torch.uint8),
+        "g.scalar": torch.tensor(2.5), "h.empty": torch.zeros(0, 4),
+    }
+
+
+def test_round_trip_header_layout_and_package_interchange(tmp_path):
+    tensors = _tensors()
+    path = tmp_path / "model.safetensors"
+    write_safetensors(path, tensors)
+    raw = path.read_bytes()
+    (hlen,) = struct.unpack("<Q", raw[:8])
+    header = json.loads(raw[8:8 + hlen])
+    assert (8 + hlen) % 8 == 0 and header["__metadata__"] == {"format": "pt"}
+    assert header["c.bf16"] == {"dtype": "BF16", "shape": [2, 3, 4], "data_offsets": header["c.bf16"]["data_offsets"]}
+    loader = HfModelLoader(path).load_metadata()
+    assert sorted(loader.names()) == sorted(tensors)
+    for name, t in tensors.items():
+        got = loader.load_tensor(name)
+        assert got.dtype == t.dtype and got.shape == t.shape and torch.equal(got, t), name
+    with pytest.raises(KeyError):
+        loader.load_tensor("missing")
+    # files written by the safetensors package are read here, and the other way round
+    st = pytest.importorskip("safetensors.torch")
+    theirs = st.load_file(str(path))
+    assert all(torch.equal(theirs[n], t) for n, t in tensors.items())
+    other = tmp_path / "theirs.safetensors"
+    st.save_file({k: v for k, v in tensors.items()}, str(other))
+    back = HfModelLoader(other).load_metadata()
+    assert all(torch.equal(back.load_tensor(n), t) for n, t in tensors.items())
+    # a cast on write applies to floating tensors only
+    write_safetensors(tmp_path / "cast.safetensors", tensors, dtype=torch.bfloat16)
+    cast = HfModelLoader(tmp_path / "cast.safetensors").load_metadata()
+    assert cast.info("a.f32").dtype == torch.bfloat16 and cast.info("d.i64").dtype == torch.int64
+
+
+def test_directory_of_shards_and_bad_inputs(tmp_path):
+    d = tmp_path / "dir"
+    d.mkdir()
+    write_safetensors(d / "model-00001-of-00002.safetensors", {"x": torch.ones(3)})
+    write_safetensors(d / "model-00002-of-00002.safetensors", {"y": torch.zeros(2, 2)})
+    (d / "model.safetensors.index.json").write_text("{}")          # ignored, as by the reference's loader
+    loader = HfModelLoader(d).load_metadata()
+    assert loader.names() == ["x", "y"] and loader.has("y") and not loader.has("z")
+    with pytest.raises(RuntimeError):
+        HfModelLoader(tmp_path / "nowhere").load_metadata()
+    (tmp_path / "bad.safetensors").write_bytes(b"\x10\x00\x00\x00\x00\x00\x00\x00{ not a header")
+    with pytest.raises(RuntimeError):
+        HfModelLoader(tmp_path / "bad.safetensors").load_metadata()
+    empty = tmp_path / "empty"
+    empty.mkdir()
+    with pytest.raises(RuntimeError):
+        HfModelLoader(empty).load_metadata()
+
+
+def test_threaded_and_ranged_reads_of_a_large_tensor(tmp_path):
+    big = torch.arange(10 * 1024 * 1024, dtype=torch.int32).reshape(1024, -1)      # 40 MiB: several pread pieces
+    write_safetensors(tmp_path / "big.safetensors", {"pad": torch.zeros(3, dtype=torch.uint8), "big": big})
+    loader = HfModelLoader(tmp_path / "big.safetensors").load_metadata()
+    assert torch.equal(loader.load_tensor("big"), big)
+    for threads in (1, 4, 7):
+        assert torch.equal(loader.load_rows("big", 100, 901, threads=threads), big[100:901])
+    assert loader.bytes_read == big.numel() * 4 + 3 * 801 * big.shape[1] * 4
+    assert loader.load_rows("big", 1024, 1024).numel() == 0
+    with pytest.raises(ValueError):
+        loader.load_rows("big", 5, 4)

@@ -119,3 +119,30 @@ def test_activation_checkpointing_same_gradients_fewer_saved_bytes(moe):
     m.eval()
     with torch.no_grad():
         assert torch.isfinite(m.response_logprobs(ids, 8)).all()
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_sharded_ranks_read_only_their_bytes(moe, tmp_path):
+    """A tensor-parallel rank reads its rows of row-sharded tensors, an expert-parallel rank skips the other ranks'
+    experts: the loaded shard equals what slicing the full tensors gives, from a fraction of the bytes."""
+    from cverl_b200.models.hf_io import HfModelLoader, load_model_weights, synthesize_model_dir
+    from cverl_b200.parallel.context import ParallelContext
+    cfg = Qwen35TextConfig.tiny(moe=moe, layers=2)
+    d = synthesize_model_dir(cfg, tmp_path / "m", dtype=torch.float32)
+    full_loader = HfModelLoader(d).load_metadata()
+    total = sum(full_loader.info(n).nbytes for n in full_loader.names())
+    for rank in (0, 1):
+        ctx = ParallelContext(tp_rank=rank, tp_size=2, ep_rank=rank if moe else 0, ep_size=2 if moe else 1)
+        a = Qwen35Model(cfg, dtype=torch.float32, ctx=ctx, with_main_grad=False)
+        b = Qwen35Model(cfg, dtype=torch.float32, ctx=ctx, with_main_grad=False)
+        loader = HfModelLoader(d)
+        load_model_weights(a, loader)
+        for spec in b.specs:                                   # the plain way: read everything, slice
+            b.load_full_tensor(spec.name, full_loader.load_tensor(spec.name))
+        assert torch.equal(a.flat.flat, b.flat.flat) and a.flat.flat.abs().sum() > 0
+        assert loader.bytes_read < (0.62 if moe else 0.8) * total, (loader.bytes_read, total)
+    rows = full_loader.load_rows(cfg.embed_name, 3, 9, threads=3)
+    assert torch.equal(rows, full_loader.load_tensor(cfg.embed_name)[3:9])
+    assert full_loader.load_rows(cfg.embed_name, 5, 5).shape[0] == 0
+    with pytest.raises(ValueError):
+        full_loader.load_rows(cfg.embed_name, 0, cfg.vocab_size + 1)
