@@ -182,3 +182,17 @@ def test_env_driven_trainer_launcher_script():
     assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-2500:]
     assert len([ln for ln in p.stdout.splitlines() if ln.startswith("step=")]) == 2
     assert json.loads(p.stdout.splitlines()[-1])["launch"]["ok"]
+
+
+def test_wall_clock_multi_rank_bench_script(tmp_path):
+    """examples/run_multigpu_ppo_bench.sh: two 4-rank layouts timed as whole runs, one CSV row each."""
+    env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1", CONFIG="tiny", DTYPE="float32", STEPS="2",
+               OUT_DIR=str(tmp_path), MASTER_PORT="29861")
+    p = subprocess.run(["bash", str(ROOT / "examples" / "run_multigpu_ppo_bench.sh"), "", "--backend", "gloo"],
+                       cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-2500:]
+    rows = (tmp_path / "multigpu_ppo_bench.csv").read_text().strip().splitlines()
+    assert rows[0].startswith("case,pp,tp,micro_batches,steps") and len(rows) == 3
+    a, b = rows[1].split(","), rows[2].split(",")
+    assert a[:5] == ["qwen_pp2_tp2_ppo", "2", "2", "2", "2"] and b[:5] == ["qwen_pp4_tp1_ppo", "4", "1", "4", "2"]
+    assert float(a[7]) > 0 and float(b[9]) > 0
