@@ -196,3 +196,21 @@ def test_wall_clock_multi_rank_bench_script(tmp_path):
     a, b = rows[1].split(","), rows[2].split(",")
     assert a[:5] == ["qwen_pp2_tp2_ppo", "2", "2", "2", "2"] and b[:5] == ["qwen_pp4_tp1_ppo", "4", "1", "4", "2"]
     assert float(a[7]) > 0 and float(b[9]) > 0
+
+
+def test_multi_rank_regression_script(tmp_path):
+    """examples/run_multigpu_regression.sh: four layouts, the reference's pass criteria on each log."""
+    env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1", CONFIG="tiny", DTYPE="float32", STEPS="2",
+               OUT_DIR=str(tmp_path), MASTER_PORT="29851")
+    p = subprocess.run(["bash", str(ROOT / "examples" / "run_multigpu_regression.sh"), "", "--backend", "gloo"],
+                       cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-2500:]
+    assert "multi-GPU PPO regression passed" in p.stdout
+    logs = sorted(f.name for f in tmp_path.glob("*.log"))
+    assert logs == ["qwen_dp2_pp1_tp2_ppo.log", "qwen_dp2_pp1_tp2_sharded_optim.log", "qwen_pp2_tp2_ppo.log",
+                    "qwen_pp4_tp1_ppo.log"]
+    assert "flat_shard_optimizer=false" in (tmp_path / "qwen_dp2_pp1_tp2_ppo.log").read_text()
+    assert "flat_shard_optimizer=true" in (tmp_path / "qwen_dp2_pp1_tp2_sharded_optim.log").read_text()
+    # a log with a non-finite value fails the run: the check is the script's own grep
+    bad = subprocess.run(["bash", "-c", "echo 'step=0 loss_sum=nan all' | grep -Eiq '=(nan|-?inf)( |$)'"])
+    assert bad.returncode == 0
