@@ -214,3 +214,18 @@ def test_multi_rank_regression_script(tmp_path):
     # a log with a non-finite value fails the run: the check is the script's own grep
     bad = subprocess.run(["bash", "-c", "echo 'step=0 loss_sum=nan all' | grep -Eiq '=(nan|-?inf)( |$)'"])
     assert bad.returncode == 0
+
+
+def test_rollout_files_to_trainer_script(tiny_dir, tmp_path):
+    """examples/run_rollout_to_trainer.sh: the oracle engine writes the step files, the 4-rank trainer reads them."""
+    data = tmp_path / "gsm.jsonl"
+    data.write_text("\n".join(json.dumps({"prompt": f"What is {i}+{i}?", "answer": f"#### {2 * i}"}) for i in range(6)))
+    env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1", DATASET=str(data), ROLLOUT_DIR=str(tmp_path / "r"),
+               STEPS="2", PROMPT_LEN="16", RESPONSE_LEN="24", DTYPE="float32", TP_COMM="nccl", ZERO_COMM="nccl",
+               MASTER_PORT="29841", LR="1e-4")
+    p = subprocess.run(["bash", str(ROOT / "examples" / "run_rollout_to_trainer.sh"), str(tiny_dir), "--backend", "gloo"],
+                       cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-2500:]
+    assert sorted(f.name for f in (tmp_path / "r").glob("*.json")) == ["rollout_step_000001.json", "rollout_step_000002.json"]
+    steps = [dict(kv.split("=", 1) for kv in ln.split()) for ln in p.stdout.splitlines() if ln.startswith("step=")]
+    assert len(steps) == 2 and steps[0]["pp"] == "2" and steps[0]["tp"] == "2" and steps[0]["rollout_rows"] == "4"
