@@ -229,3 +229,27 @@ def test_rollout_files_to_trainer_script(tiny_dir, tmp_path):
     assert sorted(f.name for f in (tmp_path / "r").glob("*.json")) == ["rollout_step_000001.json", "rollout_step_000002.json"]
     steps = [dict(kv.split("=", 1) for kv in ln.split()) for ln in p.stdout.splitlines() if ln.startswith("step=")]
     assert len(steps) == 2 and steps[0]["pp"] == "2" and steps[0]["tp"] == "2" and steps[0]["rollout_rows"] == "4"
+
+
+def test_vllm_online_grpo_launcher_dry_run_and_oracle(tiny_dir, tmp_path):
+    """examples/run_vllm_online_grpo.sh: the command lines it would run, and the whole loop with the oracle engine
+    (no server, CPU)."""
+    data = tmp_path / "gsm.jsonl"
+    data.write_text("\n".join(json.dumps({"prompt": f"What is {i}+{i}?", "answer": f"#### {2 * i}"}) for i in range(6)))
+    script = str(ROOT / "examples" / "run_vllm_online_grpo.sh")
+    env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1", MODEL_DIR=str(tiny_dir), DATASET=str(data))
+    dry = subprocess.run(["bash", script], cwd=ROOT, env=dict(env, DRY_RUN="1", VLLM_TP_SIZE="2", VLLM_GPUS="0,1"),
+                         capture_output=True, text=True, timeout=60)
+    assert dry.returncode == 0, dry.stderr
+    serve, loop = dry.stdout.strip().splitlines()
+    assert "vllm serve" in serve and "--tensor-parallel-size 2" in serve and "--enable-sleep-mode" in serve
+    assert "CUDA_VISIBLE_DEVICES=0,1" in serve and "--weight-sync nccl" in loop and "--rollout http" in loop
+    static = subprocess.run(["bash", script], cwd=ROOT, env=dict(env, DRY_RUN="1", STATIC_SPLIT="1", ROLLOUT_DIR="/r"),
+                            capture_output=True, text=True, timeout=60)
+    assert "--skip-train" in static.stdout and "--weight-sync" not in static.stdout and "--dump-rollout-dir /r" in static.stdout
+    run = subprocess.run(["bash", script], cwd=ROOT, capture_output=True, text=True, timeout=300,
+                         env=dict(env, ROLLOUT_BACKEND="oracle", DEVICE="cpu", PARAM_DTYPE="float32", STEPS="2", N="4",
+                                  PROMPTS="2", MAX_PROMPT_TOKENS="16", MAX_RESPONSE_TOKENS="24", LR="1e-3"))
+    assert run.returncode == 0, run.stdout[-1500:] + run.stderr[-2500:]
+    rows = [json.loads(ln) for ln in run.stdout.strip().splitlines() if ln.startswith("{")]
+    assert [r["step"] for r in rows] == [0, 1] and rows[0]["total_seq"] == 8.0
