@@ -149,3 +149,19 @@ def test_cifar10_export_and_resnet_bench(tmp_path, capsys):
     line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert rc == 0 and line["images_per_s"] > 0 and line["benchmark"] == "resnet14_cifar10_train_step"
     assert len(rb.BLOCKS[152]) == 4 and sum(rb.BLOCKS[152]) == 50      # 3 * 50 + 2 = 152 layers
+
+
+def test_demo_launcher_scripts(tmp_path):
+    """examples/run_mnist_demo.sh and run_resnet_cifar10_bench.sh map their environment onto the two tools."""
+    import os
+    import subprocess
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    env = dict(os.environ, PYTHONPATH=str(root), OMP_NUM_THREADS="2", DEVICE="cpu")
+    p = subprocess.run(["bash", str(root / "examples" / "run_mnist_demo.sh"), "", "--max-train-batches", "4",
+                        "--max-test-batches", "1"], cwd=root, env=env, capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0 and "mnist_demo finished" in p.stdout, p.stdout[-800:] + p.stderr[-1500:]
+    p = subprocess.run(["bash", str(root / "examples" / "run_resnet_cifar10_bench.sh"), "--width", "8"], cwd=root,
+                       env=dict(env, DEPTH="14", STEPS="2", WARMUP="1", BATCH_SIZE="8", DTYPE="float32"),
+                       capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0 and "images_per_s" in p.stdout, p.stdout[-800:] + p.stderr[-1500:]
