@@ -161,12 +161,19 @@ class TorchDistCollectives(Collectives):
             self._groups[ranks] = pg
         return pg
 
+    def _member_pg(self, group: Optional[Sequence[int]]):
+        """The group's process group for a collective CALL: a rank outside the group is refused (creation through
+        ``pg`` stays open to every rank, because it is collective over the world)."""
+        if group is not None:
+            self.rank_index_in_group(self.rank(), self._group(group), "collective group")
+        return self.pg(group)
+
     def register_group(self, ranks: Sequence[int], pg) -> None:
         self._groups[tuple(int(r) for r in ranks)] = pg
 
     def barrier(self, group=None) -> None:
         t = torch.zeros(1, device=self._device())
-        self._dist.all_reduce(t, group=self.pg(group))
+        self._dist.all_reduce(t, group=self._member_pg(group))
         if t.is_cuda:
             torch.cuda.current_stream().synchronize()
 
@@ -190,12 +197,12 @@ class TorchDistCollectives(Collectives):
         g = self._group(group)
         self.rank_index_in_group(root, g, "broadcast group")
         out = self._contig(tensor).clone()
-        self._dist.broadcast(out, src=root, group=self.pg(group))
+        self._dist.broadcast(out, src=root, group=self._member_pg(group))
         return out
 
     def all_reduce(self, tensor, op=ReduceOp.SUM, group=None):
         out = self._contig(tensor).clone()
-        self._dist.all_reduce(out, op=self._op(op), group=self.pg(group))
+        self._dist.all_reduce(out, op=self._op(op), group=self._member_pg(group))
         if op == ReduceOp.MEAN:
             out.div_(len(self._group(group)))
         return out
@@ -204,7 +211,7 @@ class TorchDistCollectives(Collectives):
         n = len(self._group(group))
         t = self._contig(tensor)
         out = t.new_empty((n * t.shape[0],) + tuple(t.shape[1:]))
-        self._dist.all_gather_into_tensor(out, t, group=self.pg(group))
+        self._dist.all_gather_into_tensor(out, t, group=self._member_pg(group))
         return out
 
     def reduce_scatter(self, tensor, op=ReduceOp.SUM, group=None):
@@ -214,10 +221,10 @@ class TorchDistCollectives(Collectives):
             raise ValueError("reduce_scatter: dim 0 must divide by the group size")
         out = t.new_empty((t.shape[0] // n,) + tuple(t.shape[1:]))
         if t.is_cuda:
-            self._dist.reduce_scatter_tensor(out, t, op=self._op(op), group=self.pg(group))
+            self._dist.reduce_scatter_tensor(out, t, op=self._op(op), group=self._member_pg(group))
         else:  # gloo has no reduce_scatter: all-reduce and slice
             full = t.clone()
-            self._dist.all_reduce(full, op=self._op(op), group=self.pg(group))
+            self._dist.all_reduce(full, op=self._op(op), group=self._member_pg(group))
             idx = self.rank_index_in_group(self.rank(), self._group(group))
             out.copy_(full.narrow(0, idx * out.shape[0], out.shape[0]))
         if op == ReduceOp.MEAN:
@@ -231,11 +238,14 @@ class TorchDistCollectives(Collectives):
             raise ValueError("all_to_all: dim 0 must divide by the group size")
         out = torch.empty_like(t)
         if t.is_cuda:
-            self._dist.all_to_all_single(out, t, group=self.pg(group))
+            self._dist.all_to_all_single(out, t, group=self._member_pg(group))
         else:
-            outs = list(out.chunk(n, 0))
-            ins = [c.contiguous() for c in t.chunk(n, 0)]
-            self._dist.all_to_all(outs, ins, group=self.pg(group))
+            # gloo has no all-to-all: every rank gathers every rank's tensor and keeps the chunk addressed to it
+            g = self._group(group)
+            me = self.rank_index_in_group(self.rank(), g, "all_to_all group")
+            parts = [torch.empty_like(t) for _ in range(n)]
+            self._dist.all_gather(parts, t, group=self._member_pg(group))
+            torch.cat([p.chunk(n, 0)[me] for p in parts], 0, out=out)
         return out
 
     def send(self, tensor, dst) -> None:

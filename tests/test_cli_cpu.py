@@ -253,3 +253,17 @@ def test_vllm_online_grpo_launcher_dry_run_and_oracle(tiny_dir, tmp_path):
     assert run.returncode == 0, run.stdout[-1500:] + run.stderr[-2500:]
     rows = [json.loads(ln) for ln in run.stdout.strip().splitlines() if ln.startswith("{")]
     assert [r["step"] for r in rows] == [0, 1] and rows[0]["total_seq"] == 8.0
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_collectives_smoke_script_on_gloo(world, tmp_path):
+    """examples/run_nccl_smoke.sh with the torch backend on CPU: every collective against its closed form, the
+    sub-group of the first half of the world, refusals; one log per rank from the supervising launcher."""
+    env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1", BACKEND="torch", CPU="1", WORLD_SIZE=str(world),
+               MASTER_PORT=str(29820 + world), LOG_DIR=str(tmp_path))
+    p = subprocess.run(["bash", str(ROOT / "examples" / "run_nccl_smoke.sh")], cwd=ROOT, env=env, capture_output=True,
+                       text=True, timeout=300)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    assert f"collectives smoke passed: backend=torch world={world}" in p.stdout
+    assert "all_to_all" in p.stdout and "sub_group" in p.stdout and "ring_send_recv" in p.stdout
+    assert len(list((tmp_path / "attempt_0").glob("rank_*.log"))) == world
