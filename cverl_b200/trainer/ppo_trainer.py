@@ -481,7 +481,13 @@ def run(argv=None) -> int:
     if args.dp * args.pp * args.cp * args.tp * args.ep != world:
         raise SystemExit(f"world size {world} != dp*pp*cp*tp*ep")
     if args.cp > 1 and args.tp > 1:
-        raise SystemExit("cp > 1 together with tp > 1 is not supported")
+        # The reference refuses this pair (trainer.cc:1931-1933).  Here the ring exchanges K | V of the local heads,
+        # the state hand-off carries the local heads' states, and the row-parallel sums run inside each context
+        # shard; the tensor-parallel exchanges stay on the collective path (the peer-memory forms size their
+        # buffers for an unsharded sequence).
+        if args.tp_comm != "nccl" and rank == 0:
+            print("note: --cp > 1 with --tp > 1 uses --tp-comm nccl", flush=True)
+        args.tp_comm = "nccl"
     if args.sp != 1:
         raise SystemExit("sequence parallelism (--sp) is declared in the topology but is not a trainer mode")
     if args.mode == "sft" and not args.sft_jsonl:

@@ -406,3 +406,20 @@ def test_activation_checkpointing_changes_no_number(nproc, flags, port):
         assert float(ra["loss_sum"]) == pytest.approx(float(rb["loss_sum"]), rel=1e-6, abs=1e-7)
         assert float(ra["global_grad_norm"]) == pytest.approx(float(rb["global_grad_norm"]), rel=1e-5)
         assert float(ra["grad_norm_sum"]) == pytest.approx(float(rb["grad_norm_sum"]), rel=1e-5)
+
+
+def test_context_parallel_with_tensor_parallel_trains_like_one_rank(tmp_path):
+    """cp 2 x tp 2 (a pair the reference refuses): the SFT loss of every step - after real updates - is the
+    single-rank loss, reported once per rank."""
+    data = tmp_path / "sft.jsonl"
+    data.write_text("\n".join(json.dumps({"prompt": f"Question number {i}: what is {i}+{i}? ",
+                                          "answer": f"The answer is {2 * i}."}) for i in range(8)))
+    common = ["--steps", "3", "--lr", "1e-2", "--max-grad-norm", "0", "--mode", "sft", "--sft-jsonl", str(data),
+              "--prompt-len", "16", "--response-len", "16", "--micro-batches", "2"]
+    one = _lines(_run(1, *common, port=29741))
+    four = _lines(_run(4, "--cp", "2", "--tp", "2", *common, port=29742))
+    assert len(one) == len(four) == 3
+    for ra, rb in zip(one, four):
+        assert float(rb["loss_sum"]) == pytest.approx(4.0 * float(ra["loss_sum"]), rel=2e-5)
+        assert rb["all_ranks_have_grad"] == "true" and rb["cp"] == "2" and rb["tp"] == "2"
+    assert float(one[2]["loss_sum"]) < 0.8 * float(one[0]["loss_sum"])      # the updates were real
