@@ -123,8 +123,12 @@ def moe_mlp(model, x: torch.Tensor, layer: int) -> torch.Tensor:
     T, H = x.shape
     k = cfg.num_experts_per_tok
     e_local = cfg.num_experts // ctx.ep_size
-    idx, w = router(x, model.param(p + "gate.weight"), k, cfg.norm_topk_prob)
+    # Under tensor parallelism the expert outputs below are partial sums (the FFN dimension is split), so the
+    # gradient that reaches the routing weights - and through them the router's input and its gate matrix - is this
+    # rank's share only.  The router therefore reads the copied input (whose backward sums the shares of both
+    # paths over the group), and the gate matrix is one of ``tp_partial_grad_names``.
     x_in = copy_to_tp(x, ctx.tp_group)
+    idx, w = router(x_in, model.param(p + "gate.weight"), k, cfg.norm_topk_prob)
     rows = x_in.repeat_interleave(k, dim=0)                              # one row per (token, k) pair
     flat_e = idx.reshape(-1)
     if ctx.ep_size == 1:

@@ -151,15 +151,21 @@ class Qwen35Model(torch.nn.Module):
 
     # ------------------------------------------------------------------ weights IO
     @torch.no_grad()
-    def init_weights(self, seed: int = 1234, std: float = 0.02) -> None:
+    def init_weights(self, seed: int = 1234, std: float = 0.02, per_tensor: bool = False) -> None:
         """Random initialisation (normal, std 0.02; norm weights 0 for ``1+w`` norms, 1 otherwise).
 
         The same full tensor is generated on every tensor-parallel rank and then
-        sharded, so a TP run starts from the weights a dense run would.
+        sharded, so a TP run starts from the weights a dense run would.  ``per_tensor``: every tensor has its own
+        generator, seeded by its name, so that a pipeline stage draws for its layers the values a one-stage model
+        draws and the two copies of a tied embedding (first and last stage) start equal - the distributed trainer
+        initialises this way; by default one generator runs through the stage's tensors in order.
         """
+        import zlib
         cfg = self.cfg
         gen = torch.Generator(device="cpu").manual_seed(seed)
         for s in self.specs:
+            if per_tensor:
+                gen.manual_seed((seed * 1000003 + zlib.crc32(s.name.encode())) & 0x7FFFFFFFFFFFFFFF)
             if s.name.endswith("A_log"):
                 full = torch.log(torch.empty(s.full_shape).uniform_(1.0, 8.0, generator=gen))
             elif s.name.endswith("dt_bias"):
@@ -279,6 +285,9 @@ class Qwen35Model(torch.nn.Module):
                 names += [p + "self_attn.q_norm.weight", p + "self_attn.k_norm.weight"]
             else:
                 names.append(p + "linear_attn.norm.weight")
+            if cfg.is_qwen3_moe:
+                # the routing weights multiply expert outputs that are partial sums over the split FFN dimension
+                names.append(p + "mlp.gate.weight")
             if self.sequence_parallel:
                 # token-sharded layer norms: every rank holds the gradient of its rows only
                 names += [p + "input_layernorm.weight", p + "post_attention_layernorm.weight"]
@@ -597,19 +606,27 @@ class Qwen35Model(torch.nn.Module):
         h = hidden[:, prompt_len - 1: prompt_len - 1 + R]
         return self.token_logprobs(h, input_ids[:, prompt_len:])
 
-    def _response_logprobs_cp(self, input_ids: torch.Tensor, prompt_len: int) -> torch.Tensor:
-        """Context parallel: every rank runs its contiguous shard of the sequence, scores its own
-        positions against the next tokens, and the per-position log-probs are all-gathered (the
-        backward of the gather is a reduce-scatter, so each rank back-propagates only its shard)."""
+    def cp_shard_len(self, seq: int) -> int:
+        """Tokens of a ``seq``-token sequence that one context-parallel rank holds (the last shard is padded)."""
+        from ..parallel.context_parallel import padded_shard_len
+        self._cp_original_len = seq
+        return padded_shard_len(seq, self.ctx.cp_size)
+
+    def cp_embed(self, input_ids: torch.Tensor) -> torch.Tensor:
+        """Context parallel, first stage: embeds this rank's contiguous shard of ``[B, S]`` ids -> ``[B * s_loc, H]``."""
+        from ..parallel.context_parallel import shard_sequence
+        self.cp_shard_len(input_ids.shape[1])
+        return self.embed(shard_sequence(input_ids, self.ctx.cp_rank, self.ctx.cp_size, dim=1))
+
+    def cp_response_logprobs(self, hidden: torch.Tensor, input_ids: torch.Tensor, prompt_len: int) -> torch.Tensor:
+        """Context parallel, last stage: this rank's final-normed hidden rows ``[B * s_loc, H]`` scored against the
+        next tokens of its own positions; the per-position log-probs are all-gathered (the backward of the gather
+        is a reduce-scatter, so each rank back-propagates only its shard) and cut to the response: ``[B, R]``."""
         from ..parallel.autograd_collectives import all_gather_rows
-        from ..parallel.context_parallel import padded_shard_len, shard_sequence
         ctx = self.ctx
         B, S = input_ids.shape
-        s_loc = padded_shard_len(S, ctx.cp_size)
-        self._cp_original_len = S
-        local_ids = shard_sequence(input_ids, ctx.cp_rank, ctx.cp_size, dim=1)
-        x = self.embed(local_ids)
-        hidden = self.forward_layers(x, B, s_loc).view(B, s_loc, -1)
+        s_loc = self.cp_shard_len(S)
+        hidden = hidden.view(B, s_loc, -1)
         # position p predicts token p+1; the final padded position predicts nothing (target 0, masked below)
         nxt = torch.nn.functional.pad(input_ids[:, 1:], (0, s_loc * ctx.cp_size - (S - 1)))
         targets = nxt[:, ctx.cp_rank * s_loc:(ctx.cp_rank + 1) * s_loc]
@@ -617,6 +634,13 @@ class Qwen35Model(torch.nn.Module):
         lp_full = all_gather_rows(lp_local.t().contiguous(), ctx.cp_group).t()  # [B, cp*s_loc]
         R = S - prompt_len
         return lp_full[:, prompt_len - 1: prompt_len - 1 + R]
+
+    def _response_logprobs_cp(self, input_ids: torch.Tensor, prompt_len: int) -> torch.Tensor:
+        """Context parallel: every rank runs its contiguous shard of the sequence and scores its own positions."""
+        B, S = input_ids.shape
+        x = self.cp_embed(input_ids)
+        hidden = self.forward_layers(x, B, self.cp_shard_len(S))
+        return self.cp_response_logprobs(hidden, input_ids, prompt_len)
 
     def forward_logits(self, input_ids: torch.Tensor) -> torch.Tensor:
         """Full fp32 logits ``[B, S, V]`` (debug / rollout sampling; the trainer never builds them)."""

@@ -457,8 +457,11 @@ def _loss_and_seed(model, engine_cfg: ActorConfig, hidden, batch, prompt_len, gr
     """Last-stage scoring of one micro-batch: returns (log-probs, gradient seed, metrics[6])."""
     B, S = batch["input_ids"].shape
     R = S - prompt_len
-    h = hidden.view(B, S, -1)[:, prompt_len - 1:prompt_len - 1 + R]
-    lp = model.token_logprobs(h, batch["input_ids"][:, prompt_len:])
+    if model.ctx.cp_size > 1:          # the stage holds this context-parallel rank's shard of every sequence
+        lp = model.cp_response_logprobs(hidden, batch["input_ids"], prompt_len)
+    else:
+        h = hidden.view(B, S, -1)[:, prompt_len - 1:prompt_len - 1 + R]
+        lp = model.token_logprobs(h, batch["input_ids"][:, prompt_len:])
     seed, metrics = _score(engine_cfg, lp, batch, grad_scale)
     return lp, seed, metrics
 
@@ -576,7 +579,7 @@ def run(argv=None) -> int:
     if loader is not None:
         load_model_weights(model, loader)
     else:
-        model.init_weights(seed=args.seed)
+        model.init_weights(seed=args.seed, per_tensor=True)     # a stage starts from the one-stage model's weights
     comm_dtype = None if args.dp_grad_comm_dtype in ("float32", "model") else _DTYPES[args.dp_grad_comm_dtype]
     adam_opts = AdamWOptions(lr=args.lr, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=args.weight_decay,
                              use_master_weights=args.master_weights)
@@ -635,8 +638,10 @@ def run(argv=None) -> int:
     stage = None
     if args.pp > 1:
         peers = pipeline_peers(info.pipeline_group, info.pipeline_rank)
+        from ..parallel.context_parallel import padded_shard_len
         stage = PipelineStage(peers, info.pipeline_rank, args.pp, args.micro_batches,
-                              (mbs * (S // args.cp if args.cp > 1 else S), cfg.hidden_size), dtype, device)
+                              (mbs * (padded_shard_len(S, args.cp) if args.cp > 1 else S), cfg.hidden_size), dtype,
+                              device)
     engine = ActorEngine(model, opt, ecfg)
     exit_ok = True
     log_lines = []
@@ -676,9 +681,10 @@ def run(argv=None) -> int:
 
                 def forward_fn(m, x):
                     b = batches[m]
+                    s_stage = model.cp_shard_len(S) if args.cp > 1 else S
                     if first:
-                        x = model.embed(b["input_ids"])
-                    return model.forward_layers(x, mbs, S)
+                        x = model.cp_embed(b["input_ids"]) if args.cp > 1 else model.embed(b["input_ids"])
+                    return model.forward_layers(x, mbs, s_stage)
 
                 def loss_fn(m, hidden):
                     lp, seed, metrics = _loss_and_seed(model, ecfg, hidden, batches[m], args.prompt_len, grad_scale)

@@ -347,7 +347,9 @@ def _zero2_worker(rank, world, moe):
         opt.step()
         ropt.step()
         for name, t in model.flat.named_tensors():
-            torch.testing.assert_close(t, ref.flat.params[name].data, rtol=2e-4, atol=2e-5, msg=lambda m: f"{name}: {m}")
+            # AdamW moves every element by about lr = 1e-2; an element whose gradient is near zero turns the last
+            # bits of the two summation orders into a visible fraction of that, so the bound is 1 % of a step
+            torch.testing.assert_close(t, ref.flat.params[name].data, rtol=2e-4, atol=1e-4, msg=lambda m: f"{name}: {m}")
         assert abs(opt.last_metrics[1].item() - ropt.last_metrics[1].item()) < 1e-3 * ropt.last_metrics[1].item()
         assert all(float(g.abs().max()) == 0.0 for g in model.flat.grad_buffers)
         assert float(opt.grad_shard.abs().max()) == 0.0

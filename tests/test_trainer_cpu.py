@@ -423,3 +423,47 @@ def test_context_parallel_with_tensor_parallel_trains_like_one_rank(tmp_path):
         assert float(rb["loss_sum"]) == pytest.approx(4.0 * float(ra["loss_sum"]), rel=2e-5)
         assert rb["all_ranks_have_grad"] == "true" and rb["cp"] == "2" and rb["tp"] == "2"
     assert float(one[2]["loss_sum"]) < 0.8 * float(one[0]["loss_sum"])      # the updates were real
+
+
+def _sft_flags(tmp_path, micro_batches=4):
+    data = tmp_path / "sft.jsonl"
+    data.write_text("\n".join(json.dumps({"prompt": f"Question number {i}: what is {i}+{i}? ",
+                                          "answer": f"The answer is {2 * i}."}) for i in range(8)))
+    return ["--steps", "3", "--lr", "1e-2", "--max-grad-norm", "0", "--mode", "sft", "--sft-jsonl", str(data),
+            "--prompt-len", "16", "--response-len", "16", "--micro-batches", str(micro_batches)]
+
+
+@pytest.mark.parametrize("nproc,flags,reports", [
+    (2, ["--pp", "2"], 1),
+    (4, ["--pp", "4"], 1),
+    (4, ["--pp", "2", "--cp", "2"], 2),
+    (4, ["--pp", "2", "--tp", "2"], 2),
+])
+def test_pipeline_layouts_reproduce_the_one_stage_losses(tmp_path, nproc, flags, reports):
+    """Supervised losses over three real updates: a pipeline (alone, with context parallelism, with tensor
+    parallelism) gives the one-stage loss at every step.  Every stage draws the initial values of its tensors
+    from generators seeded by the tensor names, so the runs start from the same weights."""
+    common = _sft_flags(tmp_path)
+    one = _lines(_run(1, *common, port=29751))
+    many = _lines(_run(nproc, *flags, *common, port=29752))
+    assert len(one) == len(many) == 3
+    for ra, rb in zip(one, many):
+        assert float(rb["loss_sum"]) == pytest.approx(reports * float(ra["loss_sum"]), rel=2e-5)
+    assert float(one[2]["loss_sum"]) < 0.8 * float(one[0]["loss_sum"])
+
+
+@pytest.mark.parametrize("nproc,flags,mb,reports", [
+    (2, ["--tp", "2"], 4, 2),
+    (4, ["--ep", "2", "--tp", "2"], 2, 2),
+])
+def test_moe_layouts_reproduce_the_one_rank_losses(tmp_path, nproc, flags, mb, reports):
+    """Mixture-of-experts under tensor parallelism (alone and with expert parallelism): the supervised loss after
+    each of three updates is the one-rank loss.  The routing weights multiply expert outputs that are partial sums
+    over the split FFN dimension, so the router's gradient has to be summed over the tensor-parallel group - with
+    that sum missing the losses drift apart from the second step on."""
+    moe = ["--config", "tiny_moe"]
+    one = _lines(_run(1, *_sft_flags(tmp_path, 4), *moe, port=29761))
+    many = _lines(_run(nproc, *flags, *_sft_flags(tmp_path, mb), *moe, port=29762))
+    assert len(one) == len(many) == 3
+    for ra, rb in zip(one, many):
+        assert float(rb["loss_sum"]) == pytest.approx(reports * float(ra["loss_sum"]), rel=2e-5)
