@@ -25,10 +25,13 @@ def main(argv=None) -> int:
     ap.add_argument("--token")
     ap.add_argument("--max-examples", type=int, default=-1)
     ap.add_argument("--local-files-only", action="store_true")
+    ap.add_argument("--trust-remote-code", action="store_true",
+                    help="let the datasets library run the loading script a dataset repository ships")
     a = ap.parse_args(argv)
     res = download_hf_dataset(a.dataset, a.output_file, name=a.name, split=a.split, prompt_field=a.prompt_field,
                               answer_field=a.answer_field, cache_dir=a.cache_dir, token=a.token,
-                              max_examples=a.max_examples, local_files_only=a.local_files_only)
+                              max_examples=a.max_examples, local_files_only=a.local_files_only,
+                              trust_remote_code=a.trust_remote_code)
     print(f"CVERL_HF_DATASET_FILE={res.output_file}")
     print(f"CVERL_HF_DATASET_ROWS={res.rows}")
     return 0

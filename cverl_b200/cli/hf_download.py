@@ -69,6 +69,13 @@ def main(argv=None) -> int:
     d.add_argument("repo_id")
     d.add_argument("filename")
     d.add_argument("--local-dir", required=True)
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if "--repo-id" in argv and (not argv or argv[0] not in ("model", "dataset")):
+        # the reference's form (tools/hf_snapshot_download.py): --repo-id ID [options], no sub-command
+        i = argv.index("--repo-id")
+        if i + 1 >= len(argv):
+            ap.error("--repo-id needs a value")
+        argv = ["model", argv[i + 1]] + argv[:i] + argv[i + 2:]
     a = ap.parse_args(argv)
     try:
         if a.kind == "model" and a.dry_run:

@@ -33,6 +33,8 @@ def main(argv=None) -> int:
     ap.add_argument("--packed-num-buffers", type=int, default=2)
     ap.add_argument("--checkpoint-format", action=argparse.BooleanOptionalAction, default=True)
     ap.add_argument("--timeout", type=float, default=300.0)
+    ap.add_argument("--skip-server-init", action="store_true", help="the server's side of the group is opened elsewhere")
+    ap.add_argument("--skip-update-metadata", action="store_true", help="the /update_weights request is posted elsewhere")
     ap.add_argument("--skip-pause", action="store_true")
     ap.add_argument("--dry-run", action="store_true")
     a = ap.parse_args(argv)
@@ -51,7 +53,8 @@ def main(argv=None) -> int:
         return 2
     sync = VllmNcclSync(VllmControl(a.base_url, a.timeout), a.master_address, a.master_port, a.world_size,
                         a.rank_offset, a.packed, a.packed_buffer_size_bytes, a.packed_num_buffers,
-                        a.checkpoint_format, pause=not a.skip_pause)
+                        a.checkpoint_format, pause=not a.skip_pause, server_init=not a.skip_server_init,
+                        update_metadata=not a.skip_update_metadata)
     print(json.dumps(sync.sync(params, info), indent=2))
     return 0
 

@@ -93,7 +93,7 @@ def _rows_of(path: Path):
 def download_hf_dataset(dataset: str, output_file, *, name: Optional[str] = None, split: str = "train",
                         prompt_field: str = "question", answer_field: str = "answer", cache_dir=None,
                         token: Optional[str] = None, max_examples: int = -1,
-                        local_files_only: bool = False) -> HfDatasetDownloadResult:
+                        local_files_only: bool = False, trust_remote_code: bool = False) -> HfDatasetDownloadResult:
     """One split of a Hugging Face dataset as a prompt / answer JSONL file.
 
     ``dataset`` is a Hub id (``gsm8k`` is an alias of ``openai/gsm8k``) or a local directory holding the split's
@@ -123,8 +123,9 @@ def download_hf_dataset(dataset: str, output_file, *, name: Optional[str] = None
             if local_files_only:
                 import os
                 os.environ["HF_DATASETS_OFFLINE"] = "1"
+            extra = {"trust_remote_code": True} if trust_remote_code else {}    # only sent when asked for
             ds = datasets.load_dataset(path=dataset_id, name=name, split=split, cache_dir=cache_dir, token=token,
-                                       download_mode="reuse_dataset_if_exists")
+                                       download_mode="reuse_dataset_if_exists", **extra)
             rows_iter, source = iter(ds), f"datasets:{dataset_id}"
         else:
             from huggingface_hub import snapshot_download

@@ -89,13 +89,18 @@ class VllmNcclSync:
     def __init__(self, control: VllmControl, master_address: str, master_port: int, world_size: int,
                  rank_offset: int = 1, packed: bool = True, packed_buffer_size_bytes: int = 1 << 30,
                  packed_num_buffers: int = 2, checkpoint_format: bool = True, pause: bool = True, engine=None,
-                 send_args: Optional[Callable[..., Any]] = None):
+                 send_args: Optional[Callable[..., Any]] = None, server_init: bool = True,
+                 update_metadata: bool = True):
+        """``server_init=False``: the server's side of the group was opened by someone else
+        (``vllm_native_rl_control init-nccl``), only the trainer's side is opened here.  ``update_metadata=False``:
+        the ``/update_weights`` request is posted by someone else; only the tensors are sent."""
         self.control = control
         self.init = dict(master_address=master_address, master_port=master_port, world_size=world_size)
         self.rank_offset = rank_offset
         self.packed, self.buf_bytes, self.num_buf = packed, packed_buffer_size_bytes, packed_num_buffers
         self.checkpoint_format, self.pause = checkpoint_format, pause
         self._engine, self._send_args = engine, send_args
+        self.server_init, self.update_metadata = server_init, update_metadata
         self.group = None
         self.syncs = 0
 
@@ -104,10 +109,13 @@ class VllmNcclSync:
             return
         if self._engine is None:
             self._engine, self._send_args = _vllm_engine()
-        server = pool.submit(self.control.init_weight_transfer, self.init["master_address"],
-                             self.init["master_port"], self.init["world_size"], self.rank_offset)
+        server = None
+        if self.server_init:
+            server = pool.submit(self.control.init_weight_transfer, self.init["master_address"],
+                                 self.init["master_port"], self.init["world_size"], self.rank_offset)
         self.group = self._engine.trainer_init(dict(self.init))
-        server.result()
+        if server is not None:
+            server.result()
 
     def sync(self, named_parameters: List[Tuple[str, Any]], update_info: Dict[str, Any]) -> Dict[str, Any]:
         """One weight push.  Returns the byte count and the server's answer to ``/update_weights``."""
@@ -119,12 +127,12 @@ class VllmNcclSync:
             if self.pause:
                 self.control.pause("wait")
             try:
-                server = pool.submit(self.control.update_weights, info)
+                server = pool.submit(self.control.update_weights, info) if self.update_metadata else None
                 self._engine.trainer_send_weights(
                     iter(named_parameters),
                     self._send_args(group=self.group, src=0, packed=self.packed,
                                     packed_buffer_size_bytes=self.buf_bytes, packed_num_buffers=self.num_buf))
-                answer = server.result()
+                answer = server.result() if server is not None else None
             finally:
                 if self.pause:
                     self.control.resume()

@@ -31,6 +31,12 @@ def test_weight_manifest_and_inspect(tiny_dir, capsys):
     assert inspect_hf_model.main(["--model-dir", str(tiny_dir), "--check", "--tensors"]) == 0
     rep = json.loads(capsys.readouterr().out)
     assert rep["check"]["ok"] and rep["num_tensors"] == len(rep["tensors"])
+    assert inspect_hf_model.main([str(tiny_dir), "--find", "embed_tokens", "--load-tensor", info["names"][0],
+                                  "--load-all"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["match_count"] == 1 and rep["matches"][0]["name"].endswith("embed_tokens.weight")
+    assert rep["loaded_tensor"]["shape"] == rep["matches"][0]["shape"] and rep["loaded_tensor"]["nbytes"] > 0
+    assert rep["loaded_all"]["tensor_count"] == rep["num_tensors"] and rep["loaded_all"]["nbytes"] == rep["total_bytes"]
 
 
 def test_forward_dump_and_compare(tiny_dir, tmp_path, capsys):
@@ -42,6 +48,19 @@ def test_forward_dump_and_compare(tiny_dir, tmp_path, capsys):
     assert qwen3_5_forward.main(["--model-dir", str(tiny_dir), "--ids", "5,6,7,8,9", "--compare", str(dump)]) == 0
     second = json.loads(capsys.readouterr().out)
     assert second["compare"]["max_abs"] < 1e-5 and second["compare"]["argmax_equal"]
+    # the reference's command line: positional model directory, --tokens / --layers / --logits / --save-output
+    raw = tmp_path / "logits.bin"
+    assert qwen3_5_forward.main([str(tiny_dir), "--tokens", "5,6,7,8,9", "--logits", "--save-output", str(raw)]) == 0
+    third = json.loads(capsys.readouterr().out)
+    assert third["saved_output"] == str(raw) and len(third["top5_token_ids"]) == 5 and third["tokens"] == 5
+    assert raw.read_bytes()[:8] == b"CVTENSR1"
+    back = qwen3_5_forward.load_tensor_binary(raw)
+    assert list(back.shape) == third["shape"] and abs(float(back.mean()) - third["mean"]) < 1e-6
+    assert qwen3_5_forward.main([str(tiny_dir), "--tokens", "5,6,7,8,9", "--compare", str(raw)]) == 0
+    assert json.loads(capsys.readouterr().out)["compare"]["max_abs"] < 1e-5
+    assert qwen3_5_forward.main([str(tiny_dir), "--tokens", "5,6,7", "--layers", "2", "--hidden"]) == 0
+    hid = json.loads(capsys.readouterr().out)
+    assert hid["output"] == "hidden" and hid["layers"] == 2 and hid["shape"][:2] == [1, 3] and "top5_token_ids" not in hid
 
 
 def test_rollout_batch_source_to_receiver_gloo():

@@ -375,5 +375,14 @@ def test_vllm_control_plane_and_weight_sync_sequence():
         sync.sync(params, info)                               # the group is opened once
         assert [p for p, _ in calls] == ["/pause?mode=wait", "/update_weights", "/resume"]
         assert normalize_dtype_name("torch.bfloat16") == "bfloat16" and normalize_dtype_name("Float") == "float32"
+        # the server's side handled elsewhere: no init request, no update request - the engine is still driven
+        calls.clear()
+        sent.clear()
+        update_seen.set()
+        bare = VllmNcclSync(c, "127.0.0.1", 29998, 3, engine=FakeEngine, send_args=lambda **kw: kw, pause=False,
+                            server_init=False, update_metadata=False, packed=False)
+        out = bare.sync(params, info)
+        assert calls == [] and out["server"] is None and out["sent"] == 2
+        assert sent[0][0] == "init" and sent[1][0] == "send" and sent[1][2]["packed"] is False
     finally:
         server.shutdown()

@@ -59,3 +59,7 @@ def test_hf_download_cli_options_and_offline_behaviour(tmp_path, capsys, monkeyp
     assert hf_download.main(["model", "org/name", "--dry-run"]) == 0
     out = capsys.readouterr().out
     assert "CVERL_HF_SHA=abc123" in out and "CVERL_HF_FILE_COUNT=3" in out
+    # the reference's form: --repo-id instead of a sub-command
+    calls.clear()
+    assert hf_download.main(["--local-dir", str(tmp_path / "n2"), "--repo-id", "org/other", "--revision", "v2"]) == 0
+    assert calls["repo_id"] == "org/other" and calls["revision"] == "v2"

@@ -120,3 +120,18 @@ def test_parallel_plan_cli():
     assert "rank=5 dp=1 pp=0 cp=0 tp=1 ep=0" in out
     assert "schedule=F0 F1 B0 F2 B1 F3 B2 B3" in out
     assert "layer_begin=0 layer_end=12" in out
+    assert "world_size=8" in out and "parallel=dp2_pp2_cp1_tp2_ep1_sp1" in out and "micro_batches=4" in out
+    # the reference's spellings: --num-layers, --all-ranks (every rank's block), --help
+    every = subprocess.run([str(LIB_DIR / "cverl_parallel_plan"), "--dp", "2", "--pp", "2", "--all-ranks", "--num-layers",
+                            "6", "--micro-batches", "4", "--local-rank", "1", "--local-world-size", "4", "--schedule"],
+                           capture_output=True, text=True, check=True).stdout
+    assert every.count("\nrank=") == 4 and "rank=3 dp=1 pp=1" in every and "layer_begin=3 layer_end=6" in every
+    assert every.count("max_live_activations=2") == 2 and every.count("max_live_activations=1") == 2
+    quiet = subprocess.run([str(LIB_DIR / "cverl_parallel_plan"), "--pp", "2", "--no-schedule"], capture_output=True,
+                           text=True, check=True).stdout
+    assert "schedule=" not in quiet and "max_live_activations=" in quiet
+    usage = subprocess.run([str(LIB_DIR / "cverl_parallel_plan"), "--help"], capture_output=True, text=True, check=True)
+    assert "--all-ranks" in usage.stdout and "--num-layers" in usage.stdout
+    bad = subprocess.run([str(LIB_DIR / "cverl_parallel_plan"), "--pp", "4", "--micro-batches", "2"], capture_output=True,
+                         text=True)
+    assert bad.returncode == 1 and "cverl_parallel_plan:" in bad.stderr
