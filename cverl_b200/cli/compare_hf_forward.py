@@ -106,6 +106,7 @@ def _from_dir(model_dir: str, layers):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("model_dir_positional", nargs="?", default="", help="model directory (the reference's argv[1])")
     ap.add_argument("--random", choices=["qwen3_5", "qwen3_moe"])
     ap.add_argument("--model-dir", default="")
     ap.add_argument("--tokens", default="1,7,3,250,9,42,100,5,17,8,300,2")
@@ -115,6 +116,9 @@ def main(argv=None) -> int:
     ap.add_argument("--atol", type=float, default=1e-3)
     ap.add_argument("--seed", type=int, default=0)
     a = ap.parse_args(argv)
+    a.model_dir = a.model_dir or a.model_dir_positional
+    if not a.random and not a.model_dir:
+        ap.error("give a model directory or --random")
     tokens = [int(t) for t in a.tokens.split(",") if t]
     if not tokens:
         raise SystemExit("--tokens must contain at least one id")
