@@ -386,3 +386,15 @@ def test_vllm_control_plane_and_weight_sync_sequence():
         assert sent[0][0] == "init" and sent[1][0] == "send" and sent[1][2]["packed"] is False
     finally:
         server.shutdown()
+
+
+def test_bridge_module_name_of_the_reference():
+    import inspect
+    import _cverl_vllm_bridge as bridge
+    from cverl_b200.rollout.vllm_bridge import QwenPolicy
+    assert bridge.QwenPolicy is QwenPolicy
+    sig = inspect.signature(QwenPolicy.gsm8k_grpo_update)
+    assert list(sig.parameters)[1:6] == ["prompts", "responses", "answers", "prompt_indices", "sample_indices"]
+    assert sig.parameters["learning_rate"].default == 3.0e-6 and sig.parameters["reward_method"].default == "flexible"
+    assert list(inspect.signature(QwenPolicy.__init__).parameters)[1:] == ["model_dir", "tokenizer_path", "device",
+                                                                          "param_dtype", "max_layers"]
