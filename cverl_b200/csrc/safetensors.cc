@@ -53,6 +53,36 @@ struct Scanner {
   void expect(char c) {
     if (!eat(c)) throw std::runtime_error(std::string("safetensors header: expected '") + c + "'");
   }
+  uint32_t hex4(size_t at) const {
+    if (at + 4 > s.size()) throw std::runtime_error("safetensors header: truncated \\u escape");
+    uint32_t v = 0;
+    for (size_t k = at; k < at + 4; ++k) {
+      const char c = s[k];
+      v <<= 4;
+      if (c >= '0' && c <= '9') v |= static_cast<uint32_t>(c - '0');
+      else if (c >= 'a' && c <= 'f') v |= static_cast<uint32_t>(c - 'a' + 10);
+      else if (c >= 'A' && c <= 'F') v |= static_cast<uint32_t>(c - 'A' + 10);
+      else throw std::runtime_error("safetensors header: bad \\u escape");
+    }
+    return v;
+  }
+  static void append_utf8(uint32_t cp, std::string& out) {
+    if (cp < 0x80) {
+      out.push_back(static_cast<char>(cp));
+    } else if (cp < 0x800) {
+      out.push_back(static_cast<char>(0xC0 | (cp >> 6)));
+      out.push_back(static_cast<char>(0x80 | (cp & 0x3F)));
+    } else if (cp < 0x10000) {
+      out.push_back(static_cast<char>(0xE0 | (cp >> 12)));
+      out.push_back(static_cast<char>(0x80 | ((cp >> 6) & 0x3F)));
+      out.push_back(static_cast<char>(0x80 | (cp & 0x3F)));
+    } else {
+      out.push_back(static_cast<char>(0xF0 | (cp >> 18)));
+      out.push_back(static_cast<char>(0x80 | ((cp >> 12) & 0x3F)));
+      out.push_back(static_cast<char>(0x80 | ((cp >> 6) & 0x3F)));
+      out.push_back(static_cast<char>(0x80 | (cp & 0x3F)));
+    }
+  }
   std::string str() {
     ws();
     if (i >= s.size() || s[i] != '"') throw std::runtime_error("safetensors header: expected string");
@@ -64,7 +94,22 @@ struct Scanner {
         switch (s[i]) {
           case 'n': out.push_back('\n'); break;
           case 't': out.push_back('\t'); break;
-          case 'u': out.push_back('?'); i += 4; break;
+          case 'r': out.push_back('\r'); break;
+          case 'b': out.push_back('\b'); break;
+          case 'f': out.push_back('\f'); break;
+          case 'u': {                        // \uXXXX, a surrogate pair when two follow each other: UTF-8 out
+            uint32_t cp = hex4(i + 1);
+            i += 4;
+            if (cp >= 0xD800 && cp <= 0xDBFF && i + 6 < s.size() && s[i + 1] == '\\' && s[i + 2] == 'u') {
+              const uint32_t lo = hex4(i + 3);
+              if (lo >= 0xDC00 && lo <= 0xDFFF) {
+                cp = 0x10000 + ((cp - 0xD800) << 10) + (lo - 0xDC00);
+                i += 6;
+              }
+            }
+            append_utf8(cp, out);
+            break;
+          }
           default: out.push_back(s[i]);
         }
       } else {
@@ -322,6 +367,13 @@ int cverl_st_write(const char* path, int64_t n, const char* const* names, const 
       sizes[static_cast<size_t>(i)] = numel * static_cast<uint64_t>(esz);
       std::string nm;
       for (const char* c = names[i]; *c; ++c) {
+        const unsigned char u = static_cast<unsigned char>(*c);
+        if (u < 0x20) {                       // control characters must be escaped in JSON
+          char buf[8];
+          std::snprintf(buf, sizeof(buf), "\\u%04x", u);
+          nm += buf;
+          continue;
+        }
         if (*c == '"' || *c == '\\') nm.push_back('\\');
         nm.push_back(*c);
       }

@@ -80,3 +80,27 @@ def test_threaded_and_ranged_reads_of_a_large_tensor(tmp_path):
     assert loader.load_rows("big", 1024, 1024).numel() == 0
     with pytest.raises(ValueError):
         loader.load_rows("big", 5, 4)
+
+
+def test_tensor_names_with_escapes_and_unicode(tmp_path):
+    """Names travel through the JSON header: quotes, backslashes, control characters and non-ASCII text written
+    here are read back by the safetensors package, and a header that spells non-ASCII names as \\uXXXX escapes
+    (surrogate pairs included) is decoded to the same UTF-8 names."""
+    st = pytest.importorskip("safetensors.torch")
+    names = ['plain', 'q"uote', 'back\\slash', 'tab\there', 'line\nbreak', 'ü.weight', '数学', 'emoji🙂']
+    tensors = {n: torch.full((2,), float(i)) for i, n in enumerate(names)}
+    path = tmp_path / "names.safetensors"
+    write_safetensors(path, tensors)
+    theirs = st.load_file(str(path))
+    assert sorted(theirs) == sorted(names) and all(float(theirs[n][0]) == float(tensors[n][0]) for n in names)
+    # the same content with an ASCII-only header
+    raw = path.read_bytes()
+    (hlen,) = struct.unpack("<Q", raw[:8])
+    header = json.dumps(json.loads(raw[8:8 + hlen]), ensure_ascii=True).encode()
+    assert b"\\ud83d\\ude42" in header and b"\\u6570" in header
+    header += b" " * ((8 - (8 + len(header)) % 8) % 8)
+    ascii_path = tmp_path / "ascii.safetensors"
+    ascii_path.write_bytes(struct.pack("<Q", len(header)) + header + raw[8 + hlen:])
+    loader = HfModelLoader(ascii_path).load_metadata()
+    assert sorted(loader.names()) == sorted(names)
+    assert all(torch.equal(loader.load_tensor(n), tensors[n]) for n in names)
