@@ -19,6 +19,10 @@ rank - and adds the supervision:
   newest step directory whose manifest is marked complete and whose rank files all exist is chosen, so a
   checkpoint that the failure interrupted half-way is skipped.
 
+With ``--nnodes > 1`` one launcher runs per node (``--node-rank``); each supervises and restarts its own ranks, a
+failure on one node reaches the others through their ranks (watchdog, process-group timeout), and attempt ``k``
+uses ``--master-port + k * --port-stride`` on every node, so the restarted attempts meet again.
+
 Everything here is host code: no CUDA call, no device state.  The last line printed is a JSON summary of the
 attempts.  Exit code: 0 when an attempt finished with every rank at 0, otherwise the first failing rank's code
 (124 for a stall or a timeout).
@@ -137,8 +141,13 @@ class Attempt:
         for lr in range(self.args.nproc):
             log = self.log_dir / f"rank_{self.args.node_rank * self.args.nproc + lr}.log"
             handle = open(log, "wb")
-            proc = subprocess.Popen(argv, env=self._env(lr), stdout=handle, stderr=subprocess.STDOUT,
-                                    stdin=subprocess.DEVNULL, start_new_session=True)
+            try:
+                proc = subprocess.Popen(argv, env=self._env(lr), stdout=handle, stderr=subprocess.STDOUT,
+                                        stdin=subprocess.DEVNULL, start_new_session=True)
+            except OSError as exc:             # the program cannot be started at all: end what already runs
+                handle.close()
+                self.terminate()
+                raise RuntimeError(f"cannot start {argv[0]!r}: {exc}") from exc
             self.ranks.append(_Rank(self.args.node_rank * self.args.nproc + lr, proc, log, handle))
         if self.args.tee_rank >= 0:
             for r in self.ranks:
@@ -198,8 +207,14 @@ class Attempt:
     def run(self) -> dict:
         a = self.args
         t0 = time.monotonic()
-        self.start()
         result = {"ok": False, "cause": "", "rank": -1, "code": 0}
+        try:
+            self.start()
+        except RuntimeError as exc:
+            for r in self.ranks:
+                r.handle.close()
+            result.update(cause=str(exc), code=127, seconds=round(time.monotonic() - t0, 3), exit_codes={})
+            return result
         try:
             while True:
                 self._poll()
@@ -275,7 +290,9 @@ def supervise(args, program: Sequence[str], out=sys.stdout) -> dict:
             res = att.run()
             res["attempt"], res["resumed_from"] = attempt, resumed
             history.append(res)
-            if res["ok"]:
+            if res["ok"] or res["code"] == 127:        # done, or a program that cannot be started: no point retrying
+                if not res["ok"]:
+                    print(f"[launch] {res['cause']}", file=out, flush=True)
                 break
             print(f"[launch] attempt {attempt} failed: {res['cause']}"
                   + (f" (rank {res['rank']} exit {res['code']})" if res["rank"] >= 0 else "")

@@ -128,6 +128,12 @@ def test_restart_resumes_from_the_latest_checkpoint(tmp_path):
     assert (tmp_path / "faulty" / "attempt_1" / "rank_0.log").read_text().count("step=") == 2
 
 
+def test_a_program_that_cannot_be_started_is_reported_not_retried(tmp_path):
+    p, res = _launch(tmp_path, "nope", 29951, "--max-restarts", "3", program=["/no/such/program", "x"])
+    assert p.returncode == 127 and not res["ok"] and len(res["attempts"]) == 1
+    assert "cannot start" in res["attempts"][0]["cause"] and "cannot start" in p.stdout
+
+
 def test_failure_without_restarts_returns_the_rank_exit_code(tmp_path):
     p, res = _launch(tmp_path, "once", 29931, "--grace-s", "2", program=TRAINER + ["--steps", "3"],
                      fault="rank=0,step=1,kind=exit,code=23")
