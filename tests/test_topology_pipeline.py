@@ -113,6 +113,59 @@ def test_cpp_twin_matches_python():
                                    C.byref(cnt), C.byref(live)) == 1
 
 
+def test_cpp_twin_agrees_on_random_layouts():
+    """The C++ planner and the Python one over 300 random layouts, valid and invalid: same verdict on validity,
+    same coordinates, same groups on every axis, same layer ranges, same 1F1B action list and peak live count."""
+    import random
+    rng = random.Random(7)
+    lib = nv.host()
+    axes = ["data", "pipeline", "context", "tensor", "expert"]
+    valid = invalid = 0
+    for _ in range(300):
+        dp, pp, cp, tp, ep = (rng.choice([1, 1, 2, 3, 4]) for _ in range(5))
+        sp = rng.choice([1, 1, 1, tp, 2])
+        mb = rng.choice([pp, pp, pp + 1, 2 * pp, max(pp - 1, 0), 0])
+        gpn = rng.choice([1, 2, 4, 8])
+        world = dp * pp * cp * tp * ep
+        if rng.random() < 0.1:
+            world += 1                                  # a world that the layout does not tile
+        dims = (C.c_int64 * 7)(dp, pp, cp, tp, ep, sp, mb)
+        rank = rng.randrange(0, max(world, 1))
+        out = (C.c_int64 * 5)()
+        rc = lib.cverl_topology_coords(dims, C.c_int64(world), C.c_int64(gpn), C.c_int64(rank), out)
+        try:
+            t = Topology(ParallelDims(dp, pp, cp, tp, ep, sp, mb), ClusterSpec(world_size=world, rank=rank, gpus_per_node=gpn))
+            py_ok = True
+        except ValueError:
+            py_ok = False
+        assert (rc == 0) == py_ok, (dp, pp, cp, tp, ep, sp, mb, gpn, world, rc, py_ok)
+        if not py_ok:
+            invalid += 1
+            continue
+        valid += 1
+        assert tuple(out) == t.coords_of(rank)
+        info = t.rank_info(rank)
+        for axis, name in enumerate(axes):
+            buf, cnt = (C.c_int64 * 256)(), C.c_int64()
+            assert lib.cverl_topology_group(dims, C.c_int64(world), C.c_int64(gpn), C.c_int64(rank), axis, buf,
+                                            C.c_int64(256), C.byref(cnt)) == 0
+            assert list(buf[:cnt.value]) == getattr(info, name + "_group")
+        layers = rng.randrange(pp, 70)
+        b, e = C.c_int64(), C.c_int64()
+        assert lib.cverl_pipeline_layer_range(C.c_int64(layers), C.c_int64(pp), C.c_int64(info.pipeline_rank),
+                                              C.byref(b), C.byref(e)) == 0
+        assert (b.value, e.value) == tuple(t.pipeline_layer_range(layers, info.pipeline_rank))
+        types, micro = (C.c_int32 * 128)(), (C.c_int64 * 128)()
+        cnt, live = C.c_int64(), C.c_int64()
+        assert lib.cverl_pipeline_1f1b(C.c_int64(info.pipeline_rank), C.c_int64(pp), C.c_int64(mb), types, micro,
+                                       C.c_int64(128), C.byref(cnt), C.byref(live)) == 0
+        py = pipeline_1f1b_schedule(info.pipeline_rank, pp, mb)
+        assert [(int(types[i]), int(micro[i])) for i in range(cnt.value)] == \
+            [(0 if a.type == PipelineActionType.FORWARD else 1, a.micro_batch) for a in py]
+        assert live.value == pipeline_schedule_max_live_activations(py, mb)
+    assert valid > 60 and invalid > 30, (valid, invalid)
+
+
 def test_parallel_plan_cli():
     from cverl_b200._build import LIB_DIR
     out = subprocess.run([str(LIB_DIR / "cverl_parallel_plan"), "--dp", "2", "--pp", "2", "--tp", "2", "--rank", "5",
