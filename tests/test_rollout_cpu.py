@@ -398,3 +398,36 @@ def test_bridge_module_name_of_the_reference():
     assert sig.parameters["learning_rate"].default == 3.0e-6 and sig.parameters["reward_method"].default == "flexible"
     assert list(inspect.signature(QwenPolicy.__init__).parameters)[1:] == ["model_dir", "tokenizer_path", "device",
                                                                           "param_dtype", "max_layers"]
+
+
+def test_transport_messages_round_trip_for_arbitrary_content():
+    """Property test of the wire format: any request / response - empty lists, non-ASCII and NUL-bearing text,
+    extreme integers, special floats - comes back equal, and every proper prefix of a message is refused."""
+    hyp = pytest.importorskip("hypothesis")
+    st = pytest.importorskip("hypothesis.strategies")
+    from cverl_b200.rollout.transport import RolloutRequest, RolloutResponse, RolloutSequence
+    i64 = st.integers(min_value=-2 ** 63, max_value=2 ** 63 - 1)
+    u31 = st.integers(min_value=0, max_value=2 ** 31 - 1)
+    text = st.text(max_size=20)
+    flt = st.floats(allow_nan=False, width=64)
+    requests = st.builds(RolloutRequest, prompts=st.lists(text, max_size=3),
+                         prompt_token_ids=st.lists(st.lists(i64, max_size=5), max_size=3), n=u31, max_tokens=u31,
+                         temperature=flt, top_p=flt, top_k=u31, stop=st.lists(text, max_size=2), flags=u31, seed=i64,
+                         model=text, extra_params=st.dictionaries(text, text, max_size=3), request_id=i64)
+    sequences = st.builds(RolloutSequence, prompt_index=u31, sample_index=u31, text=text,
+                          token_ids=st.lists(i64, max_size=6), logprobs=st.lists(flt, max_size=6), finish_reason=text)
+    responses = st.builds(RolloutResponse, sequences=st.lists(sequences, max_size=3),
+                          metrics=st.dictionaries(text, flt, max_size=3))
+
+    @hyp.settings(max_examples=150, deadline=None)
+    @hyp.given(requests, responses, st.data())
+    def check(req, resp, data):
+        raw = serialize_request(req)
+        assert deserialize_request(raw) == req
+        out = serialize_response(resp)
+        assert deserialize_response(out) == resp
+        if len(raw) > 1:
+            cut = data.draw(st.integers(min_value=0, max_value=len(raw) - 1))
+            with pytest.raises(Exception):
+                deserialize_request(raw[:cut])
+    check()
