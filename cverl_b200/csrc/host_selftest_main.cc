@@ -35,6 +35,7 @@ int64_t cverl_st_count(void* h);
 const char* cverl_st_name(void* h, int64_t i);
 int cverl_st_info(void* h, const char* name, int* dtype, int* ndim, int64_t* shape8, int64_t* nbytes);
 int cverl_st_read(void* h, const char* name, void* dst, int64_t nbytes);
+int cverl_st_read_range(void* h, const char* name, int64_t offset, int64_t nbytes, void* dst, int threads);
 int cverl_st_write(const char* path, int64_t n, const char* const* names, const int* dtypes, const int* ndims,
                    const int64_t* shapes, const void* const* data);
 int64_t cverl_byte_encode(const char* text, int64_t len, int add_bos, int add_eos, int64_t max_tokens, int64_t* out,
@@ -267,6 +268,33 @@ void safetensors_round_trip() {
     cverl_st_close(h);
   }
   EXPECT(cverl_st_open("/tmp/cverl_selftest_no_such_file", err, sizeof(err)) == nullptr && err[0] != 0);
+  std::remove(path.c_str());
+  // a 24 MiB tensor read in pieces by three threads, a byte range of it, and ranges that are refused; the name
+  // carries a control character (escaped on write) and the reader decodes it back
+  std::vector<int32_t> big(6u << 20);
+  for (size_t i = 0; i < big.size(); ++i) big[i] = static_cast<int32_t>(i * 2654435761u);
+  const char* big_names[1] = {"big\ttensor"};
+  const int big_dtypes[1] = {4}, big_ndims[1] = {1};
+  const int64_t big_shape[1] = {static_cast<int64_t>(big.size())};
+  const void* big_data[1] = {big.data()};
+  EXPECT(cverl_st_write(path.c_str(), 1, big_names, big_dtypes, big_ndims, big_shape, big_data) == 0);
+  h = cverl_st_open(path.c_str(), err, sizeof(err));
+  EXPECT(h != nullptr);
+  if (h) {
+    const int64_t total = static_cast<int64_t>(big.size() * sizeof(int32_t));
+    std::vector<int32_t> got(big.size());
+    EXPECT(std::string(cverl_st_name(h, 0)) == "big\ttensor");
+    EXPECT(cverl_st_read_range(h, "big\ttensor", 0, total, got.data(), 3) == 0 && got == big);
+    std::fill(got.begin(), got.end(), 0);
+    EXPECT(cverl_st_read(h, "big\ttensor", got.data(), total) == 0 && got == big);
+    const int64_t off = 4 * 1000003, len = 4 * 2000001;
+    EXPECT(cverl_st_read_range(h, "big\ttensor", off, len, got.data(), 2) == 0 &&
+           std::memcmp(got.data(), big.data() + off / 4, static_cast<size_t>(len)) == 0);
+    EXPECT(cverl_st_read_range(h, "big\ttensor", total - 8, 16, got.data(), 1) != 0);     // runs past the end
+    EXPECT(cverl_st_read_range(h, "big\ttensor", -4, 8, got.data(), 1) != 0);
+    EXPECT(cverl_st_read_range(h, "big\ttensor", 8, 0, got.data(), 4) == 0);              // empty range
+    cverl_st_close(h);
+  }
   std::remove(path.c_str());
 }
 
