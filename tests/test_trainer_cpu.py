@@ -48,17 +48,6 @@ def test_parallel_configs_train(nproc, flags):
         assert float(r["step_time_s"]) > 0
 
 
-def test_pipeline_matches_single_stage(tmp_path):
-    common = ["--micro-batches", "2", "--steps", "2", "--max-grad-norm", "0"]
-    a = _lines(_run(1, *common, port=29671))
-    b = _lines(_run(2, "--pp", "2", *common, port=29672))
-    for ra, rb in zip(a, b):
-        assert float(ra["loss_sum"]) == pytest.approx(float(rb["loss_sum"]), rel=1e-4, abs=1e-6)
-        # the tied embedding's gradient is held (summed) on both the first and the last stage, so the
-        # pipeline's global norm counts it twice: equal only up to that term
-        assert 0.99 * float(ra["global_grad_norm"]) <= float(rb["global_grad_norm"]) <= 1.5 * float(ra["global_grad_norm"])
-
-
 def test_checkpoint_resume_equality_and_formats(tmp_path):
     ck = tmp_path / "ck"
     csv_a, csv_b = tmp_path / "a.csv", tmp_path / "b.csv"
@@ -435,7 +424,6 @@ def _sft_flags(tmp_path, micro_batches=4):
 
 @pytest.mark.parametrize("nproc,flags,reports", [
     (2, ["--pp", "2"], 1),
-    (4, ["--pp", "4"], 1),
     (4, ["--pp", "2", "--cp", "2"], 2),
     (4, ["--pp", "2", "--tp", "2"], 2),
 ])
