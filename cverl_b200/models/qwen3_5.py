@@ -318,6 +318,29 @@ class Qwen35Model(torch.nn.Module):
             g.copy_(flat[off:off + g.numel()].view_as(g))
             off += g.numel()
 
+    @torch.no_grad()
+    def sync_bucket_grads(self, bucket: int) -> None:
+        """Model-parallel sums of ONE gradient bucket (bucketed gradients: there is no whole-model gradient buffer
+        to sum after the backward pass): the tensor-parallel shares of the bucket's ``tp_partial_grad_names``, then
+        the context-parallel sum of the whole bucket.  Called by the bucketed optimizer just before it reduces
+        the bucket over the data-parallel group."""
+        ctx = self.ctx
+        if ctx.tp_size == 1 and ctx.cp_size == 1:
+            return
+        import torch.distributed as dist
+        if ctx.tp_size > 1:
+            grads = [self.flat.params[n].main_grad for n in self.tp_partial_grad_names()
+                     if self._bucket_of_entry(n) == bucket]
+            if grads:
+                flat = torch.cat([g.reshape(-1) for g in grads])
+                dist.all_reduce(flat, group=ctx.tp_group)
+                off = 0
+                for g in grads:
+                    g.copy_(flat[off:off + g.numel()].view_as(g))
+                    off += g.numel()
+        if ctx.cp_size > 1:
+            dist.all_reduce(self.flat.bucket_grad(bucket), group=ctx.cp_group)
+
     def trainable_parameters(self) -> List[torch.nn.Parameter]:
         return list(self.flat.params.values())
 

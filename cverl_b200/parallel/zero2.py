@@ -194,6 +194,10 @@ class BucketedZero2Optimizer:
         self._active: List[int] = []                          # layer buckets written in this pass, not yet reduced
         self._tmp: Optional[torch.Tensor] = None
         self.reduced_buckets = 0                              # reductions launched from inside the backward pass
+        # ``pre_reduce(bucket)``: runs on the main stream once a bucket's gradients are complete and before they are
+        # reduced over the data-parallel group - the place for the model-parallel sums of that bucket (tensor-parallel
+        # shares of replicated parameters, the context-parallel sum)
+        self.pre_reduce = getattr(model, "sync_bucket_grads", None)
         model.backward_boundary = self._boundary
 
     # ---- layout ---------------------------------------------------------------------------------------------
@@ -240,6 +244,8 @@ class BucketedZero2Optimizer:
         if b in self._active:
             self._active.remove(b)
         self._fold_autograd(b)
+        if self.pre_reduce is not None:
+            self.pre_reduce(b)
         g = self.fp.bucket_grad(b)
         c = self.chunk[b]
         out = self._piece(self.grad_shard, b)
