@@ -325,9 +325,27 @@ class Qwen35Model(torch.nn.Module):
         the context-parallel sum of the whole bucket.  Called by the bucketed optimizer just before it reduces
         the bucket over the data-parallel group."""
         ctx = self.ctx
-        if ctx.tp_size == 1 and ctx.cp_size == 1:
+        if ctx.tp_size == 1 and ctx.cp_size == 1 and ctx.ep_size == 1:
             return
         import torch.distributed as dist
+
+        def all_reduce_list(grads, group, scale=1.0):
+            if not grads:
+                return
+            flat = torch.cat([g.reshape(-1) for g in grads])
+            dist.all_reduce(flat, group=group)
+            if scale != 1.0:
+                flat *= scale
+            off = 0
+            for g in grads:
+                g.copy_(flat[off:off + g.numel()].view_as(g))
+                off += g.numel()
+        if ctx.ep_size > 1:
+            # expert-parallel ranks train different micro-batches: everything but the expert weights is a
+            # data-parallel replica over that group and takes the mean of the group's gradients
+            all_reduce_list([p.main_grad for n, p in self.flat.params.items()
+                             if not n.startswith("__packed_moe") and self._bucket_of_entry(n) == bucket],
+                            ctx.ep_group, 1.0 / ctx.ep_size)
         if ctx.tp_size > 1:
             grads = [self.flat.params[n].main_grad for n in self.tp_partial_grad_names()
                      if self._bucket_of_entry(n) == bucket]

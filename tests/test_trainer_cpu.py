@@ -467,3 +467,14 @@ def test_zero_stage2_with_tensor_or_context_parallelism(tmp_path, flags):
     assert len(one) == len(many) == 3
     for ra, rb in zip(one, many):
         assert float(rb["loss_sum"]) == pytest.approx(2.0 * float(ra["loss_sum"]), rel=2e-5)
+
+
+def test_zero_stage2_with_expert_parallelism(tmp_path):
+    """dp 2 x ep 2 on the mixture-of-experts model with bucketed gradients: the non-expert parameters take the
+    mean over the expert-parallel group per bucket; one-rank losses over three updates."""
+    moe = ["--config", "tiny_moe"]
+    one = _lines(_run(1, *_sft_flags(tmp_path, 4), *moe, port=29781))
+    many = _lines(_run(4, "--dp", "2", "--ep", "2", "--zero-stage", "2", *_sft_flags(tmp_path, 1), *moe, port=29782))
+    assert len(one) == len(many) == 3
+    for ra, rb in zip(one, many):
+        assert float(rb["loss_sum"]) == pytest.approx(float(ra["loss_sum"]), rel=2e-5)
