@@ -325,7 +325,9 @@ class Qwen35Model(torch.nn.Module):
         the context-parallel sum of the whole bucket.  Called by the bucketed optimizer just before it reduces
         the bucket over the data-parallel group."""
         ctx = self.ctx
-        if ctx.tp_size == 1 and ctx.cp_size == 1 and ctx.ep_size == 1:
+        tied_pp = (bucket == 0 and ctx.pp_size > 1 and self.cfg.lm_head_name == self.cfg.embed_name
+                   and (self.first_stage or self.last_stage) and getattr(ctx, "embed_group", None) is not None)
+        if ctx.tp_size == 1 and ctx.cp_size == 1 and ctx.ep_size == 1 and not tied_pp:
             return
         import torch.distributed as dist
 
@@ -358,6 +360,10 @@ class Qwen35Model(torch.nn.Module):
                     off += g.numel()
         if ctx.cp_size > 1:
             dist.all_reduce(self.flat.bucket_grad(bucket), group=ctx.cp_group)
+        if tied_pp:
+            # the tied embedding lives on the first and the last pipeline stage: both copies take the sum of the two
+            # gradient halves (bucket 0 is reduced once per step, after the last backward pass)
+            dist.all_reduce(self.param(self.cfg.embed_name).main_grad, group=ctx.embed_group)
 
     def trainable_parameters(self) -> List[torch.nn.Parameter]:
         return list(self.flat.params.values())

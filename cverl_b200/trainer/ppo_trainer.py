@@ -521,16 +521,16 @@ def run(argv=None) -> int:
     first, last = info.pipeline_rank == 0, info.pipeline_rank == args.pp - 1
     fused_comm = None
     zero2 = args.zero_stage == 2
-    if zero2 and (opt_mode != "flat" or args.pp != 1 or args.skip_optimizer_step):
-        raise SystemExit("--zero-stage 2 needs the flat sharded optimizer, --pp 1 and an optimizer step")
+    if zero2 and (opt_mode != "flat" or args.skip_optimizer_step):
+        raise SystemExit("--zero-stage 2 needs the flat sharded optimizer and an optimizer step")
     if zero2 and args.tp > 1:
         # the sequence-parallel and mirror-store layer paths do not carry the bucket boundaries
         if args.tp_comm != "nccl" and rank == 0:
             print("note: --zero-stage 2 with --tp > 1 uses --tp-comm nccl", flush=True)
         args.tp_comm = "nccl"
-    if zero2 and (args.tp > 1 or args.cp > 1 or args.ep > 1) and args.zero_comm == "symm":
+    if zero2 and (args.tp > 1 or args.cp > 1 or args.ep > 1 or args.pp > 1) and args.zero_comm == "symm":
         if rank == 0:
-            print("note: --zero-stage 2 with --tp / --cp / --ep > 1 uses --zero-comm nccl", flush=True)
+            print("note: --zero-stage 2 with model parallelism uses --zero-comm nccl", flush=True)
         args.zero_comm = "nccl"
     if args.zero_comm == "symm" and args.dp > 1 and opt_mode == "flat":
         if not use_cuda or dtype != torch.bfloat16:
@@ -706,7 +706,7 @@ def run(argv=None) -> int:
             model.sync_replicated_grads()
             if args.cp > 1:
                 dist.all_reduce(model.flat.main_grad, group=ctx.cp_group)
-        if args.pp > 1 and cfg.lm_head_name == cfg.embed_name and (first or last):
+        if args.pp > 1 and cfg.lm_head_name == cfg.embed_name and (first or last) and not zero2:
             # the tied embedding lives on the first and the last stage: sum its two gradient halves so
             # that both copies take the same update (the reference leaves them unsynchronised)
             dist.all_reduce(model.param(cfg.embed_name).main_grad, group=ctx.embed_group)

@@ -364,7 +364,7 @@ def test_zero_stage2_matches_stage1_and_resumes(tmp_path):
     assert [r["step"] for r in resumed] == ["2", "3"]
     for ra, rb in zip(z2[2:], resumed):
         assert float(ra["loss_sum"]) == pytest.approx(float(rb["loss_sum"]), rel=1e-5, abs=1e-7)
-    bad = _run(2, "--pp", "2", "--micro-batches", "2", "--zero-stage", "2", port=29715, check=False)
+    bad = _run(2, "--dp", "2", "--dp-flat-shard-optimizer", "false", "--zero-stage", "2", port=29715, check=False)
     assert bad.returncode != 0 and "--zero-stage 2 needs" in (bad.stdout + bad.stderr)
 
 
@@ -457,16 +457,18 @@ def test_moe_layouts_reproduce_the_one_rank_losses(tmp_path, nproc, flags, mb, r
         assert float(rb["loss_sum"]) == pytest.approx(reports * float(ra["loss_sum"]), rel=2e-5)
 
 
-@pytest.mark.parametrize("flags", [["--dp", "2", "--tp", "2"], ["--dp", "2", "--cp", "2"]])
+@pytest.mark.parametrize("flags", [["--dp", "2", "--tp", "2"], ["--dp", "2", "--cp", "2"], ["--dp", "2", "--pp", "2"]])
 def test_zero_stage2_with_tensor_or_context_parallelism(tmp_path, flags):
-    """Bucketed gradients under model parallelism: the tensor-parallel shares of replicated parameters and the
-    context-parallel sum are formed bucket by bucket, just before each bucket's data-parallel reduction - the
-    supervised losses over three updates are the one-rank losses."""
+    """Bucketed gradients under model parallelism: the tensor-parallel shares of replicated parameters, the
+    context-parallel sum and the two halves of a tied embedding's gradient under a pipeline are formed bucket by
+    bucket, just before each bucket's data-parallel reduction - the supervised losses over three updates are the
+    one-rank losses."""
     one = _lines(_run(1, *_sft_flags(tmp_path, 4), port=29771))
     many = _lines(_run(4, *flags, "--zero-stage", "2", *_sft_flags(tmp_path, 2), port=29772))
     assert len(one) == len(many) == 3
+    reports = 1.0 if "--pp" in flags else 2.0            # one last-stage rank per replica reports under a pipeline
     for ra, rb in zip(one, many):
-        assert float(rb["loss_sum"]) == pytest.approx(2.0 * float(ra["loss_sum"]), rel=2e-5)
+        assert float(rb["loss_sum"]) == pytest.approx(reports * float(ra["loss_sum"]), rel=2e-5)
 
 
 def test_zero_stage2_with_expert_parallelism(tmp_path):
