@@ -397,21 +397,15 @@ def test_activation_checkpointing_changes_no_number(nproc, flags, port):
         assert float(ra["grad_norm_sum"]) == pytest.approx(float(rb["grad_norm_sum"]), rel=1e-5)
 
 
-def test_context_parallel_with_tensor_parallel_trains_like_one_rank(tmp_path):
-    """cp 2 x tp 2 (a pair the reference refuses): the SFT loss of every step - after real updates - is the
-    single-rank loss, reported once per rank."""
-    data = tmp_path / "sft.jsonl"
-    data.write_text("\n".join(json.dumps({"prompt": f"Question number {i}: what is {i}+{i}? ",
-                                          "answer": f"The answer is {2 * i}."}) for i in range(8)))
-    common = ["--steps", "3", "--lr", "1e-2", "--max-grad-norm", "0", "--mode", "sft", "--sft-jsonl", str(data),
-              "--prompt-len", "16", "--response-len", "16", "--micro-batches", "2"]
-    one = _lines(_run(1, *common, port=29741))
-    four = _lines(_run(4, "--cp", "2", "--tp", "2", *common, port=29742))
-    assert len(one) == len(four) == 3
-    for ra, rb in zip(one, four):
-        assert float(rb["loss_sum"]) == pytest.approx(4.0 * float(ra["loss_sum"]), rel=2e-5)
-        assert rb["all_ranks_have_grad"] == "true" and rb["cp"] == "2" and rb["tp"] == "2"
-    assert float(one[2]["loss_sum"]) < 0.8 * float(one[0]["loss_sum"])      # the updates were real
+_ONE_RANK = {}
+
+
+def _one_rank_sft(tmp_path, moe=False):
+    """The one-rank supervised run every layout is compared with (4 micro-batches); run once per model kind."""
+    if moe not in _ONE_RANK:
+        extra = ["--config", "tiny_moe"] if moe else []
+        _ONE_RANK[moe] = _lines(_run(1, *_sft_flags(tmp_path, 4), *extra, port=29791 + int(moe)))
+    return _ONE_RANK[moe]
 
 
 def _sft_flags(tmp_path, micro_batches=4):
@@ -426,14 +420,15 @@ def _sft_flags(tmp_path, micro_batches=4):
     (2, ["--pp", "2"], 1),
     (4, ["--pp", "2", "--cp", "2"], 2),
     (4, ["--pp", "2", "--tp", "2"], 2),
+    (4, ["--cp", "2", "--tp", "2"], 4),
 ])
-def test_pipeline_layouts_reproduce_the_one_stage_losses(tmp_path, nproc, flags, reports):
+def test_dense_layouts_reproduce_the_one_rank_losses(tmp_path, nproc, flags, reports):
     """Supervised losses over three real updates: a pipeline (alone, with context parallelism, with tensor
-    parallelism) gives the one-stage loss at every step.  Every stage draws the initial values of its tensors
-    from generators seeded by the tensor names, so the runs start from the same weights."""
-    common = _sft_flags(tmp_path)
-    one = _lines(_run(1, *common, port=29751))
-    many = _lines(_run(nproc, *flags, *common, port=29752))
+    parallelism) and context x tensor parallelism (a pair the reference refuses) give the one-rank loss at every
+    step, reported once per last-stage rank.  Every stage draws the initial values of its tensors from generators
+    seeded by the tensor names, so the runs start from the same weights."""
+    one = _one_rank_sft(tmp_path)
+    many = _lines(_run(nproc, *flags, *_sft_flags(tmp_path), port=29752))
     assert len(one) == len(many) == 3
     for ra, rb in zip(one, many):
         assert float(rb["loss_sum"]) == pytest.approx(reports * float(ra["loss_sum"]), rel=2e-5)
@@ -450,7 +445,7 @@ def test_moe_layouts_reproduce_the_one_rank_losses(tmp_path, nproc, flags, mb, r
     over the split FFN dimension, so the router's gradient has to be summed over the tensor-parallel group - with
     that sum missing the losses drift apart from the second step on."""
     moe = ["--config", "tiny_moe"]
-    one = _lines(_run(1, *_sft_flags(tmp_path, 4), *moe, port=29761))
+    one = _one_rank_sft(tmp_path, moe=True)
     many = _lines(_run(nproc, *flags, *_sft_flags(tmp_path, mb), *moe, port=29762))
     assert len(one) == len(many) == 3
     for ra, rb in zip(one, many):
@@ -463,7 +458,7 @@ def test_zero_stage2_with_tensor_or_context_parallelism(tmp_path, flags):
     context-parallel sum and the two halves of a tied embedding's gradient under a pipeline are formed bucket by
     bucket, just before each bucket's data-parallel reduction - the supervised losses over three updates are the
     one-rank losses."""
-    one = _lines(_run(1, *_sft_flags(tmp_path, 4), port=29771))
+    one = _one_rank_sft(tmp_path)
     many = _lines(_run(4, *flags, "--zero-stage", "2", *_sft_flags(tmp_path, 2), port=29772))
     assert len(one) == len(many) == 3
     reports = 1.0 if "--pp" in flags else 2.0            # one last-stage rank per replica reports under a pipeline
@@ -475,7 +470,7 @@ def test_zero_stage2_with_expert_parallelism(tmp_path):
     """dp 2 x ep 2 on the mixture-of-experts model with bucketed gradients: the non-expert parameters take the
     mean over the expert-parallel group per bucket; one-rank losses over three updates."""
     moe = ["--config", "tiny_moe"]
-    one = _lines(_run(1, *_sft_flags(tmp_path, 4), *moe, port=29781))
+    one = _one_rank_sft(tmp_path, moe=True)
     many = _lines(_run(4, "--dp", "2", "--ep", "2", "--zero-stage", "2", *_sft_flags(tmp_path, 1), *moe, port=29782))
     assert len(one) == len(many) == 3
     for ra, rb in zip(one, many):
