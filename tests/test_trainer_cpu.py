@@ -113,6 +113,37 @@ def test_reads_an_archive_written_by_libtorch():
         assert sorted(n for n, _ in mod.named_parameters()) == sorted(arch) and not list(mod.named_buffers())
 
 
+def test_libtorch_reads_an_archive_written_here(tmp_path):
+    """The other direction: ``torch::serialize::InputArchive`` - the reader the reference's trainer resumes with -
+    loads a rank archive written by ``save_archive`` and finds every key with its dtype and values.  The small
+    reader (``tests/fixtures/read_archive_with_libtorch.cc``) is compiled against the installed LibTorch."""
+    import shutil
+    from torch.utils import cpp_extension
+    from cverl_b200.utils.checkpoint import save_archive
+    if shutil.which("g++") is None:
+        pytest.skip("no C++ compiler")
+    tensors = {"flat_param_shard": torch.arange(8).float().mul(0.25).bfloat16(), "flat_exp_avg": torch.arange(8).float() * 0.5,
+               "flat_exp_avg_sq": torch.arange(8).float() * 2.0, "optim_step": torch.tensor(3, dtype=torch.int64),
+               "param_0": torch.arange(6).float().view(2, 3)}
+    save_archive(tmp_path / "rank_0.pt", tensors)
+    lib = Path(torch.__file__).parent / "lib"
+    exe = tmp_path / "read_archive"
+    cmd = ["g++", "-std=c++17", "-O1", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           str(Path(__file__).parent / "fixtures" / "read_archive_with_libtorch.cc"),
+           *[f for i in cpp_extension.include_paths() for f in ("-I", i)], "-L", str(lib), "-ltorch", "-ltorch_cpu",
+           "-lc10", f"-Wl,-rpath,{lib}", "-o", str(exe)]
+    built = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    if built.returncode != 0:
+        pytest.skip("LibTorch headers / libraries are not usable from g++ here: " + built.stderr[-300:])
+    p = subprocess.run([str(exe), str(tmp_path / "rank_0.pt"), *tensors], capture_output=True, text=True, timeout=120)
+    assert p.returncode == 0, p.stderr[-1000:]
+    rows = {ln.split()[0]: ln.split()[1:] for ln in p.stdout.strip().splitlines()}
+    assert rows["flat_param_shard"][0] == "c10::BFloat16" and rows["flat_param_shard"][-2:] == ["8", "7"]
+    assert rows["flat_exp_avg"][-2:] == ["8", "14"] and rows["flat_exp_avg_sq"][-2:] == ["8", "56"]
+    assert rows["optim_step"][-2:] == ["1", "3"] and "long" in " ".join(rows["optim_step"])
+    assert rows["param_0"][-2:] == ["6", "15"]
+
+
 def test_resume_refuses_damaged_checkpoints(tmp_path):
     """Host-side fault injection on the checkpoint: an incomplete manifest, a manifest whose step disagrees with
     the archive, and a missing rank file must each stop the resume with an error instead of training on."""
