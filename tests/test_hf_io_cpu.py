@@ -104,3 +104,20 @@ def test_tensor_names_with_escapes_and_unicode(tmp_path):
     loader = HfModelLoader(ascii_path).load_metadata()
     assert sorted(loader.names()) == sorted(names)
     assert all(torch.equal(loader.load_tensor(n), tensors[n]) for n in names)
+
+
+def test_reference_loader_reads_directories_written_here():
+    """``baseline/ref_loader_check.py``: the reference's own ``HfModelLoader`` (its compiled object, linked into a small
+    driver) reads a dense and a mixture-of-experts model directory written by this package and finds the same
+    tensors, element counts and values.  Skipped where the reference objects have not been built."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    p = subprocess.run([sys.executable, str(root / "baseline" / "ref_loader_check.py")], capture_output=True, text=True,
+                       timeout=900, cwd=root)
+    if p.returncode == 3:
+        pytest.skip(p.stdout.strip()[-300:])
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-1500:]
+    rows = [json.loads(ln) for ln in p.stdout.strip().splitlines() if ln.startswith("{")]
+    assert [r["model"] for r in rows] == ["qwen3_5", "qwen3_moe"] and all(r["agree"] for r in rows)
