@@ -165,3 +165,24 @@ def test_demo_launcher_scripts(tmp_path):
                        env=dict(env, DEPTH="14", STEPS="2", WARMUP="1", BATCH_SIZE="8", DTYPE="float32"),
                        capture_output=True, text=True, timeout=300)
     assert p.returncode == 0 and "images_per_s" in p.stdout, p.stdout[-800:] + p.stderr[-1500:]
+
+
+def test_forward_matches_the_reference_itself():
+    """``baseline/ref_forward_check.py``: the reference's own forward tool (its source as it is, linked against the
+    reference library) and this package's model agree on hidden states and logits of a Qwen3.5 hybrid and a
+    Qwen3-MoE model directory written here (fp32, CPU).  Skipped where the reference library has not been built."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    p = subprocess.run([sys.executable, str(root / "baseline" / "ref_forward_check.py")], capture_output=True, text=True,
+                       timeout=1200, cwd=root)
+    if p.returncode == 3:
+        import pytest
+        pytest.skip(p.stdout.strip()[-300:])
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-1500:]
+    rows = [json.loads(ln) for ln in p.stdout.strip().splitlines() if ln.startswith("{")]
+    assert len(rows) == 4 and all(r["agree"] and r["argmax_equal"] and r["max_abs"] < 2e-5 for r in rows)
+    assert {(r["model"], r["output"]) for r in rows} == {("qwen3_5", "hidden"), ("qwen3_5", "logits"),
+                                                         ("qwen3_moe", "hidden"), ("qwen3_moe", "logits")}
