@@ -186,3 +186,24 @@ def test_forward_matches_the_reference_itself():
     assert len(rows) == 4 and all(r["agree"] and r["argmax_equal"] and r["max_abs"] < 2e-5 for r in rows)
     assert {(r["model"], r["output"]) for r in rows} == {("qwen3_5", "hidden"), ("qwen3_5", "logits"),
                                                          ("qwen3_moe", "hidden"), ("qwen3_moe", "logits")}
+
+
+def test_gradients_match_the_reference_itself():
+    """``baseline/ref_backward_check.py``: the reference's policy class (linked from the reference library) and this
+    package's model back-propagate the same weighted log-likelihood on model directories written here; the loss and
+    every parameter gradient agree (Qwen3.5 hybrid: 55 tensors; Qwen3-MoE: every expert that received a token)."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    p = subprocess.run([sys.executable, str(root / "baseline" / "ref_backward_check.py")], capture_output=True, text=True,
+                       timeout=1200, cwd=root)
+    if p.returncode == 3:
+        import pytest
+        pytest.skip(p.stdout.strip()[-300:])
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-1500:]
+    rows = [json.loads(ln) for ln in p.stdout.strip().splitlines() if ln.startswith("{")]
+    assert [r["model"] for r in rows] == ["qwen3_5", "qwen3_moe"] and all(r["agree"] for r in rows)
+    assert rows[0]["gradients_compared"] == 55 and rows[1]["gradients_compared"] > 60
+    assert all(r["worst_relative_difference"] < 1e-3 for r in rows)
