@@ -207,3 +207,21 @@ def test_gradients_match_the_reference_itself():
     assert [r["model"] for r in rows] == ["qwen3_5", "qwen3_moe"] and all(r["agree"] for r in rows)
     assert rows[0]["gradients_compared"] == 55 and rows[1]["gradients_compared"] > 60
     assert all(r["worst_relative_difference"] < 1e-3 for r in rows)
+
+
+def test_optimizers_match_the_reference_itself():
+    """``baseline/ref_optimizer_check.py``: five AdamW steps of the reference's ``FlatAdamW`` and ``Fp32MasterAdamW``
+    (with and without fp32 master weights) against this package's: parameters and moments agree to the last bits."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    p = subprocess.run([sys.executable, str(root / "baseline" / "ref_optimizer_check.py")], capture_output=True, text=True,
+                       timeout=1200, cwd=root)
+    if p.returncode == 3:
+        import pytest
+        pytest.skip(p.stdout.strip()[-300:])
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-1500:]
+    row = json.loads([ln for ln in p.stdout.strip().splitlines() if ln.startswith("{")][-1])
+    assert row["agree"] and row["tensors_compared"] == 12 and row["largest_difference"] <= 2e-6
