@@ -27,6 +27,7 @@
 #include <string>
 #include <string_view>
 #include <thread>
+#include <tuple>
 #include <unordered_map>
 #include <vector>
 
@@ -221,6 +222,8 @@ struct Tokenizer {
   std::vector<std::string> id_to_token;
   std::unordered_map<std::string, int64_t> merge_rank;  // "a b" -> rank
   std::vector<std::pair<std::string, int64_t>> added;   // sorted longest first
+  std::vector<std::tuple<std::string, int64_t, bool>> added_in_file_order;   // (content, id, special)
+  std::string unk_token_name;
   std::unordered_map<int64_t, bool> special_ids;
   std::string byte_to_uni[256];
   std::unordered_map<std::string, int> uni_to_byte;
@@ -322,9 +325,13 @@ struct Tokenizer {
         vocab[content->str] = tid;
         added.emplace_back(content->str, tid);
         const JValue* sp = t.get("special");
-        special_ids[tid] = sp && sp->b;
+        const bool special = sp ? sp->b : true;        // absent means special (reference: hf_bpe_tokenizer.cc:317)
+        special_ids[tid] = special;
+        added_in_file_order.emplace_back(content->str, tid, special);
       }
     }
+    if (const JValue* unk = model->get("unk_token"))
+      if (unk->kind == JValue::Str) unk_token_name = unk->str;
     std::sort(added.begin(), added.end(), [](const auto& a, const auto& b) {
       return a.first.size() != b.first.size() ? a.first.size() > b.first.size() : a.first < b.first;
     });
@@ -400,12 +407,34 @@ struct Tokenizer {
     }
     return -1;
   }
+  // The reference's rules (src/text/hf_bpe_tokenizer.cc:310-356): walk the added tokens in file order and take, for
+  // each role, the FIRST special token with one of the usual spellings; model.unk_token overrides unk; a missing pad
+  // falls back to a token spelled <|pad|> and then to eos.  (For the Qwen vocabularies this makes <|endoftext|>
+  // both eos and pad and <|im_start|> bos.)
   void discover_special() {
-    eos_id = find_token({"<|im_end|>", "<|endoftext|>", "</s>", "<eos>"});
-    pad_id = find_token({"<|endoftext|>", "<pad>", "<|pad|>", "[PAD]"});
-    if (pad_id < 0) pad_id = eos_id;
-    bos_id = find_token({"<|im_start|>", "<s>", "<bos>", "<|begin_of_text|>"});
-    unk_id = find_token({"<unk>", "<|unk|>", "[UNK]"});
+    auto is_one_of = [](const std::string& s, std::initializer_list<const char*> names) {
+      for (const char* n : names)
+        if (s == n) return true;
+      return false;
+    };
+    pad_id = bos_id = eos_id = unk_id = -1;
+    for (const auto& t : added_in_file_order) {
+      const std::string& c = std::get<0>(t);
+      const int64_t id = std::get<1>(t);
+      if (!std::get<2>(t)) continue;
+      if (pad_id < 0 && is_one_of(c, {"<|pad|>", "<pad>", "[PAD]"})) pad_id = id;
+      if (eos_id < 0 && is_one_of(c, {"<|endoftext|>", "</s>", "<|im_end|>", "<eos>", "[EOS]"})) eos_id = id;
+      if (bos_id < 0 && is_one_of(c, {"<s>", "<bos>", "[BOS]", "<|im_start|>"})) bos_id = id;
+      if (unk_id < 0 && is_one_of(c, {"<unk>", "[UNK]"})) unk_id = id;
+    }
+    if (!unk_token_name.empty()) {
+      auto it = vocab.find(unk_token_name);
+      if (it != vocab.end()) unk_id = it->second;
+    }
+    if (pad_id < 0) {
+      auto it = vocab.find("<|pad|>");
+      pad_id = it != vocab.end() ? it->second : eos_id;
+    }
   }
 
   // --- pre-tokenisation ------------------------------------------------------

@@ -59,7 +59,8 @@ int cverl_build_gsm8k_rollout_batch(int tokenizer_kind, void* tokenizer, int64_t
                                     const int64_t* sample_prompt, const char* const* responses,
                                     const int64_t* response_lens, const int64_t* given_ids,
                                     const int64_t* given_offsets, const uint8_t* has_given, int64_t n_samples,
-                                    int64_t max_prompt_len, int64_t max_response_len, int flexible, int64_t clip_chars,
+                                    int64_t max_prompt_len, int64_t max_response_len, int add_bos, int add_eos,
+                                    int64_t bos_id, int64_t eos_id, int flexible, int64_t clip_chars,
                                     double correct_score, double format_score, double no_answer_score, int threads,
                                     int64_t* prompt_ids, int64_t* response_ids, float* response_mask,
                                     float* token_rewards, float* rewards, int64_t* group_ids);
@@ -344,21 +345,28 @@ void rollout_batch() {
   std::vector<int64_t> pid(B * P), rid(B * R), gid(B);
   std::vector<float> mask(B * R), trew(B * R), rew(B);
   EXPECT(cverl_build_gsm8k_rollout_batch(0, nullptr, 0, prompts, plen, answers, 3, sp, responses, rlen, given, goff, has,
-                                         B, P, R, 0, 300, 1.0, 0.0, 0.0, 4, pid.data(), rid.data(), mask.data(),
-                                         trew.data(), rew.data(), gid.data()) == 0);
+                                         B, P, R, 0, 1, 1, 2, 0, 300, 1.0, 0.0, 0.0, 4, pid.data(), rid.data(),
+                                         mask.data(), trew.data(), rew.data(), gid.data()) == 0);
   EXPECT(rew[0] == 1.0f && rew[1] == 0.0f && rew[2] == 0.0f && rew[3] == 1.0f && rew[4] == 1.0f);
-  EXPECT(pid[0] == 4 + ' ' && pid[7] == 4 + '?');                       // tail of the 12-byte prompt
+  EXPECT(pid[0] == 4 + 'W' && pid[7] == 4 + ' ');                       // first 8 bytes of the 12-byte prompt
   EXPECT(pid[2 * P] == 0 && pid[2 * P + 6] == 4 + 'h');                 // left padded
+  EXPECT(rid[12] == 2 && mask[12] == 1.0f && mask[13] == 0.0f && trew[12] == 1.0f);   // 12 bytes, then the EOS
+  EXPECT(rid[2 * R] == 2 && mask[2 * R] == 1.0f && mask[2 * R + 1] == 0.0f);          // empty text: the EOS alone
   EXPECT(rid[3 * R] == 9 && rid[3 * R + 2] == 7 && mask[3 * R + 2] == 1.0f && mask[3 * R + 3] == 0.0f);
   EXPECT(trew[3 * R + 2] == 1.0f && trew[4 * R + R - 1] == 1.0f && mask[4 * R + R - 1] == 1.0f);
-  EXPECT(mask[2 * R] == 0.0f && gid[2] == 2 && gid[4] == 0);
+  EXPECT(rid[4 * R + R - 1] == 4 + 'e');                                // cut at 16 bytes: no room for an EOS
+  EXPECT(gid[2] == 2 && gid[4] == 0);
+  EXPECT(cverl_build_gsm8k_rollout_batch(0, nullptr, 0, prompts, plen, answers, 3, sp, responses, rlen, given, goff, has,
+                                         B, P, R, 1, 0, 1, 2, 0, 300, 1.0, 0.0, 0.0, 2, pid.data(), rid.data(),
+                                         mask.data(), trew.data(), rew.data(), gid.data()) == 0);
+  EXPECT(pid[0] == 1 && pid[1] == 4 + 'W' && mask[2 * R] == 0.0f && mask[12] == 0.0f);   // BOS in front, no EOS
   sp[1] = 3;                                                            // prompt index out of range
   EXPECT(cverl_build_gsm8k_rollout_batch(0, nullptr, 0, prompts, plen, answers, 3, sp, responses, rlen, nullptr, nullptr,
-                                         nullptr, B, P, R, 0, 300, 1.0, 0.0, 0.0, 4, pid.data(), rid.data(), mask.data(),
-                                         trew.data(), rew.data(), gid.data()) == 1);
+                                         nullptr, B, P, R, 0, 1, 1, 2, 0, 300, 1.0, 0.0, 0.0, 4, pid.data(), rid.data(),
+                                         mask.data(), trew.data(), rew.data(), gid.data()) == 1);
   EXPECT(cverl_build_gsm8k_rollout_batch(1, nullptr, 0, prompts, plen, answers, 3, sp, responses, rlen, nullptr, nullptr,
-                                         nullptr, B, P, R, 0, 300, 1.0, 0.0, 0.0, 4, pid.data(), rid.data(), mask.data(),
-                                         trew.data(), rew.data(), gid.data()) == 1);   // BPE without a handle
+                                         nullptr, B, P, R, 0, 1, 1, 2, 0, 300, 1.0, 0.0, 0.0, 4, pid.data(), rid.data(),
+                                         mask.data(), trew.data(), rew.data(), gid.data()) == 1);   // BPE without a handle
 }
 
 // argv[1] (optional): a Hugging Face tokenizer.json; encode / decode round trips from two threads sharing one handle

@@ -1,9 +1,12 @@
 // Builds the tensors of a GRPO step from prompts, sampled responses and gold answers, on several threads.
 //
-// Same rules as the reference's builder (src/rollout/rollout_batch.cc:12-136): a prompt is tokenised once per prompt
-// index, LEFT-padded and truncated keeping its tail; a response is RIGHT-padded and truncated keeping its head;
-// response_mask marks real response tokens; group_ids is the prompt index; the scalar GSM8K rule reward sits on
-// the last real response token.  The reference walks the samples in one thread; here the distinct prompts and then
+// Same rules as the reference's builder (src/rollout/rollout_batch.cc:42-136): a prompt is tokenised once per prompt
+// index with the limit max_prompt_len (the FIRST max_prompt_len tokens of an over-long prompt are kept, an
+// optional BOS in front) and LEFT-padded; a response that comes as text is tokenised with the limit
+// max_response_len and gets an EOS where the limit leaves room (add_eos, the reference's default), a response that
+// comes with token ids keeps its first max_response_len ids; responses are RIGHT-padded; response_mask marks
+// real response tokens; group_ids is the prompt index; the scalar GSM8K rule reward sits on the last real
+// response token.  The reference walks the samples in one thread; here the distinct prompts and then
 // the samples are spread over worker threads (tokenisation and the reward rule are the whole cost), and every
 // worker writes only its own rows of the caller's buffers.
 #include <algorithm>
@@ -25,12 +28,18 @@ namespace {
 
 enum { TOK_BYTE = 0, TOK_BPE = 1 };
 
-std::vector<int64_t> encode(int kind, void* handle, const char* text, int64_t len) {
+// text -> ids with the reference's option rules: BOS in front when asked for (and the vocabulary has one), EOS at
+// the end only if the limit leaves room, at most max_tokens ids (the head is kept)
+std::vector<int64_t> encode(int kind, void* handle, const char* text, int64_t len, bool add_bos, bool add_eos,
+                            int64_t bos_id, int64_t eos_id, int64_t max_tokens) {
   std::vector<int64_t> ids(static_cast<size_t>(len) + 8);   // a token covers at least one byte
   const int64_t cap = static_cast<int64_t>(ids.size());
   const int64_t n = kind == TOK_BPE ? cverl_bpe_encode(handle, text, len, ids.data(), cap)
                                     : cverl_byte_encode(text, len, 0, 0, 0, ids.data(), cap);
   ids.resize(static_cast<size_t>(std::max<int64_t>(0, std::min(n, cap))));
+  if (add_bos && bos_id >= 0) ids.insert(ids.begin(), bos_id);
+  if (max_tokens > 0 && static_cast<int64_t>(ids.size()) > max_tokens) ids.resize(static_cast<size_t>(max_tokens));
+  if (add_eos && eos_id >= 0 && (max_tokens <= 0 || static_cast<int64_t>(ids.size()) < max_tokens)) ids.push_back(eos_id);
   return ids;
 }
 
@@ -65,7 +74,8 @@ int cverl_build_gsm8k_rollout_batch(int tokenizer_kind, void* tokenizer, int64_t
                                     int64_t n_prompts, const int64_t* sample_prompt, const char* const* responses,
                                     const int64_t* response_lens, const int64_t* given_ids,
                                     const int64_t* given_offsets, const uint8_t* has_given, int64_t n_samples,
-                                    int64_t max_prompt_len, int64_t max_response_len, int flexible, int64_t clip_chars,
+                                    int64_t max_prompt_len, int64_t max_response_len, int add_bos, int add_eos,
+                                    int64_t bos_id, int64_t eos_id, int flexible, int64_t clip_chars,
                                     double correct_score, double format_score, double no_answer_score, int threads,
                                     int64_t* prompt_ids, int64_t* response_ids, float* response_mask,
                                     float* token_rewards, float* rewards, int64_t* group_ids) {
@@ -87,7 +97,8 @@ int cverl_build_gsm8k_rollout_batch(int tokenizer_kind, void* tokenizer, int64_t
   std::vector<std::vector<int64_t>> prompt_tokens(static_cast<size_t>(n_prompts));
   parallel_for(static_cast<int64_t>(distinct.size()), threads, [&](int64_t k) {
     const int64_t p = distinct[static_cast<size_t>(k)];
-    prompt_tokens[static_cast<size_t>(p)] = encode(tokenizer_kind, tokenizer, prompts[p], prompt_lens[p]);
+    prompt_tokens[static_cast<size_t>(p)] = encode(tokenizer_kind, tokenizer, prompts[p], prompt_lens[p], add_bos != 0,
+                                                   false, bos_id, eos_id, max_prompt_len);
   });
   const int64_t P = max_prompt_len, R = max_response_len;
   parallel_for(n_samples, threads, [&](int64_t b) {
@@ -101,14 +112,15 @@ int cverl_build_gsm8k_rollout_batch(int tokenizer_kind, void* tokenizer, int64_t
     std::fill(mrow, mrow + R, 0.0f);
     std::fill(trow, trow + R, 0.0f);
     const auto& pt = prompt_tokens[static_cast<size_t>(p)];
-    const int64_t keep = std::min<int64_t>(P, static_cast<int64_t>(pt.size()));          // the tail of the prompt
+    const int64_t keep = std::min<int64_t>(P, static_cast<int64_t>(pt.size()));          // already cut to P ids
     std::copy(pt.end() - keep, pt.end(), prow + (P - keep));
     int64_t n = 0;
     if (given && has_given[b]) {
       n = std::min<int64_t>(R, given_offsets[b + 1] - given_offsets[b]);
       std::copy(given_ids + given_offsets[b], given_ids + given_offsets[b] + n, rrow);
     } else {
-      const auto rt = encode(tokenizer_kind, tokenizer, responses[b], response_lens[b]);
+      const auto rt = encode(tokenizer_kind, tokenizer, responses[b], response_lens[b], false, add_eos != 0, bos_id,
+                             eos_id, R);
       n = std::min<int64_t>(R, static_cast<int64_t>(rt.size()));                         // the head of the response
       std::copy(rt.begin(), rt.begin() + n, rrow);
     }

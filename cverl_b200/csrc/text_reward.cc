@@ -216,12 +216,9 @@ int64_t cverl_byte_encode(const char* text, int64_t len, int add_bos, int add_eo
   };
   if (add_bos) push(CVERL_BYTE_BOS);
   for (int64_t i = 0; i < len; ++i) push(4 + static_cast<unsigned char>(text[i]));
-  if (add_eos) {
-    if (max_tokens > 0 && n >= max_tokens) {
-      n = max_tokens - 1;  // keep room for the terminator
-    }
-    push(CVERL_BYTE_EOS);
-  }
+  // the terminator is appended only where the limit leaves room for it: a text cut off by max_tokens ends on
+  // its last kept byte (reference: src/text/byte_tokenizer.cc:20-28)
+  if (add_eos) push(CVERL_BYTE_EOS);
   return n;
 }
 

@@ -1,9 +1,13 @@
 """Builds the tensor batch of a GRPO step from prompts, sampled responses and gold answers.
 
-Prompts are tokenised once per prompt index, LEFT-padded and truncated keeping the tail;
-responses are RIGHT-padded; ``response_mask`` marks real response tokens; ``group_ids`` is
-the prompt index; the scalar GSM8K rule reward sits on the last real response token.
-Reference: src/rollout/rollout_batch.cc:12-136.
+Prompts are tokenised once per prompt index with the limit ``max_prompt_len`` (an over-long prompt keeps its
+FIRST ``max_prompt_len`` tokens) and LEFT-padded; a response that comes as text is tokenised with the limit
+``max_response_len`` and gets an EOS where the limit leaves room (``add_eos``, on by default as in the reference),
+a response that comes with token ids keeps its first ``max_response_len`` ids (an empty id list counts as "no
+ids": the text is tokenised); responses are RIGHT-padded; ``response_mask`` marks real response tokens;
+``group_ids`` is the prompt index; the scalar GSM8K rule reward sits on the last real response token.
+Reference: src/rollout/rollout_batch.cc:42-136 (checked against the reference's own function by
+``baseline/ref_rollout_batch_check.py``).
 
 With one of the two native tokenizers the whole batch is built by ``cverl_build_gsm8k_rollout_batch``
 (csrc/rollout_batch.cc): distinct prompts and then samples are tokenised and scored on several threads, each
@@ -42,7 +46,7 @@ class RolloutBatch:
 
 
 def _build_native(tokenizer, prompts, answers, samples, P: int, R: int, opts: Gsm8kRewardOptions, pad: int,
-                  threads: int) -> RolloutBatch:
+                  threads: int, add_bos: bool, add_eos: bool) -> RolloutBatch:
     import ctypes as C
     import os
 
@@ -54,17 +58,18 @@ def _build_native(tokenizer, prompts, answers, samples, P: int, R: int, opts: Gs
     i64, i64p, cpp = C.c_int64, C.POINTER(C.c_int64), C.POINTER(C.c_char_p)
     fn.restype = C.c_int
     fn.argtypes = [C.c_int, C.c_void_p, i64, cpp, i64p, cpp, i64, i64p, cpp, i64p, i64p, i64p, C.POINTER(C.c_uint8),
-                   i64, i64, i64, C.c_int, i64, C.c_double, C.c_double, C.c_double, C.c_int, i64p, i64p,
+                   i64, i64, i64, C.c_int, C.c_int, i64, i64, C.c_int, i64, C.c_double, C.c_double, C.c_double, C.c_int,
+                   i64p, i64p,
                    C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float), i64p]
     B, NP = len(samples), len(prompts)
     praw = [p.encode("utf-8") for p in prompts]
     araw = [a.encode("utf-8") for a in answers]
     rraw = [s.response_text.encode("utf-8") for s in samples]
     idx = np.asarray([s.prompt_index for s in samples], dtype=np.int64)
-    has = np.asarray([s.response_token_ids is not None for s in samples], dtype=np.uint8)
+    has = np.asarray([bool(s.response_token_ids) for s in samples], dtype=np.uint8)
     offs = np.zeros(B + 1, dtype=np.int64)
-    np.cumsum([len(s.response_token_ids) if s.response_token_ids is not None else 0 for s in samples], out=offs[1:])
-    given = np.asarray([t for s in samples if s.response_token_ids is not None for t in s.response_token_ids] or [0],
+    np.cumsum([len(s.response_token_ids) if s.response_token_ids else 0 for s in samples], out=offs[1:])
+    given = np.asarray([t for s in samples if s.response_token_ids for t in s.response_token_ids] or [0],
                        dtype=np.int64)
     out = RolloutBatch(torch.empty((B, P), dtype=torch.int64), torch.empty((B, R), dtype=torch.int64),
                        torch.empty((B, R), dtype=torch.float32), torch.empty((B, R), dtype=torch.float32),
@@ -82,7 +87,7 @@ def _build_native(tokenizer, prompts, answers, samples, P: int, R: int, opts: Gs
             (C.c_char_p * max(NP, 1))(*praw), (i64 * max(NP, 1))(*[len(b) for b in praw]),
             (C.c_char_p * max(NP, 1))(*araw), NP, nptr(idx, i64), (C.c_char_p * B)(*rraw),
             (i64 * B)(*[len(b) for b in rraw]), nptr(given, i64), nptr(offs, i64), nptr(has, C.c_uint8), B, P, R,
-            int(opts.method == "flexible"), opts.solution_clip_chars, opts.correct_score, opts.format_score,
+            int(add_bos), int(add_eos), tokenizer.bos_id, tokenizer.eos_id, int(opts.method == "flexible"), opts.solution_clip_chars, opts.correct_score, opts.format_score,
             opts.no_answer_score, threads, ptr(out.prompt_ids, i64), ptr(out.response_ids, i64),
             ptr(out.response_mask, C.c_float), ptr(out.token_rewards, C.c_float), ptr(out.rewards, C.c_float),
             ptr(out.group_ids, i64))
@@ -94,8 +99,9 @@ def _build_native(tokenizer, prompts, answers, samples, P: int, R: int, opts: Gs
 def build_gsm8k_rollout_batch(tokenizer: Tokenizer, prompts: Sequence[str], answers: Sequence[str],
                               samples: Sequence[RolloutSample], max_prompt_len: int, max_response_len: int,
                               reward_options: Gsm8kRewardOptions = Gsm8kRewardOptions(),
-                              threads: int = 0) -> RolloutBatch:
-    """``threads``: worker threads of the native builder (0: one per core, at most 16); -1 forces the Python loop."""
+                              threads: int = 0, add_bos: bool = False, add_eos: bool = True) -> RolloutBatch:
+    """``threads``: worker threads of the native builder (0: one per core, at most 16); -1 forces the Python loop.
+    ``add_bos`` / ``add_eos``: the reference's ``RolloutBatchOptions`` (include/cverl/rollout/rollout_batch.h:36-41)."""
     if len(prompts) != len(answers):
         raise ValueError("prompts and answers must have the same length")
     if not samples:
@@ -103,7 +109,9 @@ def build_gsm8k_rollout_batch(tokenizer: Tokenizer, prompts: Sequence[str], answ
     pad = tokenizer.pad_id if tokenizer.pad_id >= 0 else 0
     if threads >= 0 and type(tokenizer) in (ByteTokenizer, HfBpeTokenizer):
         return _build_native(tokenizer, prompts, answers, samples, max_prompt_len, max_response_len, reward_options,
-                             pad, threads)
+                             pad, threads, add_bos, add_eos)
+    prompt_opts = EncodeOptions(add_bos=add_bos, add_eos=False, max_tokens=max_prompt_len)
+    response_opts = EncodeOptions(add_bos=False, add_eos=add_eos, max_tokens=max_response_len)
     cache: Dict[int, List[int]] = {}
     B = len(samples)
     prompt_ids = torch.full((B, max_prompt_len), pad, dtype=torch.int64)
@@ -116,11 +124,11 @@ def build_gsm8k_rollout_batch(tokenizer: Tokenizer, prompts: Sequence[str], answ
         if not (0 <= s.prompt_index < len(prompts)):
             raise ValueError("sample prompt_index out of range")
         if s.prompt_index not in cache:
-            cache[s.prompt_index] = tokenizer.encode(prompts[s.prompt_index], EncodeOptions())
-        p = cache[s.prompt_index][-max_prompt_len:]          # keep the tail
+            cache[s.prompt_index] = tokenizer.encode(prompts[s.prompt_index], prompt_opts)
+        p = cache[s.prompt_index][-max_prompt_len:]          # already cut to the first max_prompt_len tokens
         if p:
             prompt_ids[b, max_prompt_len - len(p):] = torch.tensor(p, dtype=torch.int64)
-        r = s.response_token_ids if s.response_token_ids is not None else tokenizer.encode(s.response_text)
+        r = s.response_token_ids if s.response_token_ids else tokenizer.encode(s.response_text, response_opts)
         r = list(r)[:max_response_len]
         if r:
             response_ids[b, :len(r)] = torch.tensor(r, dtype=torch.int64)

@@ -225,3 +225,21 @@ def test_optimizers_match_the_reference_itself():
     assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-1500:]
     row = json.loads([ln for ln in p.stdout.strip().splitlines() if ln.startswith("{")][-1])
     assert row["agree"] and row["tensors_compared"] == 12 and row["largest_difference"] <= 2e-6
+
+
+def test_rollout_batch_builder_matches_the_reference_itself():
+    """``baseline/ref_rollout_batch_check.py``: random cases through the reference's own ``build_gsm8k_rollout_batch``
+    (byte tokenizer and BPE tokenizer) and through this package's two builders give the same six tensors."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    p = subprocess.run([sys.executable, str(root / "baseline" / "ref_rollout_batch_check.py"), "--cases", "25"],
+                       capture_output=True, text=True, timeout=1200, cwd=root)
+    if p.returncode == 3:
+        import pytest
+        pytest.skip(p.stdout.strip()[-300:])
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-1500:]
+    rows = [json.loads(ln) for ln in p.stdout.strip().splitlines() if ln.startswith("{")]
+    assert [r["tokenizer"] for r in rows] == ["byte", "bpe"] and all(r["agree"] and not r["mismatches"] for r in rows)

@@ -197,10 +197,15 @@ def test_build_gsm8k_rollout_batch():
     samples = [RolloutSample(0, "it is #### 4"), RolloutSample(0, "it is #### 5"), RolloutSample(1, "no idea")]
     b = build_gsm8k_rollout_batch(tok, prompts, answers, samples, max_prompt_len=8, max_response_len=16)
     assert b.prompt_ids.shape == (3, 8) and b.response_ids.shape == (3, 16)
-    assert tok.decode(b.prompt_ids[0].tolist()) == " is 2+2?"     # truncated keeping the tail
+    assert tok.decode(b.prompt_ids[0].tolist()) == "What is "     # an over-long prompt keeps its first tokens
     assert b.rewards.tolist() == [1.0, 0.0, 0.0]
     n0 = int(b.response_mask[0].sum())
-    assert n0 == len("it is #### 4") and b.token_rewards[0, n0 - 1] == 1.0 and b.token_rewards[0].sum() == 1.0
+    assert n0 == len("it is #### 4") + 1 and b.response_ids[0, n0 - 1] == tok.eos_id      # EOS closes the response
+    assert b.token_rewards[0, n0 - 1] == 1.0 and b.token_rewards[0].sum() == 1.0
+    plain = build_gsm8k_rollout_batch(tok, prompts, answers, samples, 8, 16, add_eos=False)
+    assert int(plain.response_mask[0].sum()) == len("it is #### 4")
+    full = build_gsm8k_rollout_batch(tok, prompts, answers, [RolloutSample(0, "x" * 40)], 8, 16)
+    assert int(full.response_mask[0].sum()) == 16 and full.response_ids[0, 15] == 4 + ord("x")   # no room: no EOS
     assert b.group_ids.tolist() == [0, 0, 1]
     short = build_gsm8k_rollout_batch(tok, ["hi"], ["1"], [RolloutSample(0, "#### 1")], 8, 16)
     assert short.prompt_ids[0, :6].tolist() == [0] * 6            # left padded
@@ -228,7 +233,10 @@ def test_native_batch_builder_equals_the_python_loop(kind):
         for f in ref.__dataclass_fields__:
             assert torch.equal(getattr(ref, f), getattr(got, f)), f
     assert ref.rewards.tolist() == [2.0, 2.0, -1.0, 2.0, 0.5, 2.0] and ref.response_mask[4].sum() == 16
-    assert ref.response_mask[2].sum() == 0 and ref.token_rewards[2].sum() == 0 and ref.response_mask[5].sum() == 0
+    # an empty response is its EOS alone (the reward sits on it); an empty id list means "tokenise the text"
+    assert ref.response_mask[2].sum() == 1 and ref.token_rewards[2, 0] == -1.0 and ref.response_mask[5].sum() > 1
+    bare = build_gsm8k_rollout_batch(tok, prompts, answers, samples, 8, 16, opts, add_eos=False)
+    assert bare.response_mask[2].sum() == 0 and bare.token_rewards[2].sum() == 0
     with pytest.raises(ValueError):
         build_gsm8k_rollout_batch(tok, prompts, answers, [RolloutSample(4, "x")], 8, 16)
     with pytest.raises(ValueError):

@@ -19,14 +19,19 @@ def test_byte_tokenizer_roundtrip_and_options():
     assert ids[0] == 1 and ids[-1] == 2 and len(ids) == 2 + len("héllo".encode())
     assert t.decode(ids) == "héllo"
     assert t.decode(ids, skip_special=False) == "<bos>héllo<eos>"
+    # the terminator is appended only where the limit leaves room (the reference's rule, checked against its own
+    # tokenizer by baseline/ref_rollout_batch_check.py): a cut-off text ends on its last kept byte
     cut = t.encode("abcdefgh", EncodeOptions(add_eos=True, max_tokens=4))
-    assert len(cut) == 4 and cut[-1] == 2
+    assert cut == [4 + ord(c) for c in "abcd"]
+    assert t.encode("abc", EncodeOptions(add_eos=True, max_tokens=4)) == [4 + ord(c) for c in "abc"] + [2]
+    assert t.encode("abcd", EncodeOptions(add_bos=True, add_eos=True, max_tokens=4)) == [1] + [4 + ord(c) for c in "abc"]
 
 
 def test_hf_bpe_matches_fixture_ids():
     tok = HfBpeTokenizer(FIX / "synthetic_tokenizer.json")
     cases = json.loads((FIX / "synthetic_tokenizer_cases.json").read_text())
-    assert tok.eos_id >= 0 and tok.pad_id >= 0
+    # the reference's discovery rule: the first special token with a usual spelling, in file order
+    assert (tok.pad_id, tok.bos_id, tok.eos_id, tok.unk_id) == (0, 1, 0, -1)
     for c in cases:
         ids = tok.encode(c["text"])
         if tok.uses_pcre2 or c["text"].isascii():
