@@ -61,8 +61,10 @@ class DynamicRolloutWorker(RolloutWorker):
 
     def generate(self, batch: TokenBatch, config: GenerationConfig) -> GenerationOutput:
         ids = batch.token_ids.to("cpu", torch.int64).contiguous()
-        mask = batch.attention_mask.to("cpu", torch.int64).contiguous()
-        lens = batch.lengths.to("cpu", torch.int64).contiguous()
+        mask = (batch.attention_mask if batch.attention_mask is not None
+                else torch.ones_like(ids)).to("cpu", torch.int64).contiguous()
+        lens = (batch.lengths if batch.lengths is not None
+                else mask.sum(-1)).to("cpu", torch.int64).contiguous()
         B, P = ids.shape
         N = config.max_new_tokens
         out_ids = torch.zeros((B, N), dtype=torch.int64)

@@ -26,19 +26,21 @@ from ..parallel.weight_sync import ParameterView, broadcast_parameters_from_root
 
 @dataclass
 class TokenBatch:
-    token_ids: torch.Tensor        # [B, T] left-padded prompts
-    attention_mask: torch.Tensor   # [B, T]
-    lengths: torch.Tensor          # [B]
+    token_ids: torch.Tensor                         # [B, T] left-padded prompts
+    attention_mask: Optional[torch.Tensor] = None   # [B, T], optional as in the reference
+    lengths: Optional[torch.Tensor] = None          # [B], optional
 
 
 @dataclass
 class GenerationConfig:
-    max_new_tokens: int = 16
+    """Defaults are the reference's (include/cverl/rollout/worker.h:20-31): ``top_k <= 0`` keeps every token,
+    ``eos_check_interval = 0`` never reads the finished mask on the host inside the loop."""
+    max_new_tokens: int = 256
     temperature: float = 1.0
     top_p: float = 1.0
-    top_k: int = 0
+    top_k: int = -1
     eos_token_id: int = -1
-    eos_check_interval: int = 8
+    eos_check_interval: int = 0
     seed: int = 0
 
 

@@ -243,3 +243,23 @@ def test_rollout_batch_builder_matches_the_reference_itself():
     assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-1500:]
     rows = [json.loads(ln) for ln in p.stdout.strip().splitlines() if ln.startswith("{")]
     assert [r["tokenizer"] for r in rows] == ["byte", "bpe"] and all(r["agree"] and not r["mismatches"] for r in rows)
+
+
+def test_cached_decode_matches_the_reference_rollout_worker():
+    """``baseline/ref_generate_check.py``: greedy generation by the reference's ``PolicyRolloutWorker`` (full forward per
+    token) and by this package's cached decode give the same tokens, lengths and log-probabilities on a Qwen3.5
+    hybrid and a Qwen3-MoE model, without and with an EOS token."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    p = subprocess.run([sys.executable, str(root / "baseline" / "ref_generate_check.py")], capture_output=True, text=True,
+                       timeout=1200, cwd=root)
+    if p.returncode == 3:
+        import pytest
+        pytest.skip(p.stdout.strip()[-300:])
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-1500:]
+    rows = [json.loads(ln) for ln in p.stdout.strip().splitlines() if ln.startswith("{")]
+    assert len(rows) == 4 and all(r["agree"] and r["tokens_equal"] and r["lengths_equal"] for r in rows)
+    assert max(r["largest_logprob_difference"] for r in rows) < 2e-5
