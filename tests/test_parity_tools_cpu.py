@@ -263,3 +263,22 @@ def test_cached_decode_matches_the_reference_rollout_worker():
     rows = [json.loads(ln) for ln in p.stdout.strip().splitlines() if ln.startswith("{")]
     assert len(rows) == 4 and all(r["agree"] and r["tokens_equal"] and r["lengths_equal"] for r in rows)
     assert max(r["largest_logprob_difference"] for r in rows) < 2e-5
+
+
+def test_planner_matches_the_reference_itself():
+    """``baseline/ref_topology_check.py``: random valid and invalid layouts through the reference's own ``Topology`` and
+    pipeline schedule and through this package's planner: same verdicts, coordinates, groups, neighbours, layer
+    ranges, 1F1B action lists, live-activation peaks and NCCL environment."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    p = subprocess.run([sys.executable, str(root / "baseline" / "ref_topology_check.py"), "--layouts", "60"],
+                       capture_output=True, text=True, timeout=1200, cwd=root)
+    if p.returncode == 3:
+        import pytest
+        pytest.skip(p.stdout.strip()[-300:])
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-1500:]
+    row = json.loads([ln for ln in p.stdout.strip().splitlines() if ln.startswith("{")][-1])
+    assert row["agree"] and row["valid"] > 10 and row["invalid"] > 10 and not row["problems"]
