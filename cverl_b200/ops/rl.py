@@ -16,6 +16,8 @@ from __future__ import annotations
 import ctypes as C
 from dataclasses import dataclass
 
+from typing import Optional
+
 import torch
 
 from .. import _native as nv
@@ -169,13 +171,16 @@ def _view(t: torch.Tensor) -> _T2:
 class _CAbi:
     """Thin ctypes front end of the ``cverl_*_f32_cpu`` entry points."""
 
-    def __init__(self):
+    def __init__(self, library_path: Optional[str] = None):
+        """``library_path``: another library exporting the same ten symbols (the reference's ``libcverl``), bound
+        instead of this package's - for side-by-side checks."""
         self._lib = None
+        self._path = library_path
 
     @property
     def lib(self):
         if self._lib is None:
-            lib = nv.host()
+            lib = C.CDLL(self._path) if self._path else nv.host()
             two = [_T2, _T2]
             lib.cverl_masked_sum_f32_cpu.argtypes = two + [C.POINTER(C.c_float)]
             lib.cverl_masked_mean_f32_cpu.argtypes = two + [C.POINTER(C.c_float)]
