@@ -173,7 +173,7 @@ def main(argv=None) -> int:
         a.weight_sync = "none"
     a.param_dtype = {"fp32": "float32", "bf16": "bfloat16", "fp16": "float16"}.get(a.param_dtype, a.param_dtype)
     rng = random.Random(a.seed)
-    examples = load_prompt_answer_jsonl(a.dataset, a.prompt_field, a.answer_field, max(a.max_examples, 0))
+    examples = load_prompt_answer_jsonl(a.dataset, a.prompt_field, a.answer_field, a.max_examples)
     if not examples:
         raise SystemExit("dataset is empty")
     policy = QwenPolicy(a.model_dir, tokenizer_path=a.tokenizer_path, device=a.device, param_dtype=a.param_dtype,

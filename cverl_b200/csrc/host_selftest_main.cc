@@ -319,7 +319,7 @@ void text_and_reward() {
   if (FILE* f = std::fopen(path.c_str(), "w")) {
     std::fputs("{\"prompt\": \"2+2?\", \"answer\": \"#### 4\"}\n{\"prompt\": \"a \\\"q\\\"\", \"answer\": \"x\"}\n", f);
     std::fclose(f);
-    void* rows = cverl_jsonl_open(path.c_str(), "prompt", "answer", 0);
+    void* rows = cverl_jsonl_open(path.c_str(), "prompt", "answer", -1);
     EXPECT(rows != nullptr);
     if (rows) {
       EXPECT(cverl_jsonl_rows(rows) == 2);
@@ -327,6 +327,12 @@ void text_and_reward() {
       EXPECT(std::string(cverl_jsonl_get(rows, 1, 0)) == "a \"q\"");
       cverl_jsonl_close(rows);
     }
+    void* none = cverl_jsonl_open(path.c_str(), "prompt", "answer", 0);      // 0 = no row, negative = all
+    EXPECT(none != nullptr && cverl_jsonl_rows(none) == 0);
+    if (none) cverl_jsonl_close(none);
+    void* one = cverl_jsonl_open(path.c_str(), "prompt", "answer", 1);
+    EXPECT(one != nullptr && cverl_jsonl_rows(one) == 1);
+    if (one) cverl_jsonl_close(one);
     std::remove(path.c_str());
   }
 }

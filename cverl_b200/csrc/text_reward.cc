@@ -163,8 +163,10 @@ struct Json {
     return true;
   }
   // any value, returned as text: strings unescaped, everything else verbatim
+  bool last_was_literal = false;   // the value just read was a bare literal (number, true, false, null), not a string
   bool value(std::string* out) {
     ws();
+    last_was_literal = false;
     if (i >= s.size()) return false;
     if (s[i] == '"') return string(out);
     if (s[i] == '{' || s[i] == '[') {
@@ -189,6 +191,7 @@ struct Json {
     const size_t b = i;
     while (i < s.size() && s[i] != ',' && s[i] != '}' && !std::isspace(static_cast<unsigned char>(s[i]))) ++i;
     *out = s.substr(b, i - b);
+    last_was_literal = true;
     return true;
   }
 };
@@ -280,7 +283,8 @@ void* cverl_jsonl_open(const char* path, const char* field_a, const char* field_
     for (char c : line)
       if (!std::isspace(static_cast<unsigned char>(c))) blank = false;
     if (blank) continue;
-    if (max_rows > 0 && static_cast<int64_t>(rows->a.size()) >= max_rows) break;
+    // negative = every row; 0 = no row at all (the reference's rule, src/data/hf_dataset.cc: max_examples)
+    if (max_rows >= 0 && static_cast<int64_t>(rows->a.size()) >= max_rows) break;
     Json j(line);
     j.ws();
     if (j.i >= line.size() || line[j.i] != '{') {
@@ -299,6 +303,7 @@ void* cverl_jsonl_open(const char* path, const char* field_a, const char* field_
       if (j.i >= line.size() || line[j.i] != ':') { ok = false; break; }
       ++j.i;
       if (!j.value(&val)) { ok = false; break; }
+      if (val == "null" && j.last_was_literal) val.clear();     // a JSON null reads as the empty string
       if (key == field_a) va = val, ha = true;
       if (key == field_b) vb = val, hb = true;
       j.ws();

@@ -34,7 +34,9 @@ def _lib():
 
 
 def load_prompt_answer_jsonl(path, prompt_field: str = "prompt", answer_field: str = "answer",
-                             max_examples: int = 0) -> List[PromptAnswerExample]:
+                             max_examples: int = -1) -> List[PromptAnswerExample]:
+    """Rows of a JSONL file as (prompt, answer) pairs.  ``max_examples``: negative = every row, 0 = none (the
+    reference's rule); numbers and booleans are kept as their JSON text, ``null`` reads as the empty string."""
     lib = _lib()
     h = lib.cverl_jsonl_open(str(path).encode(), prompt_field.encode(), answer_field.encode(), max_examples)
     try:

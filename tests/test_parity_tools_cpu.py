@@ -345,3 +345,22 @@ def test_c_abi_matches_the_reference_library_on_random_inputs():
             side.ppo_loss(torch.ones(2, 4), torch.ones(2, 4), torch.ones(2, 4), bad_mask)
         with pytest.raises(ValueError):
             side.ppo_loss(torch.ones(2, 3), torch.ones(2, 3), torch.ones(2, 3), bad_mask, c=1.0)   # dual clip needs c > 1
+
+
+def test_jsonl_reader_matches_the_reference_itself():
+    """``baseline/ref_jsonl_check.py``: random JSONL files through the reference's own ``load_prompt_answer_jsonl`` and
+    through this package's reader: same rows (numbers and booleans as their JSON text, null as the empty string,
+    ``max_examples`` 0 = no row, negative = all), same refusals."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    p = subprocess.run([sys.executable, str(root / "baseline" / "ref_jsonl_check.py"), "--files", "60"],
+                       capture_output=True, text=True, timeout=1200, cwd=root)
+    if p.returncode == 3:
+        import pytest
+        pytest.skip(p.stdout.strip()[-300:])
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-1500:]
+    row = json.loads([ln for ln in p.stdout.strip().splitlines() if ln.startswith("{")][-1])
+    assert row["agree"] and not row["problems"] and row["refused_by_both"] > 0
