@@ -364,3 +364,21 @@ def test_jsonl_reader_matches_the_reference_itself():
     assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-1500:]
     row = json.loads([ln for ln in p.stdout.strip().splitlines() if ln.startswith("{")][-1])
     assert row["agree"] and not row["problems"] and row["refused_by_both"] > 0
+
+
+def test_weight_manifest_matches_the_reference_tool():
+    """``baseline/ref_manifest_check.py``: the reference's own manifest tool (compiled as it is) and this package's print
+    the same JSON document for model directories written here - names in the same order, dtypes, shapes, packing."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    p = subprocess.run([sys.executable, str(root / "baseline" / "ref_manifest_check.py")], capture_output=True, text=True,
+                       timeout=1200, cwd=root)
+    if p.returncode == 3:
+        import pytest
+        pytest.skip(p.stdout.strip()[-300:])
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-1500:]
+    rows = [json.loads(ln) for ln in p.stdout.strip().splitlines() if ln.startswith("{")]
+    assert len(rows) == 4 and all(r["agree"] and r["names"] > 10 for r in rows)
