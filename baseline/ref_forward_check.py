@@ -30,30 +30,20 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
     import torch
 
-    import build_ref
     from cverl_b200.cli import qwen3_5_forward as fwd
     from cverl_b200.models.config import Qwen35TextConfig
     from cverl_b200.models.hf_io import HfModelLoader, load_model_weights, synthesize_model_dir
     from cverl_b200.models.qwen3_5 import Qwen35Model
-    ref_lib = HERE / "_ref" / "lib"
-    if not (ref_lib / "libcverl_ref.so").exists():
-        print(json.dumps({"unavailable": "reference library not built (python baseline/build_ref.py)"}))
+    import ref_common
+    src = ref_common.reference_source_dir()
+    try:
+        exe = ref_common.link_driver(src / "tools" / "model" / "qwen3_5_forward.cc", "qwen3_5_forward")
+    except ref_common.Unavailable as exc:
+        print(json.dumps({"unavailable": str(exc)}))
         return 3
-    paths, src = build_ref.find_paths(), build_ref.default_source_dir()
-    with tempfile.TemporaryDirectory(prefix="cverl_reffwd_") as tmp:
+    with tempfile.TemporaryDirectory(prefix="cverl_ref_") as tmp:
         work = Path(a.keep) if a.keep else Path(tmp)
         work.mkdir(parents=True, exist_ok=True)
-        lib = Path(torch.__file__).parent / "lib"
-        exe = work / "qwen3_5_forward"
-        incs = [src / "include", HERE / "shim", paths["json_inc"], *paths["torch_inc"]]
-        cmd = ["g++", "-std=c++17", "-O1", f"-D_GLIBCXX_USE_CXX11_ABI={paths['cxx11_abi']}",
-               str(src / "tools" / "model" / "qwen3_5_forward.cc"), *[f for i in incs for f in ("-I", str(i))],
-               "-L", str(ref_lib), "-lcverl_ref", "-L", str(lib), "-ltorch", "-ltorch_cpu", "-lc10",
-               f"-Wl,-rpath,{ref_lib}", f"-Wl,-rpath,{lib}", "-o", str(exe)]
-        p = subprocess.run(cmd, capture_output=True, text=True)
-        if p.returncode != 0:
-            print(json.dumps({"unavailable": "compiling the reference tool failed: " + p.stderr[-300:]}))
-            return 3
         ids = torch.tensor([[int(t) for t in a.tokens.split(",") if t]], dtype=torch.long)
         ok = True
         for moe in (False, True):

@@ -29,27 +29,16 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
     import torch
 
-    import build_ref
     from cverl_b200.data import load_prompt_answer_jsonl
-    ref_lib = HERE / "_ref" / "lib"
-    if not (ref_lib / "libcverl_ref.so").exists():
-        print(json.dumps({"unavailable": "reference library not built (python baseline/build_ref.py)"}))
+    import ref_common
+    try:
+        exe = ref_common.link_driver(HERE / "ref_jsonl_check.cc", "ref_jsonl_check")
+    except ref_common.Unavailable as exc:
+        print(json.dumps({"unavailable": str(exc)}))
         return 3
-    paths, src = build_ref.find_paths(), build_ref.default_source_dir()
-    with tempfile.TemporaryDirectory(prefix="cverl_refjsonl_") as tmp:
+    with tempfile.TemporaryDirectory(prefix="cverl_ref_") as tmp:
         work = Path(a.keep) if a.keep else Path(tmp)
         work.mkdir(parents=True, exist_ok=True)
-        lib = Path(torch.__file__).parent / "lib"
-        exe = work / "ref_jsonl_check"
-        incs = [src / "include", HERE / "shim", paths["json_inc"], *paths["torch_inc"]]
-        cmd = ["g++", "-std=c++17", "-O1", f"-D_GLIBCXX_USE_CXX11_ABI={paths['cxx11_abi']}",
-               str(HERE / "ref_jsonl_check.cc"), *[f for i in incs for f in ("-I", str(i))], "-L", str(ref_lib),
-               "-lcverl_ref", "-L", str(lib), "-ltorch", "-ltorch_cpu", "-lc10", f"-Wl,-rpath,{ref_lib}",
-               f"-Wl,-rpath,{lib}", "-o", str(exe)]
-        p = subprocess.run(cmd, capture_output=True, text=True)
-        if p.returncode != 0:
-            print(json.dumps({"unavailable": "compiling the driver failed: " + p.stderr[-300:]}))
-            return 3
         rng = random.Random(4)
         alphabet = ["a", "Z", " ", '"', "\\", "/", "\n", "\t", "é", "数", "\U0001F642", "{", "}", ":", ","]
 

