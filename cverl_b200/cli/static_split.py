@@ -109,7 +109,8 @@ def main(argv=None) -> int:
         t0 = time.time()
         if not is_trainer:
             prompts, answers = _problems(a.prompts, a.seed * 1000 + step * 64 + rank)
-            gen = GenerationConfig(max_new_tokens=a.max_response_tokens, eos_token_id=tok.eos_id, seed=a.seed + step + rank)
+            gen = GenerationConfig(max_new_tokens=a.max_response_tokens, eos_token_id=tok.eos_id, eos_check_interval=8,
+                                   seed=a.seed + step + rank)
             samples = generate_samples(worker, tok, prompts, a.n, gen, a.max_prompt_tokens, device)
             rb = build_gsm8k_rollout_batch(tok, prompts, answers, samples, a.max_prompt_tokens, a.max_response_tokens,
                                            Gsm8kRewardOptions(method="flexible")).to(device)

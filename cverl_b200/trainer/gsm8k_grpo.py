@@ -167,7 +167,8 @@ def main(argv=None) -> int:
         cursor += a.prompts
         prompts, answers = [e.prompt for e in chunk], [e.answer for e in chunk]
         gen_cfg = GenerationConfig(max_new_tokens=min(a.max_tokens, a.max_response_tokens), temperature=a.temperature,
-                                   top_p=a.top_p, eos_token_id=tokenizer.eos_id, seed=a.seed + step)
+                                   top_p=a.top_p, eos_token_id=tokenizer.eos_id, eos_check_interval=8,
+                                   seed=a.seed + step)
         samples = generate_samples(worker, tokenizer, prompts, a.n, gen_cfg, a.max_prompt_tokens, device)
         batch = build_gsm8k_rollout_batch(tokenizer, prompts, answers, samples, a.max_prompt_tokens,
                                           a.max_response_tokens, ropt).to(device)
