@@ -137,7 +137,7 @@ class HfBpeTokenizer(Tokenizer):
         return bool(self._lib.cverl_bpe_uses_id_merges(self._h))
 
     def name(self) -> str:
-        return "hf_bpe"
+        return "hf-bpe"      # the reference's spelling (include/cverl/text/hf_bpe_tokenizer.h:71)
 
     def encode_batch_flat(self, texts: Sequence[str], threads: int = 0):
         """Encodes ``texts`` on ``threads`` native threads (0: one per core, at most 16).  Returns
